@@ -1,0 +1,578 @@
+// sketch_core.cuh -- the HotSketch arithmetic, written once for device and host.
+//
+// Every function here is __host__ __device__: the CUDA kernels call them one bucket (or one batch
+// position) per thread, and a CPU build of the same header replays them in plain loops so that the
+// parallel algorithm can be checked against the sequential oracle without a GPU.
+//
+// Algorithm being reproduced: tricks/sketch.cpp of the reference (CAFE+ HotSketch).  The sequential
+// semantics are those of insert (:211-231), insertLRU (:161-210), Insert (:232-259), query (:118-128),
+// the lazy decay (:130-140) and reset (:76-116).
+//
+// Parallel insert.  A batch of lookups (positions 0..M-1, possibly several fields' calls laid end
+// to end as "segments") is applied in ROUNDS.  A round replays, from the batch-start state,
+//   1. every main bucket: its own lookups in position order, merged with the promotion events that
+//      the previous round believed would land in it;
+//   2. every LRU bucket: the lookups that missed the main table, in position order;
+//   3. the free-row FIFO: every candidate pop and every push, in position order.
+// Each decision at position p depends only on the batch-start state and on decisions at earlier
+// positions, so the prefix of positions whose beliefs are right grows every round; when a round
+// consumes exactly the beliefs it produces, all of them are right and its bucket images are the
+// state the sequential loop would have left.
+#pragma once
+#include "cafe_types.h"
+
+#ifndef INT32_MAX
+#define INT32_MAX 2147483647
+#endif
+
+#if defined(__CUDA_ARCH__)
+#define CAFE_ATOMIC_ADD(p, v) atomicAdd((p), (v))
+#define CAFE_ATOMIC_EXCH(p, v) atomicExch((p), (v))
+#define CAFE_ATOMIC_OR(p, v) atomicOr((p), (v))
+#else
+static inline int32_t cafe_host_add(int32_t* p, int32_t v) { int32_t o = *p; *p = o + v; return o; }
+static inline int32_t cafe_host_exch(int32_t* p, int32_t v) { int32_t o = *p; *p = v; return o; }
+static inline int32_t cafe_host_or(int32_t* p, int32_t v) { int32_t o = *p; *p = o | v; return o; }
+#define CAFE_ATOMIC_ADD(p, v) cafe_host_add((p), (v))
+#define CAFE_ATOMIC_EXCH(p, v) cafe_host_exch((p), (v))
+#define CAFE_ATOMIC_OR(p, v) cafe_host_or((p), (v))
+#endif
+
+#define CAFE_DECAY_BASE 10000.0   // sketch.cpp:8
+
+// ---- hashing (sketch.cpp:38-43): 64-bit product of the 32-bit id, remainder by the table size ---
+CAFE_HD int32_t cafe_hash(uint32_t x, int32_t n) {
+    return (int32_t)(((int64_t)x * 1000000007LL) % (int64_t)n);
+}
+
+CAFE_HD uint32_t cafe_float_bits(float f) {
+#if defined(__CUDA_ARCH__)
+    return __float_as_uint(f);
+#else
+    uint32_t u; __builtin_memcpy(&u, &f, 4); return u;
+#endif
+}
+
+// ---- lazy decay (sketch.cpp:130-140): float count divided by a double, rounded back to float ----
+CAFE_HD void cafe_decay4(float* cnt) {
+#pragma unroll
+    for (int i = 0; i < CAFE_SLOTS; ++i) cnt[i] = (float)((double)cnt[i] / CAFE_DECAY_BASE);
+}
+CAFE_HD void cafe_touch(CafeMainBucket& b, uint32_t gflip) {
+    if (b.flip != gflip) { b.flip = gflip; cafe_decay4(b.cnt); }
+}
+CAFE_HD void cafe_touch(CafeLruBucket& b, uint32_t gflip) {
+    if (b.flip != gflip) { b.flip = gflip; cafe_decay4(b.cnt); }
+}
+
+// ---- query (sketch.cpp:118-128): hot row of x in this bucket, 0 if none --------------------------
+CAFE_HD int32_t cafe_probe_hot(const CafeMainBucket& b, uint32_t x) {
+#pragma unroll
+    for (int i = 0; i < CAFE_SLOTS; ++i)
+        if (b.val[i] == x && b.dic[i] != 0) return b.dic[i];
+    return 0;
+}
+
+// ---- Insert (sketch.cpp:232-259): place a promoted id; returns 1 on success.  On failure
+// *pushed = the carried row that goes back to the FIFO (0 if it carried none). --------------------
+CAFE_HD int cafe_promote(CafeMainBucket& b, uint32_t x, float count, int32_t carried, int32_t* pushed) {
+    int min_i = -1;
+    float min_cnt = 1e9f;
+    *pushed = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_SLOTS; ++i) {
+        if (b.val[i] == 0) {
+            b.val[i] = x;
+            b.cnt[i] = count;
+            b.dic[i] = carried;
+            return 1;
+        }
+        if (b.cnt[i] < min_cnt) { min_cnt = b.cnt[i]; min_i = i; }
+    }
+    if (min_i >= 0 && b.dic[min_i] == 0) {
+        b.cnt[min_i] += count;
+        b.val[min_i] = x;
+        b.dic[min_i] = carried;
+        return 1;
+    }
+    *pushed = carried;
+    return 0;
+}
+
+// =================================================================================================
+// Sequential form: one thread, lookups in order, state updated in place.  This is the on-device
+// golden path (and the fallback when the parallel rounds do not converge within their cap).
+// =================================================================================================
+struct CafeSeqState {
+    CafeMainBucket* mb;
+    CafeLruBucket* lb;
+    uint32_t* ring;
+    uint32_t ring_mask;
+    int32_t n1, n2;
+    // scalars, updated in place
+    float thr;
+    uint32_t gflip;
+    int32_t real_n, num, t;
+    uint32_t q_head;
+    int32_t q_size;
+    int32_t error;
+};
+
+CAFE_HD void cafe_seq_push(CafeSeqState& S, uint32_t id) {
+    if (S.q_size > (int32_t)S.ring_mask) { S.error |= 1; return; }
+    S.ring[(S.q_head + (uint32_t)S.q_size) & S.ring_mask] = id;
+    S.q_size++;
+}
+CAFE_HD uint32_t cafe_seq_pop(CafeSeqState& S) {
+    uint32_t id = S.ring[S.q_head & S.ring_mask];
+    S.q_head++;
+    S.q_size--;
+    return id;
+}
+CAFE_HD int cafe_seq_promote(CafeSeqState& S, uint32_t x, float count, int32_t carried) {
+    CafeMainBucket& b = S.mb[cafe_hash(x, S.n1)];
+    cafe_touch(b, S.gflip);
+    int32_t pushed;
+    int ok = cafe_promote(b, x, count, carried, &pushed);
+    if (!ok && pushed != 0) cafe_seq_push(S, (uint32_t)pushed);
+    return ok;
+}
+// insertLRU, sketch.cpp:161-210
+CAFE_HD int cafe_seq_insert_lru(CafeSeqState& S, uint32_t x, float count) {
+    CafeLruBucket& b = S.lb[cafe_hash(x, S.n2)];
+    int p = -1, t_min = 1000000000, got = 0;
+    cafe_touch(b, S.gflip);
+    for (int i = 0; i < CAFE_SLOTS; ++i) {
+        if (b.val[i] == x) {
+            b.t[i] = ++S.t;
+            b.cnt[i] += count;
+            if (b.cnt[i] >= S.thr && b.cnt[i] - count < S.thr) S.real_n++;
+            if (b.cnt[i] >= S.thr && S.q_size > 0 && b.dic[i] == 0) {
+                b.dic[i] = (int32_t)cafe_seq_pop(S);
+                got = 1;
+                S.num++;
+            }
+            if (b.cnt[i] >= S.thr) {
+                if (!cafe_seq_promote(S, b.val[i], b.cnt[i], b.dic[i])) got = 0;
+                b.val[i] = 0; b.t[i] = 0; b.cnt[i] = 0.0f; b.dic[i] = 0;
+            }
+            return got;
+        }
+        if (t_min > b.t[i]) { t_min = b.t[i]; p = i; }
+    }
+    if (p < 0) { S.error |= 2; return 0; }
+    if (b.dic[p] != 0 || b.cnt[p] >= 5.0f) cafe_seq_promote(S, b.val[p], b.cnt[p], b.dic[p]);
+    b.val[p] = x;
+    b.t[p] = ++S.t;
+    b.cnt[p] = 1.0f;
+    b.dic[p] = 0;
+    if (b.cnt[p] >= S.thr && b.cnt[p] - count < S.thr) S.real_n++;
+    if (b.cnt[p] >= S.thr && S.q_size > 0) {
+        b.dic[p] = (int32_t)cafe_seq_pop(S);
+        got = 1;
+        S.num++;
+    }
+    return got;
+}
+// insert, sketch.cpp:211-231
+CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
+    CafeMainBucket& b = S.mb[cafe_hash(x, S.n1)];
+    cafe_touch(b, S.gflip);
+    for (int i = 0; i < CAFE_SLOTS; ++i) {
+        if (b.val[i] == x) {
+            b.cnt[i] += count;
+            float c = b.cnt[i];
+            int got = 0;
+            if (c >= S.thr && c - count < S.thr) S.real_n++;
+            if (c >= S.thr && b.dic[i] == 0 && S.q_size > 0) {
+                b.dic[i] = (int32_t)cafe_seq_pop(S);
+                got = 1;
+                S.num++;
+            }
+            return got;
+        }
+    }
+    return cafe_seq_insert_lru(S, x, count);
+}
+
+// =================================================================================================
+// Parallel form.
+// =================================================================================================
+struct CafeJob {
+    // the lookups
+    const uint32_t* gid;     // [M] global ids
+    const float* imp;        // [M] counts, or null for unit counts
+    int32_t M;
+    int32_t limit;           // positions >= limit are left out (commit of a prefix)
+    int32_t nseg;
+    int32_t seg_off[CAFE_MAX_SEGMENTS + 1];
+    // positions ordered by (main bucket, position) and by (LRU bucket, position); bucket ranges
+    const int32_t* ord1;
+    const int32_t* start1;   // [n1+1]
+    const int32_t* ord2;
+    const int32_t* start2;   // [n2+1]
+    // batch-start state (read) and the image this round writes
+    const CafeMainBucket* main_in;
+    CafeMainBucket* main_out;
+    const CafeLruBucket* lru_in;
+    CafeLruBucket* lru_out;
+    int32_t n1, n2;
+    float thr;
+    uint32_t gflip;
+    int32_t t0;
+    // free-row FIFO at batch start
+    const uint32_t* ring;
+    uint32_t ring_mask;
+    uint32_t q_head;
+    int32_t q_size;
+    // beliefs consumed (produced by the previous round) and produced
+    int32_t first_round;
+    const CafeEvent* ev_old;
+    CafeEvent* ev_new;
+    const int32_t* head_old;   // [n1] newest victim-promotion event per target bucket, -1 = none
+    const int32_t* nxt_old;    // [M]  next older event with the same target
+    int32_t* head_new;
+    int32_t* nxt_new;
+    const int32_t* tl_size_old;   // [2M] FIFO size before each op slot
+    const int32_t* tl_rank_old;   // [2M] successful pops before each op slot
+    const uint32_t* pushbuf_old;  // pushes in slot order
+    int32_t* tl_size_new;
+    int32_t* tl_rank_new;
+    uint32_t* pushbuf_new;
+    // per-round scratch
+    uint8_t* pflag;      // [M] bit0: missed the main table; bits1-2: op slot of its candidate pop (+1)
+    int32_t* tstamp;     // [M] inclusive count of misses up to each position
+    int32_t* ins_res;    // [M] result of the believed event of this position: 0 ok, -1 failed, >0 failed and pushed this row
+    int32_t* op_a;       // [M] FIFO-size transfer function of the position: s -> max(s + a, b)
+    int32_t* op_b;
+    int64_t* op_cnt;     // [M] (pushes << 32) | successful pops, then their exclusive prefix sums
+    // outputs
+    int32_t* mask;       // [M] 1 = this lookup was handed a hot row (the reference's insert result)
+    int32_t* post_row;   // [M] hot row of the id at the end of its segment (0 = not hot in the main table)
+    CafeRoundResult* res;
+};
+
+CAFE_HD float cafe_count_of(const CafeJob& J, int p) { return J.imp ? J.imp[p] : 1.0f; }
+
+// Belief about a pop at op slot `slot`: would the FIFO be non-empty, and which row is at its front.
+CAFE_HD bool cafe_would_pop(const CafeJob& J, int64_t slot, int32_t* id) {
+    int32_t size, rank;
+    if (J.first_round) { size = J.q_size; rank = 0; }
+    else { size = J.tl_size_old[slot]; rank = J.tl_rank_old[slot]; }
+    *id = 0;
+    if (size <= 0) return false;
+    if (rank < J.q_size) *id = (int32_t)J.ring[(J.q_head + (uint32_t)rank) & J.ring_mask];
+    else if (rank - J.q_size < J.M) *id = (int32_t)J.pushbuf_old[rank - J.q_size];
+    else { CAFE_ATOMIC_OR(&J.res->error, 4); return false; }
+    return true;
+}
+
+// Smallest event position > after in the chain of bucket events (chains are short; order in the
+// chain is arbitrary because it was built with atomic exchanges).
+CAFE_HD int cafe_next_event(const CafeJob& J, int head, int after) {
+    int best = INT32_MAX;
+    for (int e = head; e >= 0; e = J.nxt_old[e])
+        if (e > after && e < best && e < J.limit) best = e;
+    return best;
+}
+
+CAFE_HD void cafe_note_event(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
+    CafeEvent o = J.ev_old[p];
+    bool same;
+    if (J.first_round) same = (kind == CAFE_EV_NONE);
+    else if (kind == CAFE_EV_NONE) same = (o.kind == CAFE_EV_NONE);
+    else same = (o.kind == kind && o.x == x && o.dic == dic && cafe_float_bits(o.cnt) == cafe_float_bits(cnt));
+    if (!same) J.res->changed = 1;
+    if (kind == CAFE_EV_NONE) { J.ev_new[p].kind = CAFE_EV_NONE; return; }
+    CafeEvent e;
+    e.x = x; e.cnt = cnt; e.dic = dic; e.kind = kind;
+    J.ev_new[p] = e;
+}
+
+// ---- round step 1: one main bucket ---------------------------------------------------------------
+CAFE_HD void cafe_main_pass_bucket(const CafeJob& J, int k) {
+    CafeMainBucket b = J.main_in[k];
+    int i = J.start1[k];
+    const int iend = J.start1[k + 1];
+    const int evhead = J.first_round ? -1 : J.head_old[k];
+    int p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
+
+    int seg = 0, seg_end = J.seg_off[1], seg_first_i = i;
+    int real_delta = 0, num_delta = 0, n_hit = 0;
+    bool dirty = false, touched = false;
+
+    for (;;) {
+        int p_own = (i < iend) ? J.ord1[i] : INT32_MAX;
+        if (p_own >= J.limit) p_own = INT32_MAX;
+        if (p_own == INT32_MAX && p_ev == INT32_MAX) break;
+        const bool own = p_own <= p_ev;   // a lookup's probe comes before an event of the same position
+        const int p = own ? p_own : p_ev;
+        if (p >= seg_end) {
+            // the segment (one field's call) ended: record what a query at this point would return
+            if (dirty && J.post_row)
+                for (int j = seg_first_i; j < i; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
+            if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+            real_delta = 0; dirty = false; seg_first_i = i;
+            while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
+        }
+        if (!touched) { cafe_touch(b, J.gflip); touched = true; }
+        if (own) {
+            const uint32_t x = J.gid[p];
+            const float c = cafe_count_of(J, p);
+            int s = -1;
+#pragma unroll
+            for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (b.val[q] == x) s = q;
+            if (s >= 0) {   // insert(): hit in the main table (sketch.cpp:215-228)
+                ++n_hit;
+                float cn = b.cnt[s] + c;
+                b.cnt[s] = cn;
+                if (cn >= J.thr && cn - c < J.thr) ++real_delta;
+                int got = 0;
+                uint8_t pf = 0;
+                if (cn >= J.thr && b.dic[s] == 0) {
+                    pf = 1 << 1;   // candidate pop at op slot 2p
+                    int32_t id;
+                    if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[s] = id; got = 1; ++num_delta; dirty = true; }
+                }
+                J.pflag[p] = pf;
+                J.mask[p] = got;
+                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+            } else {
+                J.pflag[p] = 1;   // goes to the LRU stage; that pass fills in the rest
+                if (!J.first_round) {
+                    CafeEvent e = J.ev_old[p];
+                    if (e.kind == CAFE_EV_OWN) {   // believed: this lookup promotes its own id into this bucket
+                        int32_t pushed;
+                        int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
+                        J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
+                        dirty = true;
+                    }
+                }
+            }
+            ++i;
+        } else {   // believed victim promotion landing here (sketch.cpp:193-195 -> Insert)
+            CafeEvent e = J.ev_old[p];
+            int32_t pushed;
+            int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
+            J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
+            dirty = true;
+            p_ev = cafe_next_event(J, evhead, p);
+        }
+    }
+    if (dirty && J.post_row)
+        for (int j = seg_first_i; j < i; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
+    if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+    if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
+    if (n_hit) CAFE_ATOMIC_ADD(&J.res->n_main_hit, n_hit);
+    J.main_out[k] = b;
+}
+
+// ---- round step 2: one LRU bucket (insertLRU, sketch.cpp:161-210) ---------------------------------
+CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
+    CafeLruBucket b = J.lru_in[k];
+    const int jend = J.start2[k + 1];
+    int seg = 0, seg_end = J.seg_off[1];
+    int real_delta = 0, num_delta = 0, n_ev = 0;
+    bool touched = false;
+    for (int j = J.start2[k]; j < jend; ++j) {
+        const int p = J.ord2[j];
+        if (p >= J.limit) break;
+        if (!(J.pflag[p] & 1)) continue;
+        if (p >= seg_end) {
+            if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+            real_delta = 0;
+            while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
+        }
+        if (!touched) { cafe_touch(b, J.gflip); touched = true; }
+        const uint32_t x = J.gid[p];
+        const float c = cafe_count_of(J, p);
+        const int32_t tp = J.t0 + J.tstamp[p];
+        int hit = -1, vic = -1, t_min = 1000000000;
+#pragma unroll
+        for (int q = 0; q < CAFE_SLOTS; ++q) {
+            if (hit < 0) {
+                if (b.val[q] == x) hit = q;
+                else if (t_min > b.t[q]) { t_min = b.t[q]; vic = q; }
+            }
+        }
+        int got = 0;
+        if (hit >= 0) {
+            b.t[hit] = tp;
+            float cn = b.cnt[hit] + c;
+            b.cnt[hit] = cn;
+            if (cn >= J.thr && cn - c < J.thr) ++real_delta;
+            uint8_t pf = 1;
+            if (cn >= J.thr && b.dic[hit] == 0) {
+                pf |= 1 << 1;   // candidate pop at op slot 2p (before the possible push-back at 2p+1)
+                int32_t id;
+                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[hit] = id; got = 1; ++num_delta; }
+            }
+            J.pflag[p] = pf;
+            if (cn >= J.thr) {
+                ++n_ev;
+                cafe_note_event(J, p, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
+                // the main pass of this round replayed the believed copy of this event
+                if (!J.first_round && J.ins_res[p] != 0) got = 0;
+                b.val[hit] = 0; b.t[hit] = 0; b.cnt[hit] = 0.0f; b.dic[hit] = 0;
+            } else {
+                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+            }
+        } else {
+            if (vic < 0) { CAFE_ATOMIC_OR(&J.res->error, 2); vic = 0; }
+            if (b.dic[vic] != 0 || b.cnt[vic] >= 5.0f) {
+                ++n_ev;
+                cafe_note_event(J, p, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
+                J.nxt_new[p] = CAFE_ATOMIC_EXCH(&J.head_new[cafe_hash(b.val[vic], J.n1)], p);
+            } else {
+                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+            }
+            b.val[vic] = x;
+            b.t[vic] = tp;
+            b.cnt[vic] = 1.0f;
+            b.dic[vic] = 0;
+            if (1.0f >= J.thr && 1.0f - c < J.thr) ++real_delta;
+            uint8_t pf = 1;
+            if (1.0f >= J.thr) {
+                pf |= 2 << 1;   // candidate pop at op slot 2p+1 (after the victim's possible push-back at 2p)
+                int32_t id;
+                if (cafe_would_pop(J, 2 * (int64_t)p + 1, &id)) { b.dic[vic] = id; got = 1; ++num_delta; }
+            }
+            J.pflag[p] = pf;
+        }
+        J.mask[p] = got;
+    }
+    if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+    if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
+    if (n_ev) CAFE_ATOMIC_ADD(&J.res->n_events, n_ev);
+    J.lru_out[k] = b;
+}
+
+// ---- round step 3: the FIFO timeline ---------------------------------------------------------------
+// Each position owns two op slots (2p, 2p+1).  An op is a candidate pop or a push; the FIFO size
+// evolves as s -> max(s + a, b) per op (pop: a=-1,b=0; push: a=+1,b=-inf), a family closed under
+// composition, so sizes come from one scan; ranks of successful pops and of pushes from a second.
+#define CAFE_NEG_INF (-(1 << 29))
+struct CafeOps { int op0, op1; int32_t id0, id1; };   // op: 0 none, 1 pop, 2 push
+
+CAFE_HD CafeOps cafe_ops_of(const CafeJob& J, int p) {
+    CafeOps o; o.op0 = o.op1 = 0; o.id0 = o.id1 = 0;
+    const int ps = (J.pflag[p] >> 1) & 3;
+    if (ps == 1) o.op0 = 1;
+    if (ps == 2) o.op1 = 1;
+    const int32_t r = J.first_round ? 0 : J.ins_res[p];
+    if (r > 0) {
+        // the believed event of this position failed and pushed its row back: after the pop for an
+        // own promotion (slot 2p+1), before the pop for a victim promotion (slot 2p)
+        const uint32_t kind = J.ev_old[p].kind;
+        if (kind == CAFE_EV_OWN) { if (o.op1 == 0) { o.op1 = 2; o.id1 = r; } else J.res->changed = 1; }
+        else if (kind == CAFE_EV_VICTIM) { if (o.op0 == 0) { o.op0 = 2; o.id0 = r; } else J.res->changed = 1; }
+    }
+    return o;
+}
+CAFE_HD void cafe_op_fn(int op, int32_t* a, int32_t* b) {
+    if (op == 1) { *a = -1; *b = 0; }
+    else if (op == 2) { *a = 1; *b = CAFE_NEG_INF; }
+    else { *a = 0; *b = CAFE_NEG_INF; }
+}
+// (a2,b2) after (a1,b1)
+CAFE_HD void cafe_compose(int32_t a1, int32_t b1, int32_t a2, int32_t b2, int32_t* a, int32_t* b) {
+    int32_t bb = b1 + a2;
+    if (bb < CAFE_NEG_INF) bb = CAFE_NEG_INF;
+    *a = a1 + a2;
+    *b = bb > b2 ? bb : b2;
+}
+CAFE_HD int32_t cafe_apply_fn(int32_t a, int32_t b, int32_t s) { int32_t v = s + a; return v > b ? v : b; }
+
+// 3a: transfer function of position p
+CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) {
+    CafeOps o = cafe_ops_of(J, p);
+    int32_t a0, b0, a1, b1, a, b;
+    cafe_op_fn(o.op0, &a0, &b0);
+    cafe_op_fn(o.op1, &a1, &b1);
+    cafe_compose(a0, b0, a1, b1, &a, &b);
+    J.op_a[p] = a;
+    J.op_b[p] = b;
+}
+// 3b (after the inclusive scan of (op_a, op_b) under cafe_compose): outcome counts of position p
+CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
+    CafeOps o = cafe_ops_of(J, p);
+    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_a[p - 1], J.op_b[p - 1], J.q_size);
+    int64_t pops = 0, pushes = 0;
+    if (o.op0 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op0 == 2) { ++pushes; ++s; }
+    if (o.op1 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op1 == 2) { ++pushes; ++s; }
+    J.op_cnt[p] = (pushes << 32) | pops;
+}
+// 3c (after the exclusive prefix sum of op_cnt): write the timeline, compare with the consumed one
+CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
+    CafeOps o = cafe_ops_of(J, p);
+    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_a[p - 1], J.op_b[p - 1], J.q_size);
+    const int64_t pre = J.op_cnt[p];
+    int32_t rank = (int32_t)(pre & 0xffffffffLL);
+    int32_t npush = (int32_t)(pre >> 32);
+    int32_t sz[2], rk[2];
+    sz[0] = s; rk[0] = rank;
+    bool diff = false;
+    if (o.op0 == 1) { if (s > 0) { ++rank; --s; } }
+    else if (o.op0 == 2) {
+        if (!J.first_round && J.pushbuf_old[npush] != (uint32_t)o.id0) diff = true;
+        J.pushbuf_new[npush++] = (uint32_t)o.id0; ++s;
+    }
+    sz[1] = s; rk[1] = rank;
+    if (o.op1 == 2) {
+        if (!J.first_round && J.pushbuf_old[npush] != (uint32_t)o.id1) diff = true;
+        J.pushbuf_new[npush++] = (uint32_t)o.id1;
+    }
+    if (J.first_round) {
+        diff = diff || sz[0] != J.q_size || sz[1] != J.q_size || rk[0] != 0 || rk[1] != 0 || o.op0 == 2 || o.op1 == 2;
+    } else {
+        diff = diff || J.tl_size_old[2 * (int64_t)p] != sz[0] || J.tl_size_old[2 * (int64_t)p + 1] != sz[1] ||
+               J.tl_rank_old[2 * (int64_t)p] != rk[0] || J.tl_rank_old[2 * (int64_t)p + 1] != rk[1];
+    }
+    J.tl_size_new[2 * (int64_t)p] = sz[0];
+    J.tl_size_new[2 * (int64_t)p + 1] = sz[1];
+    J.tl_rank_new[2 * (int64_t)p] = rk[0];
+    J.tl_rank_new[2 * (int64_t)p + 1] = rk[1];
+    if (diff) J.res->changed = 1;
+    if (p == J.limit - 1) {
+        // totals: prefix up to p plus p's own outcomes
+        int32_t my_pops = 0, my_push = 0, s2 = sz[0];
+        if (o.op0 == 1) { if (s2 > 0) { ++my_pops; --s2; } } else if (o.op0 == 2) { ++my_push; ++s2; }
+        if (o.op1 == 1) { if (s2 > 0) { ++my_pops; } } else if (o.op1 == 2) { ++my_push; }
+        J.res->n_pop_ok = (int32_t)(pre & 0xffffffffLL) + my_pops;
+        J.res->n_push = (int32_t)(pre >> 32) + my_push;
+        J.res->n_miss = J.tstamp[p];
+    }
+}
+
+// ---- commit of the FIFO after a converged round: live pushes go into the ring ----------------------
+// Entry j of the round's push list has virtual rank q_size + j; ranks below n_pop_ok were consumed.
+CAFE_HD void cafe_commit_push(uint32_t* ring, uint32_t ring_mask, uint32_t q_head, int32_t q_size,
+                              int32_t n_pop_ok, const uint32_t* pushbuf, int j) {
+    int64_t rank = (int64_t)q_size + j;
+    if (rank >= n_pop_ok) ring[(q_head + (uint32_t)rank) & ring_mask] = pushbuf[j];
+}
+
+// =================================================================================================
+// Threshold re-fit (reset, sketch.cpp:76-116) helpers.  Candidates are numbered canonically: main
+// slots first (bucket-major), then LRU slots.
+// =================================================================================================
+CAFE_HD int cafe_reset_touch_count_main(CafeMainBucket& b, uint32_t gflip, float thr) {
+    cafe_touch(b, gflip);
+    int n = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_SLOTS; ++i) n += (b.cnt[i] >= thr || b.dic[i] != 0);
+    return n;
+}
+CAFE_HD int cafe_reset_touch_count_lru(CafeLruBucket& b, uint32_t gflip, float thr) {
+    cafe_touch(b, gflip);
+    int n = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_SLOTS; ++i) n += (b.cnt[i] >= thr || b.dic[i] != 0);
+    return n;
+}
+CAFE_HD int32_t* cafe_slot_dic(CafeMainBucket* mb, CafeLruBucket* lb, int32_t n1, int32_t order) {
+    const int32_t main_slots = n1 * CAFE_SLOTS;
+    if (order < main_slots) return &mb[order >> 2].dic[order & 3];
+    order -= main_slots;
+    return &lb[order >> 2].dic[order & 3];
+}

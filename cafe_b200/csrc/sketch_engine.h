@@ -1,0 +1,398 @@
+// sketch_engine.h -- host-side driver of the device-resident HotSketch.
+//
+// SketchEngine<Backend> owns the sketch state (two images of each bucket table, the free-row FIFO
+// ring, the scalars the reference keeps in class members and file-scope globals) and the workspace
+// of the parallel insert, and sequences the rounds, the call-boundary work (decay clock, flip bit,
+// threshold re-fit) and the commit.  The Backend supplies memory and the per-bucket / per-position
+// passes: the CUDA backend launches kernels, the host backend (tests only) runs the same functions
+// in loops.  Scalars live on the host; kernels receive them by value.
+//
+// Reference semantics reproduced here: batch_insert / batch_insert_val prologue
+// (tricks/sketch.cpp:266-275, 281-291), reset (:76-116), init (:309-313).
+#pragma once
+#include <stdint.h>
+#include <string.h>
+
+#include <algorithm>
+#include <vector>
+
+#include "sketch_core.cuh"
+
+struct CafeSketchStats {
+    int64_t calls, lookups, rounds, jobs, truncated_jobs, resets, resets_refused, flips;
+    int64_t seq_fallbacks, main_hits, lru_visits, events, max_rounds;
+};
+
+template <class BE>
+class SketchEngine {
+public:
+    // scalars (sketch.cpp:16-21 and the globals of :7-13)
+    int lim = 0, n1 = 0, n2 = 0, adjust = 1;
+    float thr = 0.f;
+    int real_n = 0, num = 0, t = 0;
+    uint32_t gflip = 0;
+    double alpha = 1.0, decay_importance = 1.0;
+    int batch_num = 0;
+    uint32_t q_head = 0;
+    int q_size = 0;
+    uint32_t ring_mask = 0;
+    int round_cap = 48;
+    int window = CAFE_MAX_SEGMENTS;   // segments fused per job; shrinks after a re-fit cut a job short
+    int last_status = CAFE_OK;
+    CafeSketchStats stats;
+
+    BE be;
+
+    SketchEngine() { memset(&stats, 0, sizeof(stats)); }
+    ~SketchEngine() { release(); }
+
+    int init(int lim_, float thr_, int adjust_, double alpha_, int max_lookups) {
+        release();
+        if (lim_ < 20 || max_lookups < 1) return CAFE_ERR_ARG;
+        lim = lim_; thr = thr_; adjust = adjust_; alpha = alpha_;
+        n1 = (int)(lim * 0.9);   // sketch.cpp:51-52
+        n2 = (int)(lim * 0.1);
+        if (n1 < 1 || n2 < 1) return CAFE_ERR_ARG;
+        real_n = num = t = 0; gflip = 0; decay_importance = 1.0; batch_num = 0;
+        cap = max_lookups;
+        uint32_t rc = 1;
+        while (rc < (uint32_t)lim + 1) rc <<= 1;
+        ring_mask = rc - 1;
+        for (int i = 0; i < 2; ++i) {
+            mainb[i] = (CafeMainBucket*)be.alloc(sizeof(CafeMainBucket) * (size_t)n1);
+            lrub[i] = (CafeLruBucket*)be.alloc(sizeof(CafeLruBucket) * (size_t)n2);
+            if (!mainb[i] || !lrub[i]) return CAFE_ERR_CUDA;
+        }
+        be.memset(mainb[0], 0, sizeof(CafeMainBucket) * (size_t)n1);
+        be.memset(lrub[0], 0, sizeof(CafeLruBucket) * (size_t)n2);
+        cur = 0;
+        ring = (uint32_t*)be.alloc(sizeof(uint32_t) * (size_t)rc);
+        if (!ring) return CAFE_ERR_CUDA;
+        be.fill_iota(ring, lim - 1, 1);   // free rows 1..lim-1 (sketch.cpp:55-56); row 0 is never handed out
+        q_head = 0; q_size = lim - 1;
+        // workspace of the parallel insert
+        size_t M = (size_t)cap;
+        ord1 = (int32_t*)be.alloc(4 * M); ord2 = (int32_t*)be.alloc(4 * M);
+        start1 = (int32_t*)be.alloc(4 * ((size_t)n1 + 1)); start2 = (int32_t*)be.alloc(4 * ((size_t)n2 + 1));
+        for (int i = 0; i < 2; ++i) {
+            ev[i] = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
+            head[i] = (int32_t*)be.alloc(4 * (size_t)n1);
+            nxt[i] = (int32_t*)be.alloc(4 * M);
+            tl_size[i] = (int32_t*)be.alloc(8 * M);
+            tl_rank[i] = (int32_t*)be.alloc(8 * M);
+            pushbuf[i] = (uint32_t*)be.alloc(4 * M);
+        }
+        pflag = (uint8_t*)be.alloc(M);
+        tstamp = (int32_t*)be.alloc(4 * M);
+        ins_res = (int32_t*)be.alloc(4 * M);
+        op_a = (int32_t*)be.alloc(4 * M); op_b = (int32_t*)be.alloc(4 * M);
+        op_cnt = (int64_t*)be.alloc(8 * M);
+        res_dev = (CafeRoundResult*)be.alloc(sizeof(CafeRoundResult));
+        seq_dev = (CafeSeqState*)be.alloc(sizeof(CafeSeqState));
+        size_t ncand = (size_t)(n1 + n2) * CAFE_SLOTS;
+        cand_key[0] = (uint32_t*)be.alloc(4 * ncand); cand_key[1] = (uint32_t*)be.alloc(4 * ncand);
+        cand_val[0] = (int32_t*)be.alloc(4 * ncand); cand_val[1] = (int32_t*)be.alloc(4 * ncand);
+        cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
+        reset_out = (int32_t*)be.alloc(4 * 8);
+        if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
+        if (!ord1 || !ord2 || !start1 || !start2 || !pflag || !tstamp || !ins_res || !op_a || !op_b || !op_cnt ||
+            !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
+            return CAFE_ERR_CUDA;
+        for (int i = 0; i < 2; ++i)
+            if (!ev[i] || !head[i] || !nxt[i] || !tl_size[i] || !tl_rank[i] || !pushbuf[i]) return CAFE_ERR_CUDA;
+        ready = true;
+        return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+
+    int capacity() const { return cap; }
+    const CafeMainBucket* main_table() const { return mainb[cur]; }
+    const CafeLruBucket* lru_table() const { return lrub[cur]; }
+    CafeMainBucket* main_table_mut() { return mainb[cur]; }
+    CafeLruBucket* lru_table_mut() { return lrub[cur]; }
+    const uint32_t* ring_ptr() const { return ring; }
+
+    // batch_query (sketch.cpp:260-265): out[i] = -row if hot else (int)id
+    int query(const uint32_t* gid, int n, int32_t* out) {
+        if (!ready || n < 0) return CAFE_ERR_ARG;
+        if (n == 0) return CAFE_OK;
+        be.query(mainb[cur], n1, gid, n, out);
+        return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+
+    // One batch_insert_val call per segment, in order (imp == null: batch_insert, unit counts).
+    // mask[p] = the reference's per-lookup result; post_row[p] (optional) = hot row a query would
+    // return for the id right after its own segment's call (0 = none).  parallel=false runs the
+    // sequential kernel for every segment.
+    int insert_segments(const uint32_t* gid, const float* imp, const int* seg_off, int nseg, int32_t* mask,
+                        int32_t* post_row, bool parallel) {
+        if (!ready || nseg < 1 || !seg_off || seg_off[0] != 0) return CAFE_ERR_ARG;
+        for (int s = 0; s < nseg; ++s) if (seg_off[s + 1] < seg_off[s]) return CAFE_ERR_ARG;
+        const int total = seg_off[nseg];
+        if (total > 0 && (!gid || !mask)) return CAFE_ERR_ARG;
+        last_status = CAFE_OK;
+        int s = 0;
+        while (s < nseg) {
+            call_boundary();
+            if (last_status == CAFE_ERR_CUDA) return last_status;
+            int e = s + 1;
+            if (parallel) {
+                // fuse following calls while their boundaries are known to be uneventful: the decay
+                // clock is deterministic, the re-fit condition is checked after the fact
+                double d = decay_importance;
+                const int maxe = std::min(nseg, s + std::max(1, std::min(window, (int)CAFE_MAX_SEGMENTS)));
+                while (e < maxe && (int64_t)seg_off[e + 1] - seg_off[s] <= cap) {
+                    double d2 = d * alpha;
+                    if (d2 > CAFE_DECAY_BASE) break;
+                    d = d2; ++e;
+                }
+            }
+            const int base = seg_off[s];
+            if (seg_off[e] - base > cap) return CAFE_ERR_CAPACITY;
+            int done_e = e;
+            if (seg_off[e] - base > 0) {
+                if (parallel) {
+                    int rc = run_parallel(gid + base, imp ? imp + base : nullptr, seg_off + s, e - s, mask + base,
+                                          post_row ? post_row + base : nullptr, &done_e);
+                    if (rc != CAFE_OK) return rc;
+                    done_e += s;
+                } else {
+                    int rc = run_sequential(gid + base, imp ? imp + base : nullptr, seg_off[e] - base, mask + base,
+                                            post_row ? post_row + base : nullptr);
+                    if (rc != CAFE_OK) return rc;
+                }
+            }
+            // boundaries inside the fused range: nothing happens at them except the clocks
+            for (int b = s + 1; b < done_e; ++b) { ++batch_num; decay_importance *= alpha; ++stats.calls; }
+            if (parallel) {
+                if (done_e < e) window = std::max(1, done_e - s);
+                else window = std::min((int)CAFE_MAX_SEGMENTS, window * 2);
+            }
+            s = done_e;
+        }
+        stats.lookups += total;
+        return last_status;
+    }
+
+    // reset() of the reference, callable directly for tests.
+    int refit_threshold() {
+        int32_t l = 0;
+        be.reset_collect(mainb[cur], lrub[cur], n1, n2, gflip, thr, cand_cnt, cand_key[0], cand_val[0], &l);
+        if (!be.ok()) return last_status = CAFE_ERR_CUDA;
+        if (l < lim) { ++stats.resets_refused; return last_status = CAFE_ERR_RESET_UNDERFLOW; }
+        be.sort_pairs(cand_key[0], cand_val[0], cand_key[1], cand_val[1], l, 32);
+        int32_t out[8];
+        be.reset_apply(cand_key[1], cand_val[1], l, lim, mainb[cur], lrub[cur], n1, ring, ring_mask, q_head, q_size,
+                       reset_out, out);
+        if (!be.ok()) return last_status = CAFE_ERR_CUDA;
+        uint32_t bits = (uint32_t)out[0];
+        memcpy(&thr, &bits, 4);
+        const int npush = out[1], npop = out[2];
+        q_head += (uint32_t)npop;
+        q_size += npush - npop;
+        real_n = lim;
+        ++stats.resets;
+        return CAFE_OK;
+    }
+
+    // ---- state export (tests, checkpoints): flat arrays in the oracle's dump layout ----------------
+    void dump(uint32_t* mval, float* mcnt, int32_t* mdic, uint8_t* mflip, uint32_t* lval, float* lcnt, int32_t* ldic,
+              int32_t* lt, uint8_t* lflip, uint32_t* queue) {
+        std::vector<CafeMainBucket> hm((size_t)n1);
+        std::vector<CafeLruBucket> hl((size_t)n2);
+        std::vector<uint32_t> hr((size_t)ring_mask + 1);
+        be.d2h(hm.data(), mainb[cur], sizeof(CafeMainBucket) * (size_t)n1);
+        be.d2h(hl.data(), lrub[cur], sizeof(CafeLruBucket) * (size_t)n2);
+        be.d2h(hr.data(), ring, 4 * ((size_t)ring_mask + 1));
+        for (int k = 0; k < n1; ++k) {
+            for (int i = 0; i < 4; ++i) { mval[k * 4 + i] = hm[k].val[i]; mcnt[k * 4 + i] = hm[k].cnt[i]; mdic[k * 4 + i] = hm[k].dic[i]; }
+            mflip[k] = (uint8_t)hm[k].flip;
+        }
+        for (int k = 0; k < n2; ++k) {
+            for (int i = 0; i < 4; ++i) { lval[k * 4 + i] = hl[k].val[i]; lcnt[k * 4 + i] = hl[k].cnt[i]; ldic[k * 4 + i] = hl[k].dic[i]; lt[k * 4 + i] = hl[k].t[i]; }
+            lflip[k] = (uint8_t)hl[k].flip;
+        }
+        for (int i = 0; i < q_size; ++i) queue[i] = hr[(q_head + (uint32_t)i) & ring_mask];
+    }
+
+    // inverse of dump (restore from a checkpoint)
+    int load(const uint32_t* mval, const float* mcnt, const int32_t* mdic, const uint8_t* mflip, const uint32_t* lval,
+             const float* lcnt, const int32_t* ldic, const int32_t* lt, const uint8_t* lflip, const uint32_t* queue,
+             int qn) {
+        if (!ready || qn < 0 || qn > (int)ring_mask) return CAFE_ERR_ARG;
+        std::vector<CafeMainBucket> hm((size_t)n1);
+        std::vector<CafeLruBucket> hl((size_t)n2);
+        std::vector<uint32_t> hr((size_t)ring_mask + 1, 0u);
+        memset(hm.data(), 0, sizeof(CafeMainBucket) * (size_t)n1);
+        memset(hl.data(), 0, sizeof(CafeLruBucket) * (size_t)n2);
+        for (int k = 0; k < n1; ++k) {
+            for (int i = 0; i < 4; ++i) { hm[k].val[i] = mval[k * 4 + i]; hm[k].cnt[i] = mcnt[k * 4 + i]; hm[k].dic[i] = mdic[k * 4 + i]; }
+            hm[k].flip = mflip[k];
+        }
+        for (int k = 0; k < n2; ++k) {
+            for (int i = 0; i < 4; ++i) { hl[k].val[i] = lval[k * 4 + i]; hl[k].cnt[i] = lcnt[k * 4 + i]; hl[k].dic[i] = ldic[k * 4 + i]; hl[k].t[i] = lt[k * 4 + i]; }
+            hl[k].flip = lflip[k];
+        }
+        for (int i = 0; i < qn; ++i) hr[i] = queue[i];
+        be.h2d(mainb[cur], hm.data(), sizeof(CafeMainBucket) * (size_t)n1);
+        be.h2d(lrub[cur], hl.data(), sizeof(CafeLruBucket) * (size_t)n2);
+        be.h2d(ring, hr.data(), 4 * ((size_t)ring_mask + 1));
+        q_head = 0; q_size = qn;
+        return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+
+private:
+    bool ready = false;
+    int cap = 0, cur = 0;
+    CafeMainBucket* mainb[2] = {nullptr, nullptr};
+    CafeLruBucket* lrub[2] = {nullptr, nullptr};
+    uint32_t* ring = nullptr;
+    int32_t *ord1 = nullptr, *ord2 = nullptr, *start1 = nullptr, *start2 = nullptr;
+    CafeEvent* ev[2] = {nullptr, nullptr};
+    int32_t* head[2] = {nullptr, nullptr};
+    int32_t* nxt[2] = {nullptr, nullptr};
+    int32_t* tl_size[2] = {nullptr, nullptr};
+    int32_t* tl_rank[2] = {nullptr, nullptr};
+    uint32_t* pushbuf[2] = {nullptr, nullptr};
+    uint8_t* pflag = nullptr;
+    int32_t *tstamp = nullptr, *ins_res = nullptr, *op_a = nullptr, *op_b = nullptr;
+    int64_t* op_cnt = nullptr;
+    CafeRoundResult* res_dev = nullptr;
+    CafeSeqState* seq_dev = nullptr;
+    uint32_t* cand_key[2] = {nullptr, nullptr};
+    int32_t* cand_val[2] = {nullptr, nullptr};
+    int32_t* cand_cnt = nullptr;
+    int32_t* reset_out = nullptr;
+
+    void release() {
+        if (!ready && !mainb[0]) return;
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, ev[0], ev[1], head[0],
+                        head[1], nxt[0], nxt[1], tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
+                        pflag, tstamp, ins_res, op_a, op_b, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
+                        cand_val[0], cand_val[1], cand_cnt, reset_out};
+        for (void* p : ptrs) if (p) be.free(p);
+        mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
+        ready = false;
+    }
+
+    // prologue of batch_insert / batch_insert_val (sketch.cpp:267-275, 282-291)
+    void call_boundary() {
+        ++batch_num;
+        ++stats.calls;
+        decay_importance *= alpha;
+        if (decay_importance > CAFE_DECAY_BASE) {
+            decay_importance /= CAFE_DECAY_BASE;
+            thr = (float)((double)thr / CAFE_DECAY_BASE);
+            gflip ^= 1u;
+            ++stats.flips;
+        }
+        if ((double)real_n > lim * 1.2 && adjust) {
+            int rc = refit_threshold();
+            if (rc == CAFE_ERR_RESET_UNDERFLOW) last_status = rc;   // reported, insert still proceeds
+        }
+    }
+
+    int run_sequential(const uint32_t* gid, const float* imp, int n, int32_t* mask, int32_t* post_row) {
+        CafeSeqState S;
+        S.mb = mainb[cur]; S.lb = lrub[cur]; S.ring = ring; S.ring_mask = ring_mask; S.n1 = n1; S.n2 = n2;
+        S.thr = thr; S.gflip = gflip; S.real_n = real_n; S.num = num; S.t = t; S.q_head = q_head; S.q_size = q_size;
+        S.error = 0;
+        be.seq_insert(seq_dev, &S, gid, imp, n, mask);   // runs, then copies the updated scalars back into S
+        if (!be.ok()) return last_status = CAFE_ERR_CUDA;
+        real_n = S.real_n; num = S.num; t = S.t; q_head = S.q_head; q_size = S.q_size;
+        if (S.error) return last_status = CAFE_ERR_CAPACITY;
+        if (post_row) be.post_query(mainb[cur], n1, gid, n, mask, post_row);
+        return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+
+    // Parallel rounds over segments seg[0..nseg] (offsets relative to seg[0]).  On return *done =
+    // number of leading segments committed (fewer than nseg when a threshold re-fit is due at an
+    // inner boundary).
+    int run_parallel(const uint32_t* gid, const float* imp, const int* seg, int nseg, int32_t* mask, int32_t* post_row,
+                     int* done) {
+        const int M = seg[nseg] - seg[0];
+        CafeJob J;
+        memset(&J, 0, sizeof(J));
+        J.gid = gid; J.imp = imp; J.M = M; J.limit = M; J.nseg = nseg;
+        for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i] - seg[0];
+        for (int i = nseg + 1; i <= CAFE_MAX_SEGMENTS; ++i) J.seg_off[i] = INT32_MAX;
+        be.sort_lookups(gid, M, n1, ord1, start1);
+        be.sort_lookups(gid, M, n2, ord2, start2);
+        J.ord1 = ord1; J.start1 = start1; J.ord2 = ord2; J.start2 = start2;
+        J.n1 = n1; J.n2 = n2; J.thr = thr; J.gflip = gflip; J.t0 = t;
+        J.ring = ring; J.ring_mask = ring_mask; J.q_head = q_head; J.q_size = q_size;
+        J.pflag = pflag; J.tstamp = tstamp; J.ins_res = ins_res; J.op_a = op_a; J.op_b = op_b; J.op_cnt = op_cnt;
+        J.mask = mask;
+        J.post_row = post_row;
+        J.res = res_dev;
+        ++stats.jobs;
+
+        CafeRoundResult R;
+        int rounds = 0, confirm_limit = -1;
+        int pb = 0;   // index of the belief set consumed this round
+        bool first = true;
+        for (;;) {
+            if (rounds >= round_cap) {
+                // state untouched so far (rounds only write the other image): sequential fallback
+                ++stats.seq_fallbacks;
+                last_status = CAFE_ERR_NOCONVERGE;
+                *done = 1;
+                int rc = run_sequential(gid, imp, J.seg_off[1], mask, post_row);
+                return rc == CAFE_OK ? CAFE_OK : rc;
+            }
+            J.first_round = first ? 1 : 0;
+            J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
+            J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
+            J.ev_old = ev[pb]; J.ev_new = ev[pb ^ 1];
+            J.head_old = head[pb]; J.nxt_old = nxt[pb]; J.head_new = head[pb ^ 1]; J.nxt_new = nxt[pb ^ 1];
+            J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
+            J.tl_size_new = tl_size[pb ^ 1]; J.tl_rank_new = tl_rank[pb ^ 1]; J.pushbuf_new = pushbuf[pb ^ 1];
+            be.memset(res_dev, 0, sizeof(CafeRoundResult));
+            be.memset(ins_res, 0, 4 * (size_t)M);
+            be.memset(J.head_new, 0xff, 4 * (size_t)n1);
+            if (post_row) be.memset(post_row, 0, 4 * (size_t)J.limit);
+            be.main_pass(J);
+            be.scan_miss(J);
+            be.lru_pass(J);
+            be.resolve(J);
+            be.d2h(&R, res_dev, sizeof(R));
+            if (!be.ok()) return last_status = CAFE_ERR_CUDA;
+            ++rounds; ++stats.rounds;
+            first = false;
+            pb ^= 1;
+            if (R.error) return last_status = CAFE_ERR_CAPACITY;
+            if (R.changed) continue;
+            // converged for positions < J.limit: is a threshold re-fit due at an inner boundary?
+            if (confirm_limit < 0 && adjust) {
+                int rn = real_n, cut = -1;
+                for (int b = 1; b < nseg; ++b) {
+                    rn += R.seg_real_delta[b - 1];
+                    if ((double)rn > lim * 1.2) { cut = b; break; }
+                }
+                if (cut > 0) {
+                    // beliefs for the prefix are already right: one more round over the prefix alone
+                    // reproduces them and leaves the prefix's state in the other image
+                    confirm_limit = J.seg_off[cut];
+                    J.limit = confirm_limit;
+                    J.nseg = cut;
+                    nseg = cut;
+                    ++stats.truncated_jobs;
+                    if (confirm_limit == 0) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
+                    continue;
+                }
+            }
+            break;
+        }
+        // commit
+        if (R.n_push > 0) be.commit_queue(ring, ring_mask, q_head, q_size, R.n_pop_ok, pushbuf[pb], R.n_push);
+        cur ^= 1;
+        q_head += (uint32_t)R.n_pop_ok;
+        q_size += R.n_push - R.n_pop_ok;
+        t += R.n_miss;
+        num += R.num_delta;
+        for (int b = 0; b < nseg; ++b) real_n += R.seg_real_delta[b];
+        stats.main_hits += R.n_main_hit; stats.lru_visits += R.n_miss; stats.events += R.n_events;
+        if (rounds > stats.max_rounds) stats.max_rounds = rounds;
+        *done = nseg;
+        return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+};

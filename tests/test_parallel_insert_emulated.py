@@ -1,0 +1,114 @@
+"""Exactness of the parallel (round-based) insert, checked on the CPU.
+
+The CUDA kernels call per-bucket / per-position functions from cafe_b200/csrc/sketch_core.cuh under
+the driver of sketch_engine.h.  tests/hostemu compiles the same two headers with a loop-based
+backend; here that build is compared, state for state and output for output, with the sequential
+oracle on seeded streams that reach every path (promotions of both kinds, failed promotions that
+push a row back, flip-bit decay, threshold re-fits at call boundaries inside a fused job).
+"""
+import numpy as np
+import pytest
+
+from hostemu import EmuSketch
+from kat_stream import SplitMix64, kat_call
+from oracle.hotsketch import OracleSketch, states_equal
+
+
+def drive(lim, thr, alpha, calls, n, dom, fuse, parallel=True, seed=7, unit=False, zero_ids=False, window=None,
+          round_cap=None, ragged=False):
+    o = OracleSketch(lim, thr, 1, alpha)
+    e = EmuSketch(lim, thr, 1, alpha, cap=max(1, n * fuse), parallel=parallel)
+    if window:
+        e.set_window(window)
+    if round_cap:
+        e.set_round_cap(round_cap)
+    rng = SplitMix64(seed)
+    for c in range(0, calls, fuse):
+        idl, vl, ml, pl, off = [], [], [], [], [0]
+        for f in range(fuse):
+            m = n if not ragged else (0 if (c + f) % 5 == 2 else 1 + (c * 7 + f * 13) % n)
+            ids, v = kat_call(rng, n, dom)
+            ids, v = ids[:m], v[:m]
+            if zero_ids and m:
+                ids[::7] = 0
+            idl.append(ids)
+            vl.append(v)
+            q0 = o.batch_query(ids)
+            assert np.array_equal(e.batch_query(ids), q0) or f > 0  # state before the fused job only
+            ml.append(o.batch_insert_val(ids, None if unit else v))
+            q = o.batch_query(ids)
+            pl.append(np.where((ml[-1] == 1) & (q < 0), -q, 0))
+            off.append(off[-1] + m)
+        ids, v = np.concatenate(idl), np.concatenate(vl)
+        m = e.insert_segments(ids, None if unit else v, off)
+        assert e.last_rc in (0, 4), e.last_rc
+        assert np.array_equal(m, np.concatenate(ml)), f"mask differs in job at call {c}"
+        assert np.array_equal(np.where(m == 1, e.last_post_row, 0), np.concatenate(pl)), f"post rows differ at call {c}"
+        assert states_equal(o.state(), e.state()) == [], f"state differs after job at call {c}"
+        assert np.array_equal(e.batch_query(ids), o.batch_query(ids))
+    return e.stats()
+
+
+def test_sequential_kernel_logic_matches_oracle():
+    st = drive(200, 1, 1.3, 40, 96, 3000, 1, parallel=False)
+    assert st["resets"] >= 3 and st["flips"] == 1
+
+
+@pytest.mark.parametrize("fuse", [1, 4, 13])
+def test_small_sketch_all_paths(fuse):
+    st = drive(200, 1, 1.3, 52, 96, 3000, fuse)
+    assert st["resets"] >= 3 and st["flips"] >= 1 and st["events"] > 0 and st["seq_fallbacks"] == 0
+
+
+def test_fused_fields_with_refits_cutting_jobs():
+    st = drive(20000, 1, 1.0000005, 52, 4096, 5000000, 26)
+    assert st["truncated_jobs"] > 0 and st["resets"] > 0 and st["seq_fallbacks"] == 0
+
+
+def test_kaggle_sized_sketch_fused_26():
+    st = drive(13505, 1, 1.0000005, 260, 128, 33762577, 26)
+    assert st["seq_fallbacks"] == 0
+
+
+def test_threshold_above_one_and_decay():
+    st = drive(1000, 2, 1.01, 1200, 64, 200000, 8)
+    assert st["flips"] >= 1 and st["seq_fallbacks"] == 0
+
+
+def test_high_threshold_no_refit():
+    drive(1000, 500, 1.0000005, 40, 500, 3000, 4)
+
+
+def test_unit_counts_batch_insert():
+    drive(300, 1, 1.2, 60, 64, 2500, 3, unit=True)
+
+
+def test_id_zero_is_reproduced():
+    # id 0 doubles as the empty-slot marker in the reference (sketch.cpp:238); same quirks expected
+    drive(300, 1, 1.2, 60, 64, 2500, 3, zero_ids=True)
+
+
+def test_ragged_and_empty_segments():
+    drive(200, 1, 1.3, 60, 50, 3000, 6, ragged=True)
+
+
+def test_heavy_duplicates_tiny_domain():
+    # a handful of ids repeated hundreds of times per call: long same-bucket runs, in batch order
+    drive(100, 1, 1.1, 30, 600, 40, 3)
+
+
+def test_round_cap_falls_back_to_sequential_and_stays_exact():
+    st = drive(200, 1, 1.3, 40, 96, 3000, 4, round_cap=2)
+    assert st["seq_fallbacks"] > 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_shapes(seed):
+    r = np.random.default_rng(seed)
+    lim = int(r.integers(40, 400))
+    thr = int(r.integers(1, 4))
+    alpha = float(r.choice([1.0000005, 1.05, 1.5]))
+    n = int(r.integers(1, 200))
+    dom = int(r.integers(20, 5000))
+    fuse = int(r.integers(1, 9))
+    drive(lim, thr, alpha, fuse * 8, n, dom, fuse, seed=100 + seed)
