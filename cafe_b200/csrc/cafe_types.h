@@ -15,7 +15,9 @@
 #define CAFE_SLOTS 4
 #define CAFE_MAX_SEGMENTS 64   // fields handled by one fused insert
 
-// status codes returned by every C entry point (0 = ok)
+// status codes returned by every C entry point (0 = ok); same values as include/cafe_b200.h
+#ifndef CAFE_STATUS_ENUMS
+#define CAFE_STATUS_ENUMS
 enum {
     CAFE_OK = 0,
     CAFE_ERR_ARG = 1,          // null pointer, negative size, bad handle
@@ -25,6 +27,8 @@ enum {
     CAFE_ERR_RESET_UNDERFLOW = 5, // threshold re-fit refused: fewer candidates than hot rows
     CAFE_ERR_UNSUPPORTED = 6
 };
+enum { CAFE_INSERT_PARALLEL = 0, CAFE_INSERT_SEQUENTIAL = 1 };
+#endif
 
 struct alignas(16) CafeMainBucket {   // 64 B
     uint32_t val[CAFE_SLOTS];

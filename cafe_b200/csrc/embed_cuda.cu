@@ -1,0 +1,503 @@
+// embed_cuda.cu -- the SKEmbeddingBag data path on sm_100a: fused query+gather forward, gradient-norm
+// importance, hot-row migration, and sort/segment-reduce scatter with the SGD update in place.
+//
+// Reference being replaced (tricks/sk_embedding_bag.py): query + two embedding_bag gathers + where
+// (:101-152), importance from gradient norms (:173-190), migration of newly-hot ids (:199-208), and the
+// sparse SGD step of the caller (dlrm_s_pytorch.py:1658).  All of it is HBM-bound gather/scatter work:
+// rows move as 16-byte vectors, one group of D/4 lanes per row, no tensor cores.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <cub/cub.cuh>
+
+#include "../../include/cafe_b200.h"
+#include "cafe_internal.h"
+#include "sketch_core.cuh"
+
+struct CafeFields {
+    int32_t nfields, B, D, hotn;
+    uint32_t f_offset[CAFE_MAX_SEGMENTS];   // added to a field's local id to give the global id
+    int32_t hash_size[CAFE_MAX_SEGMENTS];
+    int32_t hash_base[CAFE_MAX_SEGMENTS + 1];   // prefix sums of hash_size (unified row numbering)
+    float* w_hash[CAFE_MAX_SEGMENTS];
+    float* w_high;
+};
+
+#define FULL 0xffffffffu
+
+__device__ __forceinline__ float4 ld_row(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 ld_stream(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ void st_stream(float* p, float4 v) { __stcs(reinterpret_cast<float4*>(p), v); }
+
+template <typename T>
+__device__ __forceinline__ T* shfl_ptr(T* p, int src) {
+    return reinterpret_cast<T*>(__shfl_sync(FULL, reinterpret_cast<unsigned long long>(p), src));
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward: per lookup, probe the sketch (hot row or hash row), then copy the selected row.
+// A warp first resolves 32 lookups (32 independent bucket reads in flight), then its lanes move
+// the 32 rows, G = D/4 lanes per row, 4 rows' loads issued before their stores.
+// ---------------------------------------------------------------------------------------------
+template <int G, typename IdT>
+__global__ void __launch_bounds__(256)
+k_embed_forward(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids,
+                const CafeMainBucket* __restrict__ mb, int n1, float* __restrict__ out, int64_t field_stride,
+                int64_t sample_stride, uint32_t* __restrict__ gid_out, int32_t* __restrict__ row_out, int total) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t p = warp * 32 + lane;
+    const float* src = nullptr;
+    float* dst = nullptr;
+    if (p < total) {
+        const int f = (int)(p / F.B);
+        const int b = (int)(p - (int64_t)f * F.B);
+        const uint32_t x = (uint32_t)((int64_t)ids[p] + (int64_t)F.f_offset[f]);
+        const CafeMainBucket* bk = &mb[cafe_hash(x, n1)];
+        const uint4 v = *reinterpret_cast<const uint4*>(bk->val);
+        const int4 d = *reinterpret_cast<const int4*>(bk->dic);
+        int32_t r = 0;
+        if (v.w == x && d.w != 0) r = d.w;
+        if (v.z == x && d.z != 0) r = d.z;
+        if (v.y == x && d.y != 0) r = d.y;
+        if (v.x == x && d.x != 0) r = d.x;
+        int32_t code;
+        if (r) { src = F.w_high + (size_t)(r % F.hotn) * F.D; code = -r; }
+        else { const int32_t hr = (int32_t)(x % (uint32_t)F.hash_size[f]); src = F.w_hash[f] + (size_t)hr * F.D; code = hr; }
+        dst = out + f * field_stride + b * sample_stride;
+        gid_out[p] = x;
+        row_out[p] = code;
+    }
+    constexpr int RPI = 32 / G;   // rows moved per warp iteration
+    constexpr int U = 4;
+    const int sub = lane / G, c = (lane % G) * 4;
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += RPI * U) {
+        float4 val[U];
+        float* d_[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = j0 + u * RPI + sub;
+            const float* s = shfl_ptr(src, j);
+            d_[u] = shfl_ptr(dst, j);
+            if (s) val[u] = ld_row(s + c);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (d_[u]) st_stream(d_[u] + c, val[u]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// importance (sk_embedding_bag.py:178-189): per-lookup L2 norm of its gradient row, scaled by
+// N / (sum of the field's norms).
+// ---------------------------------------------------------------------------------------------
+template <int G>
+__global__ void __launch_bounds__(256)
+k_grad_norm(const float* __restrict__ grad, int64_t field_stride, int64_t sample_stride, int B, int total,
+            float* __restrict__ norm) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t p = t / G;
+    const int c = (int)(t % G) * 4;
+    float s = 0.f;
+    if (p < total) {
+        const int f = (int)(p / B);
+        const int b = (int)(p - (int64_t)f * B);
+        const float4 v = ld_row(grad + f * field_stride + b * sample_stride + c);
+        s = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
+    if (p < total && c == 0) norm[p] = sqrtf(s);
+}
+
+// one block per field: fixed-order sum of the field's norms
+__global__ void __launch_bounds__(1024) k_field_sum(const float* __restrict__ norm, int B, float* __restrict__ totals) {
+    __shared__ float sh[1024];
+    const float* x = norm + (size_t)blockIdx.x * B;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < B; i += 1024) s += x[i];
+    sh[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 512; o > 0; o >>= 1) {
+        if (threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) totals[blockIdx.x] = sh[0];
+}
+
+__global__ void k_importance(const float* __restrict__ norm, const float* __restrict__ totals, int B, int total,
+                             float* __restrict__ imp) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const float tot = totals[p / B];
+    // a field whose whole gradient is zero would give 0/0 in the reference; counts stay unchanged here
+    imp[p] = tot > 0.f ? __fdiv_rn(__fmul_rn(norm[p], (float)B), tot) : 0.f;
+}
+
+// ---------------------------------------------------------------------------------------------
+// migration (sk_embedding_bag.py:205-208, guarded): a lookup that was handed a hot row and whose id
+// is in the main table right after its field's call gets its hash row copied into that hot row.
+// The hash row is addressed with the LOCAL id, as the reference does at :207.
+// ---------------------------------------------------------------------------------------------
+template <typename IdT>
+__global__ void __launch_bounds__(256)
+k_migrate(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids, const int32_t* __restrict__ mask,
+          const int32_t* __restrict__ post_row, int total, int32_t* __restrict__ n_migrated) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t p = warp * 32 + lane;
+    const float* src = nullptr;
+    float* dst = nullptr;
+    if (p < total && mask[p] != 0 && post_row[p] > 0) {
+        const int f = (int)(p / F.B);
+        const int64_t local = (int64_t)ids[p];
+        src = F.w_hash[f] + (size_t)(local % F.hash_size[f]) * F.D;
+        dst = F.w_high + (size_t)post_row[p] * F.D;
+    }
+    unsigned act = __ballot_sync(FULL, dst != nullptr);
+    if (lane == 0 && act && n_migrated) atomicAdd(n_migrated, __popc(act));
+    while (act) {
+        const int j = __ffs(act) - 1;
+        act &= act - 1;
+        const float* s = shfl_ptr(src, j);
+        float* d = shfl_ptr(dst, j);
+        for (int c = lane * 4; c < F.D; c += 128) *reinterpret_cast<float4*>(d + c) = *reinterpret_cast<const float4*>(s + c);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// scatter + SGD.  Lookups are sorted by unified row (hot rows first, then each field's hash rows);
+// a group of G lanes reduces a chunk of CAFE_CHUNK consecutive sorted lookups in order.  Rows whose
+// lookups lie inside one chunk are updated at once; rows that span chunks leave per-chunk partial
+// sums that a second kernel adds in chunk order.  The order of additions is fixed by the sort, so
+// results are deterministic.
+// ---------------------------------------------------------------------------------------------
+__global__ void k_row_keys(const __grid_constant__ CafeFields F, const int32_t* __restrict__ row, int total,
+                           uint32_t* __restrict__ key, int32_t* __restrict__ pos) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const int32_t r = row[p];
+    key[p] = r < 0 ? (uint32_t)((-r) % F.hotn) : (uint32_t)(F.hotn + F.hash_base[p / F.B] + r);
+    pos[p] = p;
+}
+
+__device__ __forceinline__ float* row_ptr(const CafeFields& F, uint32_t key, int pos) {
+    if (key < (uint32_t)F.hotn) return F.w_high + (size_t)key * F.D;
+    const int f = pos / F.B;
+    return F.w_hash[f] + (size_t)(key - (uint32_t)F.hotn - (uint32_t)F.hash_base[f]) * F.D;
+}
+__device__ __forceinline__ void sgd_apply(float* w, float4 g, float lr) {
+    float4 x = *reinterpret_cast<float4*>(w);
+    x.x -= lr * g.x; x.y -= lr * g.y; x.z -= lr * g.z; x.w -= lr * g.w;
+    *reinterpret_cast<float4*>(w) = x;
+}
+
+#define NOKEY 0xffffffffu
+
+template <int G>
+__global__ void __launch_bounds__(256)
+k_scatter_chunks(const __grid_constant__ CafeFields F, const float* __restrict__ grad, int64_t field_stride,
+                 int64_t sample_stride, const uint32_t* __restrict__ skey, const int32_t* __restrict__ spos, int M,
+                 float lr, float* __restrict__ partial) {
+    constexpr int PER = CAFE_CHUNK / G;   // sorted entries held per lane
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t chunk = t / G;
+    const int gl = (int)(t % G);          // lane within the group
+    const int c = gl * 4;
+    const int64_t base = chunk * CAFE_CHUNK;
+    const int cnt = (int)max((int64_t)0, min((int64_t)CAFE_CHUNK, (int64_t)M - base));
+    uint32_t k[PER];
+    int32_t q[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int j = i * G + gl;
+        k[i] = j < cnt ? skey[base + j] : NOKEY;
+        q[i] = j < cnt ? spos[base + j] : 0;
+    }
+    const uint32_t key_prev = (cnt > 0 && base > 0) ? skey[base - 1] : NOKEY;
+    const uint32_t key_next = (cnt > 0 && base + CAFE_CHUNK < M) ? skey[base + CAFE_CHUNK] : NOKEY;
+
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    uint32_t cur = NOKEY;
+    int cur_pos = 0;
+    bool first_seg = true;
+    const int B = F.B;
+    constexpr int U = 8;
+#pragma unroll
+    for (int j0 = 0; j0 < CAFE_CHUNK; j0 += U) {
+        float4 v[U];
+        uint32_t kk[U];
+        int32_t qq[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = j0 + u;
+            kk[u] = __shfl_sync(FULL, k[j / G], j % G, G);
+            qq[u] = __shfl_sync(FULL, q[j / G], j % G, G);
+            if (kk[u] != NOKEY) {
+                const int f = qq[u] / B;
+                const int b = qq[u] - f * B;
+                v[u] = ld_stream(grad + f * field_stride + b * sample_stride + c);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (kk[u] == NOKEY) continue;
+            if (kk[u] != cur) {
+                if (cur != NOKEY) {
+                    // a row that ended inside the chunk: complete unless it came in from the previous chunk
+                    if (first_seg && cur == key_prev) *reinterpret_cast<float4*>(partial + (size_t)(chunk * 2) * CAFE_MAX_DIM + c) = acc;
+                    else sgd_apply(row_ptr(F, cur, cur_pos) + c, acc, lr);
+                    first_seg = false;
+                }
+                cur = kk[u];
+                cur_pos = qq[u];
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w;
+        }
+    }
+    if (cur != NOKEY) {
+        const bool open_left = first_seg && cur == key_prev;
+        const bool open_right = cur == key_next;
+        if (open_left || open_right)
+            *reinterpret_cast<float4*>(partial + (size_t)(chunk * 2 + (first_seg ? 0 : 1)) * CAFE_MAX_DIM + c) = acc;
+        else
+            sgd_apply(row_ptr(F, cur, cur_pos) + c, acc, lr);
+    }
+}
+
+// One group per chunk; the chunk in which a spanning row STARTS adds up that row's partial sums.
+template <int G>
+__global__ void __launch_bounds__(256)
+k_scatter_fixup(const __grid_constant__ CafeFields F, const uint32_t* __restrict__ skey,
+                const int32_t* __restrict__ spos, int M, float lr, const float* __restrict__ partial) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t chunk = t / G;
+    const int c = (int)(t % G) * 4;
+    const int64_t base = chunk * CAFE_CHUNK;
+    if (base + CAFE_CHUNK >= M) return;   // the last chunk cannot continue to the right
+    const uint32_t key = skey[base + CAFE_CHUNK - 1];
+    if (key != skey[base + CAFE_CHUNK]) return;            // its last row ends with the chunk
+    const bool single = skey[base] == key;
+    if (single && base > 0 && skey[base - 1] == key) return;   // the row started in an earlier chunk
+    // end of the row's range in the sorted keys
+    int64_t lo = base + CAFE_CHUNK, hi = M;   // first index with key' > key lies in (lo, hi]
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (skey[mid] <= key) lo = mid + 1; else hi = mid;
+    }
+    const int64_t last_chunk = (lo - 1) / CAFE_CHUNK;
+    float4 acc = *reinterpret_cast<const float4*>(partial + (size_t)(chunk * 2 + (single ? 0 : 1)) * CAFE_MAX_DIM + c);
+    constexpr int U = 8;
+    for (int64_t c0 = chunk + 1; c0 <= last_chunk; c0 += U) {
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u <= last_chunk) v[u] = *reinterpret_cast<const float4*>(partial + (size_t)((c0 + u) * 2) * CAFE_MAX_DIM + c);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (c0 + u <= last_chunk) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+    }
+    sgd_apply(row_ptr(F, key, spos[base + CAFE_CHUNK - 1]) + c, acc, lr);
+}
+
+// ---------------------------------------------------------------------------------------------
+// workspace
+// ---------------------------------------------------------------------------------------------
+int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
+    (void)hotn;
+    ws->cap = cap;
+    const size_t M = (size_t)cap;
+    const size_t chunks = (M + CAFE_CHUNK - 1) / CAFE_CHUNK;
+    cudaError_t e = cudaSuccess;
+    auto A = [&](void** p, size_t n) { if (e == cudaSuccess) e = cudaMalloc(p, n ? n : 1); };
+    A((void**)&ws->norm, 4 * M); A((void**)&ws->imp, 4 * M); A((void**)&ws->totals, 4 * CAFE_MAX_SEGMENTS);
+    A((void**)&ws->mask, 4 * M); A((void**)&ws->post_row, 4 * M);
+    for (int i = 0; i < 2; ++i) { A((void**)&ws->key[i], 4 * M); A((void**)&ws->pos[i], 4 * M); }
+    A((void**)&ws->partial, sizeof(float) * 2 * chunks * CAFE_MAX_DIM);
+    size_t b = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, b, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
+                                    (int32_t*)nullptr, cap, 0, 32, (cudaStream_t)0);
+    ws->cub_bytes = b + 1024;
+    A(&ws->cub_tmp, ws->cub_bytes);
+    if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
+    return CAFE_OK;
+}
+
+void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
+    void* ptrs[] = {ws->norm, ws->imp, ws->totals, ws->mask, ws->post_row, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1],
+                    ws->partial, ws->cub_tmp};
+    for (void* p : ptrs) if (p) cudaFree(p);
+    *ws = CafeEmbedWorkspace();
+}
+
+// ---------------------------------------------------------------------------------------------
+// C ABI (embedding part)
+// ---------------------------------------------------------------------------------------------
+static int fail_cuda(const char* where) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return CAFE_OK;
+    char buf[256];
+    snprintf(buf, sizeof(buf), "%s: %s", where, cudaGetErrorString(e));
+    cafe_internal_set_error(buf);
+    return CAFE_ERR_CUDA;
+}
+static bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+static int fill_fields(CafeFields* F, int nfields, int B, int D, int hotn, const int64_t* f_offset, const int32_t* hash_size,
+                       float* const* w_hash, float* w_high) {
+    if (nfields < 1 || nfields > CAFE_MAX_SEGMENTS || B < 0 || hotn < 1 || !f_offset || !hash_size || !w_hash || !w_high)
+        return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    if ((int64_t)nfields * B > 0x7fffffffLL) return CAFE_ERR_CAPACITY;
+    memset(F, 0, sizeof(*F));
+    F->nfields = nfields; F->B = B; F->D = D; F->hotn = hotn; F->w_high = w_high;
+    if (!aligned16(w_high)) return CAFE_ERR_ARG;
+    int64_t base = 0;
+    for (int f = 0; f < nfields; ++f) {
+        if (hash_size[f] < 1 || !w_hash[f] || !aligned16(w_hash[f])) return CAFE_ERR_ARG;
+        F->f_offset[f] = (uint32_t)f_offset[f];
+        F->hash_size[f] = hash_size[f];
+        F->hash_base[f] = (int32_t)base;
+        F->w_hash[f] = w_hash[f];
+        base += hash_size[f];
+        if (base + hotn > 0x7fffffffLL) return CAFE_ERR_CAPACITY;
+    }
+    F->hash_base[nfields] = (int32_t)base;
+    return CAFE_OK;
+}
+
+static bool strides_ok(const float* p, int64_t fs, int64_t ss) { return aligned16(p) && fs % 4 == 0 && ss % 4 == 0; }
+
+#define DISPATCH_G(D, CALL)              \
+    switch ((D) / 4) {                   \
+        case 4: { constexpr int G = 4; CALL; } break;   \
+        case 8: { constexpr int G = 8; CALL; } break;   \
+        case 16: { constexpr int G = 16; CALL; } break; \
+        default: { constexpr int G = 32; CALL; } break; \
+    }
+
+extern "C" {
+
+int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
+                       const int32_t* hash_size, float* const* weight_hash, float* weight_high, int hotn, int D,
+                       float* out_dev, int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
+                       int32_t* row_out_dev, void* stream) {
+    if (!h) return CAFE_ERR_ARG;
+    CafeFields F;
+    int rc = fill_fields(&F, nfields, B, D, hotn, f_offset, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    if (!ids_dev || !out_dev || !gid_out_dev || !row_out_dev || !strides_ok(out_dev, out_field_stride, out_sample_stride))
+        return CAFE_ERR_ARG;
+    CafeSketchView V = cafe_internal_view(h);
+    if (hotn != V.lim) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int warps = (total + 31) / 32;
+    const int blocks = (warps + 7) / 8;
+    if (ids_are_int64) {
+        DISPATCH_G(D, (k_embed_forward<G, int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, V.main, V.n1, out_dev,
+                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
+    } else {
+        DISPATCH_G(D, (k_embed_forward<G, int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, V.main, V.n1, out_dev,
+                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
+    }
+    return fail_cuda("cafe_embed_forward");
+}
+
+int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields, int B,
+                         int D, float* imp_out_dev, void* stream) {
+    if (!h || nfields < 1 || nfields > CAFE_MAX_SEGMENTS || B < 0) return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    const int64_t total64 = (int64_t)nfields * B;
+    if (total64 == 0) return CAFE_OK;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    if (total64 > ws->cap) return CAFE_ERR_CAPACITY;
+    if (!grad_dev || !imp_out_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
+    const int total = (int)total64;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)(((int64_t)total * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
+                   sample_stride, B, total, ws->norm)));
+    k_field_sum<<<nfields, 1024, 0, st>>>(ws->norm, B, ws->totals);
+    k_importance<<<(total + 255) / 256, 256, 0, st>>>(ws->norm, ws->totals, B, total, imp_out_dev);
+    return fail_cuda("cafe_grad_importance");
+}
+
+int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t* mask_dev, const int32_t* post_row_dev,
+                 int nfields, int B, const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                 float* weight_high, int hotn, int D, int32_t* n_migrated_dev, void* stream) {
+    if (!h) return CAFE_ERR_ARG;
+    CafeFields F;
+    int rc = fill_fields(&F, nfields, B, D, hotn, f_offset, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    if (!ids_dev || !mask_dev || !post_row_dev) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int blocks = ((total + 31) / 32 + 7) / 8;
+    if (ids_are_int64) k_migrate<int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
+    else k_migrate<int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
+    return fail_cuda("cafe_migrate");
+}
+
+int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                     const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                     float* weight_high, int hotn, int D, float lr, void* stream) {
+    if (!h) return CAFE_ERR_ARG;
+    CafeFields F;
+    int64_t zero_off[CAFE_MAX_SEGMENTS] = {0};
+    int rc = fill_fields(&F, nfields, B, D, hotn, zero_off, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    if (total > ws->cap) return CAFE_ERR_CAPACITY;
+    if (!grad_dev || !row_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0], ws->pos[0]);
+    int bits = 1;
+    while ((1ll << bits) < (int64_t)hotn + F.hash_base[nfields]) ++bits;
+    size_t b = ws->cub_bytes;
+    cudaError_t e = cub::DeviceRadixSort::SortPairs(ws->cub_tmp, b, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1], total, 0,
+                                                    bits, st);
+    if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
+    const int64_t chunks = ((int64_t)total + CAFE_CHUNK - 1) / CAFE_CHUNK;
+    DISPATCH_G(D, (k_scatter_chunks<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, grad_dev, field_stride,
+                   sample_stride, ws->key[1], ws->pos[1], total, lr, ws->partial)));
+    DISPATCH_G(D, (k_scatter_fixup<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, ws->key[1], ws->pos[1], total,
+                   lr, ws->partial)));
+    return fail_cuda("cafe_scatter_sgd");
+}
+
+// The whole post-backward part of one training step for `nfields` fields, in the reference's order:
+// importance -> sketch insert (one call per field, ascending) -> migration with pre-update rows ->
+// SGD with the forward-time rows.
+int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const void* ids_dev,
+                        int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                        const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash, float* weight_high,
+                        int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev, int32_t* n_migrated_dev,
+                        void* stream) {
+    if (!h) return CAFE_ERR_ARG;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    const int64_t total = (int64_t)nfields * B;
+    if (total > ws->cap) return CAFE_ERR_CAPACITY;
+    if (total == 0) return CAFE_OK;
+    int rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
+    if (rc != CAFE_OK) return rc;
+    int seg[CAFE_MAX_SEGMENTS + 1];
+    for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
+    int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
+    int status = cafe_internal_insert(h, gid_dev, ws->imp, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
+    if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
+    rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
+                      hotn, D, n_migrated_dev, stream);
+    if (rc != CAFE_OK) return rc;
+    rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
+                          hotn, D, lr, stream);
+    return rc != CAFE_OK ? rc : status;
+}
+
+}  // extern "C"

@@ -198,6 +198,8 @@ CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
 // =================================================================================================
 // Parallel form.
 // =================================================================================================
+struct CafeFn { int32_t a, b; };   // FIFO size transfer: s -> max(s + a, b)
+
 struct CafeJob {
     // the lookups
     const uint32_t* gid;     // [M] global ids
@@ -243,8 +245,7 @@ struct CafeJob {
     uint8_t* pflag;      // [M] bit0: missed the main table; bits1-2: op slot of its candidate pop (+1)
     int32_t* tstamp;     // [M] inclusive count of misses up to each position
     int32_t* ins_res;    // [M] result of the believed event of this position: 0 ok, -1 failed, >0 failed and pushed this row
-    int32_t* op_a;       // [M] FIFO-size transfer function of the position: s -> max(s + a, b)
-    int32_t* op_b;
+    CafeFn* op_fn;       // [M] FIFO-size transfer function of the position, then its inclusive scan
     int64_t* op_cnt;     // [M] (pushes << 32) | successful pops, then their exclusive prefix sums
     // outputs
     int32_t* mask;       // [M] 1 = this lookup was handed a hot row (the reference's insert result)
@@ -490,13 +491,13 @@ CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) {
     cafe_op_fn(o.op0, &a0, &b0);
     cafe_op_fn(o.op1, &a1, &b1);
     cafe_compose(a0, b0, a1, b1, &a, &b);
-    J.op_a[p] = a;
-    J.op_b[p] = b;
+    CafeFn f; f.a = a; f.b = b;
+    J.op_fn[p] = f;
 }
 // 3b (after the inclusive scan of (op_a, op_b) under cafe_compose): outcome counts of position p
 CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_a[p - 1], J.op_b[p - 1], J.q_size);
+    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
     int64_t pops = 0, pushes = 0;
     if (o.op0 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op0 == 2) { ++pushes; ++s; }
     if (o.op1 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op1 == 2) { ++pushes; ++s; }
@@ -505,7 +506,7 @@ CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
 // 3c (after the exclusive prefix sum of op_cnt): write the timeline, compare with the consumed one
 CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_a[p - 1], J.op_b[p - 1], J.q_size);
+    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
     const int64_t pre = J.op_cnt[p];
     int32_t rank = (int32_t)(pre & 0xffffffffLL);
     int32_t npush = (int32_t)(pre >> 32);

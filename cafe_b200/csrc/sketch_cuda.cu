@@ -1,0 +1,506 @@
+// sketch_cuda.cu -- CUDA backend of the HotSketch engine (sm_100a) and the sketch part of the C ABI.
+//
+// Kernels here are thin: one thread per main bucket / LRU bucket / batch position calling the
+// functions of sketch_core.cuh.  Radix sorts and prefix scans use CUB device primitives with
+// temporary storage that is allocated once per handle, so nothing is allocated on the hot path.
+//
+// Reference being replaced: the single-threaded C++ HotSketch of tricks/sketch.cpp (batch_query
+// :260-265, batch_insert_val :281-296, reset :76-116).
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+#include <cub/cub.cuh>
+#include <string>
+
+#include "../../include/cafe_b200.h"
+#include "cafe_internal.h"
+#include "sketch_engine.h"
+
+#define CAFE_TPB 256
+
+static inline int cafe_blocks(int64_t n, int tpb = CAFE_TPB) { return (int)((n + tpb - 1) / tpb); }
+
+// ---------------------------------------------------------------------------------------------
+// kernels
+// ---------------------------------------------------------------------------------------------
+__global__ void k_fill_iota(uint32_t* p, int n, uint32_t first) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = first + (uint32_t)i;
+}
+
+__global__ void k_query(const CafeMainBucket* __restrict__ mb, int n1, const uint32_t* __restrict__ gid, int n,
+                        int32_t* __restrict__ out) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t x = gid[i];
+    const CafeMainBucket* b = &mb[cafe_hash(x, n1)];
+    // val and dic share the bucket's first 32-byte sector
+    const uint4 v = *reinterpret_cast<const uint4*>(b->val);
+    const int4 d = *reinterpret_cast<const int4*>(b->dic);
+    int32_t r = 0;
+    if (v.w == x && d.w != 0) r = d.w;
+    if (v.z == x && d.z != 0) r = d.z;
+    if (v.y == x && d.y != 0) r = d.y;
+    if (v.x == x && d.x != 0) r = d.x;
+    out[i] = r ? -r : (int32_t)x;
+}
+
+__global__ void k_post_query(const CafeMainBucket* __restrict__ mb, int n1, const uint32_t* __restrict__ gid, int n,
+                             const int32_t* __restrict__ mask, int32_t* __restrict__ out) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int32_t r = 0;
+    if (mask[i]) { const uint32_t x = gid[i]; r = cafe_probe_hot(mb[cafe_hash(x, n1)], x); }
+    out[i] = r;
+}
+
+__global__ void k_hash_keys(const uint32_t* __restrict__ gid, int M, int nb, uint32_t* __restrict__ key,
+                            int32_t* __restrict__ pos) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M) return;
+    key[i] = (uint32_t)cafe_hash(gid[i], nb);
+    pos[i] = i;
+}
+
+// start[k] = first sorted index whose key is >= k, for k in [0, nb]
+__global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb, int32_t* __restrict__ start) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > M) return;
+    const int lo = (i == 0) ? 0 : (int)skey[i - 1] + 1;
+    const int hi = (i == M) ? nb : (int)skey[i];
+    for (int k = lo; k <= hi; ++k) start[k] = i;
+}
+
+__global__ void k_main_pass(const __grid_constant__ CafeJob J) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < J.n1) cafe_main_pass_bucket(J, k);
+}
+__global__ void k_lru_pass(const __grid_constant__ CafeJob J) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < J.n2) cafe_lru_pass_bucket(J, k);
+}
+__global__ void k_resolve_ops(const __grid_constant__ CafeJob J) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_resolve_ops(J, p);
+}
+__global__ void k_resolve_count(const __grid_constant__ CafeJob J) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_resolve_count(J, p);
+}
+__global__ void k_resolve_write(const __grid_constant__ CafeJob J) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_resolve_write(J, p);
+}
+__global__ void k_commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
+                               const uint32_t* __restrict__ pushbuf, int n_push) {
+    int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j < n_push) cafe_commit_push(ring, mask, q_head, q_size, n_pop_ok, pushbuf, j);
+}
+
+// The golden path: one thread, lookups strictly in order.
+__global__ void k_seq_insert(CafeSeqState* Sd, const uint32_t* __restrict__ gid, const float* __restrict__ imp, int n,
+                             int32_t* __restrict__ mask) {
+    if (blockIdx.x != 0 || threadIdx.x != 0) return;
+    CafeSeqState S = *Sd;
+    for (int i = 0; i < n; ++i) mask[i] = cafe_seq_insert(S, gid[i], imp ? imp[i] : 1.0f);
+    *Sd = S;
+}
+
+struct MissFlag {
+    __host__ __device__ __forceinline__ int32_t operator()(const uint8_t& f) const { return (int32_t)(f & 1); }
+};
+struct FnCompose {
+    __host__ __device__ __forceinline__ CafeFn operator()(const CafeFn& f, const CafeFn& g) const {
+        CafeFn r;
+        cafe_compose(f.a, f.b, g.a, g.b, &r.a, &r.b);
+        return r;
+    }
+};
+
+// threshold re-fit, step 1: lazy decay of every bucket and number of candidates per bucket
+__global__ void k_reset_count(CafeMainBucket* mb, CafeLruBucket* lb, int n1, int n2, uint32_t gflip, float thr,
+                              int32_t* __restrict__ cnt) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < n1) {
+        CafeMainBucket b = mb[k];
+        const uint32_t f0 = b.flip;
+        cnt[k] = cafe_reset_touch_count_main(b, gflip, thr);
+        if (f0 != b.flip) mb[k] = b;
+    } else if (k < n1 + n2) {
+        CafeLruBucket b = lb[k - n1];
+        const uint32_t f0 = b.flip;
+        cnt[k] = cafe_reset_touch_count_lru(b, gflip, thr);
+        if (f0 != b.flip) lb[k - n1] = b;
+    } else if (k == n1 + n2) {
+        cnt[k] = 0;
+    }
+}
+// step 2 (after an exclusive scan of cnt): candidates in canonical order
+__global__ void k_reset_emit(const CafeMainBucket* __restrict__ mb, const CafeLruBucket* __restrict__ lb, int n1, int n2,
+                             float thr, const int32_t* __restrict__ off, uint32_t* __restrict__ key,
+                             int32_t* __restrict__ val) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= n1 + n2) return;
+    int o = off[k];
+    if (k < n1) {
+        const CafeMainBucket b = mb[k];
+        for (int i = 0; i < CAFE_SLOTS; ++i)
+            if (b.cnt[i] >= thr || b.dic[i] != 0) { key[o] = cafe_float_bits(b.cnt[i]); val[o] = k * CAFE_SLOTS + i; ++o; }
+    } else {
+        const CafeLruBucket b = lb[k - n1];
+        for (int i = 0; i < CAFE_SLOTS; ++i)
+            if (b.cnt[i] >= thr || b.dic[i] != 0) { key[o] = cafe_float_bits(b.cnt[i]); val[o] = n1 * CAFE_SLOTS + (k - n1) * CAFE_SLOTS + i; ++o; }
+    }
+}
+// step 3 (after the stable sort by count): sketch.cpp:98-115.  One block; each thread owns a
+// contiguous chunk of the sorted candidates so that ranks follow the sorted order.
+#define CAFE_RESET_TPB 1024
+__global__ void __launch_bounds__(CAFE_RESET_TPB)
+k_reset_apply(const uint32_t* __restrict__ key, const int32_t* __restrict__ val, int l, int lim, CafeMainBucket* mb,
+              CafeLruBucket* lb, int n1, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size,
+              int32_t* __restrict__ out) {
+    typedef cub::BlockScan<int, CAFE_RESET_TPB> Scan;
+    __shared__ typename Scan::TempStorage tmp;
+    __shared__ int s_total;
+    const int z = l - lim;
+    const int tid = threadIdx.x;
+    // losers: candidates [0, z] give their rows back, in sorted order
+    {
+        const int n = z + 1;
+        const int per = (n + CAFE_RESET_TPB - 1) / CAFE_RESET_TPB;
+        const int lo = min(n, tid * per), hi = min(n, lo + per);
+        int c = 0;
+        for (int i = lo; i < hi; ++i) c += (*cafe_slot_dic(mb, lb, n1, val[i]) != 0);
+        int base, total;
+        Scan(tmp).ExclusiveSum(c, base, total);
+        for (int i = lo; i < hi; ++i) {
+            int32_t* d = cafe_slot_dic(mb, lb, n1, val[i]);
+            if (*d != 0) { ring[(q_head + (uint32_t)(q_size + base)) & mask] = (uint32_t)*d; *d = 0; ++base; }
+        }
+        if (tid == 0) s_total = total;
+    }
+    __syncthreads();
+    const int npush = s_total;
+    const int avail = q_size + npush;
+    __syncthreads();
+    // winners: candidates (z, l) without a row take the FIFO front, in sorted order, while it lasts
+    {
+        const int n = l - (z + 1);
+        const int per = (n + CAFE_RESET_TPB - 1) / CAFE_RESET_TPB;
+        const int lo = min(n, tid * per), hi = min(n, lo + per);
+        int c = 0;
+        for (int i = lo; i < hi; ++i) c += (*cafe_slot_dic(mb, lb, n1, val[z + 1 + i]) == 0);
+        int base, total;
+        Scan(tmp).ExclusiveSum(c, base, total);
+        for (int i = lo; i < hi; ++i) {
+            int32_t* d = cafe_slot_dic(mb, lb, n1, val[z + 1 + i]);
+            if (*d == 0) {
+                if (base < avail) *d = (int32_t)ring[(q_head + (uint32_t)base) & mask];
+                ++base;
+            }
+        }
+        if (tid == 0) { out[0] = (int32_t)key[z]; out[1] = npush; out[2] = min(total, avail); }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backend
+// ---------------------------------------------------------------------------------------------
+struct CudaBackend {
+    cudaStream_t stream = 0;
+    cudaError_t err = cudaSuccess;
+    void* cub_tmp = nullptr;
+    size_t cub_bytes = 0;
+    uint32_t *key_in = nullptr, *key_out = nullptr;
+    int32_t* pos_in = nullptr;
+    int cap = 0;
+    void* pinned = nullptr;   // staging for small device-to-host reads
+
+    ~CudaBackend() {
+        if (cub_tmp) cudaFree(cub_tmp);
+        if (key_in) cudaFree(key_in);
+        if (key_out) cudaFree(key_out);
+        if (pos_in) cudaFree(pos_in);
+        if (pinned) cudaFreeHost(pinned);
+    }
+    void check(cudaError_t e) { if (e != cudaSuccess && err == cudaSuccess) err = e; }
+    void check_launch() { check(cudaGetLastError()); }
+    bool ok() { return err == cudaSuccess; }
+
+    void* alloc(size_t n) { void* p = nullptr; check(cudaMalloc(&p, n ? n : 1)); return p; }
+    void free(void* p) { cudaFree(p); }
+    void memset(void* p, int v, size_t n) { if (n) check(cudaMemsetAsync(p, v, n, stream)); }
+    void fill_iota(uint32_t* p, int n, uint32_t first) {
+        if (n > 0) { k_fill_iota<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(p, n, first); check_launch(); }
+    }
+    void h2d(void* d, const void* s, size_t n) {
+        check(cudaMemcpyAsync(d, s, n, cudaMemcpyHostToDevice, stream));
+        check(cudaStreamSynchronize(stream));
+    }
+    void d2h(void* d, const void* s, size_t n) {
+        if (pinned && n <= 4096) {
+            check(cudaMemcpyAsync(pinned, s, n, cudaMemcpyDeviceToHost, stream));
+            check(cudaStreamSynchronize(stream));
+            memcpy(d, pinned, n);
+        } else {
+            check(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToHost, stream));
+            check(cudaStreamSynchronize(stream));
+        }
+    }
+
+    bool prepare(int cap_, int n1, int n2) {
+        cap = cap_;
+        check(cudaMalloc(&key_in, 4 * (size_t)cap));
+        check(cudaMalloc(&key_out, 4 * (size_t)cap));
+        check(cudaMalloc(&pos_in, 4 * (size_t)cap));
+        check(cudaMallocHost(&pinned, 4096));
+        // largest temporary any CUB call below can ask for
+        size_t need = 0, b = 0;
+        const int ncand = (n1 + n2) * CAFE_SLOTS;
+        const int nsort = cap > ncand ? cap : ncand;
+        cub::DeviceRadixSort::SortPairs(nullptr, b, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
+                                        (int32_t*)nullptr, nsort, 0, 32, stream);
+        need = b > need ? b : need;
+        cub::DeviceScan::InclusiveSum(nullptr, b, (int32_t*)nullptr, (int32_t*)nullptr, nsort, stream);
+        need = b > need ? b : need;
+        cub::DeviceScan::ExclusiveSum(nullptr, b, (int64_t*)nullptr, (int64_t*)nullptr, nsort, stream);
+        need = b > need ? b : need;
+        cub::DeviceScan::InclusiveScan(nullptr, b, (CafeFn*)nullptr, (CafeFn*)nullptr, FnCompose(), nsort, stream);
+        need = b > need ? b : need;
+        cub_bytes = need * 2 + 1024;
+        check(cudaMalloc(&cub_tmp, cub_bytes));
+        return ok();
+    }
+
+    void query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, int32_t* out) {
+        k_query<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(mb, n1, gid, n, out);
+        check_launch();
+    }
+    void post_query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, const int32_t* mask, int32_t* out) {
+        k_post_query<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(mb, n1, gid, n, mask, out);
+        check_launch();
+    }
+    static int bits_for(int nb) { int b = 1; while ((1ll << b) < nb) ++b; return b; }
+
+    // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
+    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
+        k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, stream>>>(gid, M, nb, key_in, pos_in);
+        check_launch();
+        size_t b = cub_bytes;
+        check(cub::DeviceRadixSort::SortPairs(cub_tmp, b, key_in, key_out, pos_in, ord, M, 0, bits_for(nb), stream));
+        k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, stream>>>(key_out, M, nb, start);
+        check_launch();
+    }
+    void main_pass(const CafeJob& J) {
+        k_main_pass<<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J);
+        check_launch();
+    }
+    void scan_miss(const CafeJob& J) {
+        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.pflag, MissFlag());
+        size_t b = cub_bytes;
+        check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp, J.limit, stream));
+    }
+    void lru_pass(const CafeJob& J) {
+        k_lru_pass<<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J);
+        check_launch();
+    }
+    void resolve(const CafeJob& J) {
+        const int g = cafe_blocks(J.limit);
+        k_resolve_ops<<<g, CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+        size_t b = cub_bytes;
+        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, J.op_fn, J.op_fn, FnCompose(), J.limit, stream));
+        k_resolve_count<<<g, CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+        b = cub_bytes;
+        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, J.op_cnt, J.op_cnt, J.limit, stream));
+        k_resolve_write<<<g, CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+    }
+    void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
+                      const uint32_t* pushbuf, int n_push) {
+        k_commit_queue<<<cafe_blocks(n_push), CAFE_TPB, 0, stream>>>(ring, mask, q_head, q_size, n_pop_ok, pushbuf, n_push);
+        check_launch();
+    }
+    void seq_insert(CafeSeqState* dev, CafeSeqState* S, const uint32_t* gid, const float* imp, int n, int32_t* mask) {
+        check(cudaMemcpyAsync(dev, S, sizeof(CafeSeqState), cudaMemcpyHostToDevice, stream));
+        k_seq_insert<<<1, 32, 0, stream>>>(dev, gid, imp, n, mask);
+        check_launch();
+        d2h(S, dev, sizeof(CafeSeqState));
+    }
+    void reset_collect(CafeMainBucket* mb, CafeLruBucket* lb, int n1, int n2, uint32_t gflip, float thr, int32_t* cnt,
+                       uint32_t* key, int32_t* val, int32_t* l_out) {
+        const int nb = n1 + n2;
+        k_reset_count<<<cafe_blocks((int64_t)nb + 1), CAFE_TPB, 0, stream>>>(mb, lb, n1, n2, gflip, thr, cnt);
+        check_launch();
+        size_t b = cub_bytes;
+        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, cnt, cnt, nb + 1, stream));
+        k_reset_emit<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(mb, lb, n1, n2, thr, cnt, key, val);
+        check_launch();
+        d2h(l_out, cnt + nb, 4);
+    }
+    void sort_pairs(const uint32_t* kin, const int32_t* vin, uint32_t* kout, int32_t* vout, int n, int bits) {
+        size_t b = cub_bytes;
+        check(cub::DeviceRadixSort::SortPairs(cub_tmp, b, kin, kout, vin, vout, n, 0, bits, stream));
+    }
+    void reset_apply(const uint32_t* key, const int32_t* val, int l, int lim, CafeMainBucket* mb, CafeLruBucket* lb,
+                     int n1, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t* dev_out,
+                     int32_t* out) {
+        k_reset_apply<<<1, CAFE_RESET_TPB, 0, stream>>>(key, val, l, lim, mb, lb, n1, ring, mask, q_head, q_size, dev_out);
+        check_launch();
+        d2h(out, dev_out, 12);
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// handle + C ABI (sketch part)
+// ---------------------------------------------------------------------------------------------
+struct CafeHandle {
+    SketchEngine<CudaBackend> eng;
+    int device = 0;
+    CafeEmbedWorkspace ws;
+};
+
+static thread_local std::string g_last_error;
+static void set_error(const char* where, cudaError_t e) {
+    g_last_error = std::string(where) + ": " + cudaGetErrorString(e);
+}
+
+#define CAFE_H(h) CafeHandle* H = (CafeHandle*)(h); if (!H) return CAFE_ERR_ARG
+
+static int finish(CafeHandle* H, int rc, const char* where) {
+    if (!H->eng.be.ok()) { set_error(where, H->eng.be.err); return CAFE_ERR_CUDA; }
+    return rc;
+}
+
+CafeSketchView cafe_internal_view(void* h) {
+    CafeHandle* H = (CafeHandle*)h;
+    CafeSketchView v;
+    v.main = H->eng.main_table(); v.n1 = H->eng.n1; v.lim = H->eng.lim; v.cap = H->eng.capacity();
+    return v;
+}
+CafeEmbedWorkspace* cafe_internal_ws(void* h) { return &((CafeHandle*)h)->ws; }
+int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const int* seg_off, int nseg, int32_t* mask,
+                         int32_t* post_row, int mode, cudaStream_t stream) {
+    CafeHandle* H = (CafeHandle*)h;
+    H->eng.be.stream = stream;
+    int rc = H->eng.insert_segments(gid, imp, seg_off, nseg, mask, post_row, mode != CAFE_INSERT_SEQUENTIAL);
+    return finish(H, rc, "cafe_sketch_insert");
+}
+void cafe_internal_set_error(const char* msg) { g_last_error = msg; }
+
+extern "C" {
+
+const char* cafe_last_error(void) { return g_last_error.c_str(); }
+
+int cafe_sketch_create(void** out, int hotn, float threshold, int adjust_thres, double alpha, int max_lookups) {
+    if (!out) return CAFE_ERR_ARG;
+    *out = nullptr;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("cafe_sketch_create", e); return CAFE_ERR_CUDA; }
+    CafeHandle* H = new CafeHandle();
+    H->device = dev;
+    int rc = H->eng.init(hotn, threshold, adjust_thres, alpha, max_lookups);
+    if (rc == CAFE_OK) rc = cafe_embed_ws_init(&H->ws, max_lookups, hotn);
+    if (rc != CAFE_OK) {
+        if (!H->eng.be.ok()) set_error("cafe_sketch_create", H->eng.be.err);
+        delete H;
+        return rc;
+    }
+    cudaError_t se = cudaStreamSynchronize(0);
+    if (se != cudaSuccess) { set_error("cafe_sketch_create", se); delete H; return CAFE_ERR_CUDA; }
+    *out = H;
+    return CAFE_OK;
+}
+
+int cafe_sketch_destroy(void* h) {
+    CAFE_H(h);
+    cudaDeviceSynchronize();
+    cafe_embed_ws_free(&H->ws);
+    delete H;
+    return CAFE_OK;
+}
+
+int cafe_sketch_query(void* h, const uint32_t* gid_dev, int n, int32_t* out_dev, void* stream) {
+    CAFE_H(h);
+    if (n < 0 || (n > 0 && (!gid_dev || !out_dev))) return CAFE_ERR_ARG;
+    H->eng.be.stream = (cudaStream_t)stream;
+    return finish(H, H->eng.query(gid_dev, n, out_dev), "cafe_sketch_query");
+}
+
+int cafe_sketch_insert(void* h, const uint32_t* gid_dev, const float* imp_dev, const int* seg_off_host, int nseg,
+                       int32_t* mask_dev, int32_t* post_row_dev, int mode, void* stream) {
+    CAFE_H(h);
+    return cafe_internal_insert(h, gid_dev, imp_dev, seg_off_host, nseg, mask_dev, post_row_dev, mode, (cudaStream_t)stream);
+}
+
+int cafe_sketch_refit(void* h, void* stream) {
+    CAFE_H(h);
+    H->eng.be.stream = (cudaStream_t)stream;
+    return finish(H, H->eng.refit_threshold(), "cafe_sketch_refit");
+}
+
+int cafe_sketch_sizes(void* h, int* n1, int* n2, int* lim, int* capacity) {
+    CAFE_H(h);
+    if (n1) *n1 = H->eng.n1;
+    if (n2) *n2 = H->eng.n2;
+    if (lim) *lim = H->eng.lim;
+    if (capacity) *capacity = H->eng.capacity();
+    return CAFE_OK;
+}
+
+// scalars[0..7] = threshold bits, real_n, num, t, flip bit, FIFO length, calls so far, fused window
+int cafe_sketch_scalars(void* h, int64_t* scalars, double* decay_importance) {
+    CAFE_H(h);
+    if (!scalars) return CAFE_ERR_ARG;
+    uint32_t bits;
+    memcpy(&bits, &H->eng.thr, 4);
+    scalars[0] = bits; scalars[1] = H->eng.real_n; scalars[2] = H->eng.num; scalars[3] = H->eng.t;
+    scalars[4] = H->eng.gflip; scalars[5] = H->eng.q_size; scalars[6] = H->eng.batch_num; scalars[7] = H->eng.window;
+    if (decay_importance) *decay_importance = H->eng.decay_importance;
+    return CAFE_OK;
+}
+
+int cafe_sketch_set_scalars(void* h, const int64_t* scalars, double decay_importance) {
+    CAFE_H(h);
+    if (!scalars) return CAFE_ERR_ARG;
+    uint32_t bits = (uint32_t)scalars[0];
+    memcpy(&H->eng.thr, &bits, 4);
+    H->eng.real_n = (int)scalars[1]; H->eng.num = (int)scalars[2]; H->eng.t = (int)scalars[3];
+    H->eng.gflip = (uint32_t)scalars[4]; H->eng.batch_num = (int)scalars[6];
+    H->eng.decay_importance = decay_importance;
+    return CAFE_OK;
+}
+
+int cafe_sketch_tuning(void* h, int window, int round_cap) {
+    CAFE_H(h);
+    if (window > 0) H->eng.window = window > CAFE_MAX_SEGMENTS ? CAFE_MAX_SEGMENTS : window;
+    if (round_cap > 0) H->eng.round_cap = round_cap;
+    return CAFE_OK;
+}
+
+int cafe_sketch_stats(void* h, int64_t* out13) {
+    CAFE_H(h);
+    if (!out13) return CAFE_ERR_ARG;
+    memcpy(out13, &H->eng.stats, sizeof(CafeSketchStats));
+    return CAFE_OK;
+}
+
+int cafe_sketch_dump(void* h, uint32_t* mval, float* mcnt, int32_t* mdic, uint8_t* mflip, uint32_t* lval, float* lcnt,
+                     int32_t* ldic, int32_t* lt, uint8_t* lflip, uint32_t* queue, void* stream) {
+    CAFE_H(h);
+    H->eng.be.stream = (cudaStream_t)stream;
+    H->eng.dump(mval, mcnt, mdic, mflip, lval, lcnt, ldic, lt, lflip, queue);
+    return finish(H, CAFE_OK, "cafe_sketch_dump");
+}
+
+int cafe_sketch_load(void* h, const uint32_t* mval, const float* mcnt, const int32_t* mdic, const uint8_t* mflip,
+                     const uint32_t* lval, const float* lcnt, const int32_t* ldic, const int32_t* lt, const uint8_t* lflip,
+                     const uint32_t* queue, int queue_len, void* stream) {
+    CAFE_H(h);
+    H->eng.be.stream = (cudaStream_t)stream;
+    return finish(H, H->eng.load(mval, mcnt, mdic, mflip, lval, lcnt, ldic, lt, lflip, queue, queue_len), "cafe_sketch_load");
+}
+
+}  // extern "C"

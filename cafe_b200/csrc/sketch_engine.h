@@ -85,7 +85,7 @@ public:
         pflag = (uint8_t*)be.alloc(M);
         tstamp = (int32_t*)be.alloc(4 * M);
         ins_res = (int32_t*)be.alloc(4 * M);
-        op_a = (int32_t*)be.alloc(4 * M); op_b = (int32_t*)be.alloc(4 * M);
+        op_fn = (CafeFn*)be.alloc(sizeof(CafeFn) * M);
         op_cnt = (int64_t*)be.alloc(8 * M);
         res_dev = (CafeRoundResult*)be.alloc(sizeof(CafeRoundResult));
         seq_dev = (CafeSeqState*)be.alloc(sizeof(CafeSeqState));
@@ -95,7 +95,7 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !pflag || !tstamp || !ins_res || !op_a || !op_b || !op_cnt ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !pflag || !tstamp || !ins_res || !op_fn || !op_cnt ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
         for (int i = 0; i < 2; ++i)
@@ -254,7 +254,8 @@ private:
     int32_t* tl_rank[2] = {nullptr, nullptr};
     uint32_t* pushbuf[2] = {nullptr, nullptr};
     uint8_t* pflag = nullptr;
-    int32_t *tstamp = nullptr, *ins_res = nullptr, *op_a = nullptr, *op_b = nullptr;
+    int32_t *tstamp = nullptr, *ins_res = nullptr;
+    CafeFn* op_fn = nullptr;
     int64_t* op_cnt = nullptr;
     CafeRoundResult* res_dev = nullptr;
     CafeSeqState* seq_dev = nullptr;
@@ -267,7 +268,7 @@ private:
         if (!ready && !mainb[0]) return;
         void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, ev[0], ev[1], head[0],
                         head[1], nxt[0], nxt[1], tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
-                        pflag, tstamp, ins_res, op_a, op_b, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
+                        pflag, tstamp, ins_res, op_fn, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
         mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
@@ -320,7 +321,7 @@ private:
         J.ord1 = ord1; J.start1 = start1; J.ord2 = ord2; J.start2 = start2;
         J.n1 = n1; J.n2 = n2; J.thr = thr; J.gflip = gflip; J.t0 = t;
         J.ring = ring; J.ring_mask = ring_mask; J.q_head = q_head; J.q_size = q_size;
-        J.pflag = pflag; J.tstamp = tstamp; J.ins_res = ins_res; J.op_a = op_a; J.op_b = op_b; J.op_cnt = op_cnt;
+        J.pflag = pflag; J.tstamp = tstamp; J.ins_res = ins_res; J.op_fn = op_fn; J.op_cnt = op_cnt;
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;

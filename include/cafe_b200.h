@@ -1,0 +1,146 @@
+/*
+ * cafe_b200.h -- C ABI of libcafe_b200.so: the CAFE compressed-embedding hot path on one B200.
+ *
+ * Plain C signatures: device and host pointers, sizes, a stream passed as void* (a cudaStream_t; 0 is
+ * the default stream).  Every function returns a status (CAFE_OK = 0) unless noted; after
+ * CAFE_ERR_CUDA, cafe_last_error() describes the failing call.  A handle belongs to the CUDA device
+ * that was current when it was created and must be used by one host thread at a time.
+ *
+ * Citations give the reference interface each entry point stands in for (paths inside the
+ * reference project).
+ */
+#ifndef CAFE_B200_H
+#define CAFE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef CAFE_STATUS_ENUMS
+#define CAFE_STATUS_ENUMS
+enum {
+    CAFE_OK = 0,
+    CAFE_ERR_ARG = 1,
+    CAFE_ERR_CAPACITY = 2,
+    CAFE_ERR_CUDA = 3,
+    CAFE_ERR_NOCONVERGE = 4,        /* informational: the sequential kernel finished the job; results are exact */
+    CAFE_ERR_RESET_UNDERFLOW = 5,   /* informational: a threshold re-fit was refused (fewer candidates than rows) */
+    CAFE_ERR_UNSUPPORTED = 6
+};
+enum { CAFE_INSERT_PARALLEL = 0, CAFE_INSERT_SEQUENTIAL = 1 };
+#endif
+#define CAFE_MAX_FIELDS 64
+
+const char* cafe_last_error(void);
+
+/* ---- HotSketch, device ABI -------------------------------------------------------------------- */
+
+/* Replaces init(n, Threshold, adjust_thres, alp) (tricks/sketch.cpp:309-313) and the SS constructor
+ * (:44-70).  hotn = number of hot rows (`lim`); max_lookups = the largest number of ids any later
+ * call will pass (all fields of one fused call together).  All device memory is allocated here. */
+int cafe_sketch_create(void** handle, int hotn, float threshold, int adjust_thres, double alpha, int max_lookups);
+int cafe_sketch_destroy(void* handle);
+
+/* Replaces batch_query (tricks/sketch.cpp:260-265, 300-302): out[i] = -hot_row if gid[i] is hot, else
+ * (int32)gid[i].  Device pointers; no host synchronisation. */
+int cafe_sketch_query(void* handle, const uint32_t* gid_dev, int n, int32_t* out_dev, void* stream);
+
+/* Replaces batch_insert_val / batch_insert (tricks/sketch.cpp:266-296, 303-308): nseg consecutive calls,
+ * call s covering lookups [seg_off_host[s], seg_off_host[s+1]).  imp_dev == NULL gives batch_insert
+ * (unit counts).  mask_dev[i] = the reference's per-lookup result (1 = handed a hot row).
+ * post_row_dev (optional) = for lookups with mask 1, the hot row a batch_query right after that
+ * lookup's own call would return (0 if none) -- what the module's guarded migration needs.
+ * mode: CAFE_INSERT_PARALLEL (round-based, all buckets at once) or CAFE_INSERT_SEQUENTIAL (one
+ * thread, the on-device golden path).  Both leave the state the reference's loop would leave.
+ * Synchronises with the host (the round loop reads a convergence flag). */
+int cafe_sketch_insert(void* handle, const uint32_t* gid_dev, const float* imp_dev, const int* seg_off_host, int nseg,
+                       int32_t* mask_dev, int32_t* post_row_dev, int mode, void* stream);
+
+/* Replaces SS::reset (tricks/sketch.cpp:76-116), normally triggered inside cafe_sketch_insert at a
+ * call boundary; exported for tests.  Ties are ordered main table before LRU table, bucket, slot. */
+int cafe_sketch_refit(void* handle, void* stream);
+
+int cafe_sketch_sizes(void* handle, int* n1, int* n2, int* lim, int* capacity);
+/* scalars[8] = threshold (float bits), real_n, num, t, flip bit, free-row FIFO length, calls so far,
+ * fused-call window.  These are the members / globals of tricks/sketch.cpp:7-21. */
+int cafe_sketch_scalars(void* handle, int64_t* scalars, double* decay_importance);
+int cafe_sketch_set_scalars(void* handle, const int64_t* scalars, double decay_importance);
+int cafe_sketch_tuning(void* handle, int window, int round_cap);
+/* out[13] = calls, lookups, rounds, jobs, truncated_jobs, resets, resets_refused, flips,
+ * seq_fallbacks, main_hits, lru_visits, events, max_rounds */
+int cafe_sketch_stats(void* handle, int64_t* out13);
+/* Full state to / from host arrays ([4*n1], [n1], [4*n2], [n2], FIFO front to back).  No counterpart
+ * in tricks/sketch.cpp (its state cannot be saved); layout follows save_state/load_state of
+ * TOIS_revision/PinSAGE/sketch.cpp:333-402 in spirit. */
+int cafe_sketch_dump(void* handle, uint32_t* main_val, float* main_cnt, int32_t* main_dic, uint8_t* main_flip,
+                     uint32_t* lru_val, float* lru_cnt, int32_t* lru_dic, int32_t* lru_t, uint8_t* lru_flip,
+                     uint32_t* queue, void* stream);
+int cafe_sketch_load(void* handle, const uint32_t* main_val, const float* main_cnt, const int32_t* main_dic,
+                     const uint8_t* main_flip, const uint32_t* lru_val, const float* lru_cnt, const int32_t* lru_dic,
+                     const int32_t* lru_t, const uint8_t* lru_flip, const uint32_t* queue, int queue_len, void* stream);
+
+/* ---- SKEmbeddingBag data path, device ABI -------------------------------------------------------
+ * Lookups are field-major: lookup p = f*B + b is sample b of field f (the reference's lS_i[F][B],
+ * one id per bag).  Host arrays f_offset[nfields], hash_size[nfields], weight_hash[nfields] (device
+ * pointers to [hash_size[f], D] fp32 tables); weight_high is the shared [hotn, D] hot table.
+ * Row tensors are addressed as base + f*field_stride + b*sample_stride (+ column), strides in
+ * floats and multiples of 4; D in {16, 32, 64, 128}. */
+
+/* Replaces SKEmbeddingBag.query + forward (tricks/sk_embedding_bag.py:101-152): global id =
+ * uint32(id + f_offset[f]); hot -> weight_high[row], else weight_hash[f][global id % hash_size[f]].
+ * Also writes the global ids and the row code (-hot_row, or +hash_row) for the backward. */
+int cafe_embed_forward(void* handle, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
+                       const int32_t* hash_size, float* const* weight_hash, float* weight_high, int hotn, int D,
+                       float* out_dev, int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
+                       int32_t* row_out_dev, void* stream);
+
+/* Replaces the importance arithmetic of insert_grad (tricks/sk_embedding_bag.py:178-189):
+ * imp[p] = ||grad row p||_2 * B / sum over the field of the norms. */
+int cafe_grad_importance(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields,
+                         int B, int D, float* imp_out_dev, void* stream);
+
+/* Replaces the row-copy loop of insert_grad (tricks/sk_embedding_bag.py:205-208), guarded: for lookups
+ * with mask 1 and post_row > 0, weight_high[post_row] = weight_hash[f][local id % hash_size[f]]. */
+int cafe_migrate(void* handle, const void* ids_dev, int ids_are_int64, const int32_t* mask_dev,
+                 const int32_t* post_row_dev, int nfields, int B, const int64_t* f_offset, const int32_t* hash_size,
+                 float* const* weight_hash, float* weight_high, int hotn, int D, int32_t* n_migrated_dev, void* stream);
+
+/* Replaces the sparse embedding_bag backward plus torch.optim.SGD.step on weight_high and every
+ * weight_hash (dlrm_s_pytorch.py:1658): row -= lr * (sum of the gradient rows of its lookups), rows
+ * as coded by cafe_embed_forward. */
+int cafe_scatter_sgd(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                     const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                     float* weight_high, int hotn, int D, float lr, void* stream);
+
+/* One call for everything between loss.backward() and the end of optimizer.step() for these fields
+ * (dlrm_s_pytorch.py:1653-1658): importance, insert (one reference call per field, ascending),
+ * migration with pre-update rows, SGD with forward-time rows.  mask_out_dev / n_migrated_dev optional. */
+int cafe_embed_backward(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                        const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev,
+                        int nfields, int B, const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                        float* weight_high, int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev,
+                        int32_t* n_migrated_dev, void* stream);
+
+/* ---- the reference's own ctypes ABI, host pointers (tricks/sketch.cpp:300-327) ------------------
+ * Same names, argument meaning and result convention (pointer to a library-owned int array that is
+ * valid until the next call), so that the reference's Python can bind this library in place of its
+ * sklib.so.  One process-global sketch; data are staged through device buffers.  On failure the
+ * pointer-returning calls return NULL and the double-returning calls return -1 (see
+ * cafe_last_error). */
+void init(int n, int Threshold, int adjust_thres, double alp);
+int* batch_query(uint32_t* data, int len);
+int* batch_insert(uint32_t* data, int len);
+int* batch_insert_val(uint32_t* data, float* v, int len);
+double analyse(uint32_t* data, int len);
+double analyse1(uint32_t* data, int len);
+/* The handle behind the six calls above (NULL before init), for use with the device ABI. */
+void* cafe_global_handle(void);
+/* Largest len the six calls accept (default 1<<21); takes effect at the next init. */
+int cafe_global_set_capacity(int max_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CAFE_B200_H */

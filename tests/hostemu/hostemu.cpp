@@ -65,8 +65,8 @@ struct HostBackend {
         for (int p = 0; p < J.limit; ++p) cafe_resolve_ops(J, p);
         for (int p = 1; p < J.limit; ++p) {
             int32_t a, b;
-            cafe_compose(J.op_a[p - 1], J.op_b[p - 1], J.op_a[p], J.op_b[p], &a, &b);
-            J.op_a[p] = a; J.op_b[p] = b;
+            cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &a, &b);
+            J.op_fn[p].a = a; J.op_fn[p].b = b;
         }
         for (int p = 0; p < J.limit; ++p) cafe_resolve_count(J, p);
         int64_t acc = 0;
