@@ -1,21 +1,37 @@
 """cafe_b200: the CAFE compressed-embedding hot path (HotSketch + SKEmbeddingBag) on B200 CUDA kernels.
 
-Importing the package loads libcafe_b200.so; it raises if the library has not been built
-(`python -m cafe_b200.build`).  There is no CPU path.
+Everything here runs on libcafe_b200.so (built by `python -m cafe_b200.build`).  The library is loaded
+the first time any name of the package is used; if it is missing that use raises with the build
+command in the message.  There is no CPU path.
 """
-from . import _lib, sizing
-from ._lib import CafeError, INSERT_PARALLEL, INSERT_SEQUENTIAL
+from __future__ import annotations
 
-_lib.load()
+__all__ = ["HotSketch", "SKEmbeddingBag", "SKEmbeddingGroup", "attach_optimizer", "sizing", "synthetic", "CafeError",
+           "INSERT_PARALLEL", "INSERT_SEQUENTIAL", "load_library", "profile"]
 
-from .sketch import HotSketch  # noqa: E402
-from .sk_embedding_bag import SKEmbeddingBag, SKEmbeddingGroup, attach_optimizer  # noqa: E402
-
-__all__ = ["HotSketch", "SKEmbeddingBag", "SKEmbeddingGroup", "attach_optimizer", "sizing", "CafeError",
-           "INSERT_PARALLEL", "INSERT_SEQUENTIAL", "load_library"]
+INSERT_PARALLEL, INSERT_SEQUENTIAL = 0, 1
 
 
 def load_library():
     """The ctypes library object; pass it where the reference's code expects `lib` (it exports init,
     batch_query, batch_insert, batch_insert_val, analyse, analyse1 like the reference's sklib.so)."""
+    from . import _lib
     return _lib.load()
+
+
+def __getattr__(name):
+    if name in ("HotSketch",):
+        load_library()
+        from .sketch import HotSketch
+        return HotSketch
+    if name in ("SKEmbeddingBag", "SKEmbeddingGroup", "attach_optimizer"):
+        load_library()
+        from . import sk_embedding_bag
+        return getattr(sk_embedding_bag, name)
+    if name == "CafeError":
+        from ._lib import CafeError
+        return CafeError
+    if name in ("sizing", "synthetic", "profile", "sharded"):
+        import importlib
+        return importlib.import_module(f".{name}", __name__)
+    raise AttributeError(f"module 'cafe_b200' has no attribute {name!r}")

@@ -49,6 +49,11 @@ SIGNATURES = {
                                  c_float, _vp]),
     "cafe_embed_backward": (c_int, [_vp, _vp, c_int64, c_int64, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                     POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp, _vp]),
+    "cafe_profile_slots": (c_int, []),
+    "cafe_profile_slot_name": (c_char_p, [c_int]),
+    "cafe_profile_enable": (c_int, [c_int]),
+    "cafe_profile_read": (c_int, [POINTER(c_double), _i64p]),
+    "cafe_launch_count": (c_int64, []),
     "init": (None, [c_int, c_int, c_int, c_double]),
     "batch_query": (_i32p, [_u32p, c_int]),
     "batch_insert": (_i32p, [_u32p, c_int]),

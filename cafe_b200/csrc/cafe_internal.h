@@ -37,3 +37,18 @@ CafeEmbedWorkspace* cafe_internal_ws(void* h);
 int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const int* seg_off, int nseg, int32_t* mask,
                          int32_t* post_row, int mode, cudaStream_t stream);
 void cafe_internal_set_error(const char* msg);
+
+// ---- per-kernel timing and launch counting (prof.cu) ------------------------------------------------
+enum {
+    CAFE_P_FORWARD = 0, CAFE_P_NORM, CAFE_P_FIELDSUM, CAFE_P_IMPORTANCE, CAFE_P_LOOKUP_SORT, CAFE_P_MAIN, CAFE_P_SCAN,
+    CAFE_P_LRU, CAFE_P_RESOLVE, CAFE_P_COMMIT, CAFE_P_REFIT, CAFE_P_MIGRATE, CAFE_P_ROWKEYS, CAFE_P_ROWSORT,
+    CAFE_P_SCATTER, CAFE_P_FIXUP, CAFE_P_SEQ, CAFE_P_QUERY, CAFE_P_MEMSET, CAFE_P_OTHER, CAFE_PROF_SLOTS
+};
+void cafe_prof_begin(int slot, cudaStream_t st);
+void cafe_prof_end(cudaStream_t st);
+struct CafeProfScope {
+    cudaStream_t st;
+    CafeProfScope(int slot, cudaStream_t s) : st(s) { cafe_prof_begin(slot, s); }
+    ~CafeProfScope() { cafe_prof_end(st); }
+};
+#define CAFE_PROF(slot, stream) CafeProfScope cafe_prof_scope_##slot(slot, stream)

@@ -398,6 +398,7 @@ int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfie
     cudaStream_t st = (cudaStream_t)stream;
     const int warps = (total + 31) / 32;
     const int blocks = (warps + 7) / 8;
+    CAFE_PROF(CAFE_P_FORWARD, st);
     if (ids_are_int64) {
         DISPATCH_G(D, (k_embed_forward<G, int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, V.main, V.n1, out_dev,
                        out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
@@ -419,10 +420,11 @@ int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, i
     if (!grad_dev || !imp_out_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
     const int total = (int)total64;
     cudaStream_t st = (cudaStream_t)stream;
+    { CAFE_PROF(CAFE_P_NORM, st);
     DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)(((int64_t)total * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
-                   sample_stride, B, total, ws->norm)));
-    k_field_sum<<<nfields, 1024, 0, st>>>(ws->norm, B, ws->totals);
-    k_importance<<<(total + 255) / 256, 256, 0, st>>>(ws->norm, ws->totals, B, total, imp_out_dev);
+                   sample_stride, B, total, ws->norm))); }
+    { CAFE_PROF(CAFE_P_FIELDSUM, st); k_field_sum<<<nfields, 1024, 0, st>>>(ws->norm, B, ws->totals); }
+    { CAFE_PROF(CAFE_P_IMPORTANCE, st); k_importance<<<(total + 255) / 256, 256, 0, st>>>(ws->norm, ws->totals, B, total, imp_out_dev); }
     return fail_cuda("cafe_grad_importance");
 }
 
@@ -438,6 +440,7 @@ int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t*
     if (!ids_dev || !mask_dev || !post_row_dev) return CAFE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const int blocks = ((total + 31) / 32 + 7) / 8;
+    CAFE_PROF(CAFE_P_MIGRATE, st);
     if (ids_are_int64) k_migrate<int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
     else k_migrate<int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
     return fail_cuda("cafe_migrate");
@@ -457,18 +460,21 @@ int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64
     if (total > ws->cap) return CAFE_ERR_CAPACITY;
     if (!grad_dev || !row_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0], ws->pos[0]);
+    { CAFE_PROF(CAFE_P_ROWKEYS, st); k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0], ws->pos[0]); }
     int bits = 1;
     while ((1ll << bits) < (int64_t)hotn + F.hash_base[nfields]) ++bits;
     size_t b = ws->cub_bytes;
-    cudaError_t e = cub::DeviceRadixSort::SortPairs(ws->cub_tmp, b, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1], total, 0,
-                                                    bits, st);
+    cudaError_t e;
+    { CAFE_PROF(CAFE_P_ROWSORT, st);
+      e = cub::DeviceRadixSort::SortPairs(ws->cub_tmp, b, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1], total, 0, bits, st); }
     if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
     const int64_t chunks = ((int64_t)total + CAFE_CHUNK - 1) / CAFE_CHUNK;
+    { CAFE_PROF(CAFE_P_SCATTER, st);
     DISPATCH_G(D, (k_scatter_chunks<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, grad_dev, field_stride,
-                   sample_stride, ws->key[1], ws->pos[1], total, lr, ws->partial)));
+                   sample_stride, ws->key[1], ws->pos[1], total, lr, ws->partial))); }
+    { CAFE_PROF(CAFE_P_FIXUP, st);
     DISPATCH_G(D, (k_scatter_fixup<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, ws->key[1], ws->pos[1], total,
-                   lr, ws->partial)));
+                   lr, ws->partial))); }
     return fail_cuda("cafe_scatter_sgd");
 }
 

@@ -229,7 +229,7 @@ struct CudaBackend {
 
     void* alloc(size_t n) { void* p = nullptr; check(cudaMalloc(&p, n ? n : 1)); return p; }
     void free(void* p) { cudaFree(p); }
-    void memset(void* p, int v, size_t n) { if (n) check(cudaMemsetAsync(p, v, n, stream)); }
+    void memset(void* p, int v, size_t n) { if (n) { CAFE_PROF(CAFE_P_MEMSET, stream); check(cudaMemsetAsync(p, v, n, stream)); } }
     void fill_iota(uint32_t* p, int n, uint32_t first) {
         if (n > 0) { k_fill_iota<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(p, n, first); check_launch(); }
     }
@@ -273,10 +273,12 @@ struct CudaBackend {
     }
 
     void query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, int32_t* out) {
+        CAFE_PROF(CAFE_P_QUERY, stream);
         k_query<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(mb, n1, gid, n, out);
         check_launch();
     }
     void post_query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, const int32_t* mask, int32_t* out) {
+        CAFE_PROF(CAFE_P_QUERY, stream);
         k_post_query<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(mb, n1, gid, n, mask, out);
         check_launch();
     }
@@ -284,6 +286,7 @@ struct CudaBackend {
 
     // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
+        CAFE_PROF(CAFE_P_LOOKUP_SORT, stream);
         k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, stream>>>(gid, M, nb, key_in, pos_in);
         check_launch();
         size_t b = cub_bytes;
@@ -292,19 +295,23 @@ struct CudaBackend {
         check_launch();
     }
     void main_pass(const CafeJob& J) {
+        CAFE_PROF(CAFE_P_MAIN, stream);
         k_main_pass<<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J);
         check_launch();
     }
     void scan_miss(const CafeJob& J) {
+        CAFE_PROF(CAFE_P_SCAN, stream);
         cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.pflag, MissFlag());
         size_t b = cub_bytes;
         check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp, J.limit, stream));
     }
     void lru_pass(const CafeJob& J) {
+        CAFE_PROF(CAFE_P_LRU, stream);
         k_lru_pass<<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J);
         check_launch();
     }
     void resolve(const CafeJob& J) {
+        CAFE_PROF(CAFE_P_RESOLVE, stream);
         const int g = cafe_blocks(J.limit);
         k_resolve_ops<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
@@ -319,11 +326,13 @@ struct CudaBackend {
     }
     void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
                       const uint32_t* pushbuf, int n_push) {
+        CAFE_PROF(CAFE_P_COMMIT, stream);
         k_commit_queue<<<cafe_blocks(n_push), CAFE_TPB, 0, stream>>>(ring, mask, q_head, q_size, n_pop_ok, pushbuf, n_push);
         check_launch();
     }
     void seq_insert(CafeSeqState* dev, CafeSeqState* S, const uint32_t* gid, const float* imp, int n, int32_t* mask) {
         check(cudaMemcpyAsync(dev, S, sizeof(CafeSeqState), cudaMemcpyHostToDevice, stream));
+        CAFE_PROF(CAFE_P_SEQ, stream);
         k_seq_insert<<<1, 32, 0, stream>>>(dev, gid, imp, n, mask);
         check_launch();
         d2h(S, dev, sizeof(CafeSeqState));
@@ -331,6 +340,7 @@ struct CudaBackend {
     void reset_collect(CafeMainBucket* mb, CafeLruBucket* lb, int n1, int n2, uint32_t gflip, float thr, int32_t* cnt,
                        uint32_t* key, int32_t* val, int32_t* l_out) {
         const int nb = n1 + n2;
+        CAFE_PROF(CAFE_P_REFIT, stream);
         k_reset_count<<<cafe_blocks((int64_t)nb + 1), CAFE_TPB, 0, stream>>>(mb, lb, n1, n2, gflip, thr, cnt);
         check_launch();
         size_t b = cub_bytes;
@@ -340,12 +350,14 @@ struct CudaBackend {
         d2h(l_out, cnt + nb, 4);
     }
     void sort_pairs(const uint32_t* kin, const int32_t* vin, uint32_t* kout, int32_t* vout, int n, int bits) {
+        CAFE_PROF(CAFE_P_REFIT, stream);
         size_t b = cub_bytes;
         check(cub::DeviceRadixSort::SortPairs(cub_tmp, b, kin, kout, vin, vout, n, 0, bits, stream));
     }
     void reset_apply(const uint32_t* key, const int32_t* val, int l, int lim, CafeMainBucket* mb, CafeLruBucket* lb,
                      int n1, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t* dev_out,
                      int32_t* out) {
+        CAFE_PROF(CAFE_P_REFIT, stream);
         k_reset_apply<<<1, CAFE_RESET_TPB, 0, stream>>>(key, val, l, lim, mb, lb, n1, ring, mask, q_head, q_size, dev_out);
         check_launch();
         d2h(out, dev_out, 12);

@@ -140,6 +140,17 @@ void* cafe_global_handle(void);
 /* Largest len the six calls accept (default 1<<21); takes effect at the next init. */
 int cafe_global_set_capacity(int max_len);
 
+/* ---- measurement ---------------------------------------------------------------------------------
+ * No counterpart in the reference.  Kernel launches of the library are always counted per slot;
+ * with cafe_profile_enable(1) each launch is also bracketed by CUDA events on its stream.
+ * cafe_profile_read fills ms[slots] (event time summed per slot) and launches[slots] since the last
+ * read, after synchronising the device. */
+int cafe_profile_slots(void);
+const char* cafe_profile_slot_name(int slot);
+int cafe_profile_enable(int on);
+int cafe_profile_read(double* ms_out, int64_t* launches_out);
+int64_t cafe_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

