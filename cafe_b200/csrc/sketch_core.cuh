@@ -277,8 +277,9 @@ CAFE_HD int cafe_next_event(const CafeJob& J, int head, int after) {
     return best;
 }
 
-CAFE_HD void cafe_note_event(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
-    CafeEvent o = J.ev_old[p];
+// Record the event produced at position p and flag a change against the belief `o` that was consumed.
+CAFE_HD void cafe_note_event(const CafeJob& J, int p, const CafeEvent& o, uint32_t kind, uint32_t x, float cnt,
+                             int32_t dic) {
     bool same;
     if (J.first_round) same = (kind == CAFE_EV_NONE);
     else if (kind == CAFE_EV_NONE) same = (o.kind == CAFE_EV_NONE);
@@ -289,105 +290,153 @@ CAFE_HD void cafe_note_event(const CafeJob& J, int p, uint32_t kind, uint32_t x,
     e.x = x; e.cnt = cnt; e.dic = dic; e.kind = kind;
     J.ev_new[p] = e;
 }
+// old belief of a position; never read in the first round (the buffer is uninitialised then)
+CAFE_HD uint32_t cafe_old_kind(const CafeJob& J, int p) { return J.first_round ? (uint32_t)CAFE_EV_NONE : J.ev_old[p].kind; }
+CAFE_HD CafeEvent cafe_old_event(const CafeJob& J, int p) {
+    if (J.first_round) { CafeEvent e; e.x = 0; e.cnt = 0.f; e.dic = 0; e.kind = CAFE_EV_NONE; return e; }
+    return J.ev_old[p];
+}
 
 // ---- round step 1: one main bucket ---------------------------------------------------------------
-CAFE_HD void cafe_main_pass_bucket(const CafeJob& J, int k) {
-    CafeMainBucket b = J.main_in[k];
-    int i = J.start1[k];
-    const int iend = J.start1[k + 1];
-    const int evhead = J.first_round ? -1 : J.head_old[k];
-    int p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
+// The replay of a bucket is a small state machine fed one own lookup at a time (feed), so that the
+// same code serves a thread that walks its bucket's lookups alone and a warp that loads a long
+// bucket's lookups together and hands them to the owning lane.
+#define CAFE_CAND 8
+struct CafeMainReplay {
+    CafeMainBucket b;
+    int k, evhead, p_ev;
+    int seg, seg_end;
+    int real_delta, num_delta, n_hit;
+    int i_first, i_cur;          // range of this bucket's sorted lookups that lie in the current segment
+    int ncand;                   // lookups of the current segment whose post-call row may be asked for
+    int cand_p[CAFE_CAND];
+    uint32_t cand_x[CAFE_CAND];
+    bool dirty, touched;
 
-    int seg = 0, seg_end = J.seg_off[1], seg_first_i = i;
-    int real_delta = 0, num_delta = 0, n_hit = 0;
-    bool dirty = false, touched = false;
-
-    for (;;) {
-        int p_own = (i < iend) ? J.ord1[i] : INT32_MAX;
-        if (p_own >= J.limit) p_own = INT32_MAX;
-        if (p_own == INT32_MAX && p_ev == INT32_MAX) break;
-        const bool own = p_own <= p_ev;   // a lookup's probe comes before an event of the same position
-        const int p = own ? p_own : p_ev;
+    CAFE_HD void init(const CafeJob& J, int k_, int i_start) {
+        k = k_;
+        b = J.main_in[k];
+        evhead = J.first_round ? -1 : J.head_old[k];
+        p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
+        seg = 0; seg_end = J.seg_off[1];
+        real_delta = num_delta = n_hit = 0;
+        i_first = i_cur = i_start;
+        ncand = 0;
+        dirty = touched = false;
+    }
+    CAFE_HD void note_cand(int p, uint32_t x) {
+        if (ncand < CAFE_CAND) { cand_p[ncand] = p; cand_x[ncand] = x; }
+        ++ncand;
+    }
+    // the segment (one field's call) ended: record what a query at this point would return
+    CAFE_HD void close_segment(const CafeJob& J) {
+        if (dirty && J.post_row) {
+            if (ncand <= CAFE_CAND) {
+                for (int j = 0; j < ncand; ++j) J.post_row[cand_p[j]] = cafe_probe_hot(b, cand_x[j]);
+            } else {
+                for (int j = i_first; j < i_cur; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
+            }
+        }
+        if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+        real_delta = 0; dirty = false; ncand = 0; i_first = i_cur;
+    }
+    CAFE_HD void enter(const CafeJob& J, int p) {
         if (p >= seg_end) {
-            // the segment (one field's call) ended: record what a query at this point would return
-            if (dirty && J.post_row)
-                for (int j = seg_first_i; j < i; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
-            if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-            real_delta = 0; dirty = false; seg_first_i = i;
+            close_segment(J);
             while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
         }
         if (!touched) { cafe_touch(b, J.gflip); touched = true; }
-        if (own) {
-            const uint32_t x = J.gid[p];
-            const float c = cafe_count_of(J, p);
-            int s = -1;
-#pragma unroll
-            for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (b.val[q] == x) s = q;
-            if (s >= 0) {   // insert(): hit in the main table (sketch.cpp:215-228)
-                ++n_hit;
-                float cn = b.cnt[s] + c;
-                b.cnt[s] = cn;
-                if (cn >= J.thr && cn - c < J.thr) ++real_delta;
-                int got = 0;
-                uint8_t pf = 0;
-                if (cn >= J.thr && b.dic[s] == 0) {
-                    pf = 1 << 1;   // candidate pop at op slot 2p
-                    int32_t id;
-                    if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[s] = id; got = 1; ++num_delta; dirty = true; }
-                }
-                J.pflag[p] = pf;
-                J.mask[p] = got;
-                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
-            } else {
-                J.pflag[p] = 1;   // goes to the LRU stage; that pass fills in the rest
-                if (!J.first_round) {
-                    CafeEvent e = J.ev_old[p];
-                    if (e.kind == CAFE_EV_OWN) {   // believed: this lookup promotes its own id into this bucket
-                        int32_t pushed;
-                        int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
-                        J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
-                        dirty = true;
-                    }
-                }
-            }
-            ++i;
-        } else {   // believed victim promotion landing here (sketch.cpp:193-195 -> Insert)
-            CafeEvent e = J.ev_old[p];
-            int32_t pushed;
-            int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
-            J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
-            dirty = true;
-            p_ev = cafe_next_event(J, evhead, p);
+    }
+    CAFE_HD void apply_event(const CafeJob& J, int p) {
+        CafeEvent e = J.ev_old[p];
+        int32_t pushed;
+        int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
+        J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
+        dirty = true;
+    }
+    // believed victim promotions (sketch.cpp:193-195 -> Insert) landing here at positions < before
+    CAFE_HD void drain_events(const CafeJob& J, int before) {
+        while (p_ev < before) {
+            enter(J, p_ev);
+            apply_event(J, p_ev);
+            p_ev = cafe_next_event(J, evhead, p_ev);
         }
     }
-    if (dirty && J.post_row)
-        for (int j = seg_first_i; j < i; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
-    if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-    if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
-    if (n_hit) CAFE_ATOMIC_ADD(&J.res->n_main_hit, n_hit);
-    J.main_out[k] = b;
+    // own lookup at position p (ascending); a lookup's probe comes before an event of the same position
+    // old_kind = kind of the event the previous round produced at p (cafe_old_kind)
+    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, uint32_t old_kind) {
+        if (p_ev < p) drain_events(J, p);
+        enter(J, p);
+        int s = -1;
+#pragma unroll
+        for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (b.val[q] == x) s = q;
+        if (s >= 0) {   // insert(): hit in the main table (sketch.cpp:215-228)
+            ++n_hit;
+            float cn = b.cnt[s] + c;
+            b.cnt[s] = cn;
+            if (cn >= J.thr && cn - c < J.thr) ++real_delta;
+            int got = 0;
+            uint8_t pf = 0;
+            if (cn >= J.thr && b.dic[s] == 0) {
+                pf = 1 << 1;   // candidate pop at op slot 2p
+                int32_t id;
+                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[s] = id; got = 1; ++num_delta; dirty = true; note_cand(p, x); }
+            }
+            J.pflag[p] = pf;
+            J.mask[p] = got;
+            if (old_kind != CAFE_EV_NONE) J.res->changed = 1;
+            J.ev_new[p].kind = CAFE_EV_NONE;
+        } else {
+            J.pflag[p] = 1;   // goes to the LRU stage; that pass fills in the rest
+            note_cand(p, x);
+            if (old_kind == CAFE_EV_OWN) apply_event(J, p);   // believed own promotion
+        }
+        ++i_cur;
+    }
+    CAFE_HD void finish(const CafeJob& J) {
+        drain_events(J, INT32_MAX);
+        close_segment(J);
+        if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
+        J.main_out[k] = b;
+    }
+};
+
+CAFE_HD void cafe_main_pass_bucket(const CafeJob& J, int k) {
+    CafeMainReplay R;
+    const int iend = J.start1[k + 1];
+    int i = J.start1[k];
+    R.init(J, k, i);
+    for (; i < iend; ++i) {
+        const int p = J.ord1[i];
+        if (p >= J.limit) break;
+        R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p));
+    }
+    R.finish(J);
 }
 
 // ---- round step 2: one LRU bucket (insertLRU, sketch.cpp:161-210) ---------------------------------
-CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
-    CafeLruBucket b = J.lru_in[k];
-    const int jend = J.start2[k + 1];
-    int seg = 0, seg_end = J.seg_off[1];
-    int real_delta = 0, num_delta = 0, n_ev = 0;
-    bool touched = false;
-    for (int j = J.start2[k]; j < jend; ++j) {
-        const int p = J.ord2[j];
-        if (p >= J.limit) break;
-        if (!(J.pflag[p] & 1)) continue;
+struct CafeLruReplay {
+    CafeLruBucket b;
+    int k, seg, seg_end;
+    int real_delta, num_delta, n_ev;
+    bool touched;
+
+    CAFE_HD void init(const CafeJob& J, int k_) {
+        k = k_;
+        b = J.lru_in[k];
+        seg = 0; seg_end = J.seg_off[1];
+        real_delta = num_delta = n_ev = 0;
+        touched = false;
+    }
+    // a lookup at position p (ascending) that missed the main table; tp = its LRU clock value
+    // old = the event the previous round produced at p (cafe_old_event)
+    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, int32_t tp, const CafeEvent& old) {
         if (p >= seg_end) {
             if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
             real_delta = 0;
             while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
         }
         if (!touched) { cafe_touch(b, J.gflip); touched = true; }
-        const uint32_t x = J.gid[p];
-        const float c = cafe_count_of(J, p);
-        const int32_t tp = J.t0 + J.tstamp[p];
         int hit = -1, vic = -1, t_min = 1000000000;
 #pragma unroll
         for (int q = 0; q < CAFE_SLOTS; ++q) {
@@ -411,21 +460,21 @@ CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
             J.pflag[p] = pf;
             if (cn >= J.thr) {
                 ++n_ev;
-                cafe_note_event(J, p, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
+                cafe_note_event(J, p, old, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
                 // the main pass of this round replayed the believed copy of this event
                 if (!J.first_round && J.ins_res[p] != 0) got = 0;
                 b.val[hit] = 0; b.t[hit] = 0; b.cnt[hit] = 0.0f; b.dic[hit] = 0;
             } else {
-                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+                cafe_note_event(J, p, old, CAFE_EV_NONE, 0, 0.0f, 0);
             }
         } else {
             if (vic < 0) { CAFE_ATOMIC_OR(&J.res->error, 2); vic = 0; }
             if (b.dic[vic] != 0 || b.cnt[vic] >= 5.0f) {
                 ++n_ev;
-                cafe_note_event(J, p, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
+                cafe_note_event(J, p, old, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
                 J.nxt_new[p] = CAFE_ATOMIC_EXCH(&J.head_new[cafe_hash(b.val[vic], J.n1)], p);
             } else {
-                cafe_note_event(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+                cafe_note_event(J, p, old, CAFE_EV_NONE, 0, 0.0f, 0);
             }
             b.val[vic] = x;
             b.t[vic] = tp;
@@ -442,11 +491,27 @@ CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
         }
         J.mask[p] = got;
     }
-    if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-    if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
-    if (n_ev) CAFE_ATOMIC_ADD(&J.res->n_events, n_ev);
-    J.lru_out[k] = b;
+    CAFE_HD void finish(const CafeJob& J) {
+        if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
+        if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
+        if (n_ev) CAFE_ATOMIC_ADD(&J.res->n_events, n_ev);
+        J.lru_out[k] = b;
+    }
+};
+
+CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
+    CafeLruReplay R;
+    R.init(J, k);
+    const int jend = J.start2[k + 1];
+    for (int j = J.start2[k]; j < jend; ++j) {
+        const int p = J.ord2[j];
+        if (p >= J.limit) break;
+        if (!(J.pflag[p] & 1)) continue;
+        R.feed(J, p, J.gid[p], cafe_count_of(J, p), J.t0 + J.tstamp[p], cafe_old_event(J, p));
+    }
+    R.finish(J);
 }
+
 
 // ---- round step 3: the FIFO timeline ---------------------------------------------------------------
 // Each position owns two op slots (2p, 2p+1).  An op is a candidate pop or a push; the FIFO size

@@ -71,13 +71,162 @@ __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb
     for (int k = lo; k <= hi; ++k) start[k] = i;
 }
 
-__global__ void k_main_pass(const __grid_constant__ CafeJob J) {
-    int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k < J.n1) cafe_main_pass_bucket(J, k);
+// Buckets with at most CAFE_LONG lookups are replayed by their own thread.  Longer ones (the ids at
+// the head of the Zipf law put thousands of lookups into one bucket) are fed by the whole warp:
+// 32 lanes load 32 lookups at once, the owning lane applies them in order.  The arithmetic stays
+// strictly sequential per bucket; only the loads are shared out.
+#define CAFE_LONG 16
+#define CAFE_FULL 0xffffffffu
+__global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J) {
+    const int lane = threadIdx.x & 31;
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = k < J.n1;
+    CafeMainReplay R;
+    int i = 0, iend = 0;
+    if (live) { i = J.start1[k]; iend = J.start1[k + 1]; R.init(J, k, i); }
+    const bool is_long = live && (iend - i > CAFE_LONG);
+    if (live && !is_long) {
+        for (; i < iend; ++i) {
+            const int p = J.ord1[i];
+            if (p >= J.limit) break;
+            R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p));
+        }
+    }
+    unsigned m = __ballot_sync(CAFE_FULL, is_long);
+    while (m) {
+        const int o = __ffs(m) - 1;
+        m &= m - 1;
+        const int s = __shfl_sync(CAFE_FULL, i, o), e = __shfl_sync(CAFE_FULL, iend, o);
+        bool stop = false;
+        for (int base = s; base < e && !stop; base += 32) {
+            const int idx = base + lane;
+            int p = INT32_MAX;
+            uint32_t x = 0, ok = CAFE_EV_NONE;
+            float c = 1.0f;
+            if (idx < e) {
+                p = J.ord1[idx];
+                if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); }
+            }
+            const int n = min(32, e - base);
+            int j = 0;
+            while (j < n) {
+                const int pj = __shfl_sync(CAFE_FULL, p, j);
+                const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
+                if (pj >= J.limit) { stop = true; break; }
+                // Quiet run: consecutive lookups of one id that sits in a slot which already owns a hot
+                // row, inside the current segment and before the next believed event.  Such a lookup can
+                // only add to the slot's count (and be counted if it crosses the threshold); it cannot
+                // pop a row, so the run needs no replay logic: the counts are added in order, every
+                // lane writes the (empty) outputs of its own lookup.
+                int slot = -1, bound = 0;
+                float cnt0 = 0.f;
+                if (lane == o && R.touched) {
+#pragma unroll
+                    for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (R.b.val[q] == xj) slot = q;
+                    if (slot >= 0) {
+                        int32_t d = 0;
+#pragma unroll
+                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { d = R.b.dic[q]; cnt0 = R.b.cnt[q]; }
+                        if (d == 0) slot = -1;
+                    }
+                    bound = min(min(R.seg_end, R.p_ev), J.limit);
+                }
+                slot = __shfl_sync(CAFE_FULL, slot, o);
+                int run = 0;
+                if (slot >= 0) {
+                    bound = __shfl_sync(CAFE_FULL, bound, o);
+                    const unsigned q = __ballot_sync(CAFE_FULL, lane >= j && lane < n && x == xj && p < bound) >> j;
+                    run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
+                    if (run < 0) run = 32 - j;    // all remaining lanes qualify
+                }
+                if (run >= 2) {
+                    float acc = __shfl_sync(CAFE_FULL, cnt0, o);
+                    int crossed = 0;
+                    for (int t = 0; t < run; ++t) {
+                        const float ct = __shfl_sync(CAFE_FULL, c, j + t);
+                        acc = acc + ct;
+                        crossed += (acc >= J.thr && acc - ct < J.thr);   // sketch.cpp:218
+                    }
+                    if (lane == o) {
+#pragma unroll
+                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc;
+                        R.real_delta += crossed;
+                        R.i_cur += run;
+                    }
+                    if (lane >= j && lane < j + run) {
+                        J.pflag[p] = 0;
+                        J.mask[p] = 0;
+                        if (ok != CAFE_EV_NONE) J.res->changed = 1;
+                        J.ev_new[p].kind = CAFE_EV_NONE;
+                    }
+                    j += run;
+                } else {
+                    const float cj = __shfl_sync(CAFE_FULL, c, j);
+                    const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
+                    if (lane == o) R.feed(J, pj, xj, cj, kj);
+                    ++j;
+                }
+            }
+        }
+    }
+    if (live) R.finish(J);
 }
-__global__ void k_lru_pass(const __grid_constant__ CafeJob J) {
-    int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k < J.n2) cafe_lru_pass_bucket(J, k);
+__global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J) {
+    const int lane = threadIdx.x & 31;
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool live = k < J.n2;
+    CafeLruReplay R;
+    int jb = 0, jend = 0;
+    if (live) { jb = J.start2[k]; jend = J.start2[k + 1]; R.init(J, k); }
+    const bool is_long = live && (jend - jb > CAFE_LONG);
+    if (live && !is_long) {
+        for (int j = jb; j < jend; ++j) {
+            const int p = J.ord2[j];
+            if (p >= J.limit) break;
+            if (!(J.pflag[p] & 1)) continue;
+            R.feed(J, p, J.gid[p], cafe_count_of(J, p), J.t0 + J.tstamp[p], cafe_old_event(J, p));
+        }
+    }
+    unsigned m = __ballot_sync(CAFE_FULL, is_long);
+    while (m) {
+        const int o = __ffs(m) - 1;
+        m &= m - 1;
+        const int s = __shfl_sync(CAFE_FULL, jb, o), e = __shfl_sync(CAFE_FULL, jend, o);
+        bool stop = false;
+        for (int base = s; base < e && !stop; base += 32) {
+            const int idx = base + lane;
+            int p = INT32_MAX, tp = 0;
+            uint32_t x = 0;
+            float c = 1.0f;
+            bool miss = false;
+            CafeEvent oe;
+            oe.x = 0; oe.cnt = 0.f; oe.dic = 0; oe.kind = CAFE_EV_NONE;
+            if (idx < e) {
+                p = J.ord2[idx];
+                if (p < J.limit && (J.pflag[p] & 1)) {
+                    miss = true; x = J.gid[p]; c = cafe_count_of(J, p); tp = J.t0 + J.tstamp[p]; oe = cafe_old_event(J, p);
+                }
+            }
+            // positions ascend inside a bucket: once one lane sees the limit, later chunks are beyond it too
+            stop = __any_sync(CAFE_FULL, idx < e && p >= J.limit);
+            unsigned mm = __ballot_sync(CAFE_FULL, miss);
+            while (mm) {
+                const int j = __ffs(mm) - 1;
+                mm &= mm - 1;
+                const int pj = __shfl_sync(CAFE_FULL, p, j);
+                const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
+                const float cj = __shfl_sync(CAFE_FULL, c, j);
+                const int tj = __shfl_sync(CAFE_FULL, tp, j);
+                CafeEvent oj;
+                oj.x = __shfl_sync(CAFE_FULL, oe.x, j);
+                oj.cnt = __shfl_sync(CAFE_FULL, oe.cnt, j);
+                oj.dic = __shfl_sync(CAFE_FULL, oe.dic, j);
+                oj.kind = __shfl_sync(CAFE_FULL, oe.kind, j);
+                if (lane == o) R.feed(J, pj, xj, cj, tj, oj);
+            }
+        }
+    }
+    if (live) R.finish(J);
 }
 __global__ void k_resolve_ops(const __grid_constant__ CafeJob J) {
     int p = blockIdx.x * blockDim.x + threadIdx.x;

@@ -328,7 +328,8 @@ private:
         ++stats.jobs;
 
         CafeRoundResult R;
-        int rounds = 0, confirm_limit = -1;
+        int rounds = 0;
+        bool truncated = false;
         int pb = 0;   // index of the belief set consumed this round
         bool first = true;
         for (;;) {
@@ -361,26 +362,28 @@ private:
             first = false;
             pb ^= 1;
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
-            if (R.changed) continue;
-            // converged for positions < J.limit: is a threshold re-fit due at an inner boundary?
-            if (confirm_limit < 0 && adjust) {
+            // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
+            // per-segment deltas of a round that has not converged yet are estimates, but shrinking
+            // the job to an estimated cut is always safe: whatever prefix is kept is iterated to
+            // convergence and checked again before it is committed, and the next job starts with the
+            // exact boundary test.  Cutting early saves replaying segments that would be discarded.
+            if (adjust) {
                 int rn = real_n, cut = -1;
                 for (int b = 1; b < nseg; ++b) {
                     rn += R.seg_real_delta[b - 1];
                     if ((double)rn > lim * 1.2) { cut = b; break; }
                 }
                 if (cut > 0) {
-                    // beliefs for the prefix are already right: one more round over the prefix alone
-                    // reproduces them and leaves the prefix's state in the other image
-                    confirm_limit = J.seg_off[cut];
-                    J.limit = confirm_limit;
+                    J.limit = J.seg_off[cut];
                     J.nseg = cut;
                     nseg = cut;
-                    ++stats.truncated_jobs;
-                    if (confirm_limit == 0) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
+                    if (!truncated) ++stats.truncated_jobs;
+                    truncated = true;
+                    if (J.limit == 0) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
                     continue;
                 }
             }
+            if (R.changed) continue;
             break;
         }
         // commit
@@ -391,7 +394,7 @@ private:
         t += R.n_miss;
         num += R.num_delta;
         for (int b = 0; b < nseg; ++b) real_n += R.seg_real_delta[b];
-        stats.main_hits += R.n_main_hit; stats.lru_visits += R.n_miss; stats.events += R.n_events;
+        stats.main_hits += (int64_t)J.limit - R.n_miss; stats.lru_visits += R.n_miss; stats.events += R.n_events;
         if (rounds > stats.max_rounds) stats.max_rounds = rounds;
         *done = nseg;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;

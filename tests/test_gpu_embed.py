@@ -200,8 +200,8 @@ def test_reference_compatible_sparse_gradients():
         # (migration may also have written hot rows; compare only rows the gradient touched and
         # migration did not)
         exp_c.index_add_(0, rows[~hot].long(), -0.5 * g[~hot])
-        close(m.weight_hash.detach().cpu().numpy(), exp_c.cpu().numpy(), "hash rows under torch SGD")
+        np.testing.assert_allclose(m.weight_hash.detach().cpu().numpy(), exp_c.cpu().numpy(), rtol=RTOL, atol=1e-6)
         if hot.any():
             exp_h.index_add_(0, (-rows[hot]).long(), -0.5 * g[hot])
             touched = torch.unique((-rows[hot]).long())
-            close(wh.detach()[touched].cpu().numpy(), exp_h[touched].cpu().numpy(), "hot rows under torch SGD")
+            np.testing.assert_allclose(wh.detach()[touched].cpu().numpy(), exp_h[touched].cpu().numpy(), rtol=RTOL, atol=1e-6)
