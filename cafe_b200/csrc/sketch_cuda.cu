@@ -142,10 +142,17 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 if (run >= 2) {
                     float acc = __shfl_sync(CAFE_FULL, cnt0, o);
                     int crossed = 0;
-                    for (int t = 0; t < run; ++t) {
-                        const float ct = __shfl_sync(CAFE_FULL, c, j + t);
-                        acc = acc + ct;
-                        crossed += (acc >= J.thr && acc - ct < J.thr);   // sketch.cpp:218
+                    for (int t0 = 0; t0 < run; t0 += 8) {
+                        float cs[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) cs[u] = __shfl_sync(CAFE_FULL, c, min(j + t0 + u, 31));
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            if (t0 + u < run) {
+                                acc = acc + cs[u];
+                                crossed += (acc >= J.thr && acc - cs[u] < J.thr);   // sketch.cpp:218
+                            }
+                        }
                     }
                     if (lane == o) {
 #pragma unroll
@@ -301,54 +308,44 @@ __global__ void k_reset_emit(const CafeMainBucket* __restrict__ mb, const CafeLr
             if (b.cnt[i] >= thr || b.dic[i] != 0) { key[o] = cafe_float_bits(b.cnt[i]); val[o] = n1 * CAFE_SLOTS + (k - n1) * CAFE_SLOTS + i; ++o; }
     }
 }
-// step 3 (after the stable sort by count): sketch.cpp:98-115.  One block; each thread owns a
-// contiguous chunk of the sorted candidates so that ranks follow the sorted order.
-#define CAFE_RESET_TPB 1024
-__global__ void __launch_bounds__(CAFE_RESET_TPB)
-k_reset_apply(const uint32_t* __restrict__ key, const int32_t* __restrict__ val, int l, int lim, CafeMainBucket* mb,
-              CafeLruBucket* lb, int n1, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size,
-              int32_t* __restrict__ out) {
-    typedef cub::BlockScan<int, CAFE_RESET_TPB> Scan;
-    __shared__ typename Scan::TempStorage tmp;
-    __shared__ int s_total;
-    const int z = l - lim;
-    const int tid = threadIdx.x;
-    // losers: candidates [0, z] give their rows back, in sorted order
-    {
-        const int n = z + 1;
-        const int per = (n + CAFE_RESET_TPB - 1) / CAFE_RESET_TPB;
-        const int lo = min(n, tid * per), hi = min(n, lo + per);
-        int c = 0;
-        for (int i = lo; i < hi; ++i) c += (*cafe_slot_dic(mb, lb, n1, val[i]) != 0);
-        int base, total;
-        Scan(tmp).ExclusiveSum(c, base, total);
-        for (int i = lo; i < hi; ++i) {
-            int32_t* d = cafe_slot_dic(mb, lb, n1, val[i]);
-            if (*d != 0) { ring[(q_head + (uint32_t)(q_size + base)) & mask] = (uint32_t)*d; *d = 0; ++base; }
-        }
-        if (tid == 0) s_total = total;
+// step 3 (after the stable sort by count): sketch.cpp:98-115.  Candidates [0, z] (z = l - lim) give
+// their rows back to the FIFO in sorted order; candidates (z, l) without a row then take rows from
+// the FIFO front in sorted order while it lasts.  Ranks come from one prefix sum over
+// (push flag << 32 | needs-row flag).
+__global__ void k_reset_flags(const int32_t* __restrict__ val, int l, int z, CafeMainBucket* mb, CafeLruBucket* lb, int n1,
+                              int64_t* __restrict__ flags) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= l) return;
+    const int32_t d = *cafe_slot_dic(mb, lb, n1, val[i]);
+    flags[i] = (i <= z) ? (d != 0 ? (1ll << 32) : 0ll) : (d == 0 ? 1ll : 0ll);
+}
+__global__ void k_reset_push(const int32_t* __restrict__ val, int z, CafeMainBucket* mb, CafeLruBucket* lb, int n1,
+                             const int64_t* __restrict__ pre, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i > z) return;
+    int32_t* d = cafe_slot_dic(mb, lb, n1, val[i]);
+    if (*d != 0) {
+        ring[(q_head + (uint32_t)(q_size + (int32_t)(pre[i] >> 32))) & mask] = (uint32_t)*d;
+        *d = 0;
     }
-    __syncthreads();
-    const int npush = s_total;
-    const int avail = q_size + npush;
-    __syncthreads();
-    // winners: candidates (z, l) without a row take the FIFO front, in sorted order, while it lasts
-    {
-        const int n = l - (z + 1);
-        const int per = (n + CAFE_RESET_TPB - 1) / CAFE_RESET_TPB;
-        const int lo = min(n, tid * per), hi = min(n, lo + per);
-        int c = 0;
-        for (int i = lo; i < hi; ++i) c += (*cafe_slot_dic(mb, lb, n1, val[z + 1 + i]) == 0);
-        int base, total;
-        Scan(tmp).ExclusiveSum(c, base, total);
-        for (int i = lo; i < hi; ++i) {
-            int32_t* d = cafe_slot_dic(mb, lb, n1, val[z + 1 + i]);
-            if (*d == 0) {
-                if (base < avail) *d = (int32_t)ring[(q_head + (uint32_t)base) & mask];
-                ++base;
-            }
-        }
-        if (tid == 0) { out[0] = (int32_t)key[z]; out[1] = npush; out[2] = min(total, avail); }
+}
+__global__ void k_reset_pop(const uint32_t* __restrict__ key, const int32_t* __restrict__ val, int l, int z,
+                            CafeMainBucket* mb, CafeLruBucket* lb, int n1, const int64_t* __restrict__ pre,
+                            const uint32_t* __restrict__ ring, uint32_t mask, uint32_t q_head, int32_t q_size,
+                            int32_t* __restrict__ out) {
+    int i = z + 1 + blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= l) return;
+    int32_t* d = cafe_slot_dic(mb, lb, n1, val[i]);
+    const int64_t pr = pre[i];
+    const int32_t rank = (int32_t)(pr & 0xffffffffll);
+    const int32_t avail = q_size + (int32_t)(pr >> 32);   // every push lies before z+1
+    const bool needs = (*d == 0);
+    if (needs && rank < avail) *d = (int32_t)ring[(q_head + (uint32_t)rank) & mask];
+    if (i == l - 1) {
+        const int32_t needy = rank + (needs ? 1 : 0);
+        out[0] = (int32_t)key[z];
+        out[1] = (int32_t)(pr >> 32);
+        out[2] = needy < avail ? needy : avail;
     }
 }
 
@@ -362,6 +359,7 @@ struct CudaBackend {
     size_t cub_bytes = 0;
     uint32_t *key_in = nullptr, *key_out = nullptr;
     int32_t* pos_in = nullptr;
+    int64_t* scan64 = nullptr;   // [4*(n1+n2)] prefix sums of the threshold re-fit
     int cap = 0;
     void* pinned = nullptr;   // staging for small device-to-host reads
 
@@ -370,6 +368,7 @@ struct CudaBackend {
         if (key_in) cudaFree(key_in);
         if (key_out) cudaFree(key_out);
         if (pos_in) cudaFree(pos_in);
+        if (scan64) cudaFree(scan64);
         if (pinned) cudaFreeHost(pinned);
     }
     void check(cudaError_t e) { if (e != cudaSuccess && err == cudaSuccess) err = e; }
@@ -406,6 +405,7 @@ struct CudaBackend {
         // largest temporary any CUB call below can ask for
         size_t need = 0, b = 0;
         const int ncand = (n1 + n2) * CAFE_SLOTS;
+        check(cudaMalloc(&scan64, 8 * (size_t)ncand));
         const int nsort = cap > ncand ? cap : ncand;
         cub::DeviceRadixSort::SortPairs(nullptr, b, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
                                         (int32_t*)nullptr, nsort, 0, 32, stream);
@@ -507,7 +507,15 @@ struct CudaBackend {
                      int n1, uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t* dev_out,
                      int32_t* out) {
         CAFE_PROF(CAFE_P_REFIT, stream);
-        k_reset_apply<<<1, CAFE_RESET_TPB, 0, stream>>>(key, val, l, lim, mb, lb, n1, ring, mask, q_head, q_size, dev_out);
+        const int z = l - lim;
+        k_reset_flags<<<cafe_blocks(l), CAFE_TPB, 0, stream>>>(val, l, z, mb, lb, n1, scan64);
+        check_launch();
+        size_t b = cub_bytes;
+        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, scan64, scan64, l, stream));
+        k_reset_push<<<cafe_blocks((int64_t)z + 1), CAFE_TPB, 0, stream>>>(val, z, mb, lb, n1, scan64, ring, mask, q_head, q_size);
+        check_launch();
+        k_reset_pop<<<cafe_blocks((int64_t)l - z - 1), CAFE_TPB, 0, stream>>>(key, val, l, z, mb, lb, n1, scan64, ring, mask,
+                                                                            q_head, q_size, dev_out);
         check_launch();
         d2h(out, dev_out, 12);
     }

@@ -177,6 +177,7 @@ def test_reference_compatible_sparse_gradients():
     """fused_update=False: the module returns the sparse gradients torch.optim.SGD expects."""
     import torch
     import cafe_b200
+    torch.manual_seed(11)
     hotn, D, B = 200, 16, 64
     sk = cafe_b200.HotSketch(hotn, 1, 1, 1.0000005, max_lookups=B)
     wh = torch.nn.Parameter(torch.randn(hotn, D).cuda() * 0.01)
