@@ -240,7 +240,9 @@ def run_ours(args, rank, world, local_rank):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a short timeout: a rank that stops (an exception, a mismatch) ends the job instead of hanging it
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
     cards = S.MICRO_CARDS
     F, D, B = len(cards), DIM, args.batch
     if world > 1:
@@ -306,14 +308,15 @@ def run_ours(args, rank, world, local_rank):
     ms_e2e = timed(e2e_fn, args.steps, 0)
     e2e_value = args.steps * total_ids / (ms_e2e / 1e3)
 
+    # per-kernel times, live, with CUDA events on the launching stream (every rank runs the pass: the steps
+    # contain collectives; rank 0 reports its own kernels)
+    prof.read()
+    prof.enable(True)
+    ms_prof = timed(step_fn, args.steps, args.warmup + args.steps)
+    slots = prof.read()
+    prof.enable(False)
     line = None
     if rank == 0:
-        # per-kernel times, live, with CUDA events on the launching stream
-        prof.read()
-        prof.enable(True)
-        ms_prof = timed(step_fn, args.steps, args.warmup + args.steps)
-        slots = prof.read()
-        prof.enable(False)
         peak, peak_kind = read_peaks()
         phases = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
                   for k, v in slots.items() if v[1] > 0}
