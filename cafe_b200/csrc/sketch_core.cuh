@@ -200,6 +200,11 @@ CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
 // =================================================================================================
 struct CafeFn { int32_t a, b; };   // FIFO size transfer: s -> max(s + a, b)
 
+// per-lookup result flags (one byte written by the main pass, one by the LRU pass)
+enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE_F_GOT = 16 };
+// per-bucket replay state kept between rounds
+enum { CAFE_S_COND = 1, CAFE_S_CAND = 2 };
+
 struct CafeJob {
     // the lookups
     const uint32_t* gid;     // [M] global ids
@@ -213,7 +218,7 @@ struct CafeJob {
     const int32_t* start1;   // [n1+1]
     const int32_t* ord2;
     const int32_t* start2;   // [n2+1]
-    // batch-start state (read) and the image this round writes
+    // batch-start state (read) and the image the rounds write
     const CafeMainBucket* main_in;
     CafeMainBucket* main_out;
     const CafeLruBucket* lru_in;
@@ -227,24 +232,31 @@ struct CafeJob {
     uint32_t ring_mask;
     uint32_t q_head;
     int32_t q_size;
-    // beliefs consumed (produced by the previous round) and produced
-    int32_t first_round;
-    const CafeEvent* ev_old;
-    CafeEvent* ev_new;
-    const int32_t* head_old;   // [n1] newest victim-promotion event per target bucket, -1 = none
-    const int32_t* nxt_old;    // [M]  next older event with the same target
-    int32_t* head_new;
-    int32_t* nxt_new;
-    const int32_t* tl_size_old;   // [2M] FIFO size before each op slot
+    // round control
+    int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
+    int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
+    int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to
+                           // record post_row; nothing else is written
+    // beliefs: the promotion event of every position, kept in place and updated by the LRU pass
+    CafeEvent* ev;           // [M]
+    int32_t* head;           // [n1] newest victim-promotion event per target bucket (-1 = none); rebuilt per round
+    int32_t* nxt;            // [M]  next older event with the same target
+    uint8_t* mark_own;       // [n1] 1 = one of the bucket's own lookups carries an own-promotion event
+    uint8_t* mstate;         // [n1] CAFE_S_* of the main bucket's last replay
+    uint8_t* mark2;          // [n2] 1 = the main pass of this round changed an input of this LRU bucket
+    uint8_t* lstate;         // [n2] CAFE_S_* of the LRU bucket's last replay
+    const int32_t* tl_size_old;   // [2M] FIFO size before each op slot (previous round)
     const int32_t* tl_rank_old;   // [2M] successful pops before each op slot
     const uint32_t* pushbuf_old;  // pushes in slot order
     int32_t* tl_size_new;
     int32_t* tl_rank_new;
     uint32_t* pushbuf_new;
-    // per-round scratch
-    uint8_t* pflag;      // [M] bit0: missed the main table; bits1-2: op slot of its candidate pop (+1)
-    int32_t* tstamp;     // [M] inclusive count of misses up to each position
-    int32_t* ins_res;    // [M] result of the believed event of this position: 0 ok, -1 failed, >0 failed and pushed this row
+    // per-lookup results, kept between rounds
+    uint8_t* mflag;      // [M] CAFE_F_* written by the main pass
+    uint8_t* lflag;      // [M] CAFE_F_* written by the LRU pass for lookups that missed the main table
+    int32_t* ins_res;    // [M] result of the event of this position when its target replayed it: 0 ok, -1 failed, >0 failed and pushed this row
+    // scratch
+    int32_t* tstamp;     // [M] inclusive count of misses up to each position (at commit)
     CafeFn* op_fn;       // [M] FIFO-size transfer function of the position, then its inclusive scan
     int64_t* op_cnt;     // [M] (pushes << 32) | successful pops, then their exclusive prefix sums
     // outputs
@@ -254,6 +266,10 @@ struct CafeJob {
 };
 
 CAFE_HD float cafe_count_of(const CafeJob& J, int p) { return J.imp ? J.imp[p] : 1.0f; }
+CAFE_HD uint32_t cafe_eff_flag(const CafeJob& J, int p) {
+    const uint32_t m = J.mflag[p];
+    return (m & CAFE_F_MISS) ? ((uint32_t)J.lflag[p] | CAFE_F_MISS) : m;
+}
 
 // Belief about a pop at op slot `slot`: would the FIFO be non-empty, and which row is at its front.
 CAFE_HD bool cafe_would_pop(const CafeJob& J, int64_t slot, int32_t* id) {
@@ -272,86 +288,95 @@ CAFE_HD bool cafe_would_pop(const CafeJob& J, int64_t slot, int32_t* id) {
 // chain is arbitrary because it was built with atomic exchanges).
 CAFE_HD int cafe_next_event(const CafeJob& J, int head, int after) {
     int best = INT32_MAX;
-    for (int e = head; e >= 0; e = J.nxt_old[e])
+    for (int e = head; e >= 0; e = J.nxt[e])
         if (e > after && e < best && e < J.limit) best = e;
     return best;
 }
 
-// Record the event produced at position p and flag a change against the belief `o` that was consumed.
-CAFE_HD void cafe_note_event(const CafeJob& J, int p, const CafeEvent& o, uint32_t kind, uint32_t x, float cnt,
-                             int32_t dic) {
-    bool same;
-    if (J.first_round) same = (kind == CAFE_EV_NONE);
-    else if (kind == CAFE_EV_NONE) same = (o.kind == CAFE_EV_NONE);
-    else same = (o.kind == kind && o.x == x && o.dic == dic && cafe_float_bits(o.cnt) == cafe_float_bits(cnt));
-    if (!same) J.res->changed = 1;
-    if (kind == CAFE_EV_NONE) { J.ev_new[p].kind = CAFE_EV_NONE; return; }
-    CafeEvent e;
-    e.x = x; e.cnt = cnt; e.dic = dic; e.kind = kind;
-    J.ev_new[p] = e;
-}
-// old belief of a position; never read in the first round (the buffer is uninitialised then)
-CAFE_HD uint32_t cafe_old_kind(const CafeJob& J, int p) { return J.first_round ? (uint32_t)CAFE_EV_NONE : J.ev_old[p].kind; }
-CAFE_HD CafeEvent cafe_old_event(const CafeJob& J, int p) {
-    if (J.first_round) { CafeEvent e; e.x = 0; e.cnt = 0.f; e.dic = 0; e.kind = CAFE_EV_NONE; return e; }
-    return J.ev_old[p];
+// old beliefs of a position; never read in the first round (the buffers are uninitialised then)
+CAFE_HD uint32_t cafe_old_kind(const CafeJob& J, int p) { return J.first_round ? (uint32_t)CAFE_EV_NONE : J.ev[p].kind; }
+CAFE_HD uint32_t cafe_old_mflag(const CafeJob& J, int p) { return J.first_round ? 0u : (uint32_t)J.mflag[p]; }
+
+// ---- between rounds: rebuild the routing of events to the main buckets they land in -----------------
+CAFE_HD void cafe_route_position(const CafeJob& J, int p) {
+    if (!(J.mflag[p] & CAFE_F_MISS)) return;   // a lookup that hit the main table has no event
+    const CafeEvent e = J.ev[p];
+    if (e.kind == CAFE_EV_VICTIM) J.nxt[p] = CAFE_ATOMIC_EXCH(&J.head[cafe_hash(e.x, J.n1)], p);
+    else if (e.kind == CAFE_EV_OWN) J.mark_own[cafe_hash(e.x, J.n1)] = 1;
 }
 
 // ---- round step 1: one main bucket ---------------------------------------------------------------
 // The replay of a bucket is a small state machine fed one own lookup at a time (feed), so that the
 // same code serves a thread that walks its bucket's lookups alone and a warp that loads a long
 // bucket's lookups together and hands them to the owning lane.
+//
+// Between rounds a bucket is replayed again only if something it depends on can have changed: it
+// receives events, one of its ids is waiting for a free row (so the FIFO timeline matters), or it was
+// in one of these cases in its previous replay (one more replay returns it to the belief-free result).
 #define CAFE_CAND 8
 struct CafeMainReplay {
     CafeMainBucket b;
     int k, evhead, p_ev;
-    int seg, seg_end;
-    int real_delta, num_delta, n_hit;
-    int i_first, i_cur;          // range of this bucket's sorted lookups that lie in the current segment
-    int ncand;                   // lookups of the current segment whose post-call row may be asked for
+    bool touched, cand, cond_now, dirty;
+    // used by the final pass only (post_row): segment bookkeeping
+    int seg_end, i_first, i_cur, ncand;
     int cand_p[CAFE_CAND];
     uint32_t cand_x[CAFE_CAND];
-    bool dirty, touched;
 
-    CAFE_HD void init(const CafeJob& J, int k_, int i_start) {
+    // returns false if the bucket does not need to be replayed this round
+    CAFE_HD bool init(const CafeJob& J, int k_, int i_start) {
         k = k_;
+        cond_now = false;
+        if (!J.first_round) {
+            const uint32_t st = J.mstate[k];
+            cond_now = J.head[k] >= 0 || J.mark_own[k] != 0 || (st & CAFE_S_CAND) != 0;
+            const bool active = J.final_pass ? cond_now : (J.all_active || cond_now || (st & CAFE_S_COND) != 0);
+            if (!active) return false;
+        }
         b = J.main_in[k];
-        evhead = J.first_round ? -1 : J.head_old[k];
+        evhead = J.first_round ? -1 : J.head[k];
         p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
-        seg = 0; seg_end = J.seg_off[1];
-        real_delta = num_delta = n_hit = 0;
+        touched = cand = dirty = false;
+        seg_end = J.seg_off[1];
         i_first = i_cur = i_start;
         ncand = 0;
-        dirty = touched = false;
+        return true;
+    }
+    CAFE_HD void set(int slot, uint32_t v, float c, int32_t d) {
+#pragma unroll
+        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { b.val[q] = v; b.cnt[q] = c; b.dic[q] = d; }
     }
     CAFE_HD void note_cand(int p, uint32_t x) {
         if (ncand < CAFE_CAND) { cand_p[ncand] = p; cand_x[ncand] = x; }
         ++ncand;
     }
-    // the segment (one field's call) ended: record what a query at this point would return
+    // final pass: the segment (one field's call) ended: record what a query at this point would return
     CAFE_HD void close_segment(const CafeJob& J) {
-        if (dirty && J.post_row) {
+        if (dirty) {
             if (ncand <= CAFE_CAND) {
                 for (int j = 0; j < ncand; ++j) J.post_row[cand_p[j]] = cafe_probe_hot(b, cand_x[j]);
             } else {
                 for (int j = i_first; j < i_cur; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
             }
         }
-        if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-        real_delta = 0; dirty = false; ncand = 0; i_first = i_cur;
+        dirty = false; ncand = 0; i_first = i_cur;
     }
     CAFE_HD void enter(const CafeJob& J, int p) {
-        if (p >= seg_end) {
+        if (J.final_pass && p >= seg_end) {
             close_segment(J);
-            while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
+            int s = 0;
+            while (p >= J.seg_off[s + 1]) ++s;
+            seg_end = J.seg_off[s + 1];
         }
         if (!touched) { cafe_touch(b, J.gflip); touched = true; }
     }
+    // the event of position p lands in this bucket (Insert, sketch.cpp:232-259)
     CAFE_HD void apply_event(const CafeJob& J, int p) {
-        CafeEvent e = J.ev_old[p];
+        const CafeEvent e = J.ev[p];
+        if (e.kind != CAFE_EV_OWN && e.kind != CAFE_EV_VICTIM) return;   // withdrawn while this pass ran
         int32_t pushed;
-        int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
-        J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
+        const int ok = cafe_promote(b, e.x, e.cnt, e.dic, &pushed);
+        if (!J.final_pass) J.ins_res[p] = ok ? 0 : (pushed != 0 ? pushed : -1);
         dirty = true;
     }
     // believed victim promotions (sketch.cpp:193-195 -> Insert) landing here at positions < before
@@ -362,41 +387,57 @@ struct CafeMainReplay {
             p_ev = cafe_next_event(J, evhead, p_ev);
         }
     }
-    // own lookup at position p (ascending); a lookup's probe comes before an event of the same position
-    // old_kind = kind of the event the previous round produced at p (cafe_old_kind)
-    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, uint32_t old_kind) {
+    // own lookup at position p (ascending); a lookup's probe comes before an event of the same position.
+    // old_kind / old_flag = what the previous round left for p (cafe_old_kind, cafe_old_mflag).
+    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, uint32_t old_kind, uint32_t old_flag) {
         if (p_ev < p) drain_events(J, p);
         enter(J, p);
         int s = -1;
 #pragma unroll
         for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (b.val[q] == x) s = q;
         if (s >= 0) {   // insert(): hit in the main table (sketch.cpp:215-228)
-            ++n_hit;
-            float cn = b.cnt[s] + c;
-            b.cnt[s] = cn;
-            if (cn >= J.thr && cn - c < J.thr) ++real_delta;
-            int got = 0;
-            uint8_t pf = 0;
-            if (cn >= J.thr && b.dic[s] == 0) {
-                pf = 1 << 1;   // candidate pop at op slot 2p
+            float cnt0 = 0.f;
+            int32_t dic0 = 0;
+#pragma unroll
+            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == s) { cnt0 = b.cnt[q]; dic0 = b.dic[q]; }
+            const float cn = cnt0 + c;
+            uint32_t nf = 0;
+            if (cn >= J.thr && cn - c < J.thr) nf |= CAFE_F_CROSS;
+            if (cn >= J.thr && dic0 == 0) {
+                cand = true;
+                nf |= CAFE_F_POP0;   // candidate pop at op slot 2p
                 int32_t id;
-                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[s] = id; got = 1; ++num_delta; dirty = true; note_cand(p, x); }
+                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) {
+                    dic0 = id; nf |= CAFE_F_GOT; dirty = true;
+                    if (J.final_pass) note_cand(p, x);
+                }
             }
-            J.pflag[p] = pf;
-            J.mask[p] = got;
-            if (old_kind != CAFE_EV_NONE) J.res->changed = 1;
-            J.ev_new[p].kind = CAFE_EV_NONE;
+            set(s, x, cn, dic0);
+            if (!J.final_pass) {
+                J.mflag[p] = (uint8_t)nf;
+                if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
+                else {
+                    if (old_kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                    if (old_flag & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;   // its LRU bucket loses this visitor
+                }
+            }
         } else {
-            J.pflag[p] = 1;   // goes to the LRU stage; that pass fills in the rest
-            note_cand(p, x);
-            if (old_kind == CAFE_EV_OWN) apply_event(J, p);   // believed own promotion
+            if (J.final_pass) note_cand(p, x);
+            else {
+                J.mflag[p] = CAFE_F_MISS;   // goes to the LRU stage; that pass writes lflag
+                if (!J.first_round && !(old_flag & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor
+            }
+            if (old_kind == CAFE_EV_OWN) {   // believed: this lookup promotes its own id into this bucket
+                apply_event(J, p);
+                if (!J.final_pass) J.mark2[cafe_hash(x, J.n2)] = 1;   // the LRU bucket reads ins_res[p]
+            }
         }
         ++i_cur;
     }
     CAFE_HD void finish(const CafeJob& J) {
         drain_events(J, INT32_MAX);
-        close_segment(J);
-        if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
+        if (J.final_pass) { close_segment(J); return; }
+        J.mstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0));
         J.main_out[k] = b;
     }
 };
@@ -405,38 +446,58 @@ CAFE_HD void cafe_main_pass_bucket(const CafeJob& J, int k) {
     CafeMainReplay R;
     const int iend = J.start1[k + 1];
     int i = J.start1[k];
-    R.init(J, k, i);
+    if (!R.init(J, k, i)) return;
     for (; i < iend; ++i) {
         const int p = J.ord1[i];
         if (p >= J.limit) break;
-        R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p));
+        R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p), cafe_old_mflag(J, p));
     }
     R.finish(J);
 }
 
 // ---- round step 2: one LRU bucket (insertLRU, sketch.cpp:161-210) ---------------------------------
+// LRU clock values are written as t0 + 1 + position while the rounds run (monotone in the order of
+// visits and above every stamp of the batch-start state, which is all the replay needs); they are
+// turned into the reference's consecutive numbering at commit (cafe_lru_tconvert).
 struct CafeLruReplay {
     CafeLruBucket b;
-    int k, seg, seg_end;
-    int real_delta, num_delta, n_ev;
-    bool touched;
+    int k, n_ev;
+    bool touched, cand, cond_now;
 
-    CAFE_HD void init(const CafeJob& J, int k_) {
+    CAFE_HD bool init(const CafeJob& J, int k_) {
         k = k_;
-        b = J.lru_in[k];
-        seg = 0; seg_end = J.seg_off[1];
-        real_delta = num_delta = n_ev = 0;
-        touched = false;
-    }
-    // a lookup at position p (ascending) that missed the main table; tp = its LRU clock value
-    // old = the event the previous round produced at p (cafe_old_event)
-    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, int32_t tp, const CafeEvent& old) {
-        if (p >= seg_end) {
-            if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-            real_delta = 0;
-            while (p >= seg_end) { ++seg; seg_end = J.seg_off[seg + 1]; }
+        cond_now = false;
+        if (!J.first_round) {
+            const uint32_t st = J.lstate[k];
+            cond_now = J.mark2[k] != 0 || (st & CAFE_S_CAND) != 0;
+            if (!(J.all_active || cond_now || (st & CAFE_S_COND) != 0)) return false;
         }
+        b = J.lru_in[k];
+        n_ev = 0;
+        touched = cand = false;
+        return true;
+    }
+    CAFE_HD void emit(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
+        if (J.first_round) {
+            if (kind == CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; return; }
+            J.res->changed = 1;
+        } else {
+            const CafeEvent o = J.ev[p];
+            bool same;
+            if (kind == CAFE_EV_NONE) same = (o.kind == CAFE_EV_NONE);
+            else same = (o.kind == kind && o.x == x && o.dic == dic && cafe_float_bits(o.cnt) == cafe_float_bits(cnt));
+            if (same) return;
+            J.res->changed = 1;
+            if (kind == CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; return; }
+        }
+        CafeEvent e;
+        e.x = x; e.cnt = cnt; e.dic = dic; e.kind = kind;
+        J.ev[p] = e;
+    }
+    // a lookup at position p (ascending) that missed the main table
+    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c) {
         if (!touched) { cafe_touch(b, J.gflip); touched = true; }
+        const int32_t tp = J.t0 + 1 + p;
         int hit = -1, vic = -1, t_min = 1000000000;
 #pragma unroll
         for (int q = 0; q < CAFE_SLOTS; ++q) {
@@ -445,73 +506,80 @@ struct CafeLruReplay {
                 else if (t_min > b.t[q]) { t_min = b.t[q]; vic = q; }
             }
         }
-        int got = 0;
+        uint32_t nf = 0;
         if (hit >= 0) {
             b.t[hit] = tp;
             float cn = b.cnt[hit] + c;
             b.cnt[hit] = cn;
-            if (cn >= J.thr && cn - c < J.thr) ++real_delta;
-            uint8_t pf = 1;
+            if (cn >= J.thr && cn - c < J.thr) nf |= CAFE_F_CROSS;
             if (cn >= J.thr && b.dic[hit] == 0) {
-                pf |= 1 << 1;   // candidate pop at op slot 2p (before the possible push-back at 2p+1)
+                cand = true;
+                nf |= CAFE_F_POP0;   // candidate pop at op slot 2p (before the possible push-back at 2p+1)
                 int32_t id;
-                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[hit] = id; got = 1; ++num_delta; }
+                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[hit] = id; nf |= CAFE_F_GOT; }
             }
-            J.pflag[p] = pf;
             if (cn >= J.thr) {
                 ++n_ev;
-                cafe_note_event(J, p, old, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
-                // the main pass of this round replayed the believed copy of this event
-                if (!J.first_round && J.ins_res[p] != 0) got = 0;
+                emit(J, p, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
+                // the main pass of this round replayed the event this position carried before the round
+                if (!J.first_round && J.ins_res[p] != 0) nf &= ~(uint32_t)CAFE_F_GOT;
                 b.val[hit] = 0; b.t[hit] = 0; b.cnt[hit] = 0.0f; b.dic[hit] = 0;
             } else {
-                cafe_note_event(J, p, old, CAFE_EV_NONE, 0, 0.0f, 0);
+                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
             }
         } else {
             if (vic < 0) { CAFE_ATOMIC_OR(&J.res->error, 2); vic = 0; }
             if (b.dic[vic] != 0 || b.cnt[vic] >= 5.0f) {
                 ++n_ev;
-                cafe_note_event(J, p, old, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
-                J.nxt_new[p] = CAFE_ATOMIC_EXCH(&J.head_new[cafe_hash(b.val[vic], J.n1)], p);
+                emit(J, p, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
             } else {
-                cafe_note_event(J, p, old, CAFE_EV_NONE, 0, 0.0f, 0);
+                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
             }
             b.val[vic] = x;
             b.t[vic] = tp;
             b.cnt[vic] = 1.0f;
             b.dic[vic] = 0;
-            if (1.0f >= J.thr && 1.0f - c < J.thr) ++real_delta;
-            uint8_t pf = 1;
+            if (1.0f >= J.thr && 1.0f - c < J.thr) nf |= CAFE_F_CROSS;
             if (1.0f >= J.thr) {
-                pf |= 2 << 1;   // candidate pop at op slot 2p+1 (after the victim's possible push-back at 2p)
+                cand = true;
+                nf |= CAFE_F_POP1;   // candidate pop at op slot 2p+1 (after the victim's possible push-back at 2p)
                 int32_t id;
-                if (cafe_would_pop(J, 2 * (int64_t)p + 1, &id)) { b.dic[vic] = id; got = 1; ++num_delta; }
+                if (cafe_would_pop(J, 2 * (int64_t)p + 1, &id)) { b.dic[vic] = id; nf |= CAFE_F_GOT; }
             }
-            J.pflag[p] = pf;
         }
-        J.mask[p] = got;
+        J.lflag[p] = (uint8_t)nf;
     }
     CAFE_HD void finish(const CafeJob& J) {
-        if (real_delta) CAFE_ATOMIC_ADD(&J.res->seg_real_delta[seg], real_delta);
-        if (num_delta) CAFE_ATOMIC_ADD(&J.res->num_delta, num_delta);
         if (n_ev) CAFE_ATOMIC_ADD(&J.res->n_events, n_ev);
+        J.lstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0));
         J.lru_out[k] = b;
     }
 };
 
 CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
     CafeLruReplay R;
-    R.init(J, k);
+    if (!R.init(J, k)) return;
     const int jend = J.start2[k + 1];
     for (int j = J.start2[k]; j < jend; ++j) {
         const int p = J.ord2[j];
         if (p >= J.limit) break;
-        if (!(J.pflag[p] & 1)) continue;
-        R.feed(J, p, J.gid[p], cafe_count_of(J, p), J.t0 + J.tstamp[p], cafe_old_event(J, p));
+        if (!(J.mflag[p] & CAFE_F_MISS)) continue;
+        R.feed(J, p, J.gid[p], cafe_count_of(J, p));
     }
     R.finish(J);
 }
 
+// at commit: LRU clock values written as t0 + 1 + position become t0 + (rank of the visit)
+CAFE_HD void cafe_lru_tconvert(const CafeJob& J, int k) {
+    CafeLruBucket& b = J.lru_out[k];
+#pragma unroll
+    for (int q = 0; q < CAFE_SLOTS; ++q)
+        if (b.t[q] > J.t0) b.t[q] = J.t0 + J.tstamp[b.t[q] - J.t0 - 1];
+}
+// at commit: the reference's per-lookup insert result
+CAFE_HD void cafe_finalize_position(const CafeJob& J, int p) {
+    J.mask[p] = (cafe_eff_flag(J, p) & CAFE_F_GOT) ? 1 : 0;
+}
 
 // ---- round step 3: the FIFO timeline ---------------------------------------------------------------
 // Each position owns two op slots (2p, 2p+1).  An op is a candidate pop or a push; the FIFO size
@@ -522,14 +590,14 @@ struct CafeOps { int op0, op1; int32_t id0, id1; };   // op: 0 none, 1 pop, 2 pu
 
 CAFE_HD CafeOps cafe_ops_of(const CafeJob& J, int p) {
     CafeOps o; o.op0 = o.op1 = 0; o.id0 = o.id1 = 0;
-    const int ps = (J.pflag[p] >> 1) & 3;
-    if (ps == 1) o.op0 = 1;
-    if (ps == 2) o.op1 = 1;
-    const int32_t r = J.first_round ? 0 : J.ins_res[p];
+    const uint32_t f = cafe_eff_flag(J, p);
+    if (f & CAFE_F_POP0) o.op0 = 1;
+    if (f & CAFE_F_POP1) o.op1 = 1;
+    const int32_t r = (J.first_round || !(f & CAFE_F_MISS)) ? 0 : J.ins_res[p];
     if (r > 0) {
-        // the believed event of this position failed and pushed its row back: after the pop for an
+        // the event of this position failed at its target and pushed its row back: after the pop for an
         // own promotion (slot 2p+1), before the pop for a victim promotion (slot 2p)
-        const uint32_t kind = J.ev_old[p].kind;
+        const uint32_t kind = J.ev[p].kind;
         if (kind == CAFE_EV_OWN) { if (o.op1 == 0) { o.op1 = 2; o.id1 = r; } else J.res->changed = 1; }
         else if (kind == CAFE_EV_VICTIM) { if (o.op0 == 0) { o.op0 = 2; o.id0 = r; } else J.res->changed = 1; }
     }
@@ -606,8 +674,23 @@ CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
         if (o.op1 == 1) { if (s2 > 0) { ++my_pops; } } else if (o.op1 == 2) { ++my_push; }
         J.res->n_pop_ok = (int32_t)(pre & 0xffffffffLL) + my_pops;
         J.res->n_push = (int32_t)(pre >> 32) + my_push;
-        J.res->n_miss = J.tstamp[p];
     }
+}
+
+// 3d: what position p adds to the per-segment change of real_n (a threshold crossing, sketch.cpp:169,
+// 200, 218) and to the number of LRU visits
+CAFE_HD void cafe_position_counts(const CafeJob& J, int p, int* crossed, int* missed) {
+    const uint32_t f = cafe_eff_flag(J, p);
+    *crossed = (f & CAFE_F_CROSS) ? 1 : 0;
+    *missed = (f & CAFE_F_MISS) ? 1 : 0;
+}
+CAFE_HD int cafe_segment_of(const CafeJob& J, int p) {
+    int lo = 0, hi = J.nseg - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (p >= J.seg_off[mid + 1]) lo = mid + 1; else hi = mid;
+    }
+    return lo;
 }
 
 // ---- commit of the FIFO after a converged round: live pushes go into the ring ----------------------

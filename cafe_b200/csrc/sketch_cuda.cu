@@ -80,16 +80,20 @@ __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb
 __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J) {
     const int lane = threadIdx.x & 31;
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
-    const bool live = k < J.n1;
     CafeMainReplay R;
     int i = 0, iend = 0;
-    if (live) { i = J.start1[k]; iend = J.start1[k + 1]; R.init(J, k, i); }
+    bool live = k < J.n1;
+    if (live) {
+        i = J.start1[k];
+        live = R.init(J, k, i);
+        if (live) iend = J.start1[k + 1];
+    }
     const bool is_long = live && (iend - i > CAFE_LONG);
     if (live && !is_long) {
         for (; i < iend; ++i) {
             const int p = J.ord1[i];
             if (p >= J.limit) break;
-            R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p));
+            R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p), cafe_old_mflag(J, p));
         }
     }
     unsigned m = __ballot_sync(CAFE_FULL, is_long);
@@ -101,11 +105,11 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         for (int base = s; base < e && !stop; base += 32) {
             const int idx = base + lane;
             int p = INT32_MAX;
-            uint32_t x = 0, ok = CAFE_EV_NONE;
+            uint32_t x = 0, ok = CAFE_EV_NONE, of = 0;
             float c = 1.0f;
             if (idx < e) {
                 p = J.ord1[idx];
-                if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); }
+                if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); of = cafe_old_mflag(J, p); }
             }
             const int n = min(32, e - base);
             int j = 0;
@@ -114,10 +118,10 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
                 if (pj >= J.limit) { stop = true; break; }
                 // Quiet run: consecutive lookups of one id that sits in a slot which already owns a hot
-                // row, inside the current segment and before the next believed event.  Such a lookup can
-                // only add to the slot's count (and be counted if it crosses the threshold); it cannot
-                // pop a row, so the run needs no replay logic: the counts are added in order, every
-                // lane writes the (empty) outputs of its own lookup.
+                // row, before the next believed event (and, in the final pass, inside the current
+                // segment).  Such a lookup can only add to the slot's count and possibly cross the
+                // threshold; it cannot pop a row, so the run needs no replay logic: the counts are added
+                // in order, every lane writes the flags of its own lookup.
                 int slot = -1, bound = 0;
                 float cnt0 = 0.f;
                 if (lane == o && R.touched) {
@@ -129,7 +133,8 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                         for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { d = R.b.dic[q]; cnt0 = R.b.cnt[q]; }
                         if (d == 0) slot = -1;
                     }
-                    bound = min(min(R.seg_end, R.p_ev), J.limit);
+                    bound = min(R.p_ev, J.limit);
+                    if (J.final_pass) bound = min(bound, R.seg_end);
                 }
                 slot = __shfl_sync(CAFE_FULL, slot, o);
                 int run = 0;
@@ -141,7 +146,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 }
                 if (run >= 2) {
                     float acc = __shfl_sync(CAFE_FULL, cnt0, o);
-                    int crossed = 0;
+                    uint32_t my_flag = 0;
                     for (int t0 = 0; t0 < run; t0 += 8) {
                         float cs[8];
 #pragma unroll
@@ -150,27 +155,30 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                         for (int u = 0; u < 8; ++u) {
                             if (t0 + u < run) {
                                 acc = acc + cs[u];
-                                crossed += (acc >= J.thr && acc - cs[u] < J.thr);   // sketch.cpp:218
+                                const bool cr = (acc >= J.thr && acc - cs[u] < J.thr);   // sketch.cpp:218
+                                if (cr && lane == j + t0 + u) my_flag = CAFE_F_CROSS;
                             }
                         }
                     }
                     if (lane == o) {
 #pragma unroll
                         for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc;
-                        R.real_delta += crossed;
                         R.i_cur += run;
                     }
-                    if (lane >= j && lane < j + run) {
-                        J.pflag[p] = 0;
-                        J.mask[p] = 0;
-                        if (ok != CAFE_EV_NONE) J.res->changed = 1;
-                        J.ev_new[p].kind = CAFE_EV_NONE;
+                    if (!J.final_pass && lane >= j && lane < j + run) {
+                        J.mflag[p] = (uint8_t)my_flag;
+                        if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
+                        else {
+                            if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                            if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                        }
                     }
                     j += run;
                 } else {
                     const float cj = __shfl_sync(CAFE_FULL, c, j);
                     const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
-                    if (lane == o) R.feed(J, pj, xj, cj, kj);
+                    const uint32_t fj = __shfl_sync(CAFE_FULL, of, j);
+                    if (lane == o) R.feed(J, pj, xj, cj, kj, fj);
                     ++j;
                 }
             }
@@ -181,17 +189,20 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
 __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J) {
     const int lane = threadIdx.x & 31;
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
-    const bool live = k < J.n2;
     CafeLruReplay R;
     int jb = 0, jend = 0;
-    if (live) { jb = J.start2[k]; jend = J.start2[k + 1]; R.init(J, k); }
+    bool live = k < J.n2;
+    if (live) {
+        live = R.init(J, k);
+        if (live) { jb = J.start2[k]; jend = J.start2[k + 1]; }
+    }
     const bool is_long = live && (jend - jb > CAFE_LONG);
     if (live && !is_long) {
         for (int j = jb; j < jend; ++j) {
             const int p = J.ord2[j];
             if (p >= J.limit) break;
-            if (!(J.pflag[p] & 1)) continue;
-            R.feed(J, p, J.gid[p], cafe_count_of(J, p), J.t0 + J.tstamp[p], cafe_old_event(J, p));
+            if (!(J.mflag[p] & CAFE_F_MISS)) continue;
+            R.feed(J, p, J.gid[p], cafe_count_of(J, p));
         }
     }
     unsigned m = __ballot_sync(CAFE_FULL, is_long);
@@ -202,17 +213,13 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         bool stop = false;
         for (int base = s; base < e && !stop; base += 32) {
             const int idx = base + lane;
-            int p = INT32_MAX, tp = 0;
+            int p = INT32_MAX;
             uint32_t x = 0;
             float c = 1.0f;
             bool miss = false;
-            CafeEvent oe;
-            oe.x = 0; oe.cnt = 0.f; oe.dic = 0; oe.kind = CAFE_EV_NONE;
             if (idx < e) {
                 p = J.ord2[idx];
-                if (p < J.limit && (J.pflag[p] & 1)) {
-                    miss = true; x = J.gid[p]; c = cafe_count_of(J, p); tp = J.t0 + J.tstamp[p]; oe = cafe_old_event(J, p);
-                }
+                if (p < J.limit && (J.mflag[p] & CAFE_F_MISS)) { miss = true; x = J.gid[p]; c = cafe_count_of(J, p); }
             }
             // positions ascend inside a bucket: once one lane sees the limit, later chunks are beyond it too
             stop = __any_sync(CAFE_FULL, idx < e && p >= J.limit);
@@ -223,17 +230,47 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
                 const int pj = __shfl_sync(CAFE_FULL, p, j);
                 const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
                 const float cj = __shfl_sync(CAFE_FULL, c, j);
-                const int tj = __shfl_sync(CAFE_FULL, tp, j);
-                CafeEvent oj;
-                oj.x = __shfl_sync(CAFE_FULL, oe.x, j);
-                oj.cnt = __shfl_sync(CAFE_FULL, oe.cnt, j);
-                oj.dic = __shfl_sync(CAFE_FULL, oe.dic, j);
-                oj.kind = __shfl_sync(CAFE_FULL, oe.kind, j);
-                if (lane == o) R.feed(J, pj, xj, cj, tj, oj);
+                if (lane == o) R.feed(J, pj, xj, cj);
             }
         }
     }
     if (live) R.finish(J);
+}
+__global__ void k_route(const __grid_constant__ CafeJob J) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_route_position(J, p);
+}
+__global__ void k_finalize_positions(const __grid_constant__ CafeJob J) {
+    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_finalize_position(J, p);
+}
+__global__ void k_lru_tconvert(const __grid_constant__ CafeJob J) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < J.n2) cafe_lru_tconvert(J, k);
+}
+// per-segment threshold crossings and the number of LRU visits: block-wide sums, one atomic per
+// block and counter (a block of consecutive positions lies in one segment except at boundaries)
+__global__ void __launch_bounds__(CAFE_TPB) k_position_counts(const __grid_constant__ CafeJob J) {
+    __shared__ int s_cross, s_miss;
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    const int first = blockIdx.x * blockDim.x;
+    const int last = min(first + (int)blockDim.x, J.limit) - 1;
+    if (threadIdx.x == 0) { s_cross = 0; s_miss = 0; }
+    __syncthreads();
+    int c = 0, mi = 0;
+    if (p < J.limit) cafe_position_counts(J, p, &c, &mi);
+    const int seg_first = cafe_segment_of(J, first), seg_last = cafe_segment_of(J, last);
+    const unsigned mc = __ballot_sync(CAFE_FULL, c != 0), mm = __ballot_sync(CAFE_FULL, mi != 0);
+    if ((threadIdx.x & 31) == 0) {
+        if (mm) atomicAdd(&s_miss, __popc(mm));
+        if (mc && seg_first == seg_last) atomicAdd(&s_cross, __popc(mc));
+    }
+    if (seg_first != seg_last && c) atomicAdd(&J.res->seg_real_delta[cafe_segment_of(J, p)], c);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (s_cross) atomicAdd(&J.res->seg_real_delta[seg_first], s_cross);
+        if (s_miss) atomicAdd(&J.res->n_miss, s_miss);
+    }
 }
 __global__ void k_resolve_ops(const __grid_constant__ CafeJob J) {
     int p = blockIdx.x * blockDim.x + threadIdx.x;
@@ -448,11 +485,21 @@ struct CudaBackend {
         k_main_pass<<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J);
         check_launch();
     }
-    void scan_miss(const CafeJob& J) {
+    void route(const CafeJob& J) {
         CAFE_PROF(CAFE_P_SCAN, stream);
-        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.pflag, MissFlag());
+        k_route<<<cafe_blocks(J.limit), CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+    }
+    // per-lookup results and the LRU clock numbering, once the rounds have converged
+    void finalize(const CafeJob& J) {
+        CAFE_PROF(CAFE_P_COMMIT, stream);
+        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.mflag, MissFlag());
         size_t b = cub_bytes;
         check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp, J.limit, stream));
+        k_finalize_positions<<<cafe_blocks(J.limit), CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+        k_lru_tconvert<<<cafe_blocks(J.n2), CAFE_TPB, 0, stream>>>(J);
+        check_launch();
     }
     void lru_pass(const CafeJob& J) {
         CAFE_PROF(CAFE_P_LRU, stream);
@@ -471,6 +518,8 @@ struct CudaBackend {
         b = cub_bytes;
         check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, J.op_cnt, J.op_cnt, J.limit, stream));
         k_resolve_write<<<g, CAFE_TPB, 0, stream>>>(J);
+        check_launch();
+        k_position_counts<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
     }
     void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,

@@ -37,7 +37,8 @@ public:
     int q_size = 0;
     uint32_t ring_mask = 0;
     int round_cap = 48;
-    int window = CAFE_MAX_SEGMENTS;   // segments fused per job; shrinks after a re-fit cut a job short
+    double cross_rate = -1.0;         // threshold crossings per lookup seen in recent jobs (-1: unknown)
+    int window = CAFE_MAX_SEGMENTS;   // upper bound on the segments fused into one job
     int last_status = CAFE_OK;
     CafeSketchStats stats;
 
@@ -74,15 +75,17 @@ public:
         size_t M = (size_t)cap;
         ord1 = (int32_t*)be.alloc(4 * M); ord2 = (int32_t*)be.alloc(4 * M);
         start1 = (int32_t*)be.alloc(4 * ((size_t)n1 + 1)); start2 = (int32_t*)be.alloc(4 * ((size_t)n2 + 1));
+        ev = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
+        head = (int32_t*)be.alloc(4 * (size_t)n1);
+        nxt = (int32_t*)be.alloc(4 * M);
+        mark_own = (uint8_t*)be.alloc((size_t)n1); mstate = (uint8_t*)be.alloc((size_t)n1);
+        mark2 = (uint8_t*)be.alloc((size_t)n2); lstate = (uint8_t*)be.alloc((size_t)n2);
+        mflag = (uint8_t*)be.alloc(M); lflag = (uint8_t*)be.alloc(M);
         for (int i = 0; i < 2; ++i) {
-            ev[i] = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
-            head[i] = (int32_t*)be.alloc(4 * (size_t)n1);
-            nxt[i] = (int32_t*)be.alloc(4 * M);
             tl_size[i] = (int32_t*)be.alloc(8 * M);
             tl_rank[i] = (int32_t*)be.alloc(8 * M);
             pushbuf[i] = (uint32_t*)be.alloc(4 * M);
         }
-        pflag = (uint8_t*)be.alloc(M);
         tstamp = (int32_t*)be.alloc(4 * M);
         ins_res = (int32_t*)be.alloc(4 * M);
         op_fn = (CafeFn*)be.alloc(sizeof(CafeFn) * M);
@@ -95,11 +98,11 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !pflag || !tstamp || !ins_res || !op_fn || !op_cnt ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn || !op_cnt ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
         for (int i = 0; i < 2; ++i)
-            if (!ev[i] || !head[i] || !nxt[i] || !tl_size[i] || !tl_rank[i] || !pushbuf[i]) return CAFE_ERR_CUDA;
+            if (!tl_size[i] || !tl_rank[i] || !pushbuf[i]) return CAFE_ERR_CUDA;
         ready = true;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
     }
@@ -143,6 +146,9 @@ public:
                 while (e < maxe && (int64_t)seg_off[e + 1] - seg_off[s] <= cap) {
                     double d2 = d * alpha;
                     if (d2 > CAFE_DECAY_BASE) break;
+                    // stop where a threshold re-fit is expected (the exact test runs on the results)
+                    if (adjust && cross_rate >= 0 &&
+                        real_n + cross_rate * ((double)seg_off[e] - seg_off[s]) > lim * 1.2) break;
                     d = d2; ++e;
                 }
             }
@@ -163,10 +169,6 @@ public:
             }
             // boundaries inside the fused range: nothing happens at them except the clocks
             for (int b = s + 1; b < done_e; ++b) { ++batch_num; decay_importance *= alpha; ++stats.calls; }
-            if (parallel) {
-                if (done_e < e) window = std::max(1, done_e - s);
-                else window = std::min((int)CAFE_MAX_SEGMENTS, window * 2);
-            }
             s = done_e;
         }
         stats.lookups += total;
@@ -247,13 +249,13 @@ private:
     CafeLruBucket* lrub[2] = {nullptr, nullptr};
     uint32_t* ring = nullptr;
     int32_t *ord1 = nullptr, *ord2 = nullptr, *start1 = nullptr, *start2 = nullptr;
-    CafeEvent* ev[2] = {nullptr, nullptr};
-    int32_t* head[2] = {nullptr, nullptr};
-    int32_t* nxt[2] = {nullptr, nullptr};
+    CafeEvent* ev = nullptr;
+    int32_t* head = nullptr;
+    int32_t* nxt = nullptr;
+    uint8_t *mark_own = nullptr, *mstate = nullptr, *mark2 = nullptr, *lstate = nullptr, *mflag = nullptr, *lflag = nullptr;
     int32_t* tl_size[2] = {nullptr, nullptr};
     int32_t* tl_rank[2] = {nullptr, nullptr};
     uint32_t* pushbuf[2] = {nullptr, nullptr};
-    uint8_t* pflag = nullptr;
     int32_t *tstamp = nullptr, *ins_res = nullptr;
     CafeFn* op_fn = nullptr;
     int64_t* op_cnt = nullptr;
@@ -266,9 +268,8 @@ private:
 
     void release() {
         if (!ready && !mainb[0]) return;
-        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, ev[0], ev[1], head[0],
-                        head[1], nxt[0], nxt[1], tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
-                        pflag, tstamp, ins_res, op_fn, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, ev, head, nxt, mark_own, mstate, mark2, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
+                        tstamp, ins_res, op_fn, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
         mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
@@ -321,16 +322,20 @@ private:
         J.ord1 = ord1; J.start1 = start1; J.ord2 = ord2; J.start2 = start2;
         J.n1 = n1; J.n2 = n2; J.thr = thr; J.gflip = gflip; J.t0 = t;
         J.ring = ring; J.ring_mask = ring_mask; J.q_head = q_head; J.q_size = q_size;
-        J.pflag = pflag; J.tstamp = tstamp; J.ins_res = ins_res; J.op_fn = op_fn; J.op_cnt = op_cnt;
+        J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
+        J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
+        J.ev = ev; J.head = head; J.nxt = nxt; J.mark_own = mark_own; J.mstate = mstate; J.mark2 = mark2; J.lstate = lstate;
+        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.tstamp = tstamp; J.op_fn = op_fn; J.op_cnt = op_cnt;
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
         ++stats.jobs;
+        be.memset(ins_res, 0, 4 * (size_t)M);
 
         CafeRoundResult R;
         int rounds = 0;
-        bool truncated = false;
-        int pb = 0;   // index of the belief set consumed this round
+        bool truncated = false, shortened = false;
+        int pb = 0;   // index of the FIFO timeline consumed this round
         bool first = true;
         for (;;) {
             if (rounds >= round_cap) {
@@ -342,18 +347,15 @@ private:
                 return rc == CAFE_OK ? CAFE_OK : rc;
             }
             J.first_round = first ? 1 : 0;
-            J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
-            J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
-            J.ev_old = ev[pb]; J.ev_new = ev[pb ^ 1];
-            J.head_old = head[pb]; J.nxt_old = nxt[pb]; J.head_new = head[pb ^ 1]; J.nxt_new = nxt[pb ^ 1];
+            J.all_active = (first || shortened) ? 1 : 0;
+            J.final_pass = 0;
+            shortened = false;
             J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
             J.tl_size_new = tl_size[pb ^ 1]; J.tl_rank_new = tl_rank[pb ^ 1]; J.pushbuf_new = pushbuf[pb ^ 1];
             be.memset(res_dev, 0, sizeof(CafeRoundResult));
-            be.memset(ins_res, 0, 4 * (size_t)M);
-            be.memset(J.head_new, 0xff, 4 * (size_t)n1);
-            if (post_row) be.memset(post_row, 0, 4 * (size_t)J.limit);
+            if (!first) route(J);
+            be.memset(mark2, 0, (size_t)n2);
             be.main_pass(J);
-            be.scan_miss(J);
             be.lru_pass(J);
             be.resolve(J);
             be.d2h(&R, res_dev, sizeof(R));
@@ -379,6 +381,7 @@ private:
                     nseg = cut;
                     if (!truncated) ++stats.truncated_jobs;
                     truncated = true;
+                    shortened = true;   // bucket images written so far include lookups beyond the new end
                     if (J.limit == 0) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
                     continue;
                 }
@@ -386,17 +389,40 @@ private:
             if (R.changed) continue;
             break;
         }
-        // commit
+        // converged: the timeline just produced (index pb) equals the one consumed
+        J.first_round = 0; J.all_active = 0;
+        J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
+        if (post_row) {
+            be.memset(post_row, 0, 4 * (size_t)J.limit);
+            route(J);
+            J.final_pass = 1;
+            be.main_pass(J);
+            J.final_pass = 0;
+        }
+        be.finalize(J);   // per-lookup results, LRU clock values
         if (R.n_push > 0) be.commit_queue(ring, ring_mask, q_head, q_size, R.n_pop_ok, pushbuf[pb], R.n_push);
         cur ^= 1;
         q_head += (uint32_t)R.n_pop_ok;
         q_size += R.n_push - R.n_pop_ok;
         t += R.n_miss;
-        num += R.num_delta;
-        for (int b = 0; b < nseg; ++b) real_n += R.seg_real_delta[b];
+        num += R.n_pop_ok;   // every successful pop hands out one hot row (sketch.cpp:176,206,224)
+        int grown = 0;
+        for (int b = 0; b < nseg; ++b) grown += R.seg_real_delta[b];
+        real_n += grown;
+        if (J.limit > 0) {
+            const double r = (double)grown / J.limit;
+            cross_rate = cross_rate < 0 ? r : 0.5 * cross_rate + 0.5 * r;
+        }
         stats.main_hits += (int64_t)J.limit - R.n_miss; stats.lru_visits += R.n_miss; stats.events += R.n_events;
         if (rounds > stats.max_rounds) stats.max_rounds = rounds;
         *done = nseg;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
+    }
+
+    // rebuild the per-bucket chains of victim promotions and the own-promotion marks from the events
+    void route(const CafeJob& J) {
+        be.memset(head, 0xff, 4 * (size_t)n1);
+        be.memset(mark_own, 0, (size_t)n1);
+        be.route(J);
     }
 };

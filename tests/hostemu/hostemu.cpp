@@ -53,9 +53,15 @@ struct HostBackend {
         if (flip_order) for (int k = J.n1 - 1; k >= 0; --k) cafe_main_pass_bucket(J, k);
         else for (int k = 0; k < J.n1; ++k) cafe_main_pass_bucket(J, k);
     }
-    void scan_miss(const CafeJob& J) {
+    void route(const CafeJob& J) {
+        for (int p = J.limit - 1; p >= 0; --p) cafe_route_position(J, p);
+    }
+    // per-lookup results and the LRU clock numbering, once the rounds have converged
+    void finalize(const CafeJob& J) {
         int32_t acc = 0;
-        for (int p = 0; p < J.limit; ++p) { acc += J.pflag[p] & 1; J.tstamp[p] = acc; }
+        for (int p = 0; p < J.limit; ++p) { acc += (J.mflag[p] & CAFE_F_MISS) ? 1 : 0; J.tstamp[p] = acc; }
+        for (int p = 0; p < J.limit; ++p) cafe_finalize_position(J, p);
+        for (int k = 0; k < J.n2; ++k) cafe_lru_tconvert(J, k);
     }
     void lru_pass(const CafeJob& J) {
         if (flip_order) for (int k = J.n2 - 1; k >= 0; --k) cafe_lru_pass_bucket(J, k);
@@ -72,6 +78,12 @@ struct HostBackend {
         int64_t acc = 0;
         for (int p = 0; p < J.limit; ++p) { int64_t v = J.op_cnt[p]; J.op_cnt[p] = acc; acc += v; }
         for (int p = J.limit - 1; p >= 0; --p) cafe_resolve_write(J, p);
+        for (int p = 0; p < J.limit; ++p) {
+            int c, m;
+            cafe_position_counts(J, p, &c, &m);
+            if (c) J.res->seg_real_delta[cafe_segment_of(J, p)] += c;
+            J.res->n_miss += m;
+        }
     }
     void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
                       const uint32_t* pushbuf, int n_push) {
