@@ -203,7 +203,7 @@ struct CafeFn { int32_t a, b; };   // FIFO size transfer: s -> max(s + a, b)
 // per-lookup result flags (one byte written by the main pass, one by the LRU pass)
 enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE_F_GOT = 16 };
 // per-bucket replay state kept between rounds
-enum { CAFE_S_COND = 1, CAFE_S_CAND = 2 };
+enum { CAFE_S_COND = 1, CAFE_S_CAND = 2, CAFE_S_DIRTY = 4 };   // DIRTY: a row was handed out or an event landed
 
 struct CafeJob {
     // the lookups
@@ -330,7 +330,8 @@ struct CafeMainReplay {
         if (!J.first_round) {
             const uint32_t st = J.mstate[k];
             cond_now = J.head[k] >= 0 || J.mark_own[k] != 0 || (st & CAFE_S_CAND) != 0;
-            const bool active = J.final_pass ? cond_now : (J.all_active || cond_now || (st & CAFE_S_COND) != 0);
+            const bool active = J.final_pass ? (st & CAFE_S_DIRTY) != 0
+                                             : (J.all_active || cond_now || (st & CAFE_S_COND) != 0);
             if (!active) return false;
         }
         b = J.main_in[k];
@@ -437,7 +438,7 @@ struct CafeMainReplay {
     CAFE_HD void finish(const CafeJob& J) {
         drain_events(J, INT32_MAX);
         if (J.final_pass) { close_segment(J); return; }
-        J.mstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0));
+        J.mstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0) | (dirty ? CAFE_S_DIRTY : 0));
         J.main_out[k] = b;
     }
 };

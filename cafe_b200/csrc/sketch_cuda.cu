@@ -117,64 +117,88 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 const int pj = __shfl_sync(CAFE_FULL, p, j);
                 const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
                 if (pj >= J.limit) { stop = true; break; }
-                // Quiet run: consecutive lookups of one id that sits in a slot which already owns a hot
-                // row, before the next believed event (and, in the final pass, inside the current
-                // segment).  Such a lookup can only add to the slot's count and possibly cross the
-                // threshold; it cannot pop a row, so the run needs no replay logic: the counts are added
-                // in order, every lane writes the flags of its own lookup.
-                int slot = -1, bound = 0;
+                // Plain run: consecutive lookups of one id that sits in a slot of this bucket, before the
+                // next believed event (and, in the final pass, inside the current segment).  While the
+                // slot cannot take a free row -- it owns one already, or its count is below the threshold,
+                // or the FIFO is believed empty at that position -- a lookup only adds to the count, may
+                // cross the threshold and may be a failed pop candidate.  The counts are added in order
+                // by a shuffle chain; every lane writes the flags of its own lookup.  The run stops before
+                // the first lookup that could take a row; that one goes through the full replay.
+                int slot = -1, bound = 0, has_row = 0;
                 float cnt0 = 0.f;
                 if (lane == o && R.touched) {
 #pragma unroll
                     for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (R.b.val[q] == xj) slot = q;
                     if (slot >= 0) {
-                        int32_t d = 0;
 #pragma unroll
-                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { d = R.b.dic[q]; cnt0 = R.b.cnt[q]; }
-                        if (d == 0) slot = -1;
+                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { has_row = R.b.dic[q] != 0; cnt0 = R.b.cnt[q]; }
                     }
                     bound = min(R.p_ev, J.limit);
                     if (J.final_pass) bound = min(bound, R.seg_end);
                 }
                 slot = __shfl_sync(CAFE_FULL, slot, o);
                 int run = 0;
+                bool advanced = false;
+                unsigned avail_mask = 0;
                 if (slot >= 0) {
                     bound = __shfl_sync(CAFE_FULL, bound, o);
-                    const unsigned q = __ballot_sync(CAFE_FULL, lane >= j && lane < n && x == xj && p < bound) >> j;
+                    has_row = __shfl_sync(CAFE_FULL, has_row, o);
+                    const bool mine = lane >= j && lane < n && x == xj && p < bound;
+                    const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
                     if (run < 0) run = 32 - j;    // all remaining lanes qualify
+                    if (!has_row && run >= 2) {
+                        // belief about the FIFO at each lookup's pop slot (2p): non-empty?
+                        bool av = false;
+                        if (mine) av = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p] > 0);
+                        avail_mask = __ballot_sync(CAFE_FULL, av);
+                    }
                 }
                 if (run >= 2) {
                     float acc = __shfl_sync(CAFE_FULL, cnt0, o);
                     uint32_t my_flag = 0;
-                    for (int t0 = 0; t0 < run; t0 += 8) {
+                    int done = 0;
+                    bool any_cand = false;
+                    for (int t0 = 0; t0 < run && done == t0; t0 += 8) {
                         float cs[8];
 #pragma unroll
                         for (int u = 0; u < 8; ++u) cs[u] = __shfl_sync(CAFE_FULL, c, min(j + t0 + u, 31));
 #pragma unroll
                         for (int u = 0; u < 8; ++u) {
-                            if (t0 + u < run) {
-                                acc = acc + cs[u];
-                                const bool cr = (acc >= J.thr && acc - cs[u] < J.thr);   // sketch.cpp:218
-                                if (cr && lane == j + t0 + u) my_flag = CAFE_F_CROSS;
+                            if (t0 + u < run && done == t0 + u) {
+                                const float nx = acc + cs[u];
+                                const bool cd = !has_row && nx >= J.thr;                 // pop candidate (sketch.cpp:221)
+                                if (!(cd && ((avail_mask >> (j + t0 + u)) & 1u))) {      // ... that cannot succeed
+                                    const bool cr = (nx >= J.thr && nx - cs[u] < J.thr);   // sketch.cpp:218
+                                    if (lane == j + t0 + u) my_flag = (cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0);
+                                    any_cand |= cd;
+                                    acc = nx;
+                                    ++done;
+                                }
                             }
                         }
                     }
-                    if (lane == o) {
+                    run = done;
+                    if (run > 0) {
+                        if (lane == o) {
 #pragma unroll
-                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc;
-                        R.i_cur += run;
-                    }
-                    if (!J.final_pass && lane >= j && lane < j + run) {
-                        J.mflag[p] = (uint8_t)my_flag;
-                        if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
-                        else {
-                            if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
-                            if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc;
+                            R.i_cur += run;
+                            if (any_cand) R.cand = true;
                         }
+                        if (!J.final_pass && lane >= j && lane < j + run) {
+                            J.mflag[p] = (uint8_t)my_flag;
+                            if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
+                            else {
+                                if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                                if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                            }
+                        }
+                        j += run;
+                        advanced = true;
                     }
-                    j += run;
-                } else {
+                }
+                if (!advanced) {
                     const float cj = __shfl_sync(CAFE_FULL, c, j);
                     const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
                     const uint32_t fj = __shfl_sync(CAFE_FULL, of, j);
