@@ -42,7 +42,8 @@ void cafe_internal_set_error(const char* msg);
 enum {
     CAFE_P_FORWARD = 0, CAFE_P_NORM, CAFE_P_FIELDSUM, CAFE_P_IMPORTANCE, CAFE_P_LOOKUP_SORT, CAFE_P_MAIN, CAFE_P_SCAN,
     CAFE_P_LRU, CAFE_P_RESOLVE, CAFE_P_COMMIT, CAFE_P_REFIT, CAFE_P_MIGRATE, CAFE_P_ROWKEYS, CAFE_P_ROWSORT,
-    CAFE_P_SCATTER, CAFE_P_FIXUP, CAFE_P_SEQ, CAFE_P_QUERY, CAFE_P_MEMSET, CAFE_P_OTHER, CAFE_PROF_SLOTS
+    CAFE_P_SCATTER, CAFE_P_FIXUP, CAFE_P_SEQ, CAFE_P_QUERY, CAFE_P_MEMSET, CAFE_P_OTHER, CAFE_P_MAIN_LATER, CAFE_P_MAIN_FINAL,
+    CAFE_P_LRU_LATER, CAFE_PROF_SLOTS
 };
 void cafe_prof_begin(int slot, cudaStream_t st);
 void cafe_prof_end(cudaStream_t st);
@@ -52,3 +53,4 @@ struct CafeProfScope {
     ~CafeProfScope() { cafe_prof_end(st); }
 };
 #define CAFE_PROF(slot, stream) CafeProfScope cafe_prof_scope_##slot(slot, stream)
+#define CAFE_PROF_DYN(slot, stream) CafeProfScope cafe_prof_scope_dyn(slot, stream)

@@ -66,5 +66,9 @@ struct CafeRoundResult {
     int32_t error;         // internal consistency problems seen (0 = none)
     int32_t n_main_hit;
     int32_t n_events;
+    int32_t n_active_main;   // diagnostics: long buckets replayed, and the most full-replay steps one of them took
+    int32_t max_slow_main;
+    int32_t n_active_lru;
+    int32_t max_feed_lru;
     int32_t seg_real_delta[CAFE_MAX_SEGMENTS];  // change of real_n per segment
 };

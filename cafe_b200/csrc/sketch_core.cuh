@@ -76,23 +76,27 @@ CAFE_HD int32_t cafe_probe_hot(const CafeMainBucket& b, uint32_t x) {
 // ---- Insert (sketch.cpp:232-259): place a promoted id; returns 1 on success.  On failure
 // *pushed = the carried row that goes back to the FIFO (0 if it carried none). --------------------
 CAFE_HD int cafe_promote(CafeMainBucket& b, uint32_t x, float count, int32_t carried, int32_t* pushed) {
-    int min_i = -1;
+    // (written with compile-time slot indices throughout so that a bucket held in registers stays there)
+    int empty_i = -1, min_i = -1;
     float min_cnt = 1e9f;
+    int32_t min_dic = 0;
     *pushed = 0;
 #pragma unroll
+    for (int i = CAFE_SLOTS - 1; i >= 0; --i) if (b.val[i] == 0) empty_i = i;   // first empty slot
+#pragma unroll
     for (int i = 0; i < CAFE_SLOTS; ++i) {
-        if (b.val[i] == 0) {
-            b.val[i] = x;
-            b.cnt[i] = count;
-            b.dic[i] = carried;
-            return 1;
-        }
-        if (b.cnt[i] < min_cnt) { min_cnt = b.cnt[i]; min_i = i; }
+        // the reference scans slots in order and returns at the first empty one: slots after it never
+        // take part in the minimum, slots before it do not matter because the empty one wins
+        if (b.cnt[i] < min_cnt) { min_cnt = b.cnt[i]; min_i = i; min_dic = b.dic[i]; }
     }
-    if (min_i >= 0 && b.dic[min_i] == 0) {
-        b.cnt[min_i] += count;
-        b.val[min_i] = x;
-        b.dic[min_i] = carried;
+    if (empty_i >= 0) {
+#pragma unroll
+        for (int i = 0; i < CAFE_SLOTS; ++i) if (i == empty_i) { b.val[i] = x; b.cnt[i] = count; b.dic[i] = carried; }
+        return 1;
+    }
+    if (min_i >= 0 && min_dic == 0) {
+#pragma unroll
+        for (int i = 0; i < CAFE_SLOTS; ++i) if (i == min_i) { b.cnt[i] += count; b.val[i] = x; b.dic[i] = carried; }
         return 1;
     }
     *pushed = carried;
@@ -235,6 +239,7 @@ struct CafeJob {
     // round control
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
+    int32_t diag;          // timing experiments only (changes results): see k_main_pass
     int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to
                            // record post_row; nothing else is written
     // beliefs: the promotion event of every position, kept in place and updated by the LRU pass
@@ -313,7 +318,7 @@ CAFE_HD void cafe_route_position(const CafeJob& J, int p) {
 // Between rounds a bucket is replayed again only if something it depends on can have changed: it
 // receives events, one of its ids is waiting for a free row (so the FIFO timeline matters), or it was
 // in one of these cases in its previous replay (one more replay returns it to the belief-free result).
-#define CAFE_CAND 8
+#define CAFE_CAND 4
 struct CafeMainReplay {
     CafeMainBucket b;
     int k, evhead, p_ev;
@@ -348,14 +353,16 @@ struct CafeMainReplay {
         for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { b.val[q] = v; b.cnt[q] = c; b.dic[q] = d; }
     }
     CAFE_HD void note_cand(int p, uint32_t x) {
-        if (ncand < CAFE_CAND) { cand_p[ncand] = p; cand_x[ncand] = x; }
+#pragma unroll
+        for (int q = 0; q < CAFE_CAND; ++q) if (q == ncand) { cand_p[q] = p; cand_x[q] = x; }
         ++ncand;
     }
     // final pass: the segment (one field's call) ended: record what a query at this point would return
     CAFE_HD void close_segment(const CafeJob& J) {
         if (dirty) {
             if (ncand <= CAFE_CAND) {
-                for (int j = 0; j < ncand; ++j) J.post_row[cand_p[j]] = cafe_probe_hot(b, cand_x[j]);
+#pragma unroll
+                for (int j = 0; j < CAFE_CAND; ++j) if (j < ncand) J.post_row[cand_p[j]] = cafe_probe_hot(b, cand_x[j]);
             } else {
                 for (int j = i_first; j < i_cur; ++j) { int q = J.ord1[j]; J.post_row[q] = cafe_probe_hot(b, J.gid[q]); }
             }
@@ -478,6 +485,10 @@ struct CafeLruReplay {
         touched = cand = false;
         return true;
     }
+    CAFE_HD void set(int slot, uint32_t v, float c, int32_t d, int32_t tt) {
+#pragma unroll
+        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { b.val[q] = v; b.cnt[q] = c; b.dic[q] = d; b.t[q] = tt; }
+    }
     CAFE_HD void emit(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
         if (J.first_round) {
             if (kind == CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; return; }
@@ -509,44 +520,50 @@ struct CafeLruReplay {
         }
         uint32_t nf = 0;
         if (hit >= 0) {
-            b.t[hit] = tp;
-            float cn = b.cnt[hit] + c;
-            b.cnt[hit] = cn;
+            float cnt0 = 0.f;
+            int32_t dic0 = 0;
+#pragma unroll
+            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hit) { cnt0 = b.cnt[q]; dic0 = b.dic[q]; }
+            const float cn = cnt0 + c;
             if (cn >= J.thr && cn - c < J.thr) nf |= CAFE_F_CROSS;
-            if (cn >= J.thr && b.dic[hit] == 0) {
+            if (cn >= J.thr && dic0 == 0) {
                 cand = true;
                 nf |= CAFE_F_POP0;   // candidate pop at op slot 2p (before the possible push-back at 2p+1)
                 int32_t id;
-                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { b.dic[hit] = id; nf |= CAFE_F_GOT; }
+                if (cafe_would_pop(J, 2 * (int64_t)p, &id)) { dic0 = id; nf |= CAFE_F_GOT; }
             }
             if (cn >= J.thr) {
                 ++n_ev;
-                emit(J, p, CAFE_EV_OWN, b.val[hit], cn, b.dic[hit]);
+                emit(J, p, CAFE_EV_OWN, x, cn, dic0);
                 // the main pass of this round replayed the event this position carried before the round
                 if (!J.first_round && J.ins_res[p] != 0) nf &= ~(uint32_t)CAFE_F_GOT;
-                b.val[hit] = 0; b.t[hit] = 0; b.cnt[hit] = 0.0f; b.dic[hit] = 0;
+                set(hit, 0u, 0.0f, 0, 0);   // the slot is cleared whether or not the promotion succeeded
             } else {
+                set(hit, x, cn, dic0, tp);
                 emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
             }
         } else {
             if (vic < 0) { CAFE_ATOMIC_OR(&J.res->error, 2); vic = 0; }
-            if (b.dic[vic] != 0 || b.cnt[vic] >= 5.0f) {
+            uint32_t vval = 0;
+            float vcnt = 0.f;
+            int32_t vdic = 0;
+#pragma unroll
+            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == vic) { vval = b.val[q]; vcnt = b.cnt[q]; vdic = b.dic[q]; }
+            if (vdic != 0 || vcnt >= 5.0f) {
                 ++n_ev;
-                emit(J, p, CAFE_EV_VICTIM, b.val[vic], b.cnt[vic], b.dic[vic]);
+                emit(J, p, CAFE_EV_VICTIM, vval, vcnt, vdic);
             } else {
                 emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
             }
-            b.val[vic] = x;
-            b.t[vic] = tp;
-            b.cnt[vic] = 1.0f;
-            b.dic[vic] = 0;
+            int32_t ndic = 0;
             if (1.0f >= J.thr && 1.0f - c < J.thr) nf |= CAFE_F_CROSS;
             if (1.0f >= J.thr) {
                 cand = true;
                 nf |= CAFE_F_POP1;   // candidate pop at op slot 2p+1 (after the victim's possible push-back at 2p)
                 int32_t id;
-                if (cafe_would_pop(J, 2 * (int64_t)p + 1, &id)) { b.dic[vic] = id; nf |= CAFE_F_GOT; }
+                if (cafe_would_pop(J, 2 * (int64_t)p + 1, &id)) { ndic = id; nf |= CAFE_F_GOT; }
             }
+            set(vic, x, 1.0f, ndic, tp);
         }
         J.lflag[p] = (uint8_t)nf;
     }

@@ -88,6 +88,10 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         live = R.init(J, k, i);
         if (live) iend = J.start1[k + 1];
     }
+    if (J.diag) {   // timing experiments: leave out classes of buckets
+        const int len = iend - i;
+        if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > CAFE_LONG && len <= 512) || ((J.diag & 4) && len <= CAFE_LONG)) iend = i;
+    }
     const bool is_long = live && (iend - i > CAFE_LONG);
     if (live && !is_long) {
         for (; i < iend; ++i) {
@@ -96,20 +100,35 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
             R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p), cafe_old_mflag(J, p));
         }
     }
+    int slow = 0;
     unsigned m = __ballot_sync(CAFE_FULL, is_long);
     while (m) {
         const int o = __ffs(m) - 1;
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, i, o), e = __shfl_sync(CAFE_FULL, iend, o);
         bool stop = false;
+        // two-deep software pipeline: positions of chunk n+2 and the per-lookup data of chunk n+1 are
+        // requested before chunk n is processed, so a long bucket pays one load latency, not one per chunk
+        int p_nx = (s + lane < e) ? J.ord1[s + lane] : INT32_MAX;
+        int p_n2 = (s + 32 + lane < e) ? J.ord1[s + 32 + lane] : INT32_MAX;
+        uint32_t x_nx = 0, ok_nx = CAFE_EV_NONE, of_nx = 0;
+        float c_nx = 1.0f;
+        bool av_nx = false;
+        if (p_nx < J.limit) {
+            x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx);
+            av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
+        }
         for (int base = s; base < e && !stop; base += 32) {
-            const int idx = base + lane;
-            int p = INT32_MAX;
-            uint32_t x = 0, ok = CAFE_EV_NONE, of = 0;
-            float c = 1.0f;
-            if (idx < e) {
-                p = J.ord1[idx];
-                if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); of = cafe_old_mflag(J, p); }
+            const int p = p_nx;
+            const uint32_t x = x_nx, ok = ok_nx, of = of_nx;
+            const float c = c_nx;
+            const bool av = av_nx;
+            p_nx = p_n2;
+            p_n2 = (base + 64 + lane < e) ? J.ord1[base + 64 + lane] : INT32_MAX;
+            x_nx = 0; ok_nx = CAFE_EV_NONE; of_nx = 0; c_nx = 1.0f; av_nx = false;
+            if (p_nx < J.limit) {
+                x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx);
+                av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
             }
             const int n = min(32, e - base);
             int j = 0;
@@ -139,7 +158,6 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 slot = __shfl_sync(CAFE_FULL, slot, o);
                 int run = 0;
                 bool advanced = false;
-                unsigned avail_mask = 0;
                 if (slot >= 0) {
                     bound = __shfl_sync(CAFE_FULL, bound, o);
                     has_row = __shfl_sync(CAFE_FULL, has_row, o);
@@ -147,54 +165,42 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                     const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
                     if (run < 0) run = 32 - j;    // all remaining lanes qualify
-                    if (!has_row && run >= 2) {
-                        // belief about the FIFO at each lookup's pop slot (2p): non-empty?
-                        bool av = false;
-                        if (mine) av = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p] > 0);
-                        avail_mask = __ballot_sync(CAFE_FULL, av);
-                    }
                 }
                 if (run >= 2) {
+                    // counts are added strictly in lookup order by one chain of float adds; every lane
+                    // keeps the running count as of its own lookup
                     float acc = __shfl_sync(CAFE_FULL, cnt0, o);
-                    uint32_t my_flag = 0;
-                    int done = 0;
-                    bool any_cand = false;
-                    for (int t0 = 0; t0 < run && done == t0; t0 += 8) {
-                        float cs[8];
+                    float my_acc = 0.f;
 #pragma unroll
-                        for (int u = 0; u < 8; ++u) cs[u] = __shfl_sync(CAFE_FULL, c, min(j + t0 + u, 31));
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            if (t0 + u < run && done == t0 + u) {
-                                const float nx = acc + cs[u];
-                                const bool cd = !has_row && nx >= J.thr;                 // pop candidate (sketch.cpp:221)
-                                if (!(cd && ((avail_mask >> (j + t0 + u)) & 1u))) {      // ... that cannot succeed
-                                    const bool cr = (nx >= J.thr && nx - cs[u] < J.thr);   // sketch.cpp:218
-                                    if (lane == j + t0 + u) my_flag = (cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0);
-                                    any_cand |= cd;
-                                    acc = nx;
-                                    ++done;
-                                }
-                            }
-                        }
+                    for (int u = 0; u < 32; ++u) {
+                        const float cu = __shfl_sync(CAFE_FULL, c, u);
+                        if (u >= j && u < j + run) acc = acc + cu;
+                        if (lane == u) my_acc = acc;
                     }
-                    run = done;
-                    if (run > 0) {
+                    const bool in_run = lane >= j && lane < j + run;
+                    const bool cd = !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
+                    const unsigned blocked = __ballot_sync(CAFE_FULL, in_run && cd && av);   // ... that could succeed
+                    const int done = blocked ? (__ffs(blocked) - 1 - j) : run;
+                    if (done > 0) {
+                        const bool in_done = lane >= j && lane < j + done;
+                        const float acc_end = __shfl_sync(CAFE_FULL, my_acc, j + done - 1);
+                        const unsigned any_cand = __ballot_sync(CAFE_FULL, in_done && cd);
                         if (lane == o) {
 #pragma unroll
-                            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc;
-                            R.i_cur += run;
+                            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc_end;
+                            R.i_cur += done;
                             if (any_cand) R.cand = true;
                         }
-                        if (!J.final_pass && lane >= j && lane < j + run) {
-                            J.mflag[p] = (uint8_t)my_flag;
+                        if (!J.final_pass && in_done) {
+                            const bool cr = (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
+                            J.mflag[p] = (uint8_t)((cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0));
                             if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
                             else {
                                 if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
                                 if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                             }
                         }
-                        j += run;
+                        j += done;
                         advanced = true;
                     }
                 }
@@ -202,12 +208,13 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                     const float cj = __shfl_sync(CAFE_FULL, c, j);
                     const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
                     const uint32_t fj = __shfl_sync(CAFE_FULL, of, j);
-                    if (lane == o) R.feed(J, pj, xj, cj, kj, fj);
+                    if (lane == o) { R.feed(J, pj, xj, cj, kj, fj); ++slow; }
                     ++j;
                 }
             }
         }
     }
+    if (is_long) { atomicAdd(&J.res->n_active_main, 1); atomicMax(&J.res->max_slow_main, slow); }
     if (live) R.finish(J);
 }
 __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J) {
@@ -220,6 +227,7 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         live = R.init(J, k);
         if (live) { jb = J.start2[k]; jend = J.start2[k + 1]; }
     }
+    int slow = 0;
     const bool is_long = live && (jend - jb > CAFE_LONG);
     if (live && !is_long) {
         for (int j = jb; j < jend; ++j) {
@@ -235,16 +243,23 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, jb, o), e = __shfl_sync(CAFE_FULL, jend, o);
         bool stop = false;
+        // same two-deep pipeline as in the main pass
+        int p_nx = (s + lane < e) ? J.ord2[s + lane] : INT32_MAX;
+        int p_n2 = (s + 32 + lane < e) ? J.ord2[s + 32 + lane] : INT32_MAX;
+        uint32_t x_nx = 0;
+        float c_nx = 1.0f;
+        bool miss_nx = false;
+        if (p_nx < J.limit && (J.mflag[p_nx] & CAFE_F_MISS)) { miss_nx = true; x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); }
         for (int base = s; base < e && !stop; base += 32) {
             const int idx = base + lane;
-            int p = INT32_MAX;
-            uint32_t x = 0;
-            float c = 1.0f;
-            bool miss = false;
-            if (idx < e) {
-                p = J.ord2[idx];
-                if (p < J.limit && (J.mflag[p] & CAFE_F_MISS)) { miss = true; x = J.gid[p]; c = cafe_count_of(J, p); }
-            }
+            const int p = p_nx;
+            const uint32_t x = x_nx;
+            const float c = c_nx;
+            const bool miss = miss_nx;
+            p_nx = p_n2;
+            p_n2 = (base + 64 + lane < e) ? J.ord2[base + 64 + lane] : INT32_MAX;
+            x_nx = 0; c_nx = 1.0f; miss_nx = false;
+            if (p_nx < J.limit && (J.mflag[p_nx] & CAFE_F_MISS)) { miss_nx = true; x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); }
             // positions ascend inside a bucket: once one lane sees the limit, later chunks are beyond it too
             stop = __any_sync(CAFE_FULL, idx < e && p >= J.limit);
             unsigned mm = __ballot_sync(CAFE_FULL, miss);
@@ -254,10 +269,11 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
                 const int pj = __shfl_sync(CAFE_FULL, p, j);
                 const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
                 const float cj = __shfl_sync(CAFE_FULL, c, j);
-                if (lane == o) R.feed(J, pj, xj, cj);
+                if (lane == o) { R.feed(J, pj, xj, cj); ++slow; }
             }
         }
     }
+    if (is_long) { atomicAdd(&J.res->n_active_lru, 1); atomicMax(&J.res->max_feed_lru, slow); }
     if (live) R.finish(J);
 }
 __global__ void k_route(const __grid_constant__ CafeJob J) {
@@ -505,7 +521,7 @@ struct CudaBackend {
         check_launch();
     }
     void main_pass(const CafeJob& J) {
-        CAFE_PROF(CAFE_P_MAIN, stream);
+        CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
         k_main_pass<<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J);
         check_launch();
     }
@@ -526,7 +542,7 @@ struct CudaBackend {
         check_launch();
     }
     void lru_pass(const CafeJob& J) {
-        CAFE_PROF(CAFE_P_LRU, stream);
+        CAFE_PROF_DYN(J.all_active ? CAFE_P_LRU : CAFE_P_LRU_LATER, stream);
         k_lru_pass<<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J);
         check_launch();
     }

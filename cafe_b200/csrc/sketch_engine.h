@@ -11,6 +11,8 @@
 // (tricks/sketch.cpp:266-275, 281-291), reset (:76-116), init (:309-313).
 #pragma once
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -37,6 +39,7 @@ public:
     int q_size = 0;
     uint32_t ring_mask = 0;
     int round_cap = 48;
+    bool diag = getenv("CAFE_B200_DIAG") != nullptr;   // print per-round diagnostics to stderr
     double cross_rate = -1.0;         // threshold crossings per lookup seen in recent jobs (-1: unknown)
     int window = CAFE_MAX_SEGMENTS;   // upper bound on the segments fused into one job
     int last_status = CAFE_OK;
@@ -329,6 +332,7 @@ private:
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
+        J.diag = getenv("CAFE_B200_EXPERIMENT") ? atoi(getenv("CAFE_B200_EXPERIMENT")) : 0;
         ++stats.jobs;
         be.memset(ins_res, 0, 4 * (size_t)M);
 
@@ -363,6 +367,7 @@ private:
             ++rounds; ++stats.rounds;
             first = false;
             pb ^= 1;
+            if (diag) fprintf(stderr, "round %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
             // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
             // per-segment deltas of a round that has not converged yet are estimates, but shrinking
