@@ -213,15 +213,18 @@ struct CafeJob {
     // the lookups
     const uint32_t* gid;     // [M] global ids
     const float* imp;        // [M] counts, or null for unit counts
-    int32_t M;
-    int32_t limit;           // positions >= limit are left out (commit of a prefix)
+    int32_t M;               // capacity of the per-lookup arrays (all lookups of the call)
+    int32_t begin;           // the job covers positions [begin, limit); earlier ones were committed by earlier jobs
+    int32_t limit;
     int32_t nseg;
     int32_t seg_off[CAFE_MAX_SEGMENTS + 1];
     // positions ordered by (main bucket, position) and by (LRU bucket, position); bucket ranges
     const int32_t* ord1;
-    const int32_t* start1;   // [n1+1]
+    const int32_t* start1;   // [n1+1] bucket ranges in ord1 (whole call)
+    const int32_t* beg1;     // [n1]   first entry of each bucket that is >= begin
     const int32_t* ord2;
     const int32_t* start2;   // [n2+1]
+    const int32_t* beg2;     // [n2]
     // batch-start state (read) and the image the rounds write
     const CafeMainBucket* main_in;
     CafeMainBucket* main_out;
@@ -453,7 +456,7 @@ struct CafeMainReplay {
 CAFE_HD void cafe_main_pass_bucket(const CafeJob& J, int k) {
     CafeMainReplay R;
     const int iend = J.start1[k + 1];
-    int i = J.start1[k];
+    int i = J.beg1[k];
     if (!R.init(J, k, i)) return;
     for (; i < iend; ++i) {
         const int p = J.ord1[i];
@@ -578,7 +581,7 @@ CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
     CafeLruReplay R;
     if (!R.init(J, k)) return;
     const int jend = J.start2[k + 1];
-    for (int j = J.start2[k]; j < jend; ++j) {
+    for (int j = J.beg2[k]; j < jend; ++j) {
         const int p = J.ord2[j];
         if (p >= J.limit) break;
         if (!(J.mflag[p] & CAFE_F_MISS)) continue;
@@ -587,6 +590,14 @@ CAFE_HD void cafe_lru_pass_bucket(const CafeJob& J, int k) {
     R.finish(J);
 }
 
+// at commit: first entry of a bucket's sorted lookups that lies at or beyond `limit` (positions ascend)
+CAFE_HD int32_t cafe_advance_cursor(const int32_t* ord, int32_t lo, int32_t hi, int32_t limit) {
+    while (lo < hi) {
+        const int32_t mid = (lo + hi) >> 1;
+        if (ord[mid] < limit) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
 // at commit: LRU clock values written as t0 + 1 + position become t0 + (rank of the visit)
 CAFE_HD void cafe_lru_tconvert(const CafeJob& J, int k) {
     CafeLruBucket& b = J.lru_out[k];
@@ -648,7 +659,7 @@ CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) {
 // 3b (after the inclusive scan of (op_a, op_b) under cafe_compose): outcome counts of position p
 CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
+    int32_t s = (p == J.begin) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
     int64_t pops = 0, pushes = 0;
     if (o.op0 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op0 == 2) { ++pushes; ++s; }
     if (o.op1 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op1 == 2) { ++pushes; ++s; }
@@ -657,7 +668,7 @@ CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
 // 3c (after the exclusive prefix sum of op_cnt): write the timeline, compare with the consumed one
 CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == 0) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
+    int32_t s = (p == J.begin) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
     const int64_t pre = J.op_cnt[p];
     int32_t rank = (int32_t)(pre & 0xffffffffLL);
     int32_t npush = (int32_t)(pre >> 32);

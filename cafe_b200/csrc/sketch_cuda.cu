@@ -77,14 +77,46 @@ __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb
 // strictly sequential per bucket; only the loads are shared out.
 #define CAFE_LONG 16
 #define CAFE_FULL 0xffffffffu
-__global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J) {
+// Very long buckets (the head of the Zipf law) are the serial tail of a pass.  They are listed when
+// the lookups are sorted, and the first blocks of the grid take one listed bucket per warp, so that
+// the tail starts at once and overlaps with everything else; the other blocks skip listed buckets.
+#define CAFE_HOT_LEN 256      // a bucket with more lookups than this is listed
+#define CAFE_HOT_CAP 512      // at most this many are listed (the rest stay in the normal path)
+#define CAFE_HOT_BLOCKS (CAFE_HOT_CAP / 4)
+struct CafeHot {
+    const int32_t* list;
+    const int32_t* count;
+    const uint8_t* flag;
+};
+__device__ __forceinline__ int cafe_bucket_of_thread(const CafeHot& H, int nb, bool* hot_warp) {
+    if (blockIdx.x < CAFE_HOT_BLOCKS) {
+        *hot_warp = true;
+        const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
+        const int n = min(*H.count, CAFE_HOT_CAP);
+        return ((threadIdx.x & 31) == 0 && w < n) ? H.list[w] : nb;   // lane 0 owns the listed bucket
+    }
+    *hot_warp = false;
+    const int k = (blockIdx.x - CAFE_HOT_BLOCKS) * blockDim.x + threadIdx.x;
+    return (k < nb && !H.flag[k]) ? k : nb;
+}
+__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int32_t* list, int32_t* count, uint8_t* flag) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= nb) return;
+    if (start[k + 1] - start[k] > CAFE_HOT_LEN) {
+        const int idx = atomicAdd(count, 1);
+        if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; }
+    }
+}
+
+__global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
     const int lane = threadIdx.x & 31;
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    bool hot_warp;
+    const int k = cafe_bucket_of_thread(H, J.n1, &hot_warp);
     CafeMainReplay R;
     int i = 0, iend = 0;
     bool live = k < J.n1;
     if (live) {
-        i = J.start1[k];
+        i = J.beg1[k];
         live = R.init(J, k, i);
         if (live) iend = J.start1[k + 1];
     }
@@ -92,7 +124,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         const int len = iend - i;
         if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > CAFE_LONG && len <= 512) || ((J.diag & 4) && len <= CAFE_LONG)) iend = i;
     }
-    const bool is_long = live && (iend - i > CAFE_LONG);
+    const bool is_long = live && (hot_warp || iend - i > CAFE_LONG);
     if (live && !is_long) {
         for (; i < iend; ++i) {
             const int p = J.ord1[i];
@@ -217,18 +249,19 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
     if (is_long) { atomicAdd(&J.res->n_active_main, 1); atomicMax(&J.res->max_slow_main, slow); }
     if (live) R.finish(J);
 }
-__global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J) {
+__global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
     const int lane = threadIdx.x & 31;
-    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    bool hot_warp;
+    const int k = cafe_bucket_of_thread(H, J.n2, &hot_warp);
     CafeLruReplay R;
     int jb = 0, jend = 0;
     bool live = k < J.n2;
     if (live) {
         live = R.init(J, k);
-        if (live) { jb = J.start2[k]; jend = J.start2[k + 1]; }
+        if (live) { jb = J.beg2[k]; jend = J.start2[k + 1]; }
     }
     int slow = 0;
-    const bool is_long = live && (jend - jb > CAFE_LONG);
+    const bool is_long = live && (hot_warp || jend - jb > CAFE_LONG);
     if (live && !is_long) {
         for (int j = jb; j < jend; ++j) {
             const int p = J.ord2[j];
@@ -277,11 +310,11 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
     if (live) R.finish(J);
 }
 __global__ void k_route(const __grid_constant__ CafeJob J) {
-    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_route_position(J, p);
 }
 __global__ void k_finalize_positions(const __grid_constant__ CafeJob J) {
-    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_finalize_position(J, p);
 }
 __global__ void k_lru_tconvert(const __grid_constant__ CafeJob J) {
@@ -292,8 +325,8 @@ __global__ void k_lru_tconvert(const __grid_constant__ CafeJob J) {
 // block and counter (a block of consecutive positions lies in one segment except at boundaries)
 __global__ void __launch_bounds__(CAFE_TPB) k_position_counts(const __grid_constant__ CafeJob J) {
     __shared__ int s_cross, s_miss;
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    const int first = blockIdx.x * blockDim.x;
+    const int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
+    const int first = J.begin + blockIdx.x * blockDim.x;
     const int last = min(first + (int)blockDim.x, J.limit) - 1;
     if (threadIdx.x == 0) { s_cross = 0; s_miss = 0; }
     __syncthreads();
@@ -313,15 +346,15 @@ __global__ void __launch_bounds__(CAFE_TPB) k_position_counts(const __grid_const
     }
 }
 __global__ void k_resolve_ops(const __grid_constant__ CafeJob J) {
-    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_resolve_ops(J, p);
 }
 __global__ void k_resolve_count(const __grid_constant__ CafeJob J) {
-    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_resolve_count(J, p);
 }
 __global__ void k_resolve_write(const __grid_constant__ CafeJob J) {
-    int p = blockIdx.x * blockDim.x + threadIdx.x;
+    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_resolve_write(J, p);
 }
 __global__ void k_commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
@@ -349,6 +382,12 @@ struct FnCompose {
         return r;
     }
 };
+
+__global__ void k_advance_cursors(const int32_t* __restrict__ ord, const int32_t* __restrict__ start, int32_t* beg, int nb,
+                                  int limit) {
+    int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k < nb) beg[k] = cafe_advance_cursor(ord, beg[k], start[k + 1], limit);
+}
 
 // threshold re-fit, step 1: lazy decay of every bucket and number of candidates per bucket
 __global__ void k_reset_count(CafeMainBucket* mb, CafeLruBucket* lb, int n1, int n2, uint32_t gflip, float thr,
@@ -437,6 +476,10 @@ struct CudaBackend {
     uint32_t *key_in = nullptr, *key_out = nullptr;
     int32_t* pos_in = nullptr;
     int64_t* scan64 = nullptr;   // [4*(n1+n2)] prefix sums of the threshold re-fit
+    int32_t* hot_list[2] = {nullptr, nullptr};   // listed long buckets of the main / LRU table
+    int32_t* hot_count[2] = {nullptr, nullptr};
+    uint8_t* hot_flag[2] = {nullptr, nullptr};
+    int hot_nb[2] = {0, 0};
     int cap = 0;
     void* pinned = nullptr;   // staging for small device-to-host reads
 
@@ -446,6 +489,7 @@ struct CudaBackend {
         if (key_out) cudaFree(key_out);
         if (pos_in) cudaFree(pos_in);
         if (scan64) cudaFree(scan64);
+        for (int i = 0; i < 2; ++i) { if (hot_list[i]) cudaFree(hot_list[i]); if (hot_count[i]) cudaFree(hot_count[i]); if (hot_flag[i]) cudaFree(hot_flag[i]); }
         if (pinned) cudaFreeHost(pinned);
     }
     void check(cudaError_t e) { if (e != cudaSuccess && err == cudaSuccess) err = e; }
@@ -457,6 +501,12 @@ struct CudaBackend {
     void memset(void* p, int v, size_t n) { if (n) { CAFE_PROF(CAFE_P_MEMSET, stream); check(cudaMemsetAsync(p, v, n, stream)); } }
     void fill_iota(uint32_t* p, int n, uint32_t first) {
         if (n > 0) { k_fill_iota<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(p, n, first); check_launch(); }
+    }
+    void copy(void* d, const void* s, size_t n) { if (n) check(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, stream)); }
+    void advance_cursors(const int32_t* ord, const int32_t* start, int32_t* beg, int nb, int limit) {
+        CAFE_PROF(CAFE_P_COMMIT, stream);
+        k_advance_cursors<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(ord, start, beg, nb, limit);
+        check_launch();
     }
     void h2d(void* d, const void* s, size_t n) {
         check(cudaMemcpyAsync(d, s, n, cudaMemcpyHostToDevice, stream));
@@ -479,6 +529,14 @@ struct CudaBackend {
         check(cudaMalloc(&key_out, 4 * (size_t)cap));
         check(cudaMalloc(&pos_in, 4 * (size_t)cap));
         check(cudaMallocHost(&pinned, 4096));
+        hot_nb[0] = n1; hot_nb[1] = n2;
+        for (int i = 0; i < 2; ++i) {
+            check(cudaMalloc(&hot_list[i], 4 * CAFE_HOT_CAP));
+            check(cudaMalloc(&hot_count[i], 4));
+            check(cudaMalloc(&hot_flag[i], (size_t)hot_nb[i]));
+            check(cudaMemsetAsync(hot_count[i], 0, 4, stream));
+            check(cudaMemsetAsync(hot_flag[i], 0, (size_t)hot_nb[i], stream));
+        }
         // largest temporary any CUB call below can ask for
         size_t need = 0, b = 0;
         const int ncand = (n1 + n2) * CAFE_SLOTS;
@@ -519,44 +577,52 @@ struct CudaBackend {
         check(cub::DeviceRadixSort::SortPairs(cub_tmp, b, key_in, key_out, pos_in, ord, M, 0, bits_for(nb), stream));
         k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, stream>>>(key_out, M, nb, start);
         check_launch();
+        const int t = (nb == hot_nb[0]) ? 0 : 1;
+        check(cudaMemsetAsync(hot_count[t], 0, 4, stream));
+        check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, stream));
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(start, nb, hot_list[t], hot_count[t], hot_flag[t]);
+        check_launch();
     }
+    CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
     void main_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
-        k_main_pass<<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J);
+        k_main_pass<<<CAFE_HOT_BLOCKS + cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
         check_launch();
     }
     void route(const CafeJob& J) {
         CAFE_PROF(CAFE_P_SCAN, stream);
-        k_route<<<cafe_blocks(J.limit), CAFE_TPB, 0, stream>>>(J);
+        k_route<<<cafe_blocks(J.limit - J.begin), CAFE_TPB, 0, stream>>>(J);
         check_launch();
     }
     // per-lookup results and the LRU clock numbering, once the rounds have converged
     void finalize(const CafeJob& J) {
         CAFE_PROF(CAFE_P_COMMIT, stream);
-        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.mflag, MissFlag());
+        const int cnt = J.limit - J.begin;
+        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.mflag + J.begin, MissFlag());
         size_t b = cub_bytes;
-        check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp, J.limit, stream));
-        k_finalize_positions<<<cafe_blocks(J.limit), CAFE_TPB, 0, stream>>>(J);
+        check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp + J.begin, cnt, stream));
+        k_finalize_positions<<<cafe_blocks(cnt), CAFE_TPB, 0, stream>>>(J);
         check_launch();
         k_lru_tconvert<<<cafe_blocks(J.n2), CAFE_TPB, 0, stream>>>(J);
         check_launch();
     }
     void lru_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.all_active ? CAFE_P_LRU : CAFE_P_LRU_LATER, stream);
-        k_lru_pass<<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J);
+        k_lru_pass<<<CAFE_HOT_BLOCKS + cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
         check_launch();
     }
     void resolve(const CafeJob& J) {
         CAFE_PROF(CAFE_P_RESOLVE, stream);
-        const int g = cafe_blocks(J.limit);
+        const int cnt = J.limit - J.begin;
+        const int g = cafe_blocks(cnt);
         k_resolve_ops<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
         size_t b = cub_bytes;
-        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, J.op_fn, J.op_fn, FnCompose(), J.limit, stream));
+        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, J.op_fn + J.begin, J.op_fn + J.begin, FnCompose(), cnt, stream));
         k_resolve_count<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
         b = cub_bytes;
-        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, J.op_cnt, J.op_cnt, J.limit, stream));
+        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, J.op_cnt + J.begin, J.op_cnt + J.begin, cnt, stream));
         k_resolve_write<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
         k_position_counts<<<g, CAFE_TPB, 0, stream>>>(J);

@@ -78,6 +78,7 @@ public:
         size_t M = (size_t)cap;
         ord1 = (int32_t*)be.alloc(4 * M); ord2 = (int32_t*)be.alloc(4 * M);
         start1 = (int32_t*)be.alloc(4 * ((size_t)n1 + 1)); start2 = (int32_t*)be.alloc(4 * ((size_t)n2 + 1));
+        beg1 = (int32_t*)be.alloc(4 * (size_t)n1); beg2 = (int32_t*)be.alloc(4 * (size_t)n2);
         ev = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
         head = (int32_t*)be.alloc(4 * (size_t)n1);
         nxt = (int32_t*)be.alloc(4 * M);
@@ -101,7 +102,7 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn || !op_cnt ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn || !op_cnt ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
         for (int i = 0; i < 2; ++i)
@@ -138,43 +139,65 @@ public:
         last_status = CAFE_OK;
         int s = 0;
         while (s < nseg) {
-            call_boundary();
-            if (last_status == CAFE_ERR_CUDA) return last_status;
-            int e = s + 1;
-            if (parallel) {
-                // fuse following calls while their boundaries are known to be uneventful: the decay
-                // clock is deterministic, the re-fit condition is checked after the fact
-                double d = decay_importance;
-                const int maxe = std::min(nseg, s + std::max(1, std::min(window, (int)CAFE_MAX_SEGMENTS)));
-                while (e < maxe && (int64_t)seg_off[e + 1] - seg_off[s] <= cap) {
-                    double d2 = d * alpha;
-                    if (d2 > CAFE_DECAY_BASE) break;
-                    // stop where a threshold re-fit is expected (the exact test runs on the results)
-                    if (adjust && cross_rate >= 0 &&
-                        real_n + cross_rate * ((double)seg_off[e] - seg_off[s]) > lim * 1.2) break;
-                    d = d2; ++e;
-                }
-            }
+            // a stretch of calls whose lookups fit the workspace is sorted by bucket once
+            int se = s;
+            while (se < nseg && seg_off[se + 1] - seg_off[s] <= cap) ++se;
+            if (se == s) return CAFE_ERR_CAPACITY;
             const int base = seg_off[s];
-            if (seg_off[e] - base > cap) return CAFE_ERR_CAPACITY;
-            int done_e = e;
-            if (seg_off[e] - base > 0) {
-                if (parallel) {
-                    int rc = run_parallel(gid + base, imp ? imp + base : nullptr, seg_off + s, e - s, mask + base,
-                                          post_row ? post_row + base : nullptr, &done_e);
-                    if (rc != CAFE_OK) return rc;
-                    done_e += s;
-                } else {
-                    int rc = run_sequential(gid + base, imp ? imp + base : nullptr, seg_off[e] - base, mask + base,
-                                            post_row ? post_row + base : nullptr);
-                    if (rc != CAFE_OK) return rc;
-                }
+            const int mtot = seg_off[se] - base;
+            const uint32_t* g = gid ? gid + base : nullptr;
+            const float* im = imp ? imp + base : nullptr;
+            int32_t* mk = mask ? mask + base : nullptr;
+            int32_t* pr = post_row ? post_row + base : nullptr;
+            if (parallel && mtot > 0) {
+                be.sort_lookups(g, mtot, n1, ord1, start1);
+                be.sort_lookups(g, mtot, n2, ord2, start2);
+                be.copy(beg1, start1, 4 * (size_t)n1);
+                be.copy(beg2, start2, 4 * (size_t)n2);
             }
-            // boundaries inside the fused range: nothing happens at them except the clocks
-            for (int b = s + 1; b < done_e; ++b) { ++batch_num; decay_importance *= alpha; ++stats.calls; }
-            s = done_e;
+            while (s < se) {
+                call_boundary();
+                if (last_status == CAFE_ERR_CUDA) return last_status;
+                int e = s + 1;
+                if (parallel) {
+                    // fuse following calls while their boundaries are known to be uneventful: the decay
+                    // clock is deterministic, the re-fit condition is checked after the fact
+                    double d = decay_importance;
+                    const int maxe = std::min(se, s + std::max(1, std::min(window, (int)CAFE_MAX_SEGMENTS)));
+                    while (e < maxe) {
+                        double d2 = d * alpha;
+                        if (d2 > CAFE_DECAY_BASE) break;
+                        // stop where a threshold re-fit is expected (the exact test runs on the results)
+                        if (adjust && cross_rate >= 0 &&
+                            real_n + cross_rate * ((double)seg_off[e] - seg_off[s]) > lim * 1.2) break;
+                        d = d2; ++e;
+                    }
+                }
+                int done_e = e;
+                const int lo = seg_off[s] - base, hi = seg_off[e] - base;
+                if (hi > lo) {
+                    if (parallel) {
+                        int rel[CAFE_MAX_SEGMENTS + 1];
+                        for (int i = 0; i <= e - s; ++i) rel[i] = seg_off[s + i] - base;
+                        int done = 0;
+                        int rc = run_parallel(g, im, mtot, rel, e - s, mk, pr, &done);
+                        if (rc != CAFE_OK) return rc;
+                        done_e = s + done;
+                        const int upto = seg_off[done_e] - base;
+                        be.advance_cursors(ord1, start1, beg1, n1, upto);
+                        be.advance_cursors(ord2, start2, beg2, n2, upto);
+                    } else {
+                        int rc = run_sequential(g + lo, im ? im + lo : nullptr, hi - lo, mk + lo, pr ? pr + lo : nullptr);
+                        if (rc != CAFE_OK) return rc;
+                    }
+                }
+                // boundaries inside the fused range: nothing happens at them except the clocks
+                for (int b = s + 1; b < done_e; ++b) { ++batch_num; decay_importance *= alpha; ++stats.calls; }
+                s = done_e;
+            }
         }
         stats.lookups += total;
+        if (!be.ok()) return last_status = CAFE_ERR_CUDA;
         return last_status;
     }
 
@@ -251,7 +274,7 @@ private:
     CafeMainBucket* mainb[2] = {nullptr, nullptr};
     CafeLruBucket* lrub[2] = {nullptr, nullptr};
     uint32_t* ring = nullptr;
-    int32_t *ord1 = nullptr, *ord2 = nullptr, *start1 = nullptr, *start2 = nullptr;
+    int32_t *ord1 = nullptr, *ord2 = nullptr, *start1 = nullptr, *start2 = nullptr, *beg1 = nullptr, *beg2 = nullptr;
     CafeEvent* ev = nullptr;
     int32_t* head = nullptr;
     int32_t* nxt = nullptr;
@@ -271,7 +294,7 @@ private:
 
     void release() {
         if (!ready && !mainb[0]) return;
-        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, ev, head, nxt, mark_own, mstate, mark2, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, mark2, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
                         tstamp, ins_res, op_fn, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
@@ -309,20 +332,18 @@ private:
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
     }
 
-    // Parallel rounds over segments seg[0..nseg] (offsets relative to seg[0]).  On return *done =
-    // number of leading segments committed (fewer than nseg when a threshold re-fit is due at an
-    // inner boundary).
-    int run_parallel(const uint32_t* gid, const float* imp, const int* seg, int nseg, int32_t* mask, int32_t* post_row,
-                     int* done) {
-        const int M = seg[nseg] - seg[0];
+    // Parallel rounds over the segments seg[0..nseg] (positions relative to the sorted stretch of M
+    // lookups that gid/imp/mask/post_row point to).  On return *done = number of leading segments
+    // committed (fewer than nseg when a threshold re-fit is due at an inner boundary).
+    int run_parallel(const uint32_t* gid, const float* imp, int M, const int* seg, int nseg, int32_t* mask,
+                     int32_t* post_row, int* done) {
         CafeJob J;
         memset(&J, 0, sizeof(J));
-        J.gid = gid; J.imp = imp; J.M = M; J.limit = M; J.nseg = nseg;
-        for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i] - seg[0];
+        const int planned = nseg;
+        J.gid = gid; J.imp = imp; J.M = M; J.begin = seg[0]; J.limit = seg[nseg]; J.nseg = nseg;
+        for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i];
         for (int i = nseg + 1; i <= CAFE_MAX_SEGMENTS; ++i) J.seg_off[i] = INT32_MAX;
-        be.sort_lookups(gid, M, n1, ord1, start1);
-        be.sort_lookups(gid, M, n2, ord2, start2);
-        J.ord1 = ord1; J.start1 = start1; J.ord2 = ord2; J.start2 = start2;
+        J.ord1 = ord1; J.start1 = start1; J.beg1 = beg1; J.ord2 = ord2; J.start2 = start2; J.beg2 = beg2;
         J.n1 = n1; J.n2 = n2; J.thr = thr; J.gflip = gflip; J.t0 = t;
         J.ring = ring; J.ring_mask = ring_mask; J.q_head = q_head; J.q_size = q_size;
         J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
@@ -334,7 +355,7 @@ private:
         J.res = res_dev;
         J.diag = getenv("CAFE_B200_EXPERIMENT") ? atoi(getenv("CAFE_B200_EXPERIMENT")) : 0;
         ++stats.jobs;
-        be.memset(ins_res, 0, 4 * (size_t)M);
+        be.memset(ins_res + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
 
         CafeRoundResult R;
         int rounds = 0;
@@ -347,7 +368,8 @@ private:
                 ++stats.seq_fallbacks;
                 last_status = CAFE_ERR_NOCONVERGE;
                 *done = 1;
-                int rc = run_sequential(gid, imp, J.seg_off[1], mask, post_row);
+                const int b0 = J.begin, n0 = J.seg_off[1] - J.begin;
+                int rc = run_sequential(gid + b0, imp ? imp + b0 : nullptr, n0, mask + b0, post_row ? post_row + b0 : nullptr);
                 return rc == CAFE_OK ? CAFE_OK : rc;
             }
             J.first_round = first ? 1 : 0;
@@ -367,7 +389,7 @@ private:
             ++rounds; ++stats.rounds;
             first = false;
             pb ^= 1;
-            if (diag) fprintf(stderr, "round %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
+            if (diag) fprintf(stderr, "round %d begin %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.begin, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
             // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
             // per-segment deltas of a round that has not converged yet are estimates, but shrinking
@@ -387,7 +409,7 @@ private:
                     if (!truncated) ++stats.truncated_jobs;
                     truncated = true;
                     shortened = true;   // bucket images written so far include lookups beyond the new end
-                    if (J.limit == 0) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
+                    if (J.limit == J.begin) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
                     continue;
                 }
             }
@@ -398,7 +420,7 @@ private:
         J.first_round = 0; J.all_active = 0;
         J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
         if (post_row) {
-            be.memset(post_row, 0, 4 * (size_t)J.limit);
+            be.memset(post_row + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
             route(J);
             J.final_pass = 1;
             be.main_pass(J);
@@ -414,11 +436,16 @@ private:
         int grown = 0;
         for (int b = 0; b < nseg; ++b) grown += R.seg_real_delta[b];
         real_n += grown;
-        if (J.limit > 0) {
-            const double r = (double)grown / J.limit;
+        if (J.limit > J.begin) {
+            const double r = (double)grown / (J.limit - J.begin);
             cross_rate = cross_rate < 0 ? r : 0.5 * cross_rate + 0.5 * r;
         }
-        stats.main_hits += (int64_t)J.limit - R.n_miss; stats.lru_visits += R.n_miss; stats.events += R.n_events;
+        if (diag) {
+            fprintf(stderr, "job real_n0 %d lim %d rate %.4f planned %d done %d deltas", real_n - grown, lim, cross_rate, planned, nseg);
+            for (int b = 0; b < nseg; ++b) fprintf(stderr, " %d", R.seg_real_delta[b]);
+            fprintf(stderr, "\n");
+        }
+        stats.main_hits += (int64_t)(J.limit - J.begin) - R.n_miss; stats.lru_visits += R.n_miss; stats.events += R.n_events;
         if (rounds > stats.max_rounds) stats.max_rounds = rounds;
         *done = nseg;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;

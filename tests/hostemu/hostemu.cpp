@@ -24,6 +24,10 @@ struct HostBackend {
     void memset(void* p, int v, size_t n) { ::memset(p, v, n); }
     void fill_iota(uint32_t* p, int n, uint32_t first) { for (int i = 0; i < n; ++i) p[i] = first + (uint32_t)i; }
     void h2d(void* d, const void* s, size_t n) { memcpy(d, s, n); }
+    void copy(void* d, const void* s, size_t n) { memcpy(d, s, n); }
+    void advance_cursors(const int32_t* ord, const int32_t* start, int32_t* beg, int nb, int limit) {
+        for (int k = 0; k < nb; ++k) beg[k] = cafe_advance_cursor(ord, beg[k], start[k + 1], limit);
+    }
     void d2h(void* d, const void* s, size_t n) { memcpy(d, s, n); }
     bool ok() { return true; }
     bool prepare(int, int, int) { return true; }
@@ -54,13 +58,13 @@ struct HostBackend {
         else for (int k = 0; k < J.n1; ++k) cafe_main_pass_bucket(J, k);
     }
     void route(const CafeJob& J) {
-        for (int p = J.limit - 1; p >= 0; --p) cafe_route_position(J, p);
+        for (int p = J.limit - 1; p >= J.begin; --p) cafe_route_position(J, p);
     }
     // per-lookup results and the LRU clock numbering, once the rounds have converged
     void finalize(const CafeJob& J) {
         int32_t acc = 0;
-        for (int p = 0; p < J.limit; ++p) { acc += (J.mflag[p] & CAFE_F_MISS) ? 1 : 0; J.tstamp[p] = acc; }
-        for (int p = 0; p < J.limit; ++p) cafe_finalize_position(J, p);
+        for (int p = J.begin; p < J.limit; ++p) { acc += (J.mflag[p] & CAFE_F_MISS) ? 1 : 0; J.tstamp[p] = acc; }
+        for (int p = J.begin; p < J.limit; ++p) cafe_finalize_position(J, p);
         for (int k = 0; k < J.n2; ++k) cafe_lru_tconvert(J, k);
     }
     void lru_pass(const CafeJob& J) {
@@ -68,17 +72,17 @@ struct HostBackend {
         else for (int k = 0; k < J.n2; ++k) cafe_lru_pass_bucket(J, k);
     }
     void resolve(const CafeJob& J) {
-        for (int p = 0; p < J.limit; ++p) cafe_resolve_ops(J, p);
-        for (int p = 1; p < J.limit; ++p) {
+        for (int p = J.begin; p < J.limit; ++p) cafe_resolve_ops(J, p);
+        for (int p = J.begin + 1; p < J.limit; ++p) {
             int32_t a, b;
             cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &a, &b);
             J.op_fn[p].a = a; J.op_fn[p].b = b;
         }
-        for (int p = 0; p < J.limit; ++p) cafe_resolve_count(J, p);
+        for (int p = J.begin; p < J.limit; ++p) cafe_resolve_count(J, p);
         int64_t acc = 0;
-        for (int p = 0; p < J.limit; ++p) { int64_t v = J.op_cnt[p]; J.op_cnt[p] = acc; acc += v; }
-        for (int p = J.limit - 1; p >= 0; --p) cafe_resolve_write(J, p);
-        for (int p = 0; p < J.limit; ++p) {
+        for (int p = J.begin; p < J.limit; ++p) { int64_t v = J.op_cnt[p]; J.op_cnt[p] = acc; acc += v; }
+        for (int p = J.limit - 1; p >= J.begin; --p) cafe_resolve_write(J, p);
+        for (int p = J.begin; p < J.limit; ++p) {
             int c, m;
             cafe_position_counts(J, p, &c, &m);
             if (c) J.res->seg_real_delta[cafe_segment_of(J, p)] += c;
