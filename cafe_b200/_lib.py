@@ -43,6 +43,7 @@ SIGNATURES = {
     "cafe_embed_forward": (c_int, [_vp, _vp, c_int, c_int, c_int, _i64p, _i32p, POINTER(_vp), _vp, c_int, c_int, _vp,
                                    c_int64, c_int64, _vp, _vp, _vp]),
     "cafe_grad_importance": (c_int, [_vp, _vp, c_int64, c_int64, c_int, c_int, c_int, _vp, _vp]),
+    "cafe_grad_importance_static": (c_int, [_vp, c_int64, c_int64, c_int, c_int, c_int, _vp, _vp]),
     "cafe_migrate": (c_int, [_vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p, POINTER(_vp), _vp, c_int, c_int,
                              _vp, _vp]),
     "cafe_scatter_sgd": (c_int, [_vp, _vp, c_int64, c_int64, _vp, c_int, c_int, _i32p, POINTER(_vp), _vp, c_int, c_int,

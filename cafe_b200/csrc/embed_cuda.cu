@@ -428,6 +428,72 @@ int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, i
     return fail_cuda("cafe_grad_importance");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Importance without any allocation.
+//
+// cafe_grad_importance keeps its two intermediates (one norm per lookup, one sum per field) in a
+// workspace that cafe_sketch_create obtained with cudaMalloc.  Some hosts cannot do that: a serving
+// process that handed the whole device to its own memory pool at start-up and forbids further
+// allocation, or a caller that must not take the device-wide stall an allocation can cause in the
+// middle of its step.  For them the same three kernels run here on a scratch area that is part of
+// the library image: a file-scope __device__ array, which every GPU that loads the library holds
+// from load to exit (CAFE_STATIC_IMPORTANCE_MAX floats for the norms plus one float per field,
+// about 1 MiB).  No handle is needed, and nothing is allocated or freed here: not with the CUDA
+// runtime, not through any library.
+//
+// The array's name is a host-side stand-in in host code, not a device address, so the address the
+// kernels get is looked up with cudaGetSymbolAddress -- once per device, on the first call made
+// while that device is current.  That first call should therefore come before any stream capture.
+// Every call on a device shares the one array: calls that can overlap on the GPU (different
+// streams, different host threads) race on it; run them one after the other.  Nothing in the array
+// has to start at zero -- each call writes every element before it reads it -- so it is not
+// cleared between calls.
+// ---------------------------------------------------------------------------------------------
+#define CAFE_STATIC_IMPORTANCE_MAX (1 << 18)   // most lookups (nfields * B) one call may cover
+#define CAFE_STATIC_MAX_DEVICES 64
+static __device__ __align__(256) float g_static_importance_scratch[CAFE_STATIC_IMPORTANCE_MAX + CAFE_MAX_SEGMENTS];
+static float* g_static_scratch_addr[CAFE_STATIC_MAX_DEVICES];   // per device, filled on first use
+
+int cafe_grad_importance_static(const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields, int B,
+                                int D, float* imp_out_dev, void* stream) {
+    if (nfields < 1 || nfields > CAFE_MAX_SEGMENTS || B < 0) return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    const int64_t total64 = (int64_t)nfields * B;
+    if (total64 > CAFE_STATIC_IMPORTANCE_MAX) {
+        char buf[160];
+        snprintf(buf, sizeof(buf), "cafe_grad_importance_static: %lld lookups exceed the built-in scratch of %d",
+                 (long long)total64, CAFE_STATIC_IMPORTANCE_MAX);
+        cafe_internal_set_error(buf);
+        return CAFE_ERR_CAPACITY;
+    }
+    if (total64 == 0) return CAFE_OK;
+    if (!grad_dev || !imp_out_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= CAFE_STATIC_MAX_DEVICES) {
+        cafe_internal_set_error(e != cudaSuccess ? cudaGetErrorString(e) : "cafe_grad_importance_static: device index out of range");
+        return e != cudaSuccess ? CAFE_ERR_CUDA : CAFE_ERR_UNSUPPORTED;
+    }
+    float* scratch = g_static_scratch_addr[dev];
+    if (!scratch) {   // set-up, once per device, with that device current
+        e = cudaGetSymbolAddress((void**)&scratch, g_static_importance_scratch);
+        if (e != cudaSuccess || !scratch) {
+            cafe_internal_set_error(e != cudaSuccess ? cudaGetErrorString(e) : "cafe_grad_importance_static: no symbol address");
+            return CAFE_ERR_CUDA;
+        }
+        g_static_scratch_addr[dev] = scratch;
+    }
+    float* norm = scratch;                                   // [total]
+    float* totals = scratch + CAFE_STATIC_IMPORTANCE_MAX;    // [nfields]
+    const int total = (int)total64;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)(((int64_t)total * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
+                   sample_stride, B, total, norm)));
+    k_field_sum<<<nfields, 1024, 0, st>>>(norm, B, totals);
+    k_importance<<<(total + 255) / 256, 256, 0, st>>>(norm, totals, B, total, imp_out_dev);
+    return fail_cuda("cafe_grad_importance_static");
+}
+
 int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t* mask_dev, const int32_t* post_row_dev,
                  int nfields, int B, const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
                  float* weight_high, int hotn, int D, int32_t* n_migrated_dev, void* stream) {

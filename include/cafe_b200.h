@@ -101,6 +101,16 @@ int cafe_embed_forward(void* handle, const void* ids_dev, int ids_are_int64, int
 int cafe_grad_importance(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields,
                          int B, int D, float* imp_out_dev, void* stream);
 
+/* No counterpart in the reference.  The same computation as cafe_grad_importance for callers that
+ * cannot allocate device memory (a process whose memory pool owns the whole device, a step that must
+ * not stall on an allocation): it needs no handle and allocates nothing, its intermediates live in a
+ * scratch array built into the library (held by every GPU that loads it).  Limits: nfields * B <=
+ * 262144 (CAFE_ERR_CAPACITY beyond that); calls on one device share the scratch, so calls that may
+ * overlap on the GPU race -- issue them one after another.  The first call on a device looks up the
+ * scratch address and should be made before any stream capture. */
+int cafe_grad_importance_static(const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields, int B,
+                                int D, float* imp_out_dev, void* stream);
+
 /* Replaces the row-copy loop of insert_grad (tricks/sk_embedding_bag.py:205-208), guarded: for lookups
  * with mask 1 and post_row > 0, weight_high[post_row] = weight_hash[f][local id % hash_size[f]]. */
 int cafe_migrate(void* handle, const void* ids_dev, int ids_are_int64, const int32_t* mask_dev,
