@@ -139,6 +139,9 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, i, o), e = __shfl_sync(CAFE_FULL, iend, o);
         bool stop = false;
+        bool hvalid = false, hrow = false;   // warp-uniform copy of the owner's view of the id last dealt with
+        uint32_t hx = 0;
+        int hslot = 0, hbound = 0;
         // two-deep software pipeline: positions of chunk n+2 and the per-lookup data of chunk n+1 are
         // requested before chunk n is processed, so a long bucket pays one load latency, not one per chunk
         int p_nx = (s + lane < e) ? J.ord1[s + lane] : INT32_MAX;
@@ -163,6 +166,37 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
             }
             const int n = min(32, e - base);
+            // Whole chunk = 32 more lookups of the id the previous step dealt with, whose slot owns a hot
+            // row: add the 32 counts in order, write 32 flags, nothing else can happen.
+            if (hvalid && hrow && n == 32 && __all_sync(CAFE_FULL, x == hx && p < hbound)) {
+                float cnt0 = 0.f;
+                if (lane == o) {
+#pragma unroll
+                    for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) cnt0 = R.b.cnt[q];
+                }
+                float acc = __shfl_sync(CAFE_FULL, cnt0, o);
+                float my_acc = 0.f;
+#pragma unroll
+                for (int u = 0; u < 32; ++u) {
+                    acc = acc + __shfl_sync(CAFE_FULL, c, u);
+                    if (lane == u) my_acc = acc;
+                }
+                if (lane == o) {
+#pragma unroll
+                    for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
+                    R.i_cur += 32;
+                }
+                if (!J.final_pass) {
+                    const bool cr = (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
+                    J.mflag[p] = (uint8_t)(cr ? CAFE_F_CROSS : 0);
+                    if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
+                    else {
+                        if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                        if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                    }
+                }
+                continue;
+            }
             int j = 0;
             while (j < n) {
                 const int pj = __shfl_sync(CAFE_FULL, p, j);
@@ -193,6 +227,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 if (slot >= 0) {
                     bound = __shfl_sync(CAFE_FULL, bound, o);
                     has_row = __shfl_sync(CAFE_FULL, has_row, o);
+                    hvalid = true; hx = xj; hslot = slot; hrow = has_row != 0; hbound = bound;
                     const bool mine = lane >= j && lane < n && x == xj && p < bound;
                     const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
@@ -241,6 +276,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                     const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
                     const uint32_t fj = __shfl_sync(CAFE_FULL, of, j);
                     if (lane == o) { R.feed(J, pj, xj, cj, kj, fj); ++slow; }
+                    hvalid = false;   // the full replay step may have changed slots, rows or the next event
                     ++j;
                 }
             }
