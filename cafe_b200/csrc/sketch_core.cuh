@@ -202,7 +202,7 @@ CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
 // =================================================================================================
 // Parallel form.
 // =================================================================================================
-struct CafeFn { int32_t a, b; };   // FIFO size transfer: s -> max(s + a, b)
+struct alignas(16) CafeFn { int32_t a, b, np, pad; };   // FIFO size transfer s -> max(s + a, b), and pushes so far
 
 // per-lookup result flags (one byte written by the main pass, one by the LRU pass)
 enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE_F_GOT = 16 };
@@ -266,7 +266,6 @@ struct CafeJob {
     // scratch
     int32_t* tstamp;     // [M] inclusive count of misses up to each position (at commit)
     CafeFn* op_fn;       // [M] FIFO-size transfer function of the position, then its inclusive scan
-    int64_t* op_cnt;     // [M] (pushes << 32) | successful pops, then their exclusive prefix sums
     // outputs
     int32_t* mask;       // [M] 1 = this lookup was handed a hot row (the reference's insert result)
     int32_t* post_row;   // [M] hot row of the id at the end of its segment (0 = not hot in the main table)
@@ -647,31 +646,26 @@ CAFE_HD void cafe_compose(int32_t a1, int32_t b1, int32_t a2, int32_t b2, int32_
 CAFE_HD int32_t cafe_apply_fn(int32_t a, int32_t b, int32_t s) { int32_t v = s + a; return v > b ? v : b; }
 
 // 3a: transfer function of position p
-CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) {
+CAFE_HD CafeFn cafe_resolve_fn(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t a0, b0, a1, b1, a, b;
+    int32_t a0, b0, a1, b1;
+    CafeFn f;
     cafe_op_fn(o.op0, &a0, &b0);
     cafe_op_fn(o.op1, &a1, &b1);
-    cafe_compose(a0, b0, a1, b1, &a, &b);
-    CafeFn f; f.a = a; f.b = b;
-    J.op_fn[p] = f;
+    cafe_compose(a0, b0, a1, b1, &f.a, &f.b);
+    f.np = (o.op0 == 2) + (o.op1 == 2);
+    f.pad = 0;
+    return f;
 }
-// 3b (after the inclusive scan of (op_a, op_b) under cafe_compose): outcome counts of position p
-CAFE_HD void cafe_resolve_count(const CafeJob& J, int p) {
-    CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == J.begin) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
-    int64_t pops = 0, pushes = 0;
-    if (o.op0 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op0 == 2) { ++pushes; ++s; }
-    if (o.op1 == 1) { if (s > 0) { ++pops; --s; } } else if (o.op1 == 2) { ++pushes; ++s; }
-    J.op_cnt[p] = (pushes << 32) | pops;
-}
-// 3c (after the exclusive prefix sum of op_cnt): write the timeline, compare with the consumed one
+CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) { J.op_fn[p] = cafe_resolve_fn(J, p); }
+// 3b (after the inclusive scan of the transfer functions): write the timeline, compare with the consumed
+// one.  Successful pops so far follow from sizes and pushes: size = q_size + pushes - pops.
 CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
     CafeOps o = cafe_ops_of(J, p);
-    int32_t s = (p == J.begin) ? J.q_size : cafe_apply_fn(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.q_size);
-    const int64_t pre = J.op_cnt[p];
-    int32_t rank = (int32_t)(pre & 0xffffffffLL);
-    int32_t npush = (int32_t)(pre >> 32);
+    int32_t s = J.q_size, npush = 0;
+    if (p != J.begin) { const CafeFn pf = J.op_fn[p - 1]; s = cafe_apply_fn(pf.a, pf.b, J.q_size); npush = pf.np; }
+    int32_t rank = J.q_size + npush - s;
+    const int32_t rank_before = rank, push_before = npush;
     int32_t sz[2], rk[2];
     sz[0] = s; rk[0] = rank;
     bool diff = false;
@@ -701,8 +695,8 @@ CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
         int32_t my_pops = 0, my_push = 0, s2 = sz[0];
         if (o.op0 == 1) { if (s2 > 0) { ++my_pops; --s2; } } else if (o.op0 == 2) { ++my_push; ++s2; }
         if (o.op1 == 1) { if (s2 > 0) { ++my_pops; } } else if (o.op1 == 2) { ++my_push; }
-        J.res->n_pop_ok = (int32_t)(pre & 0xffffffffLL) + my_pops;
-        J.res->n_push = (int32_t)(pre >> 32) + my_push;
+        J.res->n_pop_ok = rank_before + my_pops;
+        J.res->n_push = push_before + my_push;
     }
 }
 

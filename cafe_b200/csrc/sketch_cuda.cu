@@ -359,9 +359,10 @@ __global__ void k_lru_tconvert(const __grid_constant__ CafeJob J) {
 }
 // per-segment threshold crossings and the number of LRU visits: block-wide sums, one atomic per
 // block and counter (a block of consecutive positions lies in one segment except at boundaries)
-__global__ void __launch_bounds__(CAFE_TPB) k_position_counts(const __grid_constant__ CafeJob J) {
+__global__ void __launch_bounds__(CAFE_TPB) k_resolve_write(const __grid_constant__ CafeJob J) {
     __shared__ int s_cross, s_miss;
     const int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < J.limit) cafe_resolve_write(J, p);
     const int first = J.begin + blockIdx.x * blockDim.x;
     const int last = min(first + (int)blockDim.x, J.limit) - 1;
     if (threadIdx.x == 0) { s_cross = 0; s_miss = 0; }
@@ -381,18 +382,6 @@ __global__ void __launch_bounds__(CAFE_TPB) k_position_counts(const __grid_const
         if (s_miss) atomicAdd(&J.res->n_miss, s_miss);
     }
 }
-__global__ void k_resolve_ops(const __grid_constant__ CafeJob J) {
-    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < J.limit) cafe_resolve_ops(J, p);
-}
-__global__ void k_resolve_count(const __grid_constant__ CafeJob J) {
-    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < J.limit) cafe_resolve_count(J, p);
-}
-__global__ void k_resolve_write(const __grid_constant__ CafeJob J) {
-    int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < J.limit) cafe_resolve_write(J, p);
-}
 __global__ void k_commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
                                const uint32_t* __restrict__ pushbuf, int n_push) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -411,10 +400,17 @@ __global__ void k_seq_insert(CafeSeqState* Sd, const uint32_t* __restrict__ gid,
 struct MissFlag {
     __host__ __device__ __forceinline__ int32_t operator()(const uint8_t& f) const { return (int32_t)(f & 1); }
 };
+// input iterators of the two FIFO scans: values are computed from the per-lookup flags on the fly
+struct FnOfIndex {
+    CafeJob J;
+    __host__ __device__ __forceinline__ CafeFn operator()(const int& i) const { return cafe_resolve_fn(J, J.begin + i); }
+};
 struct FnCompose {
     __host__ __device__ __forceinline__ CafeFn operator()(const CafeFn& f, const CafeFn& g) const {
         CafeFn r;
         cafe_compose(f.a, f.b, g.a, g.b, &r.a, &r.b);
+        r.np = f.np + g.np;
+        r.pad = 0;
         return r;
     }
 };
@@ -583,8 +579,6 @@ struct CudaBackend {
         need = b > need ? b : need;
         cub::DeviceScan::InclusiveSum(nullptr, b, (int32_t*)nullptr, (int32_t*)nullptr, nsort, stream);
         need = b > need ? b : need;
-        cub::DeviceScan::ExclusiveSum(nullptr, b, (int64_t*)nullptr, (int64_t*)nullptr, nsort, stream);
-        need = b > need ? b : need;
         cub::DeviceScan::InclusiveScan(nullptr, b, (CafeFn*)nullptr, (CafeFn*)nullptr, FnCompose(), nsort, stream);
         need = b > need ? b : need;
         cub_bytes = need * 2 + 1024;
@@ -651,17 +645,11 @@ struct CudaBackend {
         CAFE_PROF(CAFE_P_RESOLVE, stream);
         const int cnt = J.limit - J.begin;
         const int g = cafe_blocks(cnt);
-        k_resolve_ops<<<g, CAFE_TPB, 0, stream>>>(J);
-        check_launch();
+        FnOfIndex f1; f1.J = J;
+        cub::TransformInputIterator<CafeFn, FnOfIndex, cub::CountingInputIterator<int>> in1(cub::CountingInputIterator<int>(0), f1);
         size_t b = cub_bytes;
-        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, J.op_fn + J.begin, J.op_fn + J.begin, FnCompose(), cnt, stream));
-        k_resolve_count<<<g, CAFE_TPB, 0, stream>>>(J);
-        check_launch();
-        b = cub_bytes;
-        check(cub::DeviceScan::ExclusiveSum(cub_tmp, b, J.op_cnt + J.begin, J.op_cnt + J.begin, cnt, stream));
+        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, in1, J.op_fn + J.begin, FnCompose(), cnt, stream));
         k_resolve_write<<<g, CAFE_TPB, 0, stream>>>(J);
-        check_launch();
-        k_position_counts<<<g, CAFE_TPB, 0, stream>>>(J);
         check_launch();
     }
     void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,

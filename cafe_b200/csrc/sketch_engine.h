@@ -82,8 +82,15 @@ public:
         ev = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
         head = (int32_t*)be.alloc(4 * (size_t)n1);
         nxt = (int32_t*)be.alloc(4 * M);
-        mark_own = (uint8_t*)be.alloc((size_t)n1); mstate = (uint8_t*)be.alloc((size_t)n1);
-        mark2 = (uint8_t*)be.alloc((size_t)n2); lstate = (uint8_t*)be.alloc((size_t)n2);
+        // mark_own | mark2 | round result: contiguous so that one memset clears what a round needs cleared
+        off_mark2 = ((size_t)n1 + 63) & ~(size_t)63;
+        off_res = (off_mark2 + (size_t)n2 + 63) & ~(size_t)63;
+        span_clear = off_res + sizeof(CafeRoundResult);
+        mark_own = (uint8_t*)be.alloc(span_clear);
+        mark2 = mark_own ? mark_own + off_mark2 : nullptr;
+        res_dev = mark_own ? (CafeRoundResult*)(mark_own + off_res) : nullptr;
+        mstate = (uint8_t*)be.alloc((size_t)n1);
+        lstate = (uint8_t*)be.alloc((size_t)n2);
         mflag = (uint8_t*)be.alloc(M); lflag = (uint8_t*)be.alloc(M);
         for (int i = 0; i < 2; ++i) {
             tl_size[i] = (int32_t*)be.alloc(8 * M);
@@ -93,8 +100,6 @@ public:
         tstamp = (int32_t*)be.alloc(4 * M);
         ins_res = (int32_t*)be.alloc(4 * M);
         op_fn = (CafeFn*)be.alloc(sizeof(CafeFn) * M);
-        op_cnt = (int64_t*)be.alloc(8 * M);
-        res_dev = (CafeRoundResult*)be.alloc(sizeof(CafeRoundResult));
         seq_dev = (CafeSeqState*)be.alloc(sizeof(CafeSeqState));
         size_t ncand = (size_t)(n1 + n2) * CAFE_SLOTS;
         cand_key[0] = (uint32_t*)be.alloc(4 * ncand); cand_key[1] = (uint32_t*)be.alloc(4 * ncand);
@@ -102,7 +107,7 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn || !op_cnt ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
         for (int i = 0; i < 2; ++i)
@@ -284,8 +289,8 @@ private:
     uint32_t* pushbuf[2] = {nullptr, nullptr};
     int32_t *tstamp = nullptr, *ins_res = nullptr;
     CafeFn* op_fn = nullptr;
-    int64_t* op_cnt = nullptr;
     CafeRoundResult* res_dev = nullptr;
+    size_t off_mark2 = 0, off_res = 0, span_clear = 0;
     CafeSeqState* seq_dev = nullptr;
     uint32_t* cand_key[2] = {nullptr, nullptr};
     int32_t* cand_val[2] = {nullptr, nullptr};
@@ -294,8 +299,8 @@ private:
 
     void release() {
         if (!ready && !mainb[0]) return;
-        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, mark2, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
-                        tstamp, ins_res, op_fn, op_cnt, res_dev, seq_dev, cand_key[0], cand_key[1],
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
+                        tstamp, ins_res, op_fn, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
         mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
@@ -349,7 +354,7 @@ private:
         J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
         J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
         J.ev = ev; J.head = head; J.nxt = nxt; J.mark_own = mark_own; J.mstate = mstate; J.mark2 = mark2; J.lstate = lstate;
-        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.tstamp = tstamp; J.op_fn = op_fn; J.op_cnt = op_cnt;
+        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.tstamp = tstamp; J.op_fn = op_fn;
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
@@ -378,9 +383,12 @@ private:
             shortened = false;
             J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
             J.tl_size_new = tl_size[pb ^ 1]; J.tl_rank_new = tl_rank[pb ^ 1]; J.pushbuf_new = pushbuf[pb ^ 1];
-            be.memset(res_dev, 0, sizeof(CafeRoundResult));
-            if (!first) route(J);
-            be.memset(mark2, 0, (size_t)n2);
+            if (first) be.memset(mark2, 0, span_clear - off_mark2);   // mark2 + round result
+            else {
+                be.memset(head, 0xff, 4 * (size_t)n1);
+                be.memset(mark_own, 0, span_clear);                   // mark_own + mark2 + round result
+                be.route(J);
+            }
             be.main_pass(J);
             be.lru_pass(J);
             be.resolve(J);

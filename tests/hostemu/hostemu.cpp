@@ -74,13 +74,12 @@ struct HostBackend {
     void resolve(const CafeJob& J) {
         for (int p = J.begin; p < J.limit; ++p) cafe_resolve_ops(J, p);
         for (int p = J.begin + 1; p < J.limit; ++p) {
-            int32_t a, b;
-            cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &a, &b);
-            J.op_fn[p].a = a; J.op_fn[p].b = b;
+            CafeFn r;
+            cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &r.a, &r.b);
+            r.np = J.op_fn[p - 1].np + J.op_fn[p].np;
+            r.pad = 0;
+            J.op_fn[p] = r;
         }
-        for (int p = J.begin; p < J.limit; ++p) cafe_resolve_count(J, p);
-        int64_t acc = 0;
-        for (int p = J.begin; p < J.limit; ++p) { int64_t v = J.op_cnt[p]; J.op_cnt[p] = acc; acc += v; }
         for (int p = J.limit - 1; p >= J.begin; --p) cafe_resolve_write(J, p);
         for (int p = J.begin; p < J.limit; ++p) {
             int c, m;
