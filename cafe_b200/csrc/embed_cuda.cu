@@ -97,19 +97,33 @@ template <int G>
 __global__ void __launch_bounds__(256)
 k_grad_norm(const float* __restrict__ grad, int64_t field_stride, int64_t sample_stride, int B, int total,
             float* __restrict__ norm) {
+    // a group of G lanes takes 4 consecutive lookups: 4 independent 16-byte loads per lane in flight
+    constexpr int U = 4;
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t p = t / G;
+    const int64_t p0 = (t / G) * U;
     const int c = (int)(t % G) * 4;
-    float s = 0.f;
-    if (p < total) {
-        const int f = (int)(p / B);
-        const int b = (int)(p - (int64_t)f * B);
-        const float4 v = ld_row(grad + f * field_stride + b * sample_stride + c);
-        s = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    float s[U];
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t p = p0 + u;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p < total) {
+            const int f = (int)(p / B);
+            const int b = (int)(p - (int64_t)f * B);
+            v[u] = ld_stream(grad + f * field_stride + b * sample_stride + c);
+        }
     }
 #pragma unroll
-    for (int o = G / 2; o > 0; o >>= 1) s += __shfl_xor_sync(FULL, s, o);
-    if (p < total && c == 0) norm[p] = sqrtf(s);
+    for (int u = 0; u < U; ++u) {
+        s[u] = v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s[u] += __shfl_xor_sync(FULL, s[u], o);
+    }
+    if (c == 0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) if (p0 + u < total) norm[p0 + u] = sqrtf(s[u]);
+    }
 }
 
 // one block per field: fixed-order sum of the field's norms
@@ -188,10 +202,12 @@ __device__ __forceinline__ float* row_ptr(const CafeFields& F, uint32_t key, int
     const int f = pos / F.B;
     return F.w_hash[f] + (size_t)(key - (uint32_t)F.hotn - (uint32_t)F.hash_base[f]) * F.D;
 }
+// row -= lr * g.  Every row is updated exactly once per call (by the chunk that holds all of its
+// lookups, or by the fix-up pass), so the update can be a fire-and-forget vector reduction at L2
+// instead of a load / subtract / store round trip; with a single add per element the result does
+// not depend on timing.
 __device__ __forceinline__ void sgd_apply(float* w, float4 g, float lr) {
-    float4 x = *reinterpret_cast<float4*>(w);
-    x.x -= lr * g.x; x.y -= lr * g.y; x.z -= lr * g.z; x.w -= lr * g.w;
-    *reinterpret_cast<float4*>(w) = x;
+    atomicAdd(reinterpret_cast<float4*>(w), make_float4(-(lr * g.x), -(lr * g.y), -(lr * g.z), -(lr * g.w)));
 }
 
 #define NOKEY 0xffffffffu
@@ -421,7 +437,7 @@ int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, i
     const int total = (int)total64;
     cudaStream_t st = (cudaStream_t)stream;
     { CAFE_PROF(CAFE_P_NORM, st);
-    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)(((int64_t)total * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
+    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)((((int64_t)total + 3) / 4 * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
                    sample_stride, B, total, ws->norm))); }
     { CAFE_PROF(CAFE_P_FIELDSUM, st); k_field_sum<<<nfields, 1024, 0, st>>>(ws->norm, B, ws->totals); }
     { CAFE_PROF(CAFE_P_IMPORTANCE, st); k_importance<<<(total + 255) / 256, 256, 0, st>>>(ws->norm, ws->totals, B, total, imp_out_dev); }
@@ -487,7 +503,7 @@ int cafe_grad_importance_static(const float* grad_dev, int64_t field_stride, int
     float* totals = scratch + CAFE_STATIC_IMPORTANCE_MAX;    // [nfields]
     const int total = (int)total64;
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)(((int64_t)total * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
+    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)((((int64_t)total + 3) / 4 * G + 255) / 256), 256, 0, st>>>(grad_dev, field_stride,
                    sample_stride, B, total, norm)));
     k_field_sum<<<nfields, 1024, 0, st>>>(norm, B, totals);
     k_importance<<<(total + 255) / 256, 256, 0, st>>>(norm, totals, B, total, imp_out_dev);
