@@ -325,18 +325,23 @@ def run_ours(args, rank, world, local_rank):
         roof = None
         if top:
             per_launch_ms = cand[top][0] / cand[top][1]
-            ach = alg_bytes(top, D) * ids_per_step / (per_launch_ms / 1e3) / 1e9
+            # lookups one launch processes: the per-step kernels see every lookup of the step once; the
+            # sketch passes run once or more per job over that job's window, and all windows of a step
+            # add up to the step's lookups, so an average launch covers ids_per_step / launches_per_step
+            launches_per_step = cand[top][1] / args.steps
+            units = ids_per_step / max(1.0, launches_per_step)
+            ach = alg_bytes(top, D) * units / (per_launch_ms / 1e3) / 1e9
             traffic = None
             tp = ROOT / "profiles" / "traffic.json"
             if tp.exists():
                 try:
                     per_id = json.loads(tp.read_text()).get(top, {}).get("dram_bytes_per_id")
-                    traffic = per_id * ids_per_step if per_id else None
+                    traffic = per_id * units if per_id else None
                 except Exception:
                     traffic = None
             roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                     "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, D),
-                    "ms_per_launch": per_launch_ms,
+                    "ms_per_launch": per_launch_ms, "ids_per_launch": units,
                     "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(D),
                                    "achieved": FUSED_BYTES_PER_ID(D) * total_ids / (ms / args.steps / 1e3) / 1e9 / max(world, 1),
                                    "frac": FUSED_BYTES_PER_ID(D) * total_ids / (ms / args.steps / 1e3) / 1e9 / max(world, 1) / peak}}
