@@ -247,7 +247,8 @@ def run_ours(args, rank, world, local_rank):
     F, D, B = len(cards), DIM, args.batch
     if world > 1:
         from cafe_b200.sharded import ShardedSKEmbedding
-        model = ShardedSKEmbedding(cards, D, CR, HR, THR, ADJ, ALPHA, device=dev, global_batch=B * world, lr=LR, seed=1)
+        model = ShardedSKEmbedding(cards, D, CR, HR, THR, ADJ, ALPHA, device=dev, global_batch=B * world, lr=LR, seed=1,
+                                   exchange=args.exchange)
         step_fn, e2e_fn, ids_per_step = model.bench_closures(S, ZIPF_S, SEED)
     else:
         grp = cafe_b200.SKEmbeddingGroup(cards, D, CR, HR, THR, ADJ, ALPHA, device=dev, max_batch=B, lr=LR, seed=1)
@@ -375,6 +376,7 @@ def main():
     ap.add_argument("--cpu-batch", type=int, default=16384, help="batch of the CPU baseline sample")
     ap.add_argument("--cpu-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU exchange of pooled rows / gradients")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -24,6 +24,15 @@ struct CafeFields {
     float* w_high;
 };
 
+// Where the rows of a batch go (forward) or come from (backward) when the batch is spread over the
+// GPUs of a node: sample b belongs to rank b / rows_per_rank, whose buffer starts at base[rank]
+// (this GPU's own memory for its own slice, a peer mapping for the others).  One rank: base[0], all rows.
+#define CAFE_MAX_RANKS 8
+struct CafeRankBuffers {
+    float* base[CAFE_MAX_RANKS];
+    int32_t rows_per_rank;
+};
+
 #define FULL 0xffffffffu
 
 __device__ __forceinline__ float4 ld_row(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
@@ -43,7 +52,7 @@ __device__ __forceinline__ T* shfl_ptr(T* p, int src) {
 template <int G, typename IdT>
 __global__ void __launch_bounds__(256)
 k_embed_forward(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids,
-                const CafeMainBucket* __restrict__ mb, int n1, float* __restrict__ out, int64_t field_stride,
+                const CafeMainBucket* __restrict__ mb, int n1, const CafeRankBuffers out, int64_t field_stride,
                 int64_t sample_stride, uint32_t* __restrict__ gid_out, int32_t* __restrict__ row_out, int total) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -65,7 +74,8 @@ k_embed_forward(const __grid_constant__ CafeFields F, const IdT* __restrict__ id
         int32_t code;
         if (r) { src = F.w_high + (size_t)(r % F.hotn) * F.D; code = -r; }
         else { const int32_t hr = (int32_t)(x % (uint32_t)F.hash_size[f]); src = F.w_hash[f] + (size_t)hr * F.D; code = hr; }
-        dst = out + f * field_stride + b * sample_stride;
+        const int dr = b / out.rows_per_rank;   // rank that consumes this sample
+        dst = out.base[dr] + f * field_stride + (b - dr * out.rows_per_rank) * sample_stride;
         gid_out[p] = x;
         row_out[p] = code;
     }
@@ -320,6 +330,70 @@ k_scatter_fixup(const __grid_constant__ CafeFields F, const uint32_t* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
+// Field-sharded exchange over peer memory (NVLink): no counterpart in the reference, which is
+// single-GPU.  Every rank owns the fields f with f % nranks == rank and serves them for the global
+// batch; buffers of other ranks are plain peer mappings (ordinary loads and stores, no multicast).
+//   ids      : each rank stores its batch slice of every field's ids straight into the owners' id
+//              buffers ([F_owner, nranks * rows] per owner);
+//   forward  : the gather kernel above stores each pooled row into the buffer of the rank that
+//              consumes the sample (CafeRankBuffers), i.e. the all-to-all is the kernel's epilogue;
+//   backward : the owner pulls the gradient rows of its fields from the consumers' buffers while it
+//              computes their norms, keeping a local copy for the scatter (all-to-all as prologue).
+// Ordering between ranks (data ready / buffer free) is the caller's: a stream-ordered collective
+// between the phases.
+// ---------------------------------------------------------------------------------------------
+struct CafeIdBuffers {
+    int64_t* base[CAFE_MAX_RANKS];
+};
+__global__ void k_scatter_ids(const int64_t* __restrict__ ids, int nfields, int rows, int nranks, int rank,
+                              const CafeIdBuffers dst) {
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (int64_t)nfields * rows) return;
+    const int f = (int)(t / rows), b = (int)(t - (int64_t)f * rows);
+    const int owner = f % nranks, j = f / nranks;   // j = index of f among its owner's fields
+    dst.base[owner][(int64_t)j * nranks * rows + (int64_t)rank * rows + b] = ids[t];
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+k_pull_norm(const CafeRankBuffers src, int64_t field_stride, int64_t sample_stride, int B, int total,
+            float* __restrict__ local, float* __restrict__ norm) {
+    constexpr int U = 4;
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t p0 = (t / G) * U;
+    const int c = (int)(t % G) * 4;
+    float s[U];
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t p = p0 + u;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p < total) {
+            const int f = (int)(p / B);
+            const int b = (int)(p - (int64_t)f * B);
+            const int r = b / src.rows_per_rank;
+            v[u] = *reinterpret_cast<const float4*>(src.base[r] + f * field_stride + (b - r * src.rows_per_rank) * sample_stride + c);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int64_t p = p0 + u;
+        if (p < total) {
+            const int f = (int)(p / B);
+            const int b = (int)(p - (int64_t)f * B);
+            *reinterpret_cast<float4*>(local + f * field_stride + b * sample_stride + c) = v[u];
+        }
+        s[u] = v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s[u] += __shfl_xor_sync(FULL, s[u], o);
+    }
+    if (c == 0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) if (p0 + u < total) norm[p0 + u] = sqrtf(s[u]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // workspace
 // ---------------------------------------------------------------------------------------------
 int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
@@ -395,6 +469,22 @@ static bool strides_ok(const float* p, int64_t fs, int64_t ss) { return aligned1
         default: { constexpr int G = 32; CALL; } break; \
     }
 
+static int launch_forward(const CafeFields& F, const void* ids_dev, int ids_are_int64, const CafeSketchView& V,
+                          const CafeRankBuffers& out_dev, int64_t out_field_stride, int64_t out_sample_stride,
+                          uint32_t* gid_out_dev, int32_t* row_out_dev, int total, int D, cudaStream_t st) {
+    const int warps = (total + 31) / 32;
+    const int blocks = (warps + 7) / 8;
+    CAFE_PROF(CAFE_P_FORWARD, st);
+    if (ids_are_int64) {
+        DISPATCH_G(D, (k_embed_forward<G, int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, V.main, V.n1, out_dev,
+                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
+    } else {
+        DISPATCH_G(D, (k_embed_forward<G, int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, V.main, V.n1, out_dev,
+                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
+    }
+    return fail_cuda("cafe_embed_forward");
+}
+
 extern "C" {
 
 int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
@@ -412,18 +502,13 @@ int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfie
     CafeSketchView V = cafe_internal_view(h);
     if (hotn != V.lim) return CAFE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    const int warps = (total + 31) / 32;
-    const int blocks = (warps + 7) / 8;
-    CAFE_PROF(CAFE_P_FORWARD, st);
-    if (ids_are_int64) {
-        DISPATCH_G(D, (k_embed_forward<G, int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, V.main, V.n1, out_dev,
-                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
-    } else {
-        DISPATCH_G(D, (k_embed_forward<G, int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, V.main, V.n1, out_dev,
-                       out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total)));
-    }
-    return fail_cuda("cafe_embed_forward");
+    CafeRankBuffers ob;
+    memset(&ob, 0, sizeof(ob));
+    ob.base[0] = out_dev;
+    ob.rows_per_rank = B > 0 ? B : 1;
+    return launch_forward(F, ids_dev, ids_are_int64, V, ob, out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total, D, st);
 }
+
 
 int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields, int B,
                          int D, float* imp_out_dev, void* stream) {
@@ -582,6 +667,94 @@ int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, in
     if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
     rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
                       hotn, D, n_migrated_dev, stream);
+    if (rc != CAFE_OK) return rc;
+    rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
+                          hotn, D, lr, stream);
+    return rc != CAFE_OK ? rc : status;
+}
+
+// ---- field-sharded exchange over peer memory (see the kernels above) ------------------------------
+int cafe_shard_scatter_ids(const int64_t* ids_local_dev, int nfields_total, int rows_local, int nranks, int rank,
+                           int64_t* const* owner_ids, void* stream) {
+    if (nfields_total < 1 || rows_local < 0 || nranks < 1 || nranks > CAFE_MAX_RANKS || rank < 0 || rank >= nranks || !owner_ids)
+        return CAFE_ERR_ARG;
+    const int64_t total = (int64_t)nfields_total * rows_local;
+    if (total == 0) return CAFE_OK;
+    if (!ids_local_dev) return CAFE_ERR_ARG;
+    CafeIdBuffers d;
+    memset(&d, 0, sizeof(d));
+    for (int r = 0; r < nranks; ++r) { if (!owner_ids[r]) return CAFE_ERR_ARG; d.base[r] = owner_ids[r]; }
+    cudaStream_t st = (cudaStream_t)stream;
+    CAFE_PROF(CAFE_P_OTHER, st);
+    k_scatter_ids<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(ids_local_dev, nfields_total, rows_local, nranks, rank, d);
+    return fail_cuda("cafe_shard_scatter_ids");
+}
+
+int cafe_embed_forward_sharded(void* h, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
+                               const int32_t* hash_size, float* const* weight_hash, float* weight_high, int hotn, int D,
+                               float* const* out_rank, int nranks, int rows_per_rank, int64_t out_field_stride,
+                               int64_t out_sample_stride, uint32_t* gid_out_dev, int32_t* row_out_dev, void* stream) {
+    if (!h || !out_rank || nranks < 1 || nranks > CAFE_MAX_RANKS || rows_per_rank < 1) return CAFE_ERR_ARG;
+    if ((int64_t)rows_per_rank * nranks != B) return CAFE_ERR_ARG;
+    CafeFields F;
+    int rc = fill_fields(&F, nfields, B, D, hotn, f_offset, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    if (!ids_dev || !gid_out_dev || !row_out_dev || out_field_stride % 4 || out_sample_stride % 4) return CAFE_ERR_ARG;
+    CafeRankBuffers ob;
+    memset(&ob, 0, sizeof(ob));
+    for (int r = 0; r < nranks; ++r) { if (!out_rank[r] || !aligned16(out_rank[r])) return CAFE_ERR_ARG; ob.base[r] = out_rank[r]; }
+    ob.rows_per_rank = rows_per_rank;
+    CafeSketchView V = cafe_internal_view(h);
+    if (hotn != V.lim) return CAFE_ERR_ARG;
+    return launch_forward(F, ids_dev, ids_are_int64, V, ob, out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total, D,
+                          (cudaStream_t)stream);
+}
+
+int cafe_shard_pull_importance(void* h, const float* const* grad_rank, int nranks, int rows_per_rank, int nfields, int D,
+                               int64_t field_stride, int64_t sample_stride, float* local_grad_dev, float* imp_out_dev,
+                               void* stream) {
+    if (!h || !grad_rank || nranks < 1 || nranks > CAFE_MAX_RANKS || rows_per_rank < 1 || nfields < 1 || nfields > CAFE_MAX_SEGMENTS)
+        return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    const int B = rows_per_rank * nranks;
+    const int64_t total64 = (int64_t)nfields * B;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    if (total64 > ws->cap) return CAFE_ERR_CAPACITY;
+    if (!local_grad_dev || !imp_out_dev || !strides_ok(local_grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
+    CafeRankBuffers sb;
+    memset(&sb, 0, sizeof(sb));
+    for (int r = 0; r < nranks; ++r) { if (!grad_rank[r] || !aligned16(grad_rank[r])) return CAFE_ERR_ARG; sb.base[r] = const_cast<float*>(grad_rank[r]); }
+    sb.rows_per_rank = rows_per_rank;
+    const int total = (int)total64;
+    cudaStream_t st = (cudaStream_t)stream;
+    { CAFE_PROF(CAFE_P_NORM, st);
+    DISPATCH_G(D, (k_pull_norm<G><<<(unsigned)((((int64_t)total + 3) / 4 * G + 255) / 256), 256, 0, st>>>(sb, field_stride,
+                   sample_stride, B, total, local_grad_dev, ws->norm))); }
+    { CAFE_PROF(CAFE_P_FIELDSUM, st); k_field_sum<<<nfields, 1024, 0, st>>>(ws->norm, B, ws->totals); }
+    { CAFE_PROF(CAFE_P_IMPORTANCE, st); k_importance<<<(total + 255) / 256, 256, 0, st>>>(ws->norm, ws->totals, B, total, imp_out_dev); }
+    return fail_cuda("cafe_shard_pull_importance");
+}
+
+// cafe_embed_backward with the importance array already computed (by cafe_shard_pull_importance)
+int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const float* imp_dev,
+                            const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev,
+                            int nfields, int B, const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                            float* weight_high, int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev,
+                            void* stream) {
+    if (!h || !imp_dev) return CAFE_ERR_ARG;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    const int64_t total = (int64_t)nfields * B;
+    if (nfields < 1 || nfields > CAFE_MAX_SEGMENTS || total > ws->cap) return CAFE_ERR_CAPACITY;
+    if (total == 0) return CAFE_OK;
+    int seg[CAFE_MAX_SEGMENTS + 1];
+    for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
+    int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
+    int status = cafe_internal_insert(h, gid_dev, imp_dev, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
+    if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
+    int rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
+                          hotn, D, nullptr, stream);
     if (rc != CAFE_OK) return rc;
     rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
                           hotn, D, lr, stream);

@@ -14,8 +14,17 @@ Each shard is bit-identical to an independent single-GPU run over its own fields
 field offsets (there is no cross-rank state).  `FieldShardPlan` and the exchange functions are plain
 torch.distributed code and also run on CPU tensors under the gloo backend, which is how the index
 arithmetic is tested without GPUs.
+
+Two ways to do the exchange: `exchange="nccl"` (library all-to-all, the baseline) and `exchange="peer"`
+(default): buffers live in symmetric memory mapped into every rank, the gather kernel stores each pooled
+row straight into the consuming rank's buffer, and the owner pulls gradient rows from the consumers while
+it computes their norms (cafe_embed_forward_sharded / cafe_shard_pull_importance), so the transfers
+overlap the kernels' own work row by row; ranks are ordered by three one-element all-reduces per step.
 """
 from __future__ import annotations
+
+import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -88,6 +97,102 @@ class FieldShardPlan:
         return torch.cat([full[:, r::self.G, :].reshape(-1) for r in range(self.G)])
 
 
+class PeerBuffers:
+    """Symmetric-memory buffers of one rank and the addresses of every rank's copies.
+
+    ids    [2][Fmax * G * B_local] int64 : this rank as OWNER: ids of its fields for the global batch
+                                           (two generations, so that a fast peer never overwrites ids
+                                           the owner is still reading in its backward)
+    pooled [B_local * F * D] fp32        : this rank as CONSUMER: pooled rows of its batch slice, blocks
+                                           [B_local, F_r, D] ordered by owner r
+    grad   [B_local * F * D] fp32        : this rank as CONSUMER: gradient of `pooled`, same layout
+    """
+
+    def __init__(self, plan: "FieldShardPlan", rows: int, dim: int, device, group=None):
+        # plain peer mappings only: no NVLink multicast objects are bound to these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        grp = group if group is not None else dist.group.WORLD
+        self.plan, self.rows, self.dim = plan, rows, dim
+        fmax = max(plan.counts)
+        self.ids = symm.empty(2 * fmax * plan.G * rows, dtype=torch.int64, device=device)
+        self.pooled = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
+        self.grad = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
+        self.h_ids = symm.rendezvous(self.ids, grp)
+        self.h_pooled = symm.rendezvous(self.pooled, grp)
+        self.h_grad = symm.rendezvous(self.grad, grp)
+        self.ids_gen_elems = fmax * plan.G * rows
+        # offset (elements) of owner r's block inside every consumer's pooled / grad buffer
+        self.block_off = [rows * dim * sum(plan.counts[:r]) for r in range(plan.G)]
+        self.flag = torch.zeros(1, device=device)
+        self.gen = 0
+
+    def ptr_array(self, handle, elem_offset: int, elem_size: int):
+        return (ctypes.c_void_p * self.plan.G)(*[int(p) + elem_offset * elem_size for p in handle.buffer_ptrs])
+
+    def fence(self, group=None):
+        """All ranks have issued everything before this point on their streams (stream-ordered)."""
+        dist.all_reduce(self.flag, group=group)
+
+
+class _PeerFunction(torch.autograd.Function):
+    """The exchange folded into the kernels (see the module docstring)."""
+
+    @staticmethod
+    def forward(ctx, anchor, model, ids):
+        from . import _lib
+        from .sketch import _stream
+        plan, grp, pb = model.plan, model.group, model.peer
+        lib = grp.sketch.lib
+        F, Bl = ids.shape
+        G, Fg, D = plan.G, grp.num_fields, grp.embedding_dim
+        pb.gen ^= 1
+        gen_off = pb.gen * pb.ids_gen_elems
+        with torch.cuda.device(ids.device):
+            _lib.check(lib.cafe_shard_scatter_ids(ids.data_ptr(), F, Bl, G, plan.rank, pb.ptr_array(pb.h_ids, gen_off, 8),
+                                                  _stream()), "cafe_shard_scatter_ids")
+            pb.fence()                                   # every owner now holds the global batch's ids
+            own = pb.ids[gen_off:gen_off + Fg * G * Bl]  # [F_g, G*B_local], field-major
+            gid = torch.empty(own.numel(), dtype=torch.int32, device=ids.device)
+            row = torch.empty(own.numel(), dtype=torch.int32, device=ids.device)
+            f = grp._fields
+            wp, hp = f.ptrs()
+            out_rank = pb.ptr_array(pb.h_pooled, pb.block_off[plan.rank], 4)
+            _lib.check(lib.cafe_embed_forward_sharded(grp.sketch.handle, own.data_ptr(), 1, Fg, G * Bl, f.f_offset, f.hash_size,
+                                                      wp, hp, f.hotn, D, out_rank, G, Bl, D, Fg * D, gid.data_ptr(),
+                                                      row.data_ptr(), _stream()), "cafe_embed_forward_sharded")
+            pb.fence()                                   # every consumer's pooled buffer is complete
+        ctx.model, ctx.saved, ctx.Bl = model, (own, gid, row), Bl
+        return pb.pooled
+
+    @staticmethod
+    def backward(ctx, blocked_grad):
+        from . import _lib
+        from .sketch import _stream
+        model = ctx.model
+        plan, grp, pb = model.plan, model.group, model.peer
+        lib = grp.sketch.lib
+        own, gid, row = ctx.saved
+        G, Fg, D, Bl = plan.G, grp.num_fields, grp.embedding_dim, ctx.Bl
+        f = grp._fields
+        with torch.no_grad(), torch.cuda.device(pb.grad.device):
+            if blocked_grad.data_ptr() != pb.grad.data_ptr():
+                pb.grad.copy_(blocked_grad.reshape(-1))  # consumers expose their gradients to the owners
+            pb.fence()
+            if model._gbuf is None or model._gbuf.numel() != G * Bl * Fg * D:
+                model._gbuf = torch.empty(G * Bl * Fg * D, dtype=torch.float32, device=pb.grad.device)
+                model._imp = torch.empty(G * Bl * Fg, dtype=torch.float32, device=pb.grad.device)
+            src = pb.ptr_array(pb.h_grad, pb.block_off[plan.rank], 4)
+            _lib.check(lib.cafe_shard_pull_importance(grp.sketch.handle, src, G, Bl, Fg, D, D, Fg * D, model._gbuf.data_ptr(),
+                                                      model._imp.data_ptr(), _stream()), "cafe_shard_pull_importance")
+            wp, hp = f.ptrs()
+            grp.last_status = _lib.check(lib.cafe_embed_backward_imp(
+                grp.sketch.handle, model._gbuf.data_ptr(), D, Fg * D, model._imp.data_ptr(), own.data_ptr(), 1, gid.data_ptr(),
+                row.data_ptr(), Fg, G * Bl, f.f_offset, f.hash_size, wp, hp, f.hotn, D, float(grp.lr), grp.insert_mode, None,
+                _stream()), "cafe_embed_backward_imp")
+        return None, None, None
+
+
 class _ShardedFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, anchor, model, ids):
@@ -119,7 +224,8 @@ class ShardedSKEmbedding(torch.nn.Module):
     owners.  Needs an initialised NCCL process group with one rank per GPU."""
 
     def __init__(self, num_categories, embedding_dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1,
-                 sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None):
+                 sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None,
+                 exchange="peer"):
         super().__init__()
         from .sk_embedding_bag import SKEmbeddingGroup
         world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -136,9 +242,23 @@ class ShardedSKEmbedding(torch.nn.Module):
                                       f_offsets=[offs[f] for f in mine], seed=None if seed is None else seed + rank)
         self._anchor = torch.nn.Parameter(torch.zeros(1, device=self.group.weight_high.device))
         self.h2d_bytes = self.d2h_bytes = 0
+        if exchange not in ("peer", "nccl"):
+            raise ValueError("exchange must be 'peer' or 'nccl'")
+        self.exchange = exchange
+        self.peer = None
+        self._gbuf = self._imp = None
+        if exchange == "peer":
+            if world > 8:
+                raise ValueError("the peer-memory exchange serves one node (at most 8 ranks)")
+            self.peer = PeerBuffers(self.plan, self.global_batch // world, self.embedding_dim,
+                                    self.group.weight_high.device, group)
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         ids = ids.to(self.group.weight_high.device, non_blocking=True).contiguous()
+        if self.peer is not None:
+            if ids.dtype != torch.int64 or ids.shape[1] != self.peer.rows:
+                raise ValueError("peer exchange: ids must be int64 [F, global_batch / world]")
+            return _PeerFunction.apply(self._anchor, self, ids)
         return _ShardedFunction.apply(self._anchor, self, ids)
 
     # ---- benchmark plumbing ---------------------------------------------------------------------------
@@ -155,7 +275,12 @@ class ShardedSKEmbedding(torch.nn.Module):
         host = [torch.from_numpy(S.batch_ids(cards, Bl, zipf_s, seed + 7919 * plan.rank, s)).pin_memory() for s in range(nb)]
         devi = [h.to(dev) for h in host]
         g = torch.Generator(device=dev).manual_seed(seed + plan.rank)
-        grads = [torch.randn(Bl * F * D, device=dev, generator=g) * 0.01 for _ in range(2)]
+        if self.peer is not None:
+            # the gradient of the exchanged rows is produced in place, in the buffer the owners pull from
+            self.peer.grad.copy_(torch.randn(Bl * F * D, device=dev, generator=g) * 0.01)
+            grads = [self.peer.grad, self.peer.grad]
+        else:
+            grads = [torch.randn(Bl * F * D, device=dev, generator=g) * 0.01 for _ in range(2)]
         stage = torch.empty_like(devi[0])
         res = torch.empty(16 * D, dtype=torch.float32).pin_memory()
         self.h2d_bytes, self.d2h_bytes = host[0].numel() * 8 * plan.G, res.numel() * 4 * plan.G

@@ -133,6 +133,38 @@ int cafe_embed_backward(void* handle, const float* grad_dev, int64_t field_strid
                         float* weight_high, int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev,
                         int32_t* n_migrated_dev, void* stream);
 
+/* ---- field-sharded exchange over peer memory (one node, up to 8 ranks) -----------------------------
+ * No counterpart in the reference (single GPU; its --dist flags are never used, dlrm_s_pytorch.py:
+ * 1090-1091).  Rank g owns the fields f with f % nranks == g (in ascending order) and serves them for
+ * the global batch of nranks * rows samples.  Pointers in the *_rank / owner_* arrays are device
+ * pointers valid on the calling GPU: its own buffer for its own rank, peer mappings (CUDA VMM / IPC)
+ * for the others; they are accessed with ordinary loads and stores.  The caller orders the phases
+ * across ranks (a stream-ordered collective between them). */
+
+/* Every rank stores its slice ids_local[F][rows] into the owners' id buffers: owner r's buffer is
+ * [F_r][nranks * rows] int64, this rank's slice at columns [rank*rows, (rank+1)*rows). */
+int cafe_shard_scatter_ids(const int64_t* ids_local_dev, int nfields_total, int rows_local, int nranks, int rank,
+                           int64_t* const* owner_ids, void* stream);
+/* cafe_embed_forward whose output row of sample b goes to out_rank[b / rows_per_rank] at row
+ * b % rows_per_rank: the all-to-all of pooled embeddings as the gather kernel's epilogue. */
+int cafe_embed_forward_sharded(void* handle, const void* ids_dev, int ids_are_int64, int nfields, int B,
+                               const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                               float* weight_high, int hotn, int D, float* const* out_rank, int nranks, int rows_per_rank,
+                               int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
+                               int32_t* row_out_dev, void* stream);
+/* The transpose for gradients, fused with cafe_grad_importance: the owner reads the gradient row of
+ * sample b from grad_rank[b / rows_per_rank], writes it to local_grad_dev ([nranks*rows, nfields, D]
+ * through the strides) and produces the importance array. */
+int cafe_shard_pull_importance(void* handle, const float* const* grad_rank, int nranks, int rows_per_rank, int nfields,
+                               int D, int64_t field_stride, int64_t sample_stride, float* local_grad_dev,
+                               float* imp_out_dev, void* stream);
+/* cafe_embed_backward for a caller that already holds the importance array. */
+int cafe_embed_backward_imp(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                            const float* imp_dev, const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev,
+                            const int32_t* row_dev, int nfields, int B, const int64_t* f_offset, const int32_t* hash_size,
+                            float* const* weight_hash, float* weight_high, int hotn, int D, float lr, int insert_mode,
+                            int32_t* mask_out_dev, void* stream);
+
 /* ---- the reference's own ctypes ABI, host pointers (tricks/sketch.cpp:300-327) ------------------
  * Same names, argument meaning and result convention (pointer to a library-owned int array that is
  * valid until the next call), so that the reference's Python can bind this library in place of its
