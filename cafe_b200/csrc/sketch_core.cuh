@@ -243,6 +243,8 @@ struct CafeJob {
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
     int32_t diag;          // timing experiments only (changes results): see k_main_pass
+    int32_t long_main;     // device hint: main buckets with more lookups than this are fed by a whole warp
+    int32_t long_lru;      // same for LRU buckets
     int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to
                            // record post_row; nothing else is written
     // beliefs: the promotion event of every position, kept in place and updated by the LRU pass

@@ -10,6 +10,7 @@
 #include <stdio.h>
 
 #include <cub/cub.cuh>
+#include <algorithm>
 #include <string>
 
 #include "../../include/cafe_b200.h"
@@ -99,10 +100,10 @@ __device__ __forceinline__ int cafe_bucket_of_thread(const CafeHot& H, int nb, b
     const int k = (blockIdx.x - CAFE_HOT_BLOCKS) * blockDim.x + threadIdx.x;
     return (k < nb && !H.flag[k]) ? k : nb;
 }
-__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int32_t* list, int32_t* count, uint8_t* flag) {
+__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int32_t* list, int32_t* count, uint8_t* flag) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= nb) return;
-    if (start[k + 1] - start[k] > CAFE_HOT_LEN) {
+    if (start[k + 1] - start[k] > hot_len) {
         const int idx = atomicAdd(count, 1);
         if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; }
     }
@@ -122,14 +123,23 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
     }
     if (J.diag) {   // timing experiments: leave out classes of buckets
         const int len = iend - i;
-        if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > CAFE_LONG && len <= 512) || ((J.diag & 4) && len <= CAFE_LONG)) iend = i;
+        if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > J.long_main && len <= 512) || ((J.diag & 4) && len <= J.long_main)) iend = i;
     }
-    const bool is_long = live && (hot_warp || iend - i > CAFE_LONG);
+    const bool is_long = live && (hot_warp || iend - i > J.long_main);
     if (live && !is_long) {
-        for (; i < iend; ++i) {
-            const int p = J.ord1[i];
-            if (p >= J.limit) break;
-            R.feed(J, p, J.gid[p], cafe_count_of(J, p), cafe_old_kind(J, p), cafe_old_mflag(J, p));
+        // one lookup ahead: the next lookup's position and data are requested before this one is replayed
+        int p = (i < iend) ? J.ord1[i] : INT32_MAX;
+        uint32_t x = 0, ok = CAFE_EV_NONE, of = 0;
+        float c = 1.0f;
+        if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); of = cafe_old_mflag(J, p); }
+        while (p < J.limit) {
+            const int pn = (i + 1 < iend) ? J.ord1[i + 1] : INT32_MAX;
+            uint32_t xn = 0, okn = CAFE_EV_NONE, ofn = 0;
+            float cn = 1.0f;
+            if (pn < J.limit) { xn = J.gid[pn]; cn = cafe_count_of(J, pn); okn = cafe_old_kind(J, pn); ofn = cafe_old_mflag(J, pn); }
+            R.feed(J, p, x, c, ok, of);
+            p = pn; x = xn; c = cn; ok = okn; of = ofn;
+            ++i;
         }
     }
     int slow = 0;
@@ -297,7 +307,7 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         if (live) { jb = J.beg2[k]; jend = J.start2[k + 1]; }
     }
     int slow = 0;
-    const bool is_long = live && (hot_warp || jend - jb > CAFE_LONG);
+    const bool is_long = live && (hot_warp || jend - jb > J.long_lru);
     if (live && !is_long) {
         for (int j = jb; j < jend; ++j) {
             const int p = J.ord2[j];
@@ -610,7 +620,8 @@ struct CudaBackend {
         const int t = (nb == hot_nb[0]) ? 0 : 1;
         check(cudaMemsetAsync(hot_count[t], 0, 4, stream));
         check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, stream));
-        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(start, nb, hot_list[t], hot_count[t], hot_flag[t]);
+        const int hot_len = std::max(CAFE_HOT_LEN, (int)(16.0 * M / nb));
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(start, nb, hot_len, hot_list[t], hot_count[t], hot_flag[t]);
         check_launch();
     }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
