@@ -354,6 +354,30 @@ __global__ void k_scatter_ids(const int64_t* __restrict__ ids, int nfields, int 
     dst.base[owner][(int64_t)j * nranks * rows + (int64_t)rank * rows + b] = ids[t];
 }
 
+// Consumer side of the gradient exchange: this rank's gradient buffer holds, per owner g, a block
+// [rows, F_g, D]; every row is stored into owner g's buffer at sample (rank*rows + b) -- remote
+// stores, which NVLink handles better than remote loads.
+struct CafePushPlan {
+    float* base[CAFE_MAX_RANKS];       // owner g's gradient buffer [nranks*rows, F_g, D]
+    int32_t fields_of[CAFE_MAX_RANKS];  // F_g
+    int32_t row_off[CAFE_MAX_RANKS + 1];   // first (sample, field) row of owner g's block in this rank's buffer
+};
+__global__ void __launch_bounds__(256)
+k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rank, int rows, int D, int64_t total_rows) {
+    const int lanes = D / 4;                       // lanes per row (16-byte vectors)
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t q = t / lanes;
+    const int c = (int)(t % lanes) * 4;
+    if (q >= total_rows) return;
+    int g = 0;
+    while (g + 1 < nranks && q >= P.row_off[g + 1]) ++g;
+    const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
+    const int fg = P.fields_of[g];
+    const int64_t b = local / fg, j = local - b * fg;
+    const float4 v = ld_stream(grad + q * D + c);
+    *reinterpret_cast<float4*>(P.base[g] + (((int64_t)rank * rows + b) * fg + j) * D + c) = v;
+}
+
 template <int G>
 __global__ void __launch_bounds__(256)
 k_pull_norm(const CafeRankBuffers src, int64_t field_stride, int64_t sample_stride, int B, int total,
@@ -759,6 +783,33 @@ int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride
     rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
                           hotn, D, lr, stream);
     return rc != CAFE_OK ? rc : status;
+}
+
+int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                          float* const* owner_grad, void* stream) {
+    if (nfields_total < 1 || rows_local < 0 || nranks < 1 || nranks > CAFE_MAX_RANKS || rank < 0 || rank >= nranks || !owner_grad)
+        return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    const int64_t total_rows = (int64_t)nfields_total * rows_local;
+    if (total_rows == 0) return CAFE_OK;
+    if (!grad_blocked_dev || !aligned16(grad_blocked_dev)) return CAFE_ERR_ARG;
+    CafePushPlan P;
+    memset(&P, 0, sizeof(P));
+    int64_t off = 0;
+    for (int g = 0; g < nranks; ++g) {
+        if (!owner_grad[g] || !aligned16(owner_grad[g])) return CAFE_ERR_ARG;
+        P.base[g] = owner_grad[g];
+        P.fields_of[g] = nfields_total / nranks + (g < nfields_total % nranks ? 1 : 0);   // round-robin ownership
+        P.row_off[g] = (int32_t)off;
+        off += (int64_t)P.fields_of[g] * rows_local;
+    }
+    P.row_off[nranks] = (int32_t)off;
+    if (off != total_rows || total_rows > 0x7fffffffLL) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    CAFE_PROF(CAFE_P_OTHER, st);
+    const int64_t threads = total_rows * (D / 4);
+    k_push_grads<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D, total_rows);
+    return fail_cuda("cafe_shard_push_grads");
 }
 
 }  // extern "C"

@@ -106,6 +106,8 @@ class PeerBuffers:
     pooled [B_local * F * D] fp32        : this rank as CONSUMER: pooled rows of its batch slice, blocks
                                            [B_local, F_r, D] ordered by owner r
     grad   [B_local * F * D] fp32        : this rank as CONSUMER: gradient of `pooled`, same layout
+    gown   [G * B_local * Fmax * D] fp32 : this rank as OWNER: gradient rows of its fields for the global
+                                           batch, stored there by the consumers
     """
 
     def __init__(self, plan: "FieldShardPlan", rows: int, dim: int, device, group=None):
@@ -118,9 +120,11 @@ class PeerBuffers:
         self.ids = symm.empty(2 * fmax * plan.G * rows, dtype=torch.int64, device=device)
         self.pooled = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
         self.grad = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
+        self.gown = symm.empty(plan.G * rows * fmax * dim, dtype=torch.float32, device=device)   # as OWNER: gradients of its fields, global batch
         self.h_ids = symm.rendezvous(self.ids, grp)
         self.h_pooled = symm.rendezvous(self.pooled, grp)
         self.h_grad = symm.rendezvous(self.grad, grp)
+        self.h_gown = symm.rendezvous(self.gown, grp)
         self.ids_gen_elems = fmax * plan.G * rows
         # offset (elements) of owner r's block inside every consumer's pooled / grad buffer
         self.block_off = [rows * dim * sum(plan.counts[:r]) for r in range(plan.G)]
@@ -176,20 +180,13 @@ class _PeerFunction(torch.autograd.Function):
         G, Fg, D, Bl = plan.G, grp.num_fields, grp.embedding_dim, ctx.Bl
         f = grp._fields
         with torch.no_grad(), torch.cuda.device(pb.grad.device):
-            if blocked_grad.data_ptr() != pb.grad.data_ptr():
-                pb.grad.copy_(blocked_grad.reshape(-1))  # consumers expose their gradients to the owners
+            g = blocked_grad.reshape(-1).contiguous()
+            # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
+            _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank, pb.ptr_array(pb.h_gown, 0, 4),
+                                                 _stream()), "cafe_shard_push_grads")
             pb.fence()
-            if model._gbuf is None or model._gbuf.numel() != G * Bl * Fg * D:
-                model._gbuf = torch.empty(G * Bl * Fg * D, dtype=torch.float32, device=pb.grad.device)
-                model._imp = torch.empty(G * Bl * Fg, dtype=torch.float32, device=pb.grad.device)
-            src = pb.ptr_array(pb.h_grad, pb.block_off[plan.rank], 4)
-            _lib.check(lib.cafe_shard_pull_importance(grp.sketch.handle, src, G, Bl, Fg, D, D, Fg * D, model._gbuf.data_ptr(),
-                                                      model._imp.data_ptr(), _stream()), "cafe_shard_pull_importance")
-            wp, hp = f.ptrs()
-            grp.last_status = _lib.check(lib.cafe_embed_backward_imp(
-                grp.sketch.handle, model._gbuf.data_ptr(), D, Fg * D, model._imp.data_ptr(), own.data_ptr(), 1, gid.data_ptr(),
-                row.data_ptr(), Fg, G * Bl, f.f_offset, f.hash_size, wp, hp, f.hotn, D, float(grp.lr), grp.insert_mode, None,
-                _stream()), "cafe_embed_backward_imp")
+            # ... and every owner runs the ordinary fused backward on its local buffer [G*B_local, F_g, D]
+            grp.last_status = f.backward(pb.gown, D, Fg * D, own, gid, row, G * Bl, grp.lr, grp.insert_mode)
         return None, None, None
 
 

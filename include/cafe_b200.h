@@ -158,6 +158,12 @@ int cafe_embed_forward_sharded(void* handle, const void* ids_dev, int ids_are_in
 int cafe_shard_pull_importance(void* handle, const float* const* grad_rank, int nranks, int rows_per_rank, int nfields,
                                int D, int64_t field_stride, int64_t sample_stride, float* local_grad_dev,
                                float* imp_out_dev, void* stream);
+/* The same exchange driven from the other side (stores instead of loads over NVLink): this rank's
+ * gradient buffer holds, per owner g, a block [rows, F_g, D]; each row is stored into owner g's
+ * buffer owner_grad[g] ([nranks*rows, F_g, D]) at sample rank*rows + b.  The owner then runs the
+ * ordinary cafe_embed_backward on its local buffer. */
+int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                          float* const* owner_grad, void* stream);
 /* cafe_embed_backward for a caller that already holds the importance array. */
 int cafe_embed_backward_imp(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
                             const float* imp_dev, const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev,

@@ -73,6 +73,14 @@ def test_emulated_two_rank_exchange_matches_unsharded_calls():
 
     # --- backward: owners pull gradient rows from the consumers' buffers and get the importance
     gradc = [torch.randn(Bl * F * D, device="cuda") * 0.01 for _ in range(G)]
+    # (the same exchange driven by the consumers: every rank stores its rows into the owners' buffers)
+    owner_grad = [torch.zeros(G * Bl * fmax * D, device="cuda") for _ in range(G)]
+    for r in range(G):
+        assert lib.cafe_shard_push_grads(gradc[r].data_ptr(), F, Bl, D, G, r, _ptrs(owner_grad), _stream()) == 0
+    for g in range(G):
+        Fg = groups[g].num_fields
+        want = torch.cat([plans[r].blocks(gradc[r], Bl, D)[g] for r in range(G)], dim=0)
+        assert torch.equal(owner_grad[g][:G * Bl * Fg * D].view(G * Bl, Fg, D), want)
     for g in range(G):
         grp = groups[g]
         Fg = grp.num_fields
