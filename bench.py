@@ -243,7 +243,7 @@ def run_ours(args, rank, world, local_rank):
         import datetime
         # a short timeout: a rank that stops (an exception, a mismatch) ends the job instead of hanging it
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
-    cards = S.MICRO_CARDS
+    cards = S.MICRO_CARDS[:args.fields]
     F, D, B = len(cards), DIM, args.batch
     if world > 1:
         from cafe_b200.sharded import ShardedSKEmbedding
@@ -376,6 +376,7 @@ def main():
     ap.add_argument("--cpu-batch", type=int, default=16384, help="batch of the CPU baseline sample")
     ap.add_argument("--cpu-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fields", type=int, default=26, help="use only the first N fields of the workload (experiments)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU exchange of pooled rows / gradients")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
