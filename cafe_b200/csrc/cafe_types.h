@@ -59,6 +59,7 @@ struct alignas(16) CafeEvent {
 // Totals one round of the parallel insert reports to the host.
 struct CafeRoundResult {
     int32_t changed;       // beliefs consumed this round differ from the ones it produced
+    int32_t tl_changed;    // ... in particular the FIFO timeline
     int32_t n_miss;        // lookups that went to the LRU stage
     int32_t num_delta;     // hot rows handed out
     int32_t n_pop_ok;      // successful pops of the free-row FIFO

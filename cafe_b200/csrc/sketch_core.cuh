@@ -242,6 +242,7 @@ struct CafeJob {
     // round control
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
+    int32_t cand_active;   // the FIFO timeline changed in the previous round: buckets with ids waiting for a row replay
     int32_t diag;          // timing experiments only (changes results): see k_main_pass
     int32_t long_main;     // device hint: main buckets with more lookups than this are fed by a whole warp
     int32_t long_lru;      // same for LRU buckets
@@ -338,9 +339,14 @@ struct CafeMainReplay {
         cond_now = false;
         if (!J.first_round) {
             const uint32_t st = J.mstate[k];
-            cond_now = J.head[k] >= 0 || J.mark_own[k] != 0 || (st & CAFE_S_CAND) != 0;
+            // cond_now: events land here, so results depend on beliefs that may be withdrawn later (one more
+            // replay after the last such round returns the bucket to its belief-free result); an id waiting
+            // for a row makes the results depend on the FIFO timeline only, which needs a replay exactly when
+            // the timeline changed
+            cond_now = J.head[k] >= 0 || J.mark_own[k] != 0;
+            const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
             const bool active = J.final_pass ? (st & CAFE_S_DIRTY) != 0
-                                             : (J.all_active || cond_now || (st & CAFE_S_COND) != 0);
+                                             : (J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0);
             if (!active) return false;
         }
         b = J.main_in[k];
@@ -481,8 +487,9 @@ struct CafeLruReplay {
         cond_now = false;
         if (!J.first_round) {
             const uint32_t st = J.lstate[k];
-            cond_now = J.mark2[k] != 0 || (st & CAFE_S_CAND) != 0;
-            if (!(J.all_active || cond_now || (st & CAFE_S_COND) != 0)) return false;
+            cond_now = J.mark2[k] != 0;
+            const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
+            if (!(J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0)) return false;
         }
         b = J.lru_in[k];
         n_ev = 0;
@@ -691,7 +698,7 @@ CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
     J.tl_size_new[2 * (int64_t)p + 1] = sz[1];
     J.tl_rank_new[2 * (int64_t)p] = rk[0];
     J.tl_rank_new[2 * (int64_t)p + 1] = rk[1];
-    if (diff) J.res->changed = 1;
+    if (diff) { J.res->changed = 1; J.res->tl_changed = 1; }
     if (p == J.limit - 1) {
         // totals: prefix up to p plus p's own outcomes
         int32_t my_pops = 0, my_push = 0, s2 = sz[0];

@@ -368,7 +368,7 @@ private:
 
         CafeRoundResult R;
         int rounds = 0;
-        bool truncated = false, shortened = false;
+        bool truncated = false, shortened = false, tl_changed_prev = true;
         int pb = 0;   // index of the FIFO timeline consumed this round
         bool first = true;
         for (;;) {
@@ -383,6 +383,7 @@ private:
             }
             J.first_round = first ? 1 : 0;
             J.all_active = (first || shortened) ? 1 : 0;
+            J.cand_active = (first || tl_changed_prev) ? 1 : 0;
             J.final_pass = 0;
             shortened = false;
             J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
@@ -400,6 +401,7 @@ private:
             if (!be.ok()) return last_status = CAFE_ERR_CUDA;
             ++rounds; ++stats.rounds;
             first = false;
+            tl_changed_prev = R.tl_changed != 0;
             pb ^= 1;
             if (diag) fprintf(stderr, "round %d begin %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.begin, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
@@ -429,7 +431,7 @@ private:
             break;
         }
         // converged: the timeline just produced (index pb) equals the one consumed
-        J.first_round = 0; J.all_active = 0;
+        J.first_round = 0; J.all_active = 0; J.cand_active = 1;
         J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
         if (post_row) {
             be.memset(post_row + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
