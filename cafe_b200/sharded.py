@@ -222,13 +222,18 @@ class ShardedSKEmbedding(torch.nn.Module):
 
     def __init__(self, num_categories, embedding_dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1,
                  sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None,
-                 exchange="peer"):
+                 exchange="peer", f_offsets=None):
         super().__init__()
         from .sk_embedding_bag import SKEmbeddingGroup
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         cards = [int(n) for n in num_categories]
+        self.num_categories = cards
         self.plan = FieldShardPlan(len(cards), world, rank)
-        offs = sizing.field_offsets(cards)
+        # global ids (id + offset) must stay below 2**31; with very many fields pass offsets that are only
+        # distinct within each rank (ranks never share sketch state)
+        offs = list(f_offsets) if f_offsets is not None else sizing.field_offsets(cards)
+        if max(o + n for o, n in zip(offs, cards)) > 2 ** 31:
+            raise ValueError("field offsets push ids beyond 2**31; pass per-rank offsets via f_offsets")
         mine = self.plan.local_fields
         if not mine:
             raise ValueError("more ranks than fields")
@@ -268,7 +273,7 @@ class ShardedSKEmbedding(torch.nn.Module):
         nb = 4
         import numpy as np
         from . import synthetic
-        cards = synthetic.MICRO_CARDS
+        cards = self.num_categories
         host = [torch.from_numpy(S.batch_ids(cards, Bl, zipf_s, seed + 7919 * plan.rank, s)).pin_memory() for s in range(nb)]
         devi = [h.to(dev) for h in host]
         g = torch.Generator(device=dev).manual_seed(seed + plan.rank)
