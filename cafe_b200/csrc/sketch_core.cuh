@@ -303,7 +303,8 @@ CAFE_HD int cafe_next_event(const CafeJob& J, int head, int after) {
     return best;
 }
 
-// old beliefs of a position; never read in the first round (the buffers are uninitialised then)
+// old beliefs of a position; in the first round they are known to be empty (the engine clears the window's
+// flags and events before it) and are not read
 CAFE_HD uint32_t cafe_old_kind(const CafeJob& J, int p) { return J.first_round ? (uint32_t)CAFE_EV_NONE : J.ev[p].kind; }
 CAFE_HD uint32_t cafe_old_mflag(const CafeJob& J, int p) { return J.first_round ? 0u : (uint32_t)J.mflag[p]; }
 
@@ -432,9 +433,10 @@ struct CafeMainReplay {
             }
             set(s, x, cn, dic0);
             if (!J.final_pass) {
-                J.mflag[p] = (uint8_t)nf;
-                if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
-                else {
+                // flags and events of the job's window are zero before the first round, so a plain hit
+                // (no flag set) has nothing to store then; later rounds store what changed
+                if (nf != old_flag) J.mflag[p] = (uint8_t)nf;
+                if (!J.first_round) {
                     if (old_kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
                     if (old_flag & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;   // its LRU bucket loses this visitor
                 }
@@ -442,7 +444,7 @@ struct CafeMainReplay {
         } else {
             if (J.final_pass) note_cand(p, x);
             else {
-                J.mflag[p] = CAFE_F_MISS;   // goes to the LRU stage; that pass writes lflag
+                if (old_flag != CAFE_F_MISS) J.mflag[p] = CAFE_F_MISS;   // goes to the LRU stage; that pass writes lflag
                 if (!J.first_round && !(old_flag & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor
             }
             if (old_kind == CAFE_EV_OWN) {   // believed: this lookup promotes its own id into this bucket
@@ -502,7 +504,7 @@ struct CafeLruReplay {
     }
     CAFE_HD void emit(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
         if (J.first_round) {
-            if (kind == CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; return; }
+            if (kind == CAFE_EV_NONE) return;   // events of the window are cleared before the first round
             J.res->changed = 1;
         } else {
             const CafeEvent o = J.ev[p];

@@ -110,7 +110,9 @@ __global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_le
 }
 
 __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up
     const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
     bool hot_warp;
     const int k = cafe_bucket_of_thread(H, J.n1, &hot_warp);
     CafeMainReplay R;
@@ -185,22 +187,46 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) cnt0 = R.b.cnt[q];
                 }
                 float acc = __shfl_sync(CAFE_FULL, cnt0, o);
+                // Far above the threshold (count > 2*thr, every addend in [0, count]) no lookup of the chunk
+                // can satisfy the crossing test "cn >= thr && cn - c < thr" (sketch.cpp:218): cn - c stays
+                // within two ulps of a value >= 2*thr.  Then all 32 flags are zero and only the sum is
+                // needed; otherwise every lane keeps the running count as of its own lookup.
+                const bool calm = acc > 2.0f * J.thr && __all_sync(CAFE_FULL, c >= 0.f && c <= acc);
                 float my_acc = 0.f;
+                // the 32 counts go through shared memory: every lane reads them back as 8 broadcast 16-byte
+                // loads and runs the same chain of 32 dependent adds
+                s_c[wib][lane] = c;
+                __syncwarp();
+                {
+                    const float4* cv = reinterpret_cast<const float4*>(s_c[wib]);
+                    if (calm) {
 #pragma unroll
-                for (int u = 0; u < 32; ++u) {
-                    acc = acc + __shfl_sync(CAFE_FULL, c, u);
-                    if (lane == u) my_acc = acc;
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 t = cv[q];
+                            acc = acc + t.x; acc = acc + t.y; acc = acc + t.z; acc = acc + t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 t = cv[q];
+                            acc = acc + t.x; if (lane == 4 * q) my_acc = acc;
+                            acc = acc + t.y; if (lane == 4 * q + 1) my_acc = acc;
+                            acc = acc + t.z; if (lane == 4 * q + 2) my_acc = acc;
+                            acc = acc + t.w; if (lane == 4 * q + 3) my_acc = acc;
+                        }
+                    }
                 }
+                __syncwarp();
                 if (lane == o) {
 #pragma unroll
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
                     R.i_cur += 32;
                 }
                 if (!J.final_pass) {
-                    const bool cr = (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
-                    J.mflag[p] = (uint8_t)(cr ? CAFE_F_CROSS : 0);
-                    if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
-                    else {
+                    const bool cr = !calm && (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
+                    const uint32_t nf = cr ? CAFE_F_CROSS : 0;
+                    if (nf != of) J.mflag[p] = (uint8_t)nf;
+                    if (!J.first_round) {
                         if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
                         if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                     }
@@ -270,9 +296,9 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                         }
                         if (!J.final_pass && in_done) {
                             const bool cr = (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
-                            J.mflag[p] = (uint8_t)((cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0));
-                            if (J.first_round) J.ev[p].kind = CAFE_EV_NONE;
-                            else {
+                            const uint32_t nf = (cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0);
+                            if (nf != of) J.mflag[p] = (uint8_t)nf;
+                            if (!J.first_round) {
                                 if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
                                 if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                             }

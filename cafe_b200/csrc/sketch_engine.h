@@ -365,6 +365,8 @@ private:
         J.diag = getenv("CAFE_B200_EXPERIMENT") ? atoi(getenv("CAFE_B200_EXPERIMENT")) : 0;
         ++stats.jobs;
         be.memset(ins_res + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
+        be.memset(mflag + J.begin, 0, (size_t)(J.limit - J.begin));
+        be.memset(ev + J.begin, 0, sizeof(CafeEvent) * (size_t)(J.limit - J.begin));   // kind 0 = no event
 
         CafeRoundResult R;
         int rounds = 0;
