@@ -326,6 +326,24 @@ class SKEmbeddingGroup(nn.Module):
         self.last_status = 0
         self.last_rows = None
 
+    # ---- checkpointing: the sketch travels with the module's state_dict ----------------------------------
+    # (the reference cannot resume a CAFE run: its sketch state is never saved and the lib.update() it calls
+    # on load does not exist, dlrm_s_pytorch.py:1488-1511)
+    def get_extra_state(self):
+        st = self.sketch.state()
+        return {k: (torch.from_numpy(v.astype(np.int64) if v.dtype == np.uint32 else v) if isinstance(v, np.ndarray) else v)
+                for k, v in st.items()}
+
+    def set_extra_state(self, state):
+        st = {}
+        for k, v in state.items():
+            if isinstance(v, torch.Tensor):
+                a = v.cpu().numpy()
+                st[k] = a.astype(np.uint32) if k in ("main_val", "lru_val", "queue") else a
+            else:
+                st[k] = v
+        self.sketch.load_state(st)
+
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         if ids.dim() != 2 or ids.shape[0] != self.num_fields:
             raise ValueError("ids must be [num_fields, batch]")

@@ -206,3 +206,29 @@ def test_reference_compatible_sparse_gradients():
             exp_h.index_add_(0, (-rows[hot]).long(), -0.5 * g[hot])
             touched = torch.unique((-rows[hot]).long())
             np.testing.assert_allclose(wh.detach()[touched].cpu().numpy(), exp_h[touched].cpu().numpy(), rtol=RTOL, atol=1e-6)
+
+
+def test_checkpoint_resume_through_state_dict(tmp_path):
+    """torch.save(model.state_dict()) carries the sketch; a resumed run continues bit for bit."""
+    import torch
+    import cafe_b200
+    cards, D, B = [5000, 120000, 800000], 16, 128
+    rng = np.random.default_rng(8)
+    a = cafe_b200.SKEmbeddingGroup(cards, D, 0.01, 0.3, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=1)
+    batches = [np.stack([zipf_ids(rng, n, B) for n in cards]) for _ in range(12)]
+    grads = [torch.from_numpy((rng.standard_normal((B, 3, D)) * 0.01).astype(np.float32)).cuda() for _ in range(12)]
+    for s in range(6):
+        a(torch.from_numpy(batches[s])).backward(grads[s])
+    torch.save(a.state_dict(), tmp_path / "ckpt.pt")
+    b = cafe_b200.SKEmbeddingGroup(cards, D, 0.01, 0.3, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=99)
+    b.load_state_dict(torch.load(tmp_path / "ckpt.pt", weights_only=False))
+    for s in range(6, 12):
+        oa = a(torch.from_numpy(batches[s]))
+        ob = b(torch.from_numpy(batches[s]))
+        assert torch.equal(oa, ob)
+        oa.backward(grads[s])
+        ob.backward(grads[s])
+    assert states_equal(a.sketch.state(), b.sketch.state()) == []
+    assert torch.equal(a.weight_high, b.weight_high)
+    for wa, wb in zip(a.weight_hash, b.weight_hash):
+        assert torch.equal(wa, wb)
