@@ -27,6 +27,8 @@ struct CafeEmbedWorkspace {
     float* partial = nullptr;    // [2 * ceil(cap/CAFE_CHUNK) * CAFE_MAX_DIM] partial row sums of chunk-spanning rows
     void* cub_tmp = nullptr;
     size_t cub_bytes = 0;
+    cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn);

@@ -436,6 +436,9 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
                                     (int32_t*)nullptr, cap, 0, 32, (cudaStream_t)0);
     ws->cub_bytes = b + 1024;
     A(&ws->cub_tmp, ws->cub_bytes);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_join, cudaEventDisableTiming);
     if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
     return CAFE_OK;
 }
@@ -444,6 +447,9 @@ void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
     void* ptrs[] = {ws->norm, ws->imp, ws->totals, ws->mask, ws->post_row, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1],
                     ws->partial, ws->cub_tmp};
     for (void* p : ptrs) if (p) cudaFree(p);
+    if (ws->side) { cudaStreamSynchronize(ws->side); cudaStreamDestroy(ws->side); }
+    if (ws->ev_fork) cudaEventDestroy(ws->ev_fork);
+    if (ws->ev_join) cudaEventDestroy(ws->ev_join);
     *ws = CafeEmbedWorkspace();
 }
 
@@ -637,28 +643,24 @@ int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t*
     return fail_cuda("cafe_migrate");
 }
 
-int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
-                     const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
-                     float* weight_high, int hotn, int D, float lr, void* stream) {
-    if (!h) return CAFE_ERR_ARG;
-    CafeFields F;
-    int64_t zero_off[CAFE_MAX_SEGMENTS] = {0};
-    int rc = fill_fields(&F, nfields, B, D, hotn, zero_off, hash_size, weight_hash, weight_high);
-    if (rc != CAFE_OK) return rc;
-    const int total = nfields * B;
-    if (total == 0) return CAFE_OK;
-    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
-    if (total > ws->cap) return CAFE_ERR_CAPACITY;
-    if (!grad_dev || !row_dev || !strides_ok(grad_dev, field_stride, sample_stride)) return CAFE_ERR_ARG;
-    cudaStream_t st = (cudaStream_t)stream;
+// The scatter in two parts.  scatter_prepare needs only the forward's row numbers (unified row keys and
+// their radix sort); scatter_apply reads the sorted keys, the gradient and the tables.  The split lets a
+// caller run the first part on the workspace's side stream while the sketch insert runs on the main one.
+static int scatter_prepare(CafeEmbedWorkspace* ws, const CafeFields& F, const int32_t* row_dev, int total, int hotn,
+                           cudaStream_t st) {
     { CAFE_PROF(CAFE_P_ROWKEYS, st); k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0], ws->pos[0]); }
     int bits = 1;
-    while ((1ll << bits) < (int64_t)hotn + F.hash_base[nfields]) ++bits;
+    while ((1ll << bits) < (int64_t)hotn + F.hash_base[F.nfields]) ++bits;
     size_t b = ws->cub_bytes;
     cudaError_t e;
     { CAFE_PROF(CAFE_P_ROWSORT, st);
       e = cub::DeviceRadixSort::SortPairs(ws->cub_tmp, b, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1], total, 0, bits, st); }
     if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
+    return CAFE_OK;
+}
+
+static int scatter_apply(CafeEmbedWorkspace* ws, const CafeFields& F, const float* grad_dev, int64_t field_stride,
+                         int64_t sample_stride, int total, int D, float lr, cudaStream_t st) {
     const int64_t chunks = ((int64_t)total + CAFE_CHUNK - 1) / CAFE_CHUNK;
     { CAFE_PROF(CAFE_P_SCATTER, st);
     DISPATCH_G(D, (k_scatter_chunks<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, grad_dev, field_stride,
@@ -667,6 +669,48 @@ int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64
     DISPATCH_G(D, (k_scatter_fixup<G><<<(unsigned)((chunks * G + 255) / 256), 256, 0, st>>>(F, ws->key[1], ws->pos[1], total,
                    lr, ws->partial))); }
     return fail_cuda("cafe_scatter_sgd");
+}
+
+static int scatter_check(void* h, CafeFields* F, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                         const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                         float* weight_high, int hotn, int D) {
+    if (!h) return CAFE_ERR_ARG;
+    int64_t zero_off[CAFE_MAX_SEGMENTS] = {0};
+    int rc = fill_fields(F, nfields, B, D, hotn, zero_off, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    if ((int64_t)nfields * B > cafe_internal_ws(h)->cap) return CAFE_ERR_CAPACITY;
+    if (nfields * B > 0 && (!grad_dev || !row_dev || !strides_ok(grad_dev, field_stride, sample_stride))) return CAFE_ERR_ARG;
+    return CAFE_OK;
+}
+
+int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                     const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                     float* weight_high, int hotn, int D, float lr, void* stream) {
+    CafeFields F;
+    int rc = scatter_check(h, &F, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
+                           weight_high, hotn, D);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    rc = scatter_prepare(ws, F, row_dev, total, hotn, st);
+    if (rc != CAFE_OK) return rc;
+    return scatter_apply(ws, F, grad_dev, field_stride, sample_stride, total, D, lr, st);
+}
+
+// Starts scatter_prepare on the side stream, ordered after everything already queued on `st`.
+static int scatter_prepare_aside(CafeEmbedWorkspace* ws, const CafeFields& F, const int32_t* row_dev, int total, int hotn,
+                                 cudaStream_t st) {
+    if (cudaEventRecord(ws->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ws->side, ws->ev_fork, 0) != cudaSuccess)
+        return fail_cuda("scatter fork");
+    int rc = scatter_prepare(ws, F, row_dev, total, hotn, ws->side);
+    // the join is recorded even after a failure so that the main stream never waits on a stale event
+    if (cudaEventRecord(ws->ev_join, ws->side) != cudaSuccess) return fail_cuda("scatter join");
+    return rc;
+}
+static int scatter_join(CafeEmbedWorkspace* ws, cudaStream_t st) {
+    return cudaStreamWaitEvent(st, ws->ev_join, 0) == cudaSuccess ? CAFE_OK : fail_cuda("scatter join wait");
 }
 
 // The whole post-backward part of one training step for `nfields` fields, in the reference's order:
@@ -682,18 +726,25 @@ int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, in
     const int64_t total = (int64_t)nfields * B;
     if (total > ws->cap) return CAFE_ERR_CAPACITY;
     if (total == 0) return CAFE_OK;
-    int rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
+    CafeFields FS;
+    int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
+                           weight_high, hotn, D);
     if (rc != CAFE_OK) return rc;
+    rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
+    if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
+    rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
+    if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
     int seg[CAFE_MAX_SEGMENTS + 1];
     for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
     int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
     int status = cafe_internal_insert(h, gid_dev, ws->imp, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
+    rc = scatter_join(ws, (cudaStream_t)stream);
     if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
+    if (rc != CAFE_OK) return rc;
     rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
                       hotn, D, n_migrated_dev, stream);
     if (rc != CAFE_OK) return rc;
-    rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
-                          hotn, D, lr, stream);
+    rc = scatter_apply(ws, FS, grad_dev, field_stride, sample_stride, (int)total, D, lr, (cudaStream_t)stream);
     return rc != CAFE_OK ? rc : status;
 }
 
@@ -775,13 +826,20 @@ int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride
     int seg[CAFE_MAX_SEGMENTS + 1];
     for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
     int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
-    int status = cafe_internal_insert(h, gid_dev, imp_dev, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
-    if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
-    int rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
-                          hotn, D, nullptr, stream);
+    CafeFields FS;
+    int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
+                           weight_high, hotn, D);
     if (rc != CAFE_OK) return rc;
-    rc = cafe_scatter_sgd(h, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash, weight_high,
-                          hotn, D, lr, stream);
+    rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
+    if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
+    int status = cafe_internal_insert(h, gid_dev, imp_dev, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
+    rc = scatter_join(ws, (cudaStream_t)stream);
+    if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
+    if (rc != CAFE_OK) return rc;
+    rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
+                      hotn, D, nullptr, stream);
+    if (rc != CAFE_OK) return rc;
+    rc = scatter_apply(ws, FS, grad_dev, field_stride, sample_stride, (int)total, D, lr, (cudaStream_t)stream);
     return rc != CAFE_OK ? rc : status;
 }
 

@@ -541,8 +541,14 @@ struct CudaBackend {
     cudaError_t err = cudaSuccess;
     void* cub_tmp = nullptr;
     size_t cub_bytes = 0;
-    uint32_t *key_in = nullptr, *key_out = nullptr;
-    int32_t* pos_in = nullptr;
+    // lane 0 sorts on `stream`; lane 1 on `side` with buffers of its own, forked from and joined to `stream`
+    void* sort_tmp[2] = {nullptr, nullptr};
+    size_t sort_bytes = 0;
+    uint32_t *key_in[2] = {nullptr, nullptr}, *key_out[2] = {nullptr, nullptr};
+    int32_t* pos_in[2] = {nullptr, nullptr};
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool side_pending = false;
     int64_t* scan64 = nullptr;   // [4*(n1+n2)] prefix sums of the threshold re-fit
     int32_t* hot_list[2] = {nullptr, nullptr};   // listed long buckets of the main / LRU table
     int32_t* hot_count[2] = {nullptr, nullptr};
@@ -553,9 +559,15 @@ struct CudaBackend {
 
     ~CudaBackend() {
         if (cub_tmp) cudaFree(cub_tmp);
-        if (key_in) cudaFree(key_in);
-        if (key_out) cudaFree(key_out);
-        if (pos_in) cudaFree(pos_in);
+        if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
+        if (ev_fork) cudaEventDestroy(ev_fork);
+        if (ev_join) cudaEventDestroy(ev_join);
+        for (int i = 0; i < 2; ++i) {
+            if (sort_tmp[i]) cudaFree(sort_tmp[i]);
+            if (key_in[i]) cudaFree(key_in[i]);
+            if (key_out[i]) cudaFree(key_out[i]);
+            if (pos_in[i]) cudaFree(pos_in[i]);
+        }
         if (scan64) cudaFree(scan64);
         for (int i = 0; i < 2; ++i) { if (hot_list[i]) cudaFree(hot_list[i]); if (hot_count[i]) cudaFree(hot_count[i]); if (hot_flag[i]) cudaFree(hot_flag[i]); }
         if (pinned) cudaFreeHost(pinned);
@@ -593,9 +605,21 @@ struct CudaBackend {
 
     bool prepare(int cap_, int n1, int n2) {
         cap = cap_;
-        check(cudaMalloc(&key_in, 4 * (size_t)cap));
-        check(cudaMalloc(&key_out, 4 * (size_t)cap));
-        check(cudaMalloc(&pos_in, 4 * (size_t)cap));
+        for (int i = 0; i < 2; ++i) {
+            check(cudaMalloc(&key_in[i], 4 * (size_t)cap));
+            check(cudaMalloc(&key_out[i], 4 * (size_t)cap));
+            check(cudaMalloc(&pos_in[i], 4 * (size_t)cap));
+        }
+        check(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+        check(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        check(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+        {
+            size_t sb = 0;
+            cub::DeviceRadixSort::SortPairs(nullptr, sb, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
+                                            (int32_t*)nullptr, cap, 0, 32, stream);
+            sort_bytes = sb + 1024;
+            for (int i = 0; i < 2; ++i) check(cudaMalloc(&sort_tmp[i], sort_bytes));
+        }
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
         for (int i = 0; i < 2; ++i) {
@@ -635,20 +659,40 @@ struct CudaBackend {
     static int bits_for(int nb) { int b = 1; while ((1ll << b) < nb) ++b; return b; }
 
     // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
-    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
-        CAFE_PROF(CAFE_P_LOOKUP_SORT, stream);
-        k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, stream>>>(gid, M, nb, key_in, pos_in);
+    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
+        cudaStream_t st = stream;
+        if (lane == 1) {
+            check(cudaEventRecord(ev_fork, stream));
+            check(cudaStreamWaitEvent(side, ev_fork, 0));
+            st = side;
+        }
+        {
+        CAFE_PROF(CAFE_P_LOOKUP_SORT, st);
+        k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, st>>>(gid, M, nb, key_in[lane], pos_in[lane]);
         check_launch();
-        size_t b = cub_bytes;
-        check(cub::DeviceRadixSort::SortPairs(cub_tmp, b, key_in, key_out, pos_in, ord, M, 0, bits_for(nb), stream));
-        k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, stream>>>(key_out, M, nb, start);
+        size_t b = sort_bytes;
+        check(cub::DeviceRadixSort::SortPairs(sort_tmp[lane], b, key_in[lane], key_out[lane], pos_in[lane], ord, M, 0,
+                                              bits_for(nb), st));
+        k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start);
         check_launch();
         const int t = (nb == hot_nb[0]) ? 0 : 1;
-        check(cudaMemsetAsync(hot_count[t], 0, 4, stream));
-        check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, stream));
+        check(cudaMemsetAsync(hot_count[t], 0, 4, st));
+        check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, st));
         const int hot_len = std::max(CAFE_HOT_LEN, (int)(16.0 * M / nb));
-        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, stream>>>(start, nb, hot_len, hot_list[t], hot_count[t], hot_flag[t]);
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, hot_list[t], hot_count[t], hot_flag[t]);
         check_launch();
+        check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
+        }
+        if (lane == 1) {
+            check(cudaEventRecord(ev_join, side));
+            side_pending = true;
+        }
+    }
+    // makes `stream` wait for the second lane's sort (no-op when none is outstanding)
+    void sort_join() {
+        if (!side_pending) return;
+        check(cudaStreamWaitEvent(stream, ev_join, 0));
+        side_pending = false;
     }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
     void main_pass(const CafeJob& J) {

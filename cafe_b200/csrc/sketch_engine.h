@@ -154,11 +154,12 @@ public:
             const float* im = imp ? imp + base : nullptr;
             int32_t* mk = mask ? mask + base : nullptr;
             int32_t* pr = post_row ? post_row + base : nullptr;
+            struct SortJoin { BE& be; ~SortJoin() { be.sort_join(); } } sort_join_guard{be};
             if (parallel && mtot > 0) {
-                be.sort_lookups(g, mtot, n1, ord1, start1);
-                be.sort_lookups(g, mtot, n2, ord2, start2);
-                be.copy(beg1, start1, 4 * (size_t)n1);
-                be.copy(beg2, start2, 4 * (size_t)n2);
+                // the LRU table's order is first needed by the first LRU pass: it is built on the
+                // backend's second lane while the main table's order and first pass proceed
+                be.sort_lookups(g, mtot, n2, ord2, start2, beg2, 1);
+                be.sort_lookups(g, mtot, n1, ord1, start1, beg1, 0);
             }
             while (s < se) {
                 call_boundary();
@@ -397,6 +398,7 @@ private:
                 be.route(J);
             }
             be.main_pass(J);
+            be.sort_join();
             be.lru_pass(J);
             be.resolve(J);
             be.d2h(&R, res_dev, sizeof(R));

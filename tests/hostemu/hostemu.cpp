@@ -41,7 +41,13 @@ struct HostBackend {
     void post_query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, const int32_t* mask, int32_t* out) {
         for (int i = 0; i < n; ++i) out[i] = mask[i] ? cafe_probe_hot(mb[cafe_hash(gid[i], n1)], gid[i]) : 0;
     }
-    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
+    void sort_join() {}
+    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
+        (void)lane;
+        sort_lookups_impl(gid, M, nb, ord, start);
+        memcpy(beg, start, 4 * (size_t)nb);
+    }
+    void sort_lookups_impl(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
         std::vector<int32_t> key((size_t)M);
         for (int i = 0; i < M; ++i) key[i] = cafe_hash(gid[i], nb);
         std::iota(ord, ord + M, 0);
