@@ -38,6 +38,8 @@ CafeSketchView cafe_internal_view(void* h);
 CafeEmbedWorkspace* cafe_internal_ws(void* h);
 int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const int* seg_off, int nseg, int32_t* mask,
                          int32_t* post_row, int mode, cudaStream_t stream);
+// starts the insert's bucket sorts of `gid` beside whatever the caller queues next on `stream`
+void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t stream);
 void cafe_internal_set_error(const char* msg);
 
 // ---- per-kernel timing and launch counting (prof.cu) ------------------------------------------------

@@ -732,8 +732,13 @@ int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, in
     if (rc != CAFE_OK) return rc;
     rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
     if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
+    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, (int)total, (cudaStream_t)stream);
     rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
-    if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
+    if (rc != CAFE_OK) {
+        cafe_internal_presort(h, nullptr, 0, (cudaStream_t)stream);   // withdraws the sorts started above
+        scatter_join(ws, (cudaStream_t)stream);
+        return rc;
+    }
     int seg[CAFE_MAX_SEGMENTS + 1];
     for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
     int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
@@ -832,6 +837,7 @@ int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride
     if (rc != CAFE_OK) return rc;
     rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
     if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
+    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, (int)total, (cudaStream_t)stream);
     int status = cafe_internal_insert(h, gid_dev, imp_dev, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
     rc = scatter_join(ws, (cudaStream_t)stream);
     if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;

@@ -541,14 +541,16 @@ struct CudaBackend {
     cudaError_t err = cudaSuccess;
     void* cub_tmp = nullptr;
     size_t cub_bytes = 0;
-    // lane 0 sorts on `stream`; lane 1 on `side` with buffers of its own, forked from and joined to `stream`
-    void* sort_tmp[2] = {nullptr, nullptr};
+    // lane 0 sorts on `stream`; lanes 1 and 2 on side streams with buffers of their own, forked from
+    // and joined to `stream`
+    static const int LANES = 3;
+    void* sort_tmp[LANES] = {nullptr, nullptr, nullptr};
     size_t sort_bytes = 0;
-    uint32_t *key_in[2] = {nullptr, nullptr}, *key_out[2] = {nullptr, nullptr};
-    int32_t* pos_in[2] = {nullptr, nullptr};
-    cudaStream_t side = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-    bool side_pending = false;
+    uint32_t *key_in[LANES] = {nullptr, nullptr, nullptr}, *key_out[LANES] = {nullptr, nullptr, nullptr};
+    int32_t* pos_in[LANES] = {nullptr, nullptr, nullptr};
+    cudaStream_t side[LANES] = {nullptr, nullptr, nullptr};
+    cudaEvent_t ev_fork[LANES] = {nullptr, nullptr, nullptr}, ev_join[LANES] = {nullptr, nullptr, nullptr};
+    bool side_pending[LANES] = {false, false, false};
     int64_t* scan64 = nullptr;   // [4*(n1+n2)] prefix sums of the threshold re-fit
     int32_t* hot_list[2] = {nullptr, nullptr};   // listed long buckets of the main / LRU table
     int32_t* hot_count[2] = {nullptr, nullptr};
@@ -559,10 +561,10 @@ struct CudaBackend {
 
     ~CudaBackend() {
         if (cub_tmp) cudaFree(cub_tmp);
-        if (side) { cudaStreamSynchronize(side); cudaStreamDestroy(side); }
-        if (ev_fork) cudaEventDestroy(ev_fork);
-        if (ev_join) cudaEventDestroy(ev_join);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < LANES; ++i) {
+            if (side[i]) { cudaStreamSynchronize(side[i]); cudaStreamDestroy(side[i]); }
+            if (ev_fork[i]) cudaEventDestroy(ev_fork[i]);
+            if (ev_join[i]) cudaEventDestroy(ev_join[i]);
             if (sort_tmp[i]) cudaFree(sort_tmp[i]);
             if (key_in[i]) cudaFree(key_in[i]);
             if (key_out[i]) cudaFree(key_out[i]);
@@ -605,20 +607,21 @@ struct CudaBackend {
 
     bool prepare(int cap_, int n1, int n2) {
         cap = cap_;
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < LANES; ++i) {
             check(cudaMalloc(&key_in[i], 4 * (size_t)cap));
             check(cudaMalloc(&key_out[i], 4 * (size_t)cap));
             check(cudaMalloc(&pos_in[i], 4 * (size_t)cap));
+            if (i == 0) continue;
+            check(cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking));
+            check(cudaEventCreateWithFlags(&ev_fork[i], cudaEventDisableTiming));
+            check(cudaEventCreateWithFlags(&ev_join[i], cudaEventDisableTiming));
         }
-        check(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
-        check(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
-        check(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
         {
             size_t sb = 0;
             cub::DeviceRadixSort::SortPairs(nullptr, sb, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
                                             (int32_t*)nullptr, cap, 0, 32, stream);
             sort_bytes = sb + 1024;
-            for (int i = 0; i < 2; ++i) check(cudaMalloc(&sort_tmp[i], sort_bytes));
+            for (int i = 0; i < LANES; ++i) check(cudaMalloc(&sort_tmp[i], sort_bytes));
         }
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
@@ -661,10 +664,10 @@ struct CudaBackend {
     // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
         cudaStream_t st = stream;
-        if (lane == 1) {
-            check(cudaEventRecord(ev_fork, stream));
-            check(cudaStreamWaitEvent(side, ev_fork, 0));
-            st = side;
+        if (lane != 0) {
+            check(cudaEventRecord(ev_fork[lane], stream));
+            check(cudaStreamWaitEvent(side[lane], ev_fork[lane], 0));
+            st = side[lane];
         }
         {
         CAFE_PROF(CAFE_P_LOOKUP_SORT, st);
@@ -683,16 +686,18 @@ struct CudaBackend {
         check_launch();
         check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
         }
-        if (lane == 1) {
-            check(cudaEventRecord(ev_join, side));
-            side_pending = true;
+        if (lane != 0) {
+            check(cudaEventRecord(ev_join[lane], side[lane]));
+            side_pending[lane] = true;
         }
     }
-    // makes `stream` wait for the second lane's sort (no-op when none is outstanding)
-    void sort_join() {
-        if (!side_pending) return;
-        check(cudaStreamWaitEvent(stream, ev_join, 0));
-        side_pending = false;
+    // makes `stream` wait for the sorts outstanding on the side lanes (no-op when there are none)
+    void sort_join(int which) {
+        for (int lane = 1; lane < LANES; ++lane) {
+            if (!side_pending[lane] || (which >= 0 && which != lane)) continue;
+            check(cudaStreamWaitEvent(stream, ev_join[lane], 0));
+            side_pending[lane] = false;
+        }
     }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
     void main_pass(const CafeJob& J) {
@@ -815,6 +820,11 @@ int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const i
     H->eng.be.stream = stream;
     int rc = H->eng.insert_segments(gid, imp, seg_off, nseg, mask, post_row, mode != CAFE_INSERT_SEQUENTIAL);
     return finish(H, rc, "cafe_sketch_insert");
+}
+void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t stream) {
+    CafeHandle* H = (CafeHandle*)h;
+    H->eng.be.stream = stream;
+    H->eng.presort(gid, n);
 }
 void cafe_internal_set_error(const char* msg) { g_last_error = msg; }
 

@@ -131,6 +131,18 @@ public:
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
     }
 
+    // Starts the bucket sorts of the next insert_segments call early, on the backend's side lanes, for
+    // a caller that knows the ids before it knows the counts.  Only honoured when that call passes the
+    // same pointer and its whole input is one stretch of n lookups.
+    void presort(const uint32_t* gid, int n) {
+        presorted_gid = nullptr;
+        if (ready) be.sort_join(-1);   // a null gid withdraws an earlier presort
+        if (!ready || !gid || n <= 0 || n > cap) return;
+        be.sort_lookups(gid, n, n1, ord1, start1, beg1, 1);
+        be.sort_lookups(gid, n, n2, ord2, start2, beg2, 2);
+        presorted_gid = gid; presorted_n = n;
+    }
+
     // One batch_insert_val call per segment, in order (imp == null: batch_insert, unit counts).
     // mask[p] = the reference's per-lookup result; post_row[p] (optional) = hot row a query would
     // return for the id right after its own segment's call (0 = none).  parallel=false runs the
@@ -154,13 +166,14 @@ public:
             const float* im = imp ? imp + base : nullptr;
             int32_t* mk = mask ? mask + base : nullptr;
             int32_t* pr = post_row ? post_row + base : nullptr;
-            struct SortJoin { BE& be; ~SortJoin() { be.sort_join(); } } sort_join_guard{be};
-            if (parallel && mtot > 0) {
-                // the LRU table's order is first needed by the first LRU pass: it is built on the
-                // backend's second lane while the main table's order and first pass proceed
-                be.sort_lookups(g, mtot, n2, ord2, start2, beg2, 1);
+            struct SortJoin { BE& be; ~SortJoin() { be.sort_join(-1); } } sort_join_guard{be};
+            if (parallel && mtot > 0 && !(presorted_gid == g && presorted_n == mtot)) {
+                // the LRU table's order is first needed by the first LRU pass: it is built on a side
+                // lane of the backend while the main table's order and first pass proceed
+                be.sort_lookups(g, mtot, n2, ord2, start2, beg2, 2);
                 be.sort_lookups(g, mtot, n1, ord1, start1, beg1, 0);
             }
+            presorted_gid = nullptr;
             while (s < se) {
                 call_boundary();
                 if (last_status == CAFE_ERR_CUDA) return last_status;
@@ -190,6 +203,7 @@ public:
                         if (rc != CAFE_OK) return rc;
                         done_e = s + done;
                         const int upto = seg_off[done_e] - base;
+                        be.sort_join(-1);
                         be.advance_cursors(ord1, start1, beg1, n1, upto);
                         be.advance_cursors(ord2, start2, beg2, n2, upto);
                     } else {
@@ -275,6 +289,8 @@ public:
     }
 
 private:
+    const uint32_t* presorted_gid = nullptr;
+    int presorted_n = 0;
     bool ready = false;
     int cap = 0, cur = 0;
     CafeMainBucket* mainb[2] = {nullptr, nullptr};
@@ -397,8 +413,9 @@ private:
                 be.memset(mark_own, 0, span_clear);                   // mark_own + mark2 + round result
                 be.route(J);
             }
+            be.sort_join(1);
             be.main_pass(J);
-            be.sort_join();
+            be.sort_join(2);
             be.lru_pass(J);
             be.resolve(J);
             be.d2h(&R, res_dev, sizeof(R));

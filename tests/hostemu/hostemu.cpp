@@ -41,7 +41,7 @@ struct HostBackend {
     void post_query(const CafeMainBucket* mb, int n1, const uint32_t* gid, int n, const int32_t* mask, int32_t* out) {
         for (int i = 0; i < n; ++i) out[i] = mask[i] ? cafe_probe_hot(mb[cafe_hash(gid[i], n1)], gid[i]) : 0;
     }
-    void sort_join() {}
+    void sort_join(int) {}
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
         (void)lane;
         sort_lookups_impl(gid, M, nb, ord, start);
