@@ -50,6 +50,7 @@ SIGNATURES = {
                                  c_float, _vp]),
     "cafe_embed_backward": (c_int, [_vp, _vp, c_int64, c_int64, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                     POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp, _vp]),
+    "cafe_embed_backward_begin": (c_int, [_vp, _vp, _vp, c_int, c_int, _i32p, POINTER(_vp), _vp, c_int, c_int, c_int, _vp]),
     "cafe_shard_scatter_ids": (c_int, [_vp, c_int, c_int, c_int, c_int, POINTER(_vp), _vp]),
     "cafe_embed_forward_sharded": (c_int, [_vp, _vp, c_int, c_int, c_int, _i64p, _i32p, POINTER(_vp), _vp, c_int, c_int,
                                            POINTER(_vp), c_int, c_int, c_int64, c_int64, _vp, _vp, _vp]),

@@ -29,6 +29,10 @@ struct CafeEmbedWorkspace {
     size_t cub_bytes = 0;
     cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    // arrays whose side work cafe_embed_backward_begin has already started (null: none)
+    const uint32_t* begun_gid = nullptr;
+    const int32_t* begun_row = nullptr;
+    int begun_total = 0, begun_mode = 0;
 };
 
 int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn);

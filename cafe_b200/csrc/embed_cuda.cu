@@ -709,6 +709,19 @@ static int scatter_prepare_aside(CafeEmbedWorkspace* ws, const CafeFields& F, co
     if (cudaEventRecord(ws->ev_join, ws->side) != cudaSuccess) return fail_cuda("scatter join");
     return rc;
 }
+// Starts (or recognises as already started by cafe_embed_backward_begin) the side work of one backward
+// call: the scatter's row sort and, for the parallel insert, the sketch's bucket sorts.
+static int backward_side_work(void* h, CafeEmbedWorkspace* ws, const CafeFields& FS, const uint32_t* gid_dev,
+                              const int32_t* row_dev, int total, int hotn, int insert_mode, cudaStream_t st) {
+    const bool begun = ws->begun_gid == gid_dev && ws->begun_row == row_dev && ws->begun_total == total &&
+                       ws->begun_mode == insert_mode && gid_dev != nullptr;
+    ws->begun_gid = nullptr; ws->begun_row = nullptr; ws->begun_total = 0;
+    if (begun) return CAFE_OK;
+    int rc = scatter_prepare_aside(ws, FS, row_dev, total, hotn, st);
+    if (rc != CAFE_OK) return rc;
+    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, total, st);
+    return CAFE_OK;
+}
 static int scatter_join(CafeEmbedWorkspace* ws, cudaStream_t st) {
     return cudaStreamWaitEvent(st, ws->ev_join, 0) == cudaSuccess ? CAFE_OK : fail_cuda("scatter join wait");
 }
@@ -730,9 +743,8 @@ int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, in
     int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
                            weight_high, hotn, D);
     if (rc != CAFE_OK) return rc;
-    rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
+    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, (cudaStream_t)stream);
     if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
-    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, (int)total, (cudaStream_t)stream);
     rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
     if (rc != CAFE_OK) {
         cafe_internal_presort(h, nullptr, 0, (cudaStream_t)stream);   // withdraws the sorts started above
@@ -817,6 +829,25 @@ int cafe_shard_pull_importance(void* h, const float* const* grad_rank, int nrank
     return fail_cuda("cafe_shard_pull_importance");
 }
 
+int cafe_embed_backward_begin(void* h, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                              const int32_t* hash_size, float* const* weight_hash, float* weight_high, int hotn, int D,
+                              int insert_mode, void* stream) {
+    if (!h || !gid_dev || !row_dev) return CAFE_ERR_ARG;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    CafeFields FS;
+    int64_t zero_off[CAFE_MAX_SEGMENTS] = {0};
+    int rc = fill_fields(&FS, nfields, B, D, hotn, zero_off, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int64_t total = (int64_t)nfields * B;
+    if (total > ws->cap) return CAFE_ERR_CAPACITY;
+    if (total == 0) return CAFE_OK;
+    ws->begun_gid = nullptr;
+    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, (cudaStream_t)stream);
+    if (rc != CAFE_OK) return rc;
+    ws->begun_gid = gid_dev; ws->begun_row = row_dev; ws->begun_total = (int)total; ws->begun_mode = insert_mode;
+    return CAFE_OK;
+}
+
 // cafe_embed_backward with the importance array already computed (by cafe_shard_pull_importance)
 int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const float* imp_dev,
                             const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev,
@@ -835,9 +866,8 @@ int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride
     int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
                            weight_high, hotn, D);
     if (rc != CAFE_OK) return rc;
-    rc = scatter_prepare_aside(ws, FS, row_dev, (int)total, hotn, (cudaStream_t)stream);
+    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, (cudaStream_t)stream);
     if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
-    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, (int)total, (cudaStream_t)stream);
     int status = cafe_internal_insert(h, gid_dev, imp_dev, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
     rc = scatter_join(ws, (cudaStream_t)stream);
     if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;

@@ -181,6 +181,7 @@ class _PeerFunction(torch.autograd.Function):
         f = grp._fields
         with torch.no_grad(), torch.cuda.device(pb.grad.device):
             g = blocked_grad.reshape(-1).contiguous()
+            f.backward_begin(gid, row, G * Bl, grp.insert_mode)   # sorts run beside the gradient exchange
             # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
             _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank, pb.ptr_array(pb.h_gown, 0, 4),
                                                  _stream()), "cafe_shard_push_grads")
@@ -209,6 +210,7 @@ class _ShardedFunction(torch.autograd.Function):
         plan, grp = model.plan, model.group
         flat, gid, row = ctx.saved
         Fg, D = grp.num_fields, grp.embedding_dim
+        grp._fields.backward_begin(gid, row, plan.G * ctx.Bl, grp.insert_mode)   # sorts run beside the exchange
         g = plan.exchange_grads(blocked_grad.contiguous(), ctx.Bl, D)
         with torch.no_grad():
             grp.last_status = grp._fields.backward(g, D, Fg * D, flat, gid, row, plan.G * ctx.Bl, grp.lr, grp.insert_mode)

@@ -101,6 +101,15 @@ class _FieldSet:
                                                         row.data_ptr(), self.nf, B, self.hash_size, wp, hp, self.hotn,
                                                         self.dim, float(lr), _stream()), "cafe_scatter_sgd")
 
+    def backward_begin(self, gid, row, B, mode):
+        """Starts the part of the backward that needs only the forward's outputs (the bucket sorts of the
+        sketch insert and the row sort of the scatter) on the library's side streams."""
+        wp, hp = self.ptrs()
+        with torch.cuda.device(gid.device):
+            _lib.check(self.sketch.lib.cafe_embed_backward_begin(
+                self.sketch.handle, gid.data_ptr(), row.data_ptr(), self.nf, B, self.hash_size, wp, hp, self.hotn,
+                self.dim, mode, _stream()), "cafe_embed_backward_begin")
+
     def backward(self, grad, field_stride, sample_stride, ids, gid, row, B, lr, mode, mask_out=None):
         wp, hp = self.ptrs()
         with torch.cuda.device(grad.device):
@@ -266,6 +275,8 @@ class _GroupFunction(torch.autograd.Function):
         ctx.group = group
         ctx.saved = (flat, gid, row, B)
         group.last_rows = row.view(F, B)
+        if group.training and ctx.needs_input_grad[0] and flat.numel() > 0:
+            group._fields.backward_begin(gid, row, B, group.insert_mode)   # overlaps whatever runs before the backward
         return out
 
     @staticmethod

@@ -133,6 +133,17 @@ int cafe_embed_backward(void* handle, const float* grad_dev, int64_t field_strid
                         float* weight_high, int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev,
                         int32_t* n_migrated_dev, void* stream);
 
+/* Optional head start for the next cafe_embed_backward / cafe_embed_backward_imp of the same lookups:
+ * starts, on streams owned by the handle and ordered after `stream`, the work that needs only the
+ * forward's outputs (the bucket orders of the sketch insert, the row order of the scatter), so that
+ * it runs beside whatever the caller queues on `stream` in between (the dense model, an exchange of
+ * gradients).  The backward recognises the head start by the same gid_dev / row_dev / sizes /
+ * insert_mode and otherwise does the work itself; the two arrays must not change in between.  No
+ * counterpart in the reference, whose insert is one sequential loop (sketch.cpp:268-280). */
+int cafe_embed_backward_begin(void* handle, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                              const int32_t* hash_size, float* const* weight_hash, float* weight_high, int hotn, int D,
+                              int insert_mode, void* stream);
+
 /* ---- field-sharded exchange over peer memory (one node, up to 8 ranks) -----------------------------
  * No counterpart in the reference (single GPU; its --dist flags are never used, dlrm_s_pytorch.py:
  * 1090-1091).  Rank g owns the fields f with f % nranks == g (in ascending order) and serves them for

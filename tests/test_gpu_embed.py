@@ -232,3 +232,33 @@ def test_checkpoint_resume_through_state_dict(tmp_path):
     assert torch.equal(a.weight_high, b.weight_high)
     for wa, wb in zip(a.weight_hash, b.weight_hash):
         assert torch.equal(wa, wb)
+
+
+def test_backward_head_start_is_only_a_head_start():
+    """The sorts started at forward time (training mode) must not change any result: interleaved
+    forwards and backwards, where the head start belongs to another batch than the backward that
+    follows, give the same bits as a module that never takes the head start (eval mode)."""
+    import torch
+    import cafe_b200
+    cards = [4000, 150000, 61, 700000]
+    F, D, B = len(cards), 32, 192
+    mk = lambda: cafe_b200.SKEmbeddingGroup(cards, D, 0.01, 0.3, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=3)
+    a, b = mk(), mk()
+    b.eval()                                   # no head start; the backward does all the work itself
+    rng = np.random.default_rng(11)
+    for step in range(6):
+        idsA = torch.from_numpy(np.stack([zipf_ids(rng, n, B) for n in cards]))
+        idsB = torch.from_numpy(np.stack([zipf_ids(rng, n, B) for n in cards]))
+        gA = torch.from_numpy((rng.standard_normal((B, F, D)) * 0.01).astype(np.float32)).cuda()
+        gB = torch.from_numpy((rng.standard_normal((B, F, D)) * 0.01).astype(np.float32)).cuda()
+        for m in (a, b):
+            oA = m(idsA)
+            oB = m(idsB)                       # the head start now belongs to batch B ...
+            oA.backward(gA)                    # ... and this backward must notice that
+            oB.backward(gB)
+            if step % 2:
+                m(idsA).backward(gA)           # the plain case: head start used by its own backward
+        assert states_equal(a.sketch.state(), b.sketch.state()) == [], f"step {step}: sketch state"
+        assert torch.equal(a.weight_high, b.weight_high), f"step {step}: hot table"
+        for f in range(F):
+            assert torch.equal(a.weight_hash[f], b.weight_hash[f]), f"step {step}: hash table {f}"
