@@ -53,6 +53,7 @@ enum {
     CAFE_P_SCATTER, CAFE_P_FIXUP, CAFE_P_SEQ, CAFE_P_QUERY, CAFE_P_MEMSET, CAFE_P_OTHER, CAFE_P_MAIN_LATER, CAFE_P_MAIN_FINAL,
     CAFE_P_LRU_LATER, CAFE_PROF_SLOTS
 };
+bool cafe_prof_serialise();
 void cafe_prof_begin(int slot, cudaStream_t st);
 void cafe_prof_end(cudaStream_t st);
 struct CafeProfScope {

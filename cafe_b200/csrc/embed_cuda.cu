@@ -702,6 +702,11 @@ int cafe_scatter_sgd(void* h, const float* grad_dev, int64_t field_stride, int64
 // Starts scatter_prepare on the side stream, ordered after everything already queued on `st`.
 static int scatter_prepare_aside(CafeEmbedWorkspace* ws, const CafeFields& F, const int32_t* row_dev, int total, int hotn,
                                  cudaStream_t st) {
+    if (cafe_prof_serialise()) {
+        int rc0 = scatter_prepare(ws, F, row_dev, total, hotn, st);
+        cudaEventRecord(ws->ev_join, st);
+        return rc0;
+    }
     if (cudaEventRecord(ws->ev_fork, st) != cudaSuccess || cudaStreamWaitEvent(ws->side, ws->ev_fork, 0) != cudaSuccess)
         return fail_cuda("scatter fork");
     int rc = scatter_prepare(ws, F, row_dev, total, hotn, ws->side);

@@ -24,6 +24,10 @@ static int64_t g_launches[CAFE_PROF_SLOTS];
 static int64_t g_total_launches = 0;
 static Rec* g_open = nullptr;
 
+// While per-kernel timing is on, the library queues its side-stream work on the caller's stream so
+// that every event pair brackets one kernel running alone.
+bool cafe_prof_serialise() { return g_on; }
+
 static cudaEvent_t take_event() {
     if (!g_pool.empty()) { cudaEvent_t e = g_pool.back(); g_pool.pop_back(); return e; }
     cudaEvent_t e;

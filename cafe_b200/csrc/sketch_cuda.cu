@@ -29,6 +29,29 @@ __global__ void k_fill_iota(uint32_t* p, int n, uint32_t first) {
     if (i < n) p[i] = first + (uint32_t)i;
 }
 
+// Several byte fills in one launch (the engine clears a handful of small arrays per job and round).
+struct CafeFills {
+    unsigned char* p[4];
+    size_t n[4];
+    int v[4];
+    int count;
+};
+__global__ void k_fills(const CafeFills F) {
+    const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (size_t)gridDim.x * blockDim.x;
+    for (int s = 0; s < F.count; ++s) {
+        unsigned char* p = F.p[s];
+        const size_t n = F.n[s];
+        const unsigned b = (unsigned)F.v[s] & 0xffu;
+        const unsigned w = b * 0x01010101u;
+        size_t head = (16 - ((uintptr_t)p & 15)) & 15;
+        if (head > n) head = n;
+        const size_t body = (n - head) / 16, tail0 = head + 16 * body;
+        for (size_t i = tid; i < body; i += nth) reinterpret_cast<uint4*>(p + head)[i] = make_uint4(w, w, w, w);
+        for (size_t i = tid; i < head; i += nth) p[i] = (unsigned char)b;
+        for (size_t i = tail0 + tid; i < n; i += nth) p[i] = (unsigned char)b;
+    }
+}
+
 __global__ void k_query(const CafeMainBucket* __restrict__ mb, int n1, const uint32_t* __restrict__ gid, int n,
                         int32_t* __restrict__ out) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -109,8 +132,39 @@ __global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_le
     }
 }
 
+// Short buckets, staged.  The lookups of a warp's 32 buckets lie in ascending, disjoint ranges of the
+// sorted order.  Instead of every thread chasing its own chain of dependent loads (order entry ->
+// position -> id and count) one lookup at a time, the warp loads all entries of a tile in parallel,
+// lane e taking entry e, and parks them in shared memory; each thread then replays its own bucket
+// from there.  cafe_stage_owner finds, for entry number e of the warp's concatenated ranges, the lane
+// whose range holds it: the largest lane whose exclusive prefix is <= e.
+__device__ __forceinline__ int cafe_stage_owner(int pref, int e) {
+    int L = 0;
+#pragma unroll
+    for (int b = 16; b > 0; b >>= 1) {
+        const int cand = L + b;
+        const int pc = __shfl_sync(CAFE_FULL, pref, cand & 31);
+        if (pc <= e) L = cand;
+    }
+    return L;
+}
+__device__ __forceinline__ int cafe_warp_exclusive(int n, int lane, int* total) {
+    int inc = n;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(CAFE_FULL, inc, d);
+        if (lane >= d) inc += t;
+    }
+    *total = __shfl_sync(CAFE_FULL, inc, 31);
+    return inc - n;
+}
+#define CAFE_STAGE_MAIN 128   // entries per tile and warp in the main pass
+#define CAFE_STAGE_LRU 256    // ... in the LRU pass (its buckets are fewer and fuller)
+
 __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
-    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up
+    __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];  // per warp: counts of the staged tile / of the chunks being added up
+    __shared__ int s_p[4][CAFE_STAGE_MAIN];                  // staged positions, ids, old event kind | old flags << 8
+    __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     bool hot_warp;
@@ -128,20 +182,41 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > J.long_main && len <= 512) || ((J.diag & 4) && len <= J.long_main)) iend = i;
     }
     const bool is_long = live && (hot_warp || iend - i > J.long_main);
-    if (live && !is_long) {
-        // one lookup ahead: the next lookup's position and data are requested before this one is replayed
-        int p = (i < iend) ? J.ord1[i] : INT32_MAX;
-        uint32_t x = 0, ok = CAFE_EV_NONE, of = 0;
-        float c = 1.0f;
-        if (p < J.limit) { x = J.gid[p]; c = cafe_count_of(J, p); ok = cafe_old_kind(J, p); of = cafe_old_mflag(J, p); }
-        while (p < J.limit) {
-            const int pn = (i + 1 < iend) ? J.ord1[i + 1] : INT32_MAX;
-            uint32_t xn = 0, okn = CAFE_EV_NONE, ofn = 0;
-            float cn = 1.0f;
-            if (pn < J.limit) { xn = J.gid[pn]; cn = cafe_count_of(J, pn); okn = cafe_old_kind(J, pn); ofn = cafe_old_mflag(J, pn); }
-            R.feed(J, p, x, c, ok, of);
-            p = pn; x = xn; c = cn; ok = okn; of = ofn;
-            ++i;
+    {
+        const bool is_short = live && !is_long;
+        const int n_k = (is_short && !(J.diag & 8)) ? max(iend - i, 0) : 0;
+        int T;
+        const int pref = cafe_warp_exclusive(n_k, lane, &T);
+        bool done = !is_short || (J.diag & 16);
+        for (int t0 = 0; t0 < T; t0 += CAFE_STAGE_MAIN) {
+            const int tn = min(CAFE_STAGE_MAIN, T - t0);
+#pragma unroll
+            for (int r = 0; r < CAFE_STAGE_MAIN / 32; ++r) {
+                if (r * 32 >= tn) break;   // warp-uniform
+                const int e = t0 + r * 32 + lane;
+                const int L = cafe_stage_owner(pref, e);
+                const int iL = __shfl_sync(CAFE_FULL, i, L), pL = __shfl_sync(CAFE_FULL, pref, L);
+                int p = INT32_MAX;
+                uint32_t x = 0, kf = CAFE_EV_NONE;
+                float c = 1.0f;
+                if (e < t0 + tn) {
+                    p = J.ord1[iL + (e - pL)];
+                    if (p < J.limit) {
+                        x = J.gid[p]; c = cafe_count_of(J, p);
+                        kf = cafe_old_kind(J, p) | (cafe_old_mflag(J, p) << 8);
+                    }
+                }
+                s_p[wib][r * 32 + lane] = p; s_x[wib][r * 32 + lane] = x; s_c[wib][r * 32 + lane] = c; s_kf[wib][r * 32 + lane] = kf;
+            }
+            __syncwarp();
+            const int lo = max(pref, t0), hi = min(pref + n_k, t0 + tn);
+            for (int j = lo; j < hi && !done; ++j) {
+                const int p = s_p[wib][j - t0];
+                if (p >= J.limit) { done = true; break; }   // positions ascend inside a bucket
+                const uint32_t kf = s_kf[wib][j - t0];
+                R.feed(J, p, s_x[wib][j - t0], s_c[wib][j - t0], kf & 0xffu, kf >> 8);
+            }
+            __syncwarp();
         }
     }
     int slow = 0;
@@ -165,7 +240,95 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
             x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx);
             av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
         }
+        bool last_calm = false;   // the previous chunk went through the calm whole-chunk path
         for (int base = s; base < e && !stop; base += 32) {
+            if (last_calm && e - base >= 128) {
+                // A long calm stretch (the head ids of a skewed field have thousands of lookups per call)
+                // goes four chunks at a time: every lane holds four lookups, the conditions of the calm
+                // whole-chunk path are checked for all 128, and the 128 counts are added in order by one
+                // chain.  Same two-deep prefetch as the chunk loop, at group granularity.
+                float acc = 0.f;
+                if (lane == o) {
+#pragma unroll
+                    for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) acc = R.b.cnt[q];
+                }
+                acc = __shfl_sync(CAFE_FULL, acc, o);
+                int gb = base;
+                int cp[4], xp[4], n2p[4];
+                uint32_t cx[4], cok[4], cof[4], xx[4], xok[4], xof[4];
+                float cc[4], xc[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i0 = gb + 32 * q + lane, i1 = i0 + 128;
+                    cp[q] = i0 < e ? J.ord1[i0] : INT32_MAX;
+                    xp[q] = i1 < e ? J.ord1[i1] : INT32_MAX;
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    cx[q] = 0; cok[q] = CAFE_EV_NONE; cof[q] = 0; cc[q] = 1.0f;
+                    if (cp[q] < J.limit) {
+                        cx[q] = J.gid[cp[q]]; cc[q] = cafe_count_of(J, cp[q]); cok[q] = cafe_old_kind(J, cp[q]); cof[q] = cafe_old_mflag(J, cp[q]);
+                    }
+                }
+                for (;;) {
+                    bool good = true;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) good = good && cp[q] < hbound && cx[q] == hx && cc[q] >= 0.f && cc[q] <= acc;
+                    if (!__all_sync(CAFE_FULL, good)) break;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int i2 = gb + 256 + 32 * q + lane;
+                        n2p[q] = i2 < e ? J.ord1[i2] : INT32_MAX;
+                        xx[q] = 0; xok[q] = CAFE_EV_NONE; xof[q] = 0; xc[q] = 1.0f;
+                        if (xp[q] < J.limit) {
+                            xx[q] = J.gid[xp[q]]; xc[q] = cafe_count_of(J, xp[q]); xok[q] = cafe_old_kind(J, xp[q]); xof[q] = cafe_old_mflag(J, xp[q]);
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) s_c[wib][32 * q + lane] = cc[q];
+                    __syncwarp();
+                    {
+                        const float4* cv = reinterpret_cast<const float4*>(s_c[wib]);
+#pragma unroll
+                        for (int q = 0; q < 32; ++q) {
+                            const float4 t = cv[q];
+                            acc = acc + t.x; acc = acc + t.y; acc = acc + t.z; acc = acc + t.w;
+                        }
+                    }
+                    __syncwarp();
+                    if (!J.final_pass) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (cof[q] != 0) J.mflag[cp[q]] = 0;
+                            if (!J.first_round) {
+                                if (cok[q] != CAFE_EV_NONE) { J.ev[cp[q]].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                                if (cof[q] & CAFE_F_MISS) J.mark2[cafe_hash(cx[q], J.n2)] = 1;
+                            }
+                        }
+                    }
+                    gb += 128;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        cp[q] = xp[q]; cx[q] = xx[q]; cc[q] = xc[q]; cok[q] = xok[q]; cof[q] = xof[q];
+                        xp[q] = n2p[q];
+                    }
+                }
+                if (gb != base) {
+                    if (lane == o) {
+#pragma unroll
+                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
+                        R.i_cur += gb - base;
+                    }
+                    base = gb;
+                    if (base >= e) break;
+                    // hand the loaded lookups back to the chunk pipeline
+                    p_nx = cp[0]; x_nx = cx[0]; c_nx = cc[0]; ok_nx = cok[0]; of_nx = cof[0];
+                    av_nx = false;
+                    if (p_nx < J.limit) av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
+                    p_n2 = cp[1];
+                }
+            }
+            last_calm = false;
             const int p = p_nx;
             const uint32_t x = x_nx, ok = ok_nx, of = of_nx;
             const float c = c_nx;
@@ -217,6 +380,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                     }
                 }
                 __syncwarp();
+                last_calm = calm;
                 if (lane == o) {
 #pragma unroll
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
@@ -322,7 +486,11 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
     if (live) R.finish(J);
 }
 __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ int l_p[4][CAFE_STAGE_LRU];
+    __shared__ uint32_t l_x[4][CAFE_STAGE_LRU];
+    __shared__ float l_c[4][CAFE_STAGE_LRU];
     const int lane = threadIdx.x & 31;
+    const int wib = threadIdx.x >> 5;
     bool hot_warp;
     const int k = cafe_bucket_of_thread(H, J.n2, &hot_warp);
     CafeLruReplay R;
@@ -333,13 +501,46 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         if (live) { jb = J.beg2[k]; jend = J.start2[k + 1]; }
     }
     int slow = 0;
+    if (J.diag) {   // timing experiments: leave out classes of buckets
+        const int len = jend - jb;
+        if (((J.diag & 32) && len > J.long_lru) || ((J.diag & 64) && len <= J.long_lru)) jend = jb;
+    }
     const bool is_long = live && (hot_warp || jend - jb > J.long_lru);
-    if (live && !is_long) {
-        for (int j = jb; j < jend; ++j) {
-            const int p = J.ord2[j];
-            if (p >= J.limit) break;
-            if (!(J.mflag[p] & CAFE_F_MISS)) continue;
-            R.feed(J, p, J.gid[p], cafe_count_of(J, p));
+    {
+        const bool is_short = live && !is_long;
+        const int n_k = is_short ? max(jend - jb, 0) : 0;
+        int T;
+        const int pref = cafe_warp_exclusive(n_k, lane, &T);
+        bool done = !is_short;
+        for (int t0 = 0; t0 < T; t0 += CAFE_STAGE_LRU) {
+            const int tn = min(CAFE_STAGE_LRU, T - t0);
+#pragma unroll
+            for (int r = 0; r < CAFE_STAGE_LRU / 32; ++r) {
+                if (r * 32 >= tn) break;   // warp-uniform
+                const int e = t0 + r * 32 + lane;
+                const int L = cafe_stage_owner(pref, e);
+                const int jL = __shfl_sync(CAFE_FULL, jb, L), pL = __shfl_sync(CAFE_FULL, pref, L);
+                int p = INT32_MAX;       // beyond the job; -1: a lookup that hit the main table
+                uint32_t x = 0;
+                float c = 1.0f;
+                if (e < t0 + tn) {
+                    p = J.ord2[jL + (e - pL)];
+                    if (p < J.limit) {
+                        if (J.mflag[p] & CAFE_F_MISS) { x = J.gid[p]; c = cafe_count_of(J, p); }
+                        else p = -1;
+                    }
+                }
+                l_p[wib][r * 32 + lane] = p; l_x[wib][r * 32 + lane] = x; l_c[wib][r * 32 + lane] = c;
+            }
+            __syncwarp();
+            const int lo = max(pref, t0), hi = min(pref + n_k, t0 + tn);
+            for (int j = lo; j < hi && !done; ++j) {
+                const int p = l_p[wib][j - t0];
+                if (p < 0) continue;
+                if (p >= J.limit) { done = true; break; }
+                R.feed(J, p, l_x[wib][j - t0], l_c[wib][j - t0]);
+            }
+            __syncwarp();
         }
     }
     unsigned m = __ballot_sync(CAFE_FULL, is_long);
@@ -581,6 +782,28 @@ struct CudaBackend {
     void* alloc(size_t n) { void* p = nullptr; check(cudaMalloc(&p, n ? n : 1)); return p; }
     void free(void* p) { cudaFree(p); }
     void memset(void* p, int v, size_t n) { if (n) { CAFE_PROF(CAFE_P_MEMSET, stream); check(cudaMemsetAsync(p, v, n, stream)); } }
+    // up to four memsets as one launch
+    void fills(void* p0, int v0, size_t n0, void* p1 = nullptr, int v1 = 0, size_t n1 = 0, void* p2 = nullptr, int v2 = 0,
+               size_t n2 = 0, void* p3 = nullptr, int v3 = 0, size_t n3 = 0) {
+        CafeFills F;
+        F.count = 0;
+        void* ps[4] = {p0, p1, p2, p3};
+        const int vs[4] = {v0, v1, v2, v3};
+        const size_t ns[4] = {n0, n1, n2, n3};
+        size_t most = 0;
+        for (int i = 0; i < 4; ++i) {
+            if (!ps[i] || !ns[i]) continue;
+            F.p[F.count] = (unsigned char*)ps[i]; F.v[F.count] = vs[i]; F.n[F.count] = ns[i];
+            ++F.count;
+            most = ns[i] > most ? ns[i] : most;
+        }
+        if (!F.count) return;
+        CAFE_PROF(CAFE_P_MEMSET, stream);
+        const size_t want = (most / 16 + 255) / 256;
+        const int blocks = (int)(want < 1 ? 1 : (want > 1184 ? 1184 : want));   // at most 8 per SM
+        k_fills<<<blocks, 256, 0, stream>>>(F);
+        check_launch();
+    }
     void fill_iota(uint32_t* p, int n, uint32_t first) {
         if (n > 0) { k_fill_iota<<<cafe_blocks(n), CAFE_TPB, 0, stream>>>(p, n, first); check_launch(); }
     }
@@ -664,11 +887,14 @@ struct CudaBackend {
     // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
         cudaStream_t st = stream;
-        if (lane != 0) {
+        if (lane != 0 && cafe_prof_serialise()) lane = -lane;   // the lane's buffers, the caller's stream
+        if (lane > 0) {
             check(cudaEventRecord(ev_fork[lane], stream));
             check(cudaStreamWaitEvent(side[lane], ev_fork[lane], 0));
             st = side[lane];
         }
+        const bool aside = lane > 0;
+        lane = lane < 0 ? -lane : lane;
         {
         CAFE_PROF(CAFE_P_LOOKUP_SORT, st);
         k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, st>>>(gid, M, nb, key_in[lane], pos_in[lane]);
@@ -686,7 +912,7 @@ struct CudaBackend {
         check_launch();
         check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
         }
-        if (lane != 0) {
+        if (aside) {
             check(cudaEventRecord(ev_join[lane], side[lane]));
             side_pending[lane] = true;
         }

@@ -381,9 +381,12 @@ private:
         J.long_lru = std::max(16, (int)(4.0 * M / n2));
         J.diag = getenv("CAFE_B200_EXPERIMENT") ? atoi(getenv("CAFE_B200_EXPERIMENT")) : 0;
         ++stats.jobs;
-        be.memset(ins_res + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
-        be.memset(mflag + J.begin, 0, (size_t)(J.limit - J.begin));
-        be.memset(ev + J.begin, 0, sizeof(CafeEvent) * (size_t)(J.limit - J.begin));   // kind 0 = no event
+        {
+            const size_t span = (size_t)(J.limit - J.begin);
+            be.fills(ins_res + J.begin, 0, 4 * span, mflag + J.begin, 0, span,
+                     ev + J.begin, 0, sizeof(CafeEvent) * span,   // kind 0 = no event
+                     mark2, 0, span_clear - off_mark2);           // mark2 + round result, for the first round
+        }
 
         CafeRoundResult R;
         int rounds = 0;
@@ -407,10 +410,8 @@ private:
             shortened = false;
             J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
             J.tl_size_new = tl_size[pb ^ 1]; J.tl_rank_new = tl_rank[pb ^ 1]; J.pushbuf_new = pushbuf[pb ^ 1];
-            if (first) be.memset(mark2, 0, span_clear - off_mark2);   // mark2 + round result
-            else {
-                be.memset(head, 0xff, 4 * (size_t)n1);
-                be.memset(mark_own, 0, span_clear);                   // mark_own + mark2 + round result
+            if (!first) {   // (the first round's mark2 + round result were cleared with the job's arrays)
+                be.fills(head, 0xff, 4 * (size_t)n1, mark_own, 0, span_clear);   // mark_own + mark2 + round result
                 be.route(J);
             }
             be.sort_join(1);
@@ -455,8 +456,8 @@ private:
         J.first_round = 0; J.all_active = 0; J.cand_active = 1;
         J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
         if (post_row) {
-            be.memset(post_row + J.begin, 0, 4 * (size_t)(J.limit - J.begin));
-            route(J);
+            be.fills(post_row + J.begin, 0, 4 * (size_t)(J.limit - J.begin), head, 0xff, 4 * (size_t)n1, mark_own, 0, (size_t)n1);
+            be.route(J);
             J.final_pass = 1;
             be.main_pass(J);
             J.final_pass = 0;
@@ -486,10 +487,4 @@ private:
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
     }
 
-    // rebuild the per-bucket chains of victim promotions and the own-promotion marks from the events
-    void route(const CafeJob& J) {
-        be.memset(head, 0xff, 4 * (size_t)n1);
-        be.memset(mark_own, 0, (size_t)n1);
-        be.route(J);
-    }
 };

@@ -22,6 +22,13 @@ struct HostBackend {
     void* alloc(size_t n) { return calloc(n ? n : 1, 1); }
     void free(void* p) { ::free(p); }
     void memset(void* p, int v, size_t n) { ::memset(p, v, n); }
+    void fills(void* p0, int v0, size_t n0, void* p1 = nullptr, int v1 = 0, size_t n1 = 0, void* p2 = nullptr, int v2 = 0,
+               size_t n2 = 0, void* p3 = nullptr, int v3 = 0, size_t n3 = 0) {
+        if (p0 && n0) ::memset(p0, v0, n0);
+        if (p1 && n1) ::memset(p1, v1, n1);
+        if (p2 && n2) ::memset(p2, v2, n2);
+        if (p3 && n3) ::memset(p3, v3, n3);
+    }
     void fill_iota(uint32_t* p, int n, uint32_t first) { for (int i = 0; i < n; ++i) p[i] = first + (uint32_t)i; }
     void h2d(void* d, const void* s, size_t n) { memcpy(d, s, n); }
     void copy(void* d, const void* s, size_t n) { memcpy(d, s, n); }
