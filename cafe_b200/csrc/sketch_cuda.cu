@@ -104,32 +104,43 @@ __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb
 // Very long buckets (the head of the Zipf law) are the serial tail of a pass.  They are listed when
 // the lookups are sorted, and the first blocks of the grid take one listed bucket per warp, so that
 // the tail starts at once and overlaps with everything else; the other blocks skip listed buckets.
-#define CAFE_HOT_LEN 256      // a bucket with more lookups than this is listed
-#define CAFE_HOT_CAP 512      // at most this many are listed (the rest stay in the normal path)
-#define CAFE_HOT_BLOCKS (CAFE_HOT_CAP / 4)
+#define CAFE_HOT_LEN 256      // a bucket with more lookups than this is listed in the first region (taken first)
+#define CAFE_HOT_CAP 512      // size of that region
+#define CAFE_LIST_CAP (CAFE_HOT_CAP + 32768)   // the second region lists the other long buckets
+#define CAFE_LIST_BLOCKS (148 * 4)              // blocks of the launch that works through the list
+// Long buckets (more lookups in the sorted stretch than a few times the average) are listed at sort
+// time and replayed by a warp each, in a launch of their own that runs beside the thread-per-bucket
+// launch for all other buckets: the two kinds of work want different register budgets and occupancy.
+// count[0] / count[1] = entries of the two regions; a bucket that finds its region full stays unlisted
+// and is handled, correctly but serially, by the thread-per-bucket launch.
 struct CafeHot {
     const int32_t* list;
     const int32_t* count;
     const uint8_t* flag;
 };
-__device__ __forceinline__ int cafe_bucket_of_thread(const CafeHot& H, int nb, bool* hot_warp) {
-    if (blockIdx.x < CAFE_HOT_BLOCKS) {
-        *hot_warp = true;
-        const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
-        const int n = min(*H.count, CAFE_HOT_CAP);
-        return ((threadIdx.x & 31) == 0 && w < n) ? H.list[w] : nb;   // lane 0 owns the listed bucket
-    }
-    *hot_warp = false;
-    const int k = (blockIdx.x - CAFE_HOT_BLOCKS) * blockDim.x + threadIdx.x;
-    return (k < nb && !H.flag[k]) ? k : nb;
-}
-__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int32_t* list, int32_t* count, uint8_t* flag) {
+__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int long_len, int32_t* list, int32_t* count,
+                           uint8_t* flag) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= nb) return;
-    if (start[k + 1] - start[k] > hot_len) {
-        const int idx = atomicAdd(count, 1);
-        if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; }
+    const int len = start[k + 1] - start[k];
+    if (len <= long_len) return;
+    if (len > hot_len) {
+        const int idx = atomicAdd(&count[0], 1);
+        if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; return; }
     }
+    const int idx = atomicAdd(&count[1], 1);
+    if (idx < CAFE_LIST_CAP - CAFE_HOT_CAP) { list[CAFE_HOT_CAP + idx] = k; flag[k] = 1; }
+}
+// next listed bucket for this warp (lane 0 owns it; -1 = none left); the cursor is zeroed with the round result
+__device__ __forceinline__ int cafe_next_listed(const CafeHot& H, int32_t* cursor, int nb, int* widx) {
+    const int lane = threadIdx.x & 31;
+    const int n_hot = min(H.count[0], CAFE_HOT_CAP), n_long = min(H.count[1], CAFE_LIST_CAP - CAFE_HOT_CAP);
+    int w = 0;
+    if (lane == 0) w = atomicAdd(cursor, 1);
+    w = __shfl_sync(CAFE_FULL, w, 0);
+    *widx = w;
+    if (w >= n_hot + n_long) return -1;
+    return lane == 0 ? H.list[w < n_hot ? w : CAFE_HOT_CAP + (w - n_hot)] : nb;
 }
 
 // Short buckets, staged.  The lookups of a warp's 32 buckets lie in ascending, disjoint ranges of the
@@ -158,17 +169,22 @@ __device__ __forceinline__ int cafe_warp_exclusive(int n, int lane, int* total) 
     *total = __shfl_sync(CAFE_FULL, inc, 31);
     return inc - n;
 }
+__device__ __forceinline__ void cafe_diag_cycles(const CafeJob& J, int slot, long long dt) {
+    atomicMax(&J.res->diag_max_cycles[slot], (int)dt);
+    atomicAdd(&J.res->diag_sum_cycles[slot], (unsigned long long)dt);
+    atomicAdd(&J.res->diag_warps[slot], 1);
+}
 #define CAFE_STAGE_MAIN 128   // entries per tile and warp in the main pass
-#define CAFE_STAGE_LRU 256    // ... in the LRU pass (its buckets are fewer and fuller)
 
-__global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
-    __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];  // per warp: counts of the staged tile / of the chunks being added up
-    __shared__ int s_p[4][CAFE_STAGE_MAIN];                  // staged positions, ids, old event kind | old flags << 8
-    __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
+// PART 0: one listed bucket, owned by lane 0 and fed by the whole warp; PART 1: a thread per bucket.
+template <int PART>
+__device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, const int widx, float (*s_c)[CAFE_STAGE_MAIN],
+                                               int (*s_p)[CAFE_STAGE_MAIN], uint32_t (*s_x)[CAFE_STAGE_MAIN],
+                                               uint32_t (*s_kf)[CAFE_STAGE_MAIN]) {
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
-    bool hot_warp;
-    const int k = cafe_bucket_of_thread(H, J.n1, &hot_warp);
+    const bool hot_warp = PART == 0;
+    const long long t_begin = (J.diag & 128) ? clock64() : 0;
     CafeMainReplay R;
     int i = 0, iend = 0;
     bool live = k < J.n1;
@@ -181,9 +197,9 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         const int len = iend - i;
         if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > J.long_main && len <= 512) || ((J.diag & 4) && len <= J.long_main)) iend = i;
     }
-    const bool is_long = live && (hot_warp || iend - i > J.long_main);
-    {
-        const bool is_short = live && !is_long;
+    const bool is_long = PART == 0 && live;
+    if (PART == 1) {
+        const bool is_short = live;
         const int n_k = (is_short && !(J.diag & 8)) ? max(iend - i, 0) : 0;
         int T;
         const int pref = cafe_warp_exclusive(n_k, lane, &T);
@@ -220,7 +236,9 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         }
     }
     int slow = 0;
-    unsigned m = __ballot_sync(CAFE_FULL, is_long);
+    int d_groups = 0, d_calm = 0, d_runs = 0, d_runlen = 0;
+    const long long t_short = (J.diag & 128) ? clock64() : 0;
+    unsigned m = PART == 0 ? __ballot_sync(CAFE_FULL, is_long) : 0u;
     while (m) {
         const int o = __ffs(m) - 1;
         m &= m - 1;
@@ -307,6 +325,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                         }
                     }
                     gb += 128;
+                    ++d_groups;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         cp[q] = xp[q]; cx[q] = xx[q]; cc[q] = xc[q]; cok[q] = xok[q]; cof[q] = xof[q];
@@ -381,6 +400,7 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 }
                 __syncwarp();
                 last_calm = calm;
+                ++d_calm;
                 if (lane == o) {
 #pragma unroll
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
@@ -409,52 +429,72 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                 // cross the threshold and may be a failed pop candidate.  The counts are added in order
                 // by a shuffle chain; every lane writes the flags of its own lookup.  The run stops before
                 // the first lookup that could take a row; that one goes through the full replay.
-                int slot = -1, bound = 0, has_row = 0;
-                float cnt0 = 0.f;
-                if (lane == o && R.touched) {
-#pragma unroll
-                    for (int q = CAFE_SLOTS - 1; q >= 0; --q) if (R.b.val[q] == xj) slot = q;
-                    if (slot >= 0) {
-#pragma unroll
-                        for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { has_row = R.b.dic[q] != 0; cnt0 = R.b.cnt[q]; }
-                    }
+                // (several ids of one bucket may alternate: every lane finds the slot of its own id, and the
+                // counts of each slot are added in order by that slot's own chain)
+                uint32_t bv0 = 0, bv1 = 0, bv2 = 0, bv3 = 0;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                int rowmask = 0, bound = 0, tch = 0;
+                if (lane == o) {
+                    tch = R.touched ? 1 : 0;
+                    bv0 = R.b.val[0]; bv1 = R.b.val[1]; bv2 = R.b.val[2]; bv3 = R.b.val[3];
+                    a0 = R.b.cnt[0]; a1 = R.b.cnt[1]; a2 = R.b.cnt[2]; a3 = R.b.cnt[3];
+                    rowmask = (R.b.dic[0] != 0 ? 1 : 0) | (R.b.dic[1] != 0 ? 2 : 0) | (R.b.dic[2] != 0 ? 4 : 0) | (R.b.dic[3] != 0 ? 8 : 0);
                     bound = min(R.p_ev, J.limit);
                     if (J.final_pass) bound = min(bound, R.seg_end);
                 }
-                slot = __shfl_sync(CAFE_FULL, slot, o);
+                tch = __shfl_sync(CAFE_FULL, tch, o);
                 int run = 0;
                 bool advanced = false;
-                if (slot >= 0) {
+                int ms = -1;   // slot of this lane's id (lowest matching slot, as in the replay)
+                if (tch) {
+                    bv0 = __shfl_sync(CAFE_FULL, bv0, o); bv1 = __shfl_sync(CAFE_FULL, bv1, o);
+                    bv2 = __shfl_sync(CAFE_FULL, bv2, o); bv3 = __shfl_sync(CAFE_FULL, bv3, o);
+                    rowmask = __shfl_sync(CAFE_FULL, rowmask, o);
                     bound = __shfl_sync(CAFE_FULL, bound, o);
-                    has_row = __shfl_sync(CAFE_FULL, has_row, o);
-                    hvalid = true; hx = xj; hslot = slot; hrow = has_row != 0; hbound = bound;
-                    const bool mine = lane >= j && lane < n && x == xj && p < bound;
+                    ms = (x == bv0) ? 0 : (x == bv1) ? 1 : (x == bv2) ? 2 : (x == bv3) ? 3 : -1;
+                    const bool mine = lane >= j && lane < n && ms >= 0 && p < bound;
                     const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
                     if (run < 0) run = 32 - j;    // all remaining lanes qualify
+                    if (run > 0) {
+                        const int slot_j = __shfl_sync(CAFE_FULL, ms, j);
+                        const bool one_id = (__ballot_sync(CAFE_FULL, lane >= j && lane < j + run && x != xj) == 0);
+                        hvalid = one_id; hx = xj; hslot = slot_j; hrow = ((rowmask >> slot_j) & 1) != 0; hbound = bound;
+                    }
                 }
                 if (run >= 2) {
-                    // counts are added strictly in lookup order by one chain of float adds; every lane
-                    // keeps the running count as of its own lookup
-                    float acc = __shfl_sync(CAFE_FULL, cnt0, o);
+                    a0 = __shfl_sync(CAFE_FULL, a0, o); a1 = __shfl_sync(CAFE_FULL, a1, o);
+                    a2 = __shfl_sync(CAFE_FULL, a2, o); a3 = __shfl_sync(CAFE_FULL, a3, o);
                     float my_acc = 0.f;
-#pragma unroll
-                    for (int u = 0; u < 32; ++u) {
+                    for (int u = j; u < j + run; ++u) {
                         const float cu = __shfl_sync(CAFE_FULL, c, u);
-                        if (u >= j && u < j + run) acc = acc + cu;
-                        if (lane == u) my_acc = acc;
+                        const int su = __shfl_sync(CAFE_FULL, ms, u);
+                        float t = (su == 0) ? a0 : (su == 1) ? a1 : (su == 2) ? a2 : a3;
+                        t = t + cu;
+                        if (su == 0) a0 = t; else if (su == 1) a1 = t; else if (su == 2) a2 = t; else a3 = t;
+                        if (lane == u) my_acc = t;
                     }
                     const bool in_run = lane >= j && lane < j + run;
+                    const bool has_row = ms >= 0 && ((rowmask >> ms) & 1) != 0;
                     const bool cd = !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
                     const unsigned blocked = __ballot_sync(CAFE_FULL, in_run && cd && av);   // ... that could succeed
                     const int done = blocked ? (__ffs(blocked) - 1 - j) : run;
                     if (done > 0) {
                         const bool in_done = lane >= j && lane < j + done;
-                        const float acc_end = __shfl_sync(CAFE_FULL, my_acc, j + done - 1);
                         const unsigned any_cand = __ballot_sync(CAFE_FULL, in_done && cd);
+                        // new count of every slot: the running count at its last lookup inside the applied part
+                        float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
+                        unsigned l0 = __ballot_sync(CAFE_FULL, in_done && ms == 0), l1 = __ballot_sync(CAFE_FULL, in_done && ms == 1);
+                        unsigned l2 = __ballot_sync(CAFE_FULL, in_done && ms == 2), l3 = __ballot_sync(CAFE_FULL, in_done && ms == 3);
+                        e0 = __shfl_sync(CAFE_FULL, my_acc, l0 ? 31 - __clz(l0) : 0);
+                        e1 = __shfl_sync(CAFE_FULL, my_acc, l1 ? 31 - __clz(l1) : 0);
+                        e2 = __shfl_sync(CAFE_FULL, my_acc, l2 ? 31 - __clz(l2) : 0);
+                        e3 = __shfl_sync(CAFE_FULL, my_acc, l3 ? 31 - __clz(l3) : 0);
                         if (lane == o) {
-#pragma unroll
-                            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) R.b.cnt[q] = acc_end;
+                            if (l0) R.b.cnt[0] = e0;
+                            if (l1) R.b.cnt[1] = e1;
+                            if (l2) R.b.cnt[2] = e2;
+                            if (l3) R.b.cnt[3] = e3;
                             R.i_cur += done;
                             if (any_cand) R.cand = true;
                         }
@@ -467,6 +507,8 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
                                 if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                             }
                         }
+                        if (done < run) hvalid = false;
+                        ++d_runs; d_runlen += done;
                         j += done;
                         advanced = true;
                     }
@@ -483,16 +525,42 @@ __global__ void __launch_bounds__(128) k_main_pass(const __grid_constant__ CafeJ
         }
     }
     if (is_long) { atomicAdd(&J.res->n_active_main, 1); atomicMax(&J.res->max_slow_main, slow); }
+    const long long t_long = (J.diag & 128) ? clock64() : 0;
     if (live) R.finish(J);
+    if ((J.diag & 128) && lane == 0) {
+        const long long t_end = clock64();
+        if (hot_warp) {
+            cafe_diag_cycles(J, 0, t_end - t_begin);
+            if (J.diag_buf) {
+                int32_t* d = J.diag_buf + 8 * (widx & 511);
+                d[0] = (int)(t_end - t_begin); d[1] = iend - i; d[2] = d_groups; d[3] = d_calm; d[4] = d_runs; d[5] = d_runlen; d[6] = slow; d[7] = k;
+            }
+        }
+        else { cafe_diag_cycles(J, 1, t_short - t_begin); cafe_diag_cycles(J, 2, t_long - t_short); cafe_diag_cycles(J, 3, t_end - t_begin); }
+    }
 }
-__global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
-    __shared__ int l_p[4][CAFE_STAGE_LRU];
-    __shared__ uint32_t l_x[4][CAFE_STAGE_LRU];
-    __shared__ float l_c[4][CAFE_STAGE_LRU];
+template <int PART>
+__global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];  // per warp: counts of the staged tile / of the chunks being added up
+    __shared__ int s_p[4][CAFE_STAGE_MAIN];                  // staged positions, ids, old event kind | old flags << 8
+    __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
+    if (PART == 1) {
+        const int k = blockIdx.x * blockDim.x + threadIdx.x;
+        cafe_main_body<1>(J, (k < J.n1 && !H.flag[k]) ? k : J.n1, 0, s_c, s_p, s_x, s_kf);
+    } else {
+        for (;;) {
+            int widx;
+            const int k = cafe_next_listed(H, &J.res->list_cursor[J.final_pass ? 2 : 0], J.n1, &widx);
+            if (k < 0) break;
+            cafe_main_body<0>(J, k, widx, s_c, s_p, s_x, s_kf);
+        }
+    }
+}
+template <int PART>
+__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
     const int lane = threadIdx.x & 31;
-    const int wib = threadIdx.x >> 5;
-    bool hot_warp;
-    const int k = cafe_bucket_of_thread(H, J.n2, &hot_warp);
+    const bool hot_warp = PART == 0;
+    const long long t_begin = (J.diag & 128) ? clock64() : 0;
     CafeLruReplay R;
     int jb = 0, jend = 0;
     bool live = k < J.n2;
@@ -505,82 +573,113 @@ __global__ void __launch_bounds__(128) k_lru_pass(const __grid_constant__ CafeJo
         const int len = jend - jb;
         if (((J.diag & 32) && len > J.long_lru) || ((J.diag & 64) && len <= J.long_lru)) jend = jb;
     }
-    const bool is_long = live && (hot_warp || jend - jb > J.long_lru);
-    {
-        const bool is_short = live && !is_long;
-        const int n_k = is_short ? max(jend - jb, 0) : 0;
-        int T;
-        const int pref = cafe_warp_exclusive(n_k, lane, &T);
-        bool done = !is_short;
-        for (int t0 = 0; t0 < T; t0 += CAFE_STAGE_LRU) {
-            const int tn = min(CAFE_STAGE_LRU, T - t0);
+    const bool is_long = PART == 0 && live;
+    if (PART == 1 && live) {
+        // Most entries of an LRU bucket are lookups that hit the main table.  Eight entries at a time:
+        // their positions, then their flags, are loaded together, so a thread waits for two load
+        // latencies per eight entries instead of two per entry.
+        bool done = false;
+        for (int j = jb; j < jend && !done; j += 8) {
+            int pq[8];
+            uint32_t fq[8];
 #pragma unroll
-            for (int r = 0; r < CAFE_STAGE_LRU / 32; ++r) {
-                if (r * 32 >= tn) break;   // warp-uniform
-                const int e = t0 + r * 32 + lane;
-                const int L = cafe_stage_owner(pref, e);
-                const int jL = __shfl_sync(CAFE_FULL, jb, L), pL = __shfl_sync(CAFE_FULL, pref, L);
-                int p = INT32_MAX;       // beyond the job; -1: a lookup that hit the main table
-                uint32_t x = 0;
-                float c = 1.0f;
-                if (e < t0 + tn) {
-                    p = J.ord2[jL + (e - pL)];
-                    if (p < J.limit) {
-                        if (J.mflag[p] & CAFE_F_MISS) { x = J.gid[p]; c = cafe_count_of(J, p); }
-                        else p = -1;
-                    }
-                }
-                l_p[wib][r * 32 + lane] = p; l_x[wib][r * 32 + lane] = x; l_c[wib][r * 32 + lane] = c;
+            for (int q = 0; q < 8; ++q) pq[q] = (j + q < jend) ? J.ord2[j + q] : INT32_MAX;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) fq[q] = (pq[q] < J.limit) ? (uint32_t)J.mflag[pq[q]] : 0u;
+            uint32_t xq[8];
+            float cq[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {   // ids and counts of the misses among them, again all at once
+                xq[q] = 0; cq[q] = 1.0f;
+                if (fq[q] & CAFE_F_MISS) { xq[q] = J.gid[pq[q]]; cq[q] = cafe_count_of(J, pq[q]); }
             }
-            __syncwarp();
-            const int lo = max(pref, t0), hi = min(pref + n_k, t0 + tn);
-            for (int j = lo; j < hi && !done; ++j) {
-                const int p = l_p[wib][j - t0];
-                if (p < 0) continue;
-                if (p >= J.limit) { done = true; break; }
-                R.feed(J, p, l_x[wib][j - t0], l_c[wib][j - t0]);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (done) break;
+                if (pq[q] >= J.limit) { done = true; break; }   // positions ascend inside a bucket
+                if (fq[q] & CAFE_F_MISS) R.feed(J, pq[q], xq[q], cq[q]);
             }
-            __syncwarp();
         }
     }
-    unsigned m = __ballot_sync(CAFE_FULL, is_long);
+    const long long t_short = (J.diag & 128) ? clock64() : 0;
+    unsigned m = PART == 0 ? __ballot_sync(CAFE_FULL, is_long) : 0u;
     while (m) {
         const int o = __ffs(m) - 1;
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, jb, o), e = __shfl_sync(CAFE_FULL, jend, o);
         bool stop = false;
-        // same two-deep pipeline as in the main pass
-        int p_nx = (s + lane < e) ? J.ord2[s + lane] : INT32_MAX;
-        int p_n2 = (s + 32 + lane < e) ? J.ord2[s + 32 + lane] : INT32_MAX;
-        uint32_t x_nx = 0;
-        float c_nx = 1.0f;
-        bool miss_nx = false;
-        if (p_nx < J.limit && (J.mflag[p_nx] & CAFE_F_MISS)) { miss_nx = true; x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); }
-        for (int base = s; base < e && !stop; base += 32) {
-            const int idx = base + lane;
-            const int p = p_nx;
-            const uint32_t x = x_nx;
-            const float c = c_nx;
-            const bool miss = miss_nx;
-            p_nx = p_n2;
-            p_n2 = (base + 64 + lane < e) ? J.ord2[base + 64 + lane] : INT32_MAX;
-            x_nx = 0; c_nx = 1.0f; miss_nx = false;
-            if (p_nx < J.limit && (J.mflag[p_nx] & CAFE_F_MISS)) { miss_nx = true; x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); }
-            // positions ascend inside a bucket: once one lane sees the limit, later chunks are beyond it too
-            stop = __any_sync(CAFE_FULL, idx < e && p >= J.limit);
-            unsigned mm = __ballot_sync(CAFE_FULL, miss);
-            while (mm) {
-                const int j = __ffs(mm) - 1;
-                mm &= mm - 1;
-                const int pj = __shfl_sync(CAFE_FULL, p, j);
-                const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
-                const float cj = __shfl_sync(CAFE_FULL, c, j);
-                if (lane == o) { R.feed(J, pj, xj, cj); ++slow; }
+        // Two-deep pipeline at a granularity of four chunks: every lane holds four entries of the group
+        // being processed, the data of the next group and the positions of the one after.  Most entries
+        // of a long LRU bucket are lookups of a hot id that hit the main table; a group without misses
+        // costs four ballots.
+        int gp[4], np_[4], n2p[4];
+        uint32_t gx[4], nx[4];
+        float gc[4], nc[4];
+        bool gm[4], nm[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int i0 = s + 32 * q + lane, i1 = i0 + 128;
+            gp[q] = i0 < e ? J.ord2[i0] : INT32_MAX;
+            np_[q] = i1 < e ? J.ord2[i1] : INT32_MAX;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            gm[q] = false; gx[q] = 0; gc[q] = 1.0f;
+            if (gp[q] < J.limit && (J.mflag[gp[q]] & CAFE_F_MISS)) { gm[q] = true; gx[q] = J.gid[gp[q]]; gc[q] = cafe_count_of(J, gp[q]); }
+        }
+        for (int base = s; base < e && !stop; base += 128) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int i2 = base + 256 + 32 * q + lane;
+                n2p[q] = i2 < e ? J.ord2[i2] : INT32_MAX;
+                nm[q] = false; nx[q] = 0; nc[q] = 1.0f;
+                if (np_[q] < J.limit && (J.mflag[np_[q]] & CAFE_F_MISS)) { nm[q] = true; nx[q] = J.gid[np_[q]]; nc[q] = cafe_count_of(J, np_[q]); }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (stop) break;   // warp-uniform
+                const int idx = base + 32 * q + lane;
+                // positions ascend inside a bucket: once one lane sees the limit, later entries are beyond it too
+                stop = __any_sync(CAFE_FULL, idx < e && gp[q] >= J.limit);
+                unsigned mm = __ballot_sync(CAFE_FULL, gm[q]);
+                while (mm) {
+                    const int j = __ffs(mm) - 1;
+                    mm &= mm - 1;
+                    const int pj = __shfl_sync(CAFE_FULL, gp[q], j);
+                    const uint32_t xj = __shfl_sync(CAFE_FULL, gx[q], j);
+                    const float cj = __shfl_sync(CAFE_FULL, gc[q], j);
+                    if (lane == o) { R.feed(J, pj, xj, cj); ++slow; }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                gp[q] = np_[q]; gm[q] = nm[q]; gx[q] = nx[q]; gc[q] = nc[q];
+                np_[q] = n2p[q];
             }
         }
     }
     if (is_long) { atomicAdd(&J.res->n_active_lru, 1); atomicMax(&J.res->max_feed_lru, slow); }
+    const long long t_long = (J.diag & 128) ? clock64() : 0;
     if (live) R.finish(J);
+    if ((J.diag & 128) && lane == 0) {
+        const long long t_end = clock64();
+        if (hot_warp) cafe_diag_cycles(J, 4, t_end - t_begin);
+        else { cafe_diag_cycles(J, 5, t_short - t_begin); cafe_diag_cycles(J, 6, t_long - t_short); cafe_diag_cycles(J, 7, t_end - t_begin); }
+    }
+}
+template <int PART>
+__global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
+    if (PART == 1) {
+        const int k = blockIdx.x * blockDim.x + threadIdx.x;
+        cafe_lru_body<1>(J, (k < J.n2 && !H.flag[k]) ? k : J.n2);
+    } else {
+        for (;;) {
+            int widx;
+            const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2, &widx);
+            if (k < 0) break;
+            cafe_lru_body<0>(J, k);
+        }
+    }
 }
 __global__ void k_route(const __grid_constant__ CafeJob J) {
     int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
@@ -762,6 +861,9 @@ struct CudaBackend {
 
     ~CudaBackend() {
         if (cub_tmp) cudaFree(cub_tmp);
+        if (pass_side) { cudaStreamSynchronize(pass_side); cudaStreamDestroy(pass_side); }
+        if (pass_ev_fork) cudaEventDestroy(pass_ev_fork);
+        if (pass_ev_join) cudaEventDestroy(pass_ev_join);
         for (int i = 0; i < LANES; ++i) {
             if (side[i]) { cudaStreamSynchronize(side[i]); cudaStreamDestroy(side[i]); }
             if (ev_fork[i]) cudaEventDestroy(ev_fork[i]);
@@ -849,10 +951,10 @@ struct CudaBackend {
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
         for (int i = 0; i < 2; ++i) {
-            check(cudaMalloc(&hot_list[i], 4 * CAFE_HOT_CAP));
-            check(cudaMalloc(&hot_count[i], 4));
+            check(cudaMalloc(&hot_list[i], 4 * CAFE_LIST_CAP));
+            check(cudaMalloc(&hot_count[i], 8));
             check(cudaMalloc(&hot_flag[i], (size_t)hot_nb[i]));
-            check(cudaMemsetAsync(hot_count[i], 0, 4, stream));
+            check(cudaMemsetAsync(hot_count[i], 0, 8, stream));
             check(cudaMemsetAsync(hot_flag[i], 0, (size_t)hot_nb[i], stream));
         }
         // largest temporary any CUB call below can ask for
@@ -905,10 +1007,11 @@ struct CudaBackend {
         k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start);
         check_launch();
         const int t = (nb == hot_nb[0]) ? 0 : 1;
-        check(cudaMemsetAsync(hot_count[t], 0, 4, st));
+        check(cudaMemsetAsync(hot_count[t], 0, 8, st));
         check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, st));
         const int hot_len = std::max(CAFE_HOT_LEN, (int)(16.0 * M / nb));
-        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, hot_list[t], hot_count[t], hot_flag[t]);
+        const int long_len = std::max(16, (int)(4.0 * M / nb));
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, long_len, hot_list[t], hot_count[t], hot_flag[t]);
         check_launch();
         check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
         }
@@ -925,10 +1028,52 @@ struct CudaBackend {
             side_pending[lane] = false;
         }
     }
+    // the list launch of a pass runs on a high-priority stream beside the thread-per-bucket launch
+    cudaStream_t pass_side = nullptr;
+    cudaEvent_t pass_ev_fork = nullptr, pass_ev_join = nullptr;
+    void pass_fork() {
+        if (!pass_side) {
+            int lo = 0, hi = 0;
+            check(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            check(cudaStreamCreateWithPriority(&pass_side, cudaStreamNonBlocking, hi));
+            check(cudaEventCreateWithFlags(&pass_ev_fork, cudaEventDisableTiming));
+            check(cudaEventCreateWithFlags(&pass_ev_join, cudaEventDisableTiming));
+        }
+        check(cudaEventRecord(pass_ev_fork, stream));
+        check(cudaStreamWaitEvent(pass_side, pass_ev_fork, 0));
+    }
+    void pass_join() {
+        check(cudaEventRecord(pass_ev_join, pass_side));
+        check(cudaStreamWaitEvent(stream, pass_ev_join, 0));
+    }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
-    void main_pass(const CafeJob& J) {
+    int32_t* diag_buf = nullptr;
+    void diag_dump() {
+        if (!diag_buf) return;
+        std::vector<int32_t> h(512 * 8);
+        cudaMemcpy(h.data(), diag_buf, h.size() * 4, cudaMemcpyDeviceToHost);
+        std::vector<int> idx(512);
+        for (int q = 0; q < 512; ++q) idx[q] = q;
+        std::sort(idx.begin(), idx.end(), [&](int a, int b) { return h[8 * a] > h[8 * b]; });
+        for (int q = 0; q < 6; ++q) {
+            const int32_t* d = &h[8 * idx[q]];
+            fprintf(stderr, "     hot warp %3d: %7d cyc, %5d entries, %3d groups, %3d calm chunks, %4d runs (%5d lookups), %3d feeds, bucket %d\n",
+                    idx[q], d[0], d[1], d[2], d[3], d[4], d[5], d[6], d[7]);
+        }
+    }
+    void main_pass(const CafeJob& J0) {
+        CafeJob J = J0;
+        if (J.diag & 128) {
+            if (!diag_buf) cudaMalloc(&diag_buf, 512 * 8 * 4);
+            cudaMemsetAsync(diag_buf, 0, 512 * 8 * 4, stream);
+            J.diag_buf = diag_buf;
+        }
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
-        k_main_pass<<<CAFE_HOT_BLOCKS + cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
+        pass_fork();
+        k_main_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(0));
+        check_launch();
+        k_main_pass<1><<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
+        pass_join();
         check_launch();
     }
     void route(const CafeJob& J) {
@@ -950,7 +1095,11 @@ struct CudaBackend {
     }
     void lru_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.all_active ? CAFE_P_LRU : CAFE_P_LRU_LATER, stream);
-        k_lru_pass<<<CAFE_HOT_BLOCKS + cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
+        pass_fork();
+        k_lru_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(1));
+        check_launch();
+        k_lru_pass<1><<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
+        pass_join();
         check_launch();
     }
     void resolve(const CafeJob& J) {

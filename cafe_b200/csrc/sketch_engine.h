@@ -426,6 +426,12 @@ private:
             tl_changed_prev = R.tl_changed != 0;
             pb ^= 1;
             if (diag) fprintf(stderr, "round %d begin %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.begin, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
+            if (diag && (J.diag & 128)) {
+                be.diag_dump();
+                static const char* names[8] = {"main hot", "main short", "main long", "main warp", "lru hot", "lru short", "lru long", "lru warp"};
+                for (int q = 0; q < 8; ++q)
+                    if (R.diag_warps[q]) fprintf(stderr, "   %-10s warps %7d  max %8d cyc  mean %8.0f cyc\n", names[q], R.diag_warps[q], R.diag_max_cycles[q], (double)R.diag_sum_cycles[q] / R.diag_warps[q]);
+            }
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
             // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
             // per-segment deltas of a round that has not converged yet are estimates, but shrinking
