@@ -608,53 +608,62 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, jb, o), e = __shfl_sync(CAFE_FULL, jend, o);
         bool stop = false;
-        // Two-deep pipeline at a granularity of four chunks: every lane holds four entries of the group
-        // being processed, the data of the next group and the positions of the one after.  Most entries
-        // of a long LRU bucket are lookups of a hot id that hit the main table; a group without misses
-        // costs four ballots.
-        int gp[4], np_[4], n2p[4];
-        uint32_t gx[4], nx[4];
-        float gc[4], nc[4];
-        bool gm[4], nm[4];
+        // Three-stage pipeline at a granularity of eight chunks (256 entries, eight per lane): positions
+        // are requested three groups ahead, the flags of those positions two groups ahead, ids and counts
+        // of the misses among them one group ahead, so that every load has a whole iteration to arrive
+        // before the next stage needs it.  Most entries of a long LRU bucket are lookups of a hot id that
+        // hit the main table; a group without misses costs eight ballots.
+        constexpr int GL = 8;
+        int p0[GL], p1[GL], p2[GL], p3[GL];
+        uint32_t f0[GL], f1[GL], f2[GL], x0[GL], x1[GL];
+        float c0[GL], c1[GL];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int i0 = s + 32 * q + lane, i1 = i0 + 128;
-            gp[q] = i0 < e ? J.ord2[i0] : INT32_MAX;
-            np_[q] = i1 < e ? J.ord2[i1] : INT32_MAX;
+        for (int q = 0; q < GL; ++q) {
+            const int i0 = s + 32 * q + lane, i1 = i0 + 32 * GL, i2 = i1 + 32 * GL;
+            p0[q] = i0 < e ? J.ord2[i0] : INT32_MAX;
+            p1[q] = i1 < e ? J.ord2[i1] : INT32_MAX;
+            p2[q] = i2 < e ? J.ord2[i2] : INT32_MAX;
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            gm[q] = false; gx[q] = 0; gc[q] = 1.0f;
-            if (gp[q] < J.limit && (J.mflag[gp[q]] & CAFE_F_MISS)) { gm[q] = true; gx[q] = J.gid[gp[q]]; gc[q] = cafe_count_of(J, gp[q]); }
+        for (int q = 0; q < GL; ++q) {
+            f0[q] = p0[q] < J.limit ? (uint32_t)J.mflag[p0[q]] : 0u;
+            f1[q] = p1[q] < J.limit ? (uint32_t)J.mflag[p1[q]] : 0u;
         }
-        for (int base = s; base < e && !stop; base += 128) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int i2 = base + 256 + 32 * q + lane;
-                n2p[q] = i2 < e ? J.ord2[i2] : INT32_MAX;
-                nm[q] = false; nx[q] = 0; nc[q] = 1.0f;
-                if (np_[q] < J.limit && (J.mflag[np_[q]] & CAFE_F_MISS)) { nm[q] = true; nx[q] = J.gid[np_[q]]; nc[q] = cafe_count_of(J, np_[q]); }
+        for (int q = 0; q < GL; ++q) {
+            x0[q] = 0; c0[q] = 1.0f;
+            if (f0[q] & CAFE_F_MISS) { x0[q] = J.gid[p0[q]]; c0[q] = cafe_count_of(J, p0[q]); }
+        }
+        for (int base = s; base < e && !stop; base += 32 * GL) {
+#pragma unroll
+            for (int q = 0; q < GL; ++q) {
+                const int i3 = base + 3 * 32 * GL + 32 * q + lane;
+                p3[q] = i3 < e ? J.ord2[i3] : INT32_MAX;
+                f2[q] = p2[q] < J.limit ? (uint32_t)J.mflag[p2[q]] : 0u;
+                x1[q] = 0; c1[q] = 1.0f;
+                if (f1[q] & CAFE_F_MISS) { x1[q] = J.gid[p1[q]]; c1[q] = cafe_count_of(J, p1[q]); }
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < GL; ++q) {
                 if (stop) break;   // warp-uniform
                 const int idx = base + 32 * q + lane;
                 // positions ascend inside a bucket: once one lane sees the limit, later entries are beyond it too
-                stop = __any_sync(CAFE_FULL, idx < e && gp[q] >= J.limit);
-                unsigned mm = __ballot_sync(CAFE_FULL, gm[q]);
+                stop = __any_sync(CAFE_FULL, idx < e && p0[q] >= J.limit);
+                unsigned mm = __ballot_sync(CAFE_FULL, (f0[q] & CAFE_F_MISS) != 0);
                 while (mm) {
                     const int j = __ffs(mm) - 1;
                     mm &= mm - 1;
-                    const int pj = __shfl_sync(CAFE_FULL, gp[q], j);
-                    const uint32_t xj = __shfl_sync(CAFE_FULL, gx[q], j);
-                    const float cj = __shfl_sync(CAFE_FULL, gc[q], j);
+                    const int pj = __shfl_sync(CAFE_FULL, p0[q], j);
+                    const uint32_t xj = __shfl_sync(CAFE_FULL, x0[q], j);
+                    const float cj = __shfl_sync(CAFE_FULL, c0[q], j);
                     if (lane == o) { R.feed(J, pj, xj, cj); ++slow; }
                 }
             }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                gp[q] = np_[q]; gm[q] = nm[q]; gx[q] = nx[q]; gc[q] = nc[q];
-                np_[q] = n2p[q];
+            for (int q = 0; q < GL; ++q) {
+                p0[q] = p1[q]; f0[q] = f1[q]; x0[q] = x1[q]; c0[q] = c1[q];
+                p1[q] = p2[q]; f1[q] = f2[q];
+                p2[q] = p3[q];
             }
         }
     }
