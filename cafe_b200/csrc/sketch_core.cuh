@@ -202,7 +202,7 @@ CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
 // =================================================================================================
 // Parallel form.
 // =================================================================================================
-struct alignas(16) CafeFn { int32_t a, b, np, pad; };   // FIFO size transfer s -> max(s + a, b), and pushes so far
+struct alignas(16) CafeFn { int32_t a, b, np, nmiss; };   // FIFO size transfer s -> max(s + a, b); pushes and main-table misses so far
 
 // per-lookup result flags (one byte written by the main pass, one by the LRU pass)
 enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE_F_GOT = 16 };
@@ -268,7 +268,6 @@ struct CafeJob {
     uint8_t* lflag;      // [M] CAFE_F_* written by the LRU pass for lookups that missed the main table
     int32_t* ins_res;    // [M] result of the event of this position when its target replayed it: 0 ok, -1 failed, >0 failed and pushed this row
     // scratch
-    int32_t* tstamp;     // [M] inclusive count of misses up to each position (at commit)
     CafeFn* op_fn;       // [M] FIFO-size transfer function of the position, then its inclusive scan
     // outputs
     int32_t* mask;       // [M] 1 = this lookup was handed a hot row (the reference's insert result)
@@ -614,7 +613,7 @@ CAFE_HD void cafe_lru_tconvert(const CafeJob& J, int k) {
     CafeLruBucket& b = J.lru_out[k];
 #pragma unroll
     for (int q = 0; q < CAFE_SLOTS; ++q)
-        if (b.t[q] > J.t0) b.t[q] = J.t0 + J.tstamp[b.t[q] - J.t0 - 1];
+        if (b.t[q] > J.t0) b.t[q] = J.t0 + J.op_fn[b.t[q] - J.t0 - 1].nmiss;   // misses up to and including that position
 }
 // at commit: the reference's per-lookup insert result
 CAFE_HD void cafe_finalize_position(const CafeJob& J, int p) {
@@ -666,7 +665,7 @@ CAFE_HD CafeFn cafe_resolve_fn(const CafeJob& J, int p) {
     cafe_op_fn(o.op1, &a1, &b1);
     cafe_compose(a0, b0, a1, b1, &f.a, &f.b);
     f.np = (o.op0 == 2) + (o.op1 == 2);
-    f.pad = 0;
+    f.nmiss = (J.mflag[p] & CAFE_F_MISS) ? 1 : 0;
     return f;
 }
 CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) { J.op_fn[p] = cafe_resolve_fn(J, p); }

@@ -698,9 +698,14 @@ __global__ void k_finalize_positions(const __grid_constant__ CafeJob J) {
     int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_finalize_position(J, p);
 }
-__global__ void k_lru_tconvert(const __grid_constant__ CafeJob J) {
+// at commit, per bucket of either table: the LRU clock renumbering and the cursors of the sorted order
+__global__ void k_commit_tables(const __grid_constant__ CafeJob J, int32_t* beg1, int32_t* beg2) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
-    if (k < J.n2) cafe_lru_tconvert(J, k);
+    if (k < J.n2) {
+        cafe_lru_tconvert(J, k);
+        beg2[k] = cafe_advance_cursor(J.ord2, beg2[k], J.start2[k + 1], J.limit);
+    }
+    if (k < J.n1) beg1[k] = cafe_advance_cursor(J.ord1, beg1[k], J.start1[k + 1], J.limit);
 }
 // per-segment threshold crossings and the number of LRU visits: block-wide sums, one atomic per
 // block and counter (a block of consecutive positions lies in one segment except at boundaries)
@@ -742,9 +747,6 @@ __global__ void k_seq_insert(CafeSeqState* Sd, const uint32_t* __restrict__ gid,
     *Sd = S;
 }
 
-struct MissFlag {
-    __host__ __device__ __forceinline__ int32_t operator()(const uint8_t& f) const { return (int32_t)(f & 1); }
-};
 // input iterators of the two FIFO scans: values are computed from the per-lookup flags on the fly
 struct FnOfIndex {
     CafeJob J;
@@ -755,7 +757,7 @@ struct FnCompose {
         CafeFn r;
         cafe_compose(f.a, f.b, g.a, g.b, &r.a, &r.b);
         r.np = f.np + g.np;
-        r.pad = 0;
+        r.nmiss = f.nmiss + g.nmiss;
         return r;
     }
 };
@@ -1094,12 +1096,10 @@ struct CudaBackend {
     void finalize(const CafeJob& J) {
         CAFE_PROF(CAFE_P_COMMIT, stream);
         const int cnt = J.limit - J.begin;
-        cub::TransformInputIterator<int32_t, MissFlag, const uint8_t*> in(J.mflag + J.begin, MissFlag());
-        size_t b = cub_bytes;
-        check(cub::DeviceScan::InclusiveSum(cub_tmp, b, in, J.tstamp + J.begin, cnt, stream));
         k_finalize_positions<<<cafe_blocks(cnt), CAFE_TPB, 0, stream>>>(J);
         check_launch();
-        k_lru_tconvert<<<cafe_blocks(J.n2), CAFE_TPB, 0, stream>>>(J);
+        k_commit_tables<<<cafe_blocks(J.n1 > J.n2 ? J.n1 : J.n2), CAFE_TPB, 0, stream>>>(J, const_cast<int32_t*>(J.beg1),
+                                                                                 const_cast<int32_t*>(J.beg2));
         check_launch();
     }
     void lru_pass(const CafeJob& J) {

@@ -97,7 +97,6 @@ public:
             tl_rank[i] = (int32_t*)be.alloc(8 * M);
             pushbuf[i] = (uint32_t*)be.alloc(4 * M);
         }
-        tstamp = (int32_t*)be.alloc(4 * M);
         ins_res = (int32_t*)be.alloc(4 * M);
         op_fn = (CafeFn*)be.alloc(sizeof(CafeFn) * M);
         seq_dev = (CafeSeqState*)be.alloc(sizeof(CafeSeqState));
@@ -107,7 +106,7 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !tstamp || !ins_res || !op_fn ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !ins_res || !op_fn ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
         for (int i = 0; i < 2; ++i)
@@ -204,8 +203,10 @@ public:
                         done_e = s + done;
                         const int upto = seg_off[done_e] - base;
                         be.sort_join(-1);
-                        be.advance_cursors(ord1, start1, beg1, n1, upto);
-                        be.advance_cursors(ord2, start2, beg2, n2, upto);
+                        if (!cursors_advanced) {   // (the commit of a converged job moves them itself)
+                            be.advance_cursors(ord1, start1, beg1, n1, upto);
+                            be.advance_cursors(ord2, start2, beg2, n2, upto);
+                        }
                     } else {
                         int rc = run_sequential(g + lo, im ? im + lo : nullptr, hi - lo, mk + lo, pr ? pr + lo : nullptr);
                         if (rc != CAFE_OK) return rc;
@@ -289,6 +290,7 @@ public:
     }
 
 private:
+    bool cursors_advanced = false;
     const uint32_t* presorted_gid = nullptr;
     int presorted_n = 0;
     bool ready = false;
@@ -304,7 +306,7 @@ private:
     int32_t* tl_size[2] = {nullptr, nullptr};
     int32_t* tl_rank[2] = {nullptr, nullptr};
     uint32_t* pushbuf[2] = {nullptr, nullptr};
-    int32_t *tstamp = nullptr, *ins_res = nullptr;
+    int32_t* ins_res = nullptr;
     CafeFn* op_fn = nullptr;
     CafeRoundResult* res_dev = nullptr;
     size_t off_mark2 = 0, off_res = 0, span_clear = 0;
@@ -317,7 +319,7 @@ private:
     void release() {
         if (!ready && !mainb[0]) return;
         void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
-                        tstamp, ins_res, op_fn, seq_dev, cand_key[0], cand_key[1],
+                        ins_res, op_fn, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
         mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
@@ -361,6 +363,7 @@ private:
                      int32_t* post_row, int* done) {
         CafeJob J;
         memset(&J, 0, sizeof(J));
+        cursors_advanced = false;
         const int planned = nseg;
         J.gid = gid; J.imp = imp; J.M = M; J.begin = seg[0]; J.limit = seg[nseg]; J.nseg = nseg;
         for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i];
@@ -371,7 +374,7 @@ private:
         J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
         J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
         J.ev = ev; J.head = head; J.nxt = nxt; J.mark_own = mark_own; J.mstate = mstate; J.mark2 = mark2; J.lstate = lstate;
-        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.tstamp = tstamp; J.op_fn = op_fn;
+        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.op_fn = op_fn;
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
@@ -468,7 +471,8 @@ private:
             be.main_pass(J);
             J.final_pass = 0;
         }
-        be.finalize(J);   // per-lookup results, LRU clock values
+        be.finalize(J);   // per-lookup results, LRU clock values, cursors of the sorted order
+        cursors_advanced = true;
         if (R.n_push > 0) be.commit_queue(ring, ring_mask, q_head, q_size, R.n_pop_ok, pushbuf[pb], R.n_push);
         cur ^= 1;
         q_head += (uint32_t)R.n_pop_ok;

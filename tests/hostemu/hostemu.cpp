@@ -76,10 +76,10 @@ struct HostBackend {
     }
     // per-lookup results and the LRU clock numbering, once the rounds have converged
     void finalize(const CafeJob& J) {
-        int32_t acc = 0;
-        for (int p = J.begin; p < J.limit; ++p) { acc += (J.mflag[p] & CAFE_F_MISS) ? 1 : 0; J.tstamp[p] = acc; }
         for (int p = J.begin; p < J.limit; ++p) cafe_finalize_position(J, p);
         for (int k = 0; k < J.n2; ++k) cafe_lru_tconvert(J, k);
+        advance_cursors(J.ord1, J.start1, const_cast<int32_t*>(J.beg1), J.n1, J.limit);
+        advance_cursors(J.ord2, J.start2, const_cast<int32_t*>(J.beg2), J.n2, J.limit);
     }
     void lru_pass(const CafeJob& J) {
         if (flip_order) for (int k = J.n2 - 1; k >= 0; --k) cafe_lru_pass_bucket(J, k);
@@ -91,7 +91,7 @@ struct HostBackend {
             CafeFn r;
             cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &r.a, &r.b);
             r.np = J.op_fn[p - 1].np + J.op_fn[p].np;
-            r.pad = 0;
+            r.nmiss = J.op_fn[p - 1].nmiss + J.op_fn[p].nmiss;
             J.op_fn[p] = r;
         }
         for (int p = J.limit - 1; p >= J.begin; --p) cafe_resolve_write(J, p);
