@@ -324,6 +324,14 @@ def run_ours(args, rank, world, local_rank):
     ms_prof = timed(step_fn, args.steps, args.warmup + args.steps)
     slots = prof.read()
     prof.enable(False)
+    rank_info = None
+    if dist is not None:
+        # how evenly the ranks are loaded: every rank's own kernel time per step (sum of its per-kernel times)
+        mine = torch.tensor([sum(v[0] for v in slots.values()) / args.steps], device=dev)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        rank_info = {"own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
+                     "host_cpus": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()}
     line = None
     if rank == 0:
         peak, peak_kind = read_peaks()
@@ -367,6 +375,8 @@ def run_ours(args, rank, world, local_rank):
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "phases": phases,
                 "phases_note": "per-kernel CUDA-event times of a separate pass with the side-stream overlap switched off",
                 "ms_per_step_profiled": ms_prof / args.steps}
+        if rank_info is not None:
+            line["ranks"] = rank_info
         if world == 1:
             line["sketch"] = {k: v for k, v in grp.sketch.stats().items()}
         if world == 1 and not args.no_cpu_baseline:
