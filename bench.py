@@ -296,9 +296,12 @@ def run_ours(args, rank, world, local_rank):
         ms = e0.elapsed_time(e1)
         if dist is not None:
             t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            every = [torch.zeros_like(t) for _ in range(world)]
+            dist.all_gather(every, t)
+            timed.per_rank = [float(x.item()) for x in every]
+            ms = max(timed.per_rank)
         return ms
+    timed.per_rank = None
 
     for s in range(args.warmup):
         step_fn(s)
@@ -306,6 +309,7 @@ def run_ours(args, rank, world, local_rank):
     l0 = prof.launch_count()
     with ClockSampler(local_rank) as clk:
         ms = timed(step_fn, args.steps, args.warmup)
+    step_ms_per_rank = [round(x / args.steps, 3) for x in timed.per_rank] if timed.per_rank else None
     launches = prof.launch_count() - l0
     clocks = clk.summary()
     total_ids = ids_per_step * (world if world > 1 else 1)
@@ -330,7 +334,7 @@ def run_ours(args, rank, world, local_rank):
         mine = torch.tensor([sum(v[0] for v in slots.values()) / args.steps], device=dev)
         allr = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allr, mine)
-        rank_info = {"own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
+        rank_info = {"step_ms": step_ms_per_rank, "own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
                      "host_cpus": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()}
     line = None
     if rank == 0:
