@@ -53,34 +53,76 @@ def read_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons of this rank's GPU while the timed region runs.
+
+    NVML is read from a thread of this process and initialised before the warm-up, so that the timed region
+    sees only the cheap per-sample queries and not one NVML start-up per rank against the driver while the steps
+    are being launched.  Without the NVML module, rank 0 alone falls back to an nvidia-smi poller started ahead
+    of the warm-up."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
-        self.idx = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, gpu_index: int, uuid=None, allow_smi=True):
+        self.idx, self.nv, self.h, self.proc = gpu_index, None, None, None
+        self.samples, self.lines, self.on, self.t = [], [], False, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = None
+            if uuid is not None:
+                for cand in (f"GPU-{uuid}", str(uuid)):
+                    try:
+                        h = pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if hasattr(cand, "encode") else cand)
+                        break
+                    except Exception:
+                        h = None
+            if h is None:
+                h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.nv, self.h = pynvml, h
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+            if allow_smi:
+                try:
+                    self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                                  "50", "-i", str(gpu_index)], stdout=subprocess.PIPE,
+                                                 stderr=subprocess.DEVNULL, text=True)
+                    self.t = threading.Thread(target=self._read_smi, daemon=True)
+                    self.t.start()
+                except Exception:
+                    self.proc = None
+
+    def _read_smi(self):
+        for line in self.proc.stdout:
+            if self.on:
+                self.lines.append(line.strip())
+
+    def _poll(self):
+        nv = self.nv
+        while self.on:
+            try:
+                self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)),
+                                     int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))))
+            except Exception:
+                pass
+            time.sleep(0.004)
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
+        self.on = True
+        if self.nv is not None:
+            self.t = threading.Thread(target=self._poll, daemon=True)
             self.t.start()
-        except Exception:
-            self.proc = None
         return self
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
 
     def __exit__(self, *exc):
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(0.06)
+        self.on = False
+        if self.nv is not None and self.t is not None:
+            self.t.join(timeout=1)
+        if self.proc:
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -88,6 +130,14 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        if self.nv is not None and self.samples:
+            nv = self.nv
+            bits = [nv.nvmlClocksThrottleReasonHwSlowdown, nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                    nv.nvmlClocksThrottleReasonSwThermalSlowdown, nv.nvmlClocksThrottleReasonSwPowerCap]
+            reasons = sorted({n for _, r in self.samples for n, b in zip(names, bits) if r & b})
+            return {"sm_mhz": float(np.median([c for c, _ in self.samples])), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                    "samples": len(self.samples), "source": "nvml"}
         sm, mx, reasons = [], [], set()
         for ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
@@ -97,12 +147,13 @@ class ClockSampler:
                 sm.append(float(f[1])); mx.append(float(f[2]))
             except ValueError:
                 continue
-            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+            for name, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm),
+                "source": "nvidia-smi"}
 
 
 # -------------------------------------------------------------------------------------------------
@@ -303,11 +354,16 @@ def run_ours(args, rank, world, local_rank):
         return ms
     timed.per_rank = None
 
+    try:
+        uuid = torch.cuda.get_device_properties(dev).uuid
+    except Exception:
+        uuid = None
+    clk = ClockSampler(local_rank, uuid, allow_smi=(rank == 0))   # set up ahead of the warm-up; samples only inside `with`
     for s in range(args.warmup):
         step_fn(s)
     barrier()
     l0 = prof.launch_count()
-    with ClockSampler(local_rank) as clk:
+    with clk:
         ms = timed(step_fn, args.steps, args.warmup)
     step_ms_per_rank = [round(x / args.steps, 3) for x in timed.per_rank] if timed.per_rank else None
     launches = prof.launch_count() - l0
