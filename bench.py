@@ -390,7 +390,13 @@ def run_ours(args, rank, world, local_rank):
         mine = torch.tensor([sum(v[0] for v in slots.values()) / args.steps], device=dev)
         allr = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allr, mine)
-        rank_info = {"step_ms": step_ms_per_rank, "own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
+        names = sorted(slots.keys())
+        vec = torch.tensor([slots[k][0] / args.steps for k in names], device=dev, dtype=torch.float32)
+        allv = [torch.zeros_like(vec) for _ in range(world)]
+        dist.all_gather(allv, vec)
+        per_slot = {k: [round(float(allv[r][i].item()), 3) for r in range(world)] for i, k in enumerate(names)
+                    if max(float(allv[r][i].item()) for r in range(world)) >= 0.05}
+        rank_info = {"phase_ms_per_rank": per_slot, "step_ms": step_ms_per_rank, "own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
                      "host_cpus": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()}
     line = None
     if rank == 0:
