@@ -366,9 +366,13 @@ __global__ void __launch_bounds__(256)
 k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rank, int rows, int D, int64_t total_rows) {
     const int lanes = D / 4;                       // lanes per row (16-byte vectors)
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t q = t / lanes;
+    const int64_t q0 = t / lanes;
     const int c = (int)(t % lanes) * 4;
-    if (q >= total_rows) return;
+    if (q0 >= total_rows) return;
+    // Every rank starts with the block of the owner after itself and goes round: at any moment the ranks
+    // store into different owners, so no owner's NVLink ingress has to take all of them at once.
+    int64_t q = q0 + P.row_off[(rank + 1) % nranks];
+    if (q >= total_rows) q -= total_rows;
     int g = 0;
     while (g + 1 < nranks && q >= P.row_off[g + 1]) ++g;
     const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
