@@ -167,6 +167,7 @@ public:
             int32_t* pr = post_row ? post_row + base : nullptr;
             struct SortJoin { BE& be; ~SortJoin() { be.sort_join(-1); } } sort_join_guard{be};
             if (parallel && mtot > 0 && !(presorted_gid == g && presorted_n == mtot)) {
+                be.sort_join(-1);   // a head start for other arrays may still be writing the orders
                 // the LRU table's order is first needed by the first LRU pass: it is built on a side
                 // lane of the backend while the main table's order and first pass proceed
                 be.sort_lookups(g, mtot, n2, ord2, start2, beg2, 2);
