@@ -13,7 +13,7 @@ Differences from the reference that a caller can see:
     gradient for them) unless `fused_update=False`, which materialises the sparse gradients the
     reference's embedding_bag calls would produce so that torch.optim.SGD can apply them;
   * migration copies a hash row into a hot row only when the id is in the main table after its
-    field's insert call (the reference indexes out of range otherwise).
+    field's insert call (the reference indexes weight_h with a global id, out of range, otherwise).
 """
 from __future__ import annotations
 
