@@ -169,3 +169,16 @@ def test_reference_ctypes_abi_host_pointers():
             m = np.ctypeslib.as_array(lib.batch_insert(ip, 100), shape=(100,)).copy()
             assert np.array_equal(m, o.batch_insert(ids))
         assert lib.analyse(ip, 100) == o.analyse(ids) and lib.analyse1(ip, 100) == o.analyse1(ids)
+
+
+@pytest.mark.parametrize("block", range(4))
+def test_random_configurations(block):
+    """Seeded random shapes: small to mid-size sketches, calls of 200-6000 ids over domains from 30 ids (long
+    buckets whose ids alternate) to 200 000, fused windows, ragged and empty calls, id 0, unit counts.
+    Masks, post-insert rows and the whole state must equal the sequential algorithm's after every job."""
+    for seed in range(block * 12, block * 12 + 12):
+        r = np.random.default_rng(seed)
+        lim = int(r.integers(40, 3000)); thr = int(r.integers(1, 5)); alpha = float(r.choice([1.0000005, 1.05, 1.5]))
+        n = int(r.integers(200, 6000)); dom = int(r.choice([30, 200, 3000, 200000])); fuse = int(r.integers(1, 8))
+        drive(lim, thr, alpha, fuse * 6, n, dom, fuse, seed=1000 + seed, zero_ids=seed % 3 == 0, ragged=seed % 4 == 1,
+              unit=seed % 5 == 2)
