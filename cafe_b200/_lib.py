@@ -56,6 +56,9 @@ SIGNATURES = {
                                            POINTER(_vp), c_int, c_int, c_int64, c_int64, _vp, _vp, _vp]),
     "cafe_shard_pull_importance": (c_int, [_vp, POINTER(_vp), c_int, c_int, c_int, c_int, c_int64, c_int64, _vp, _vp, _vp]),
     "cafe_shard_push_grads": (c_int, [_vp, c_int, c_int, c_int, c_int, c_int, POINTER(_vp), _vp]),
+    "cafe_shard_push_grads_fields": (c_int, [_vp, c_int, c_int, c_int, c_int, c_int, POINTER(_vp), c_int, c_int, _vp]),
+    "cafe_embed_backward_gated": (c_int, [_vp, _vp, c_int64, c_int64, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
+                                          POINTER(_vp), _vp, c_int, c_int, c_float, c_int, c_int, _vp, _vp]),
     "cafe_embed_backward_imp": (c_int, [_vp, _vp, c_int64, c_int64, _vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                         POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
     "cafe_profile_slots": (c_int, []),

@@ -29,6 +29,8 @@ struct CafeEmbedWorkspace {
     size_t cub_bytes = 0;
     cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t late = nullptr;     // importance of fields whose gradients arrive behind a gate
+    cudaEvent_t ev_late = nullptr;
     // arrays whose side work cafe_embed_backward_begin has already started (null: none)
     const uint32_t* begun_gid = nullptr;
     const int32_t* begun_row = nullptr;
@@ -44,6 +46,8 @@ int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const i
                          int32_t* post_row, int mode, cudaStream_t stream);
 // starts the insert's bucket sorts of `gid` beside whatever the caller queues next on `stream`
 void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t stream);
+// counts of segments >= seg of the next cafe_internal_insert are valid once `ev` has fired (null: no gate)
+void cafe_internal_set_gate(void* h, int seg, cudaEvent_t ev);
 void cafe_internal_set_error(const char* msg);
 
 // ---- per-kernel timing and launch counting (prof.cu) ------------------------------------------------

@@ -363,7 +363,8 @@ struct CafePushPlan {
     int32_t row_off[CAFE_MAX_RANKS + 1];   // first (sample, field) row of owner g's block in this rank's buffer
 };
 __global__ void __launch_bounds__(256)
-k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rank, int rows, int D, int64_t total_rows) {
+k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rank, int rows, int D, int64_t total_rows,
+             int j_begin, int j_end) {
     const int lanes = D / 4;                       // lanes per row (16-byte vectors)
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t q0 = t / lanes;
@@ -378,6 +379,7 @@ k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, i
     const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
     const int fg = P.fields_of[g];
     const int64_t b = local / fg, j = local - b * fg;
+    if (j < j_begin || j >= j_end) return;   // only the owners' fields number j_begin .. j_end-1 go in this launch
     const float4 v = ld_stream(grad + q * D + c);
     *reinterpret_cast<float4*>(P.base[g] + (((int64_t)rank * rows + b) * fg + j) * D + c) = v;
 }
@@ -443,6 +445,8 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_join, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->late, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_late, cudaEventDisableTiming);
     if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
     return CAFE_OK;
 }
@@ -454,6 +458,8 @@ void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
     if (ws->side) { cudaStreamSynchronize(ws->side); cudaStreamDestroy(ws->side); }
     if (ws->ev_fork) cudaEventDestroy(ws->ev_fork);
     if (ws->ev_join) cudaEventDestroy(ws->ev_join);
+    if (ws->late) { cudaStreamSynchronize(ws->late); cudaStreamDestroy(ws->late); }
+    if (ws->ev_late) cudaEventDestroy(ws->ev_late);
     *ws = CafeEmbedWorkspace();
 }
 
@@ -738,40 +744,99 @@ static int scatter_join(CafeEmbedWorkspace* ws, cudaStream_t st) {
 // The whole post-backward part of one training step for `nfields` fields, in the reference's order:
 // importance -> sketch insert (one call per field, ascending) -> migration with pre-update rows ->
 // SGD with the forward-time rows.
-int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const void* ids_dev,
-                        int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
-                        const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash, float* weight_high,
-                        int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev, int32_t* n_migrated_dev,
-                        void* stream) {
+// importance of the fields [f0, f0 + nf) of a call over `nfields` fields: the same three kernels as
+// cafe_grad_importance, on that range of the workspace
+static int importance_range(CafeEmbedWorkspace* ws, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int f0,
+                            int nf, int B, int D, float* imp_dev, cudaStream_t st) {
+    if (nf <= 0 || B <= 0) return CAFE_OK;
+    const int total = nf * B;
+    const float* g = grad_dev + (int64_t)f0 * field_stride;
+    float* norm = ws->norm + (size_t)f0 * B;
+    { CAFE_PROF(CAFE_P_NORM, st);
+    DISPATCH_G(D, (k_grad_norm<G><<<(unsigned)((((int64_t)total + 3) / 4 * G + 255) / 256), 256, 0, st>>>(g, field_stride,
+                   sample_stride, B, total, norm))); }
+    { CAFE_PROF(CAFE_P_FIELDSUM, st); k_field_sum<<<nf, 1024, 0, st>>>(norm, B, ws->totals + f0); }
+    { CAFE_PROF(CAFE_P_IMPORTANCE, st); k_importance<<<(total + 255) / 256, 256, 0, st>>>(norm, ws->totals + f0, B, total,
+                                                                                           imp_dev + (size_t)f0 * B); }
+    return fail_cuda("cafe_grad_importance");
+}
+
+// gate_field in (0, nfields) with a gate event: the gradient rows of the fields from gate_field on are
+// being written by work that `stream` has not waited for; they are complete once gate_event has fired.
+static int embed_backward_impl(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const void* ids_dev,
+                               int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                               const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                               float* weight_high, int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev,
+                               int32_t* n_migrated_dev, int gate_field, cudaEvent_t gate_event, cudaStream_t st) {
     if (!h) return CAFE_ERR_ARG;
     CafeEmbedWorkspace* ws = cafe_internal_ws(h);
     const int64_t total = (int64_t)nfields * B;
     if (total > ws->cap) return CAFE_ERR_CAPACITY;
     if (total == 0) return CAFE_OK;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
     CafeFields FS;
     int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
                            weight_high, hotn, D);
     if (rc != CAFE_OK) return rc;
-    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, (cudaStream_t)stream);
-    if (rc != CAFE_OK) { scatter_join(ws, (cudaStream_t)stream); return rc; }
-    rc = cafe_grad_importance(h, grad_dev, field_stride, sample_stride, nfields, B, D, ws->imp, stream);
+    bool gated = gate_event != nullptr && gate_field > 0 && gate_field < nfields;
+    if (gate_event != nullptr && (!gated || cafe_prof_serialise())) {
+        // nothing to overlap (or per-kernel timing is on): simply wait for the late fields first
+        if (cudaStreamWaitEvent(st, gate_event, 0) != cudaSuccess) return fail_cuda("gate wait");
+        gated = false;
+    }
+    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, st);
+    if (rc != CAFE_OK) { scatter_join(ws, st); return rc; }
+    const int early = gated ? gate_field : nfields;
+    rc = importance_range(ws, grad_dev, field_stride, sample_stride, 0, early, B, D, ws->imp, st);
+    if (rc == CAFE_OK && gated) {
+        // the late fields' importance runs on a stream of its own, behind the gate; the insert waits for it
+        // only when it reaches those fields
+        if (cudaStreamWaitEvent(ws->late, gate_event, 0) != cudaSuccess) rc = fail_cuda("gate wait");
+        if (rc == CAFE_OK) rc = importance_range(ws, grad_dev, field_stride, sample_stride, gate_field, nfields - gate_field, B, D,
+                                                 ws->imp, ws->late);
+        if (cudaEventRecord(ws->ev_late, ws->late) != cudaSuccess && rc == CAFE_OK) rc = fail_cuda("gate record");
+        if (rc == CAFE_OK) cafe_internal_set_gate(h, gate_field, ws->ev_late);
+    }
     if (rc != CAFE_OK) {
-        cafe_internal_presort(h, nullptr, 0, (cudaStream_t)stream);   // withdraws the sorts started above
-        scatter_join(ws, (cudaStream_t)stream);
+        cafe_internal_presort(h, nullptr, 0, st);   // withdraws the sorts started above
+        scatter_join(ws, st);
         return rc;
     }
     int seg[CAFE_MAX_SEGMENTS + 1];
     for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
     int32_t* mask = mask_out_dev ? mask_out_dev : ws->mask;
-    int status = cafe_internal_insert(h, gid_dev, ws->imp, seg, nfields, mask, ws->post_row, insert_mode, (cudaStream_t)stream);
-    rc = scatter_join(ws, (cudaStream_t)stream);
+    int status = cafe_internal_insert(h, gid_dev, ws->imp, seg, nfields, mask, ws->post_row, insert_mode, st);
+    cafe_internal_set_gate(h, -1, nullptr);
+    if (gated) cudaStreamWaitEvent(st, ws->ev_late, 0);   // whatever the insert did: the scatter reads every field
+    rc = scatter_join(ws, st);
     if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
     if (rc != CAFE_OK) return rc;
     rc = cafe_migrate(h, ids_dev, ids_are_int64, mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
-                      hotn, D, n_migrated_dev, stream);
+                      hotn, D, n_migrated_dev, st);
     if (rc != CAFE_OK) return rc;
-    rc = scatter_apply(ws, FS, grad_dev, field_stride, sample_stride, (int)total, D, lr, (cudaStream_t)stream);
+    rc = scatter_apply(ws, FS, grad_dev, field_stride, sample_stride, (int)total, D, lr, st);
     return rc != CAFE_OK ? rc : status;
+}
+
+int cafe_embed_backward(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const void* ids_dev,
+                        int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                        const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash, float* weight_high,
+                        int hotn, int D, float lr, int insert_mode, int32_t* mask_out_dev, int32_t* n_migrated_dev,
+                        void* stream) {
+    return embed_backward_impl(h, grad_dev, field_stride, sample_stride, ids_dev, ids_are_int64, gid_dev, row_dev, nfields, B,
+                               f_offset, hash_size, weight_hash, weight_high, hotn, D, lr, insert_mode, mask_out_dev,
+                               n_migrated_dev, 0, nullptr, (cudaStream_t)stream);
+}
+
+int cafe_embed_backward_gated(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const void* ids_dev,
+                              int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev, int nfields, int B,
+                              const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                              float* weight_high, int hotn, int D, float lr, int insert_mode, int gate_field,
+                              void* gate_event, void* stream) {
+    if (!gate_event) return CAFE_ERR_ARG;
+    return embed_backward_impl(h, grad_dev, field_stride, sample_stride, ids_dev, ids_are_int64, gid_dev, row_dev, nfields, B,
+                               f_offset, hash_size, weight_hash, weight_high, hotn, D, lr, insert_mode, nullptr, nullptr,
+                               gate_field, (cudaEvent_t)gate_event, (cudaStream_t)stream);
 }
 
 // ---- field-sharded exchange over peer memory (see the kernels above) ------------------------------
@@ -888,8 +953,8 @@ int cafe_embed_backward_imp(void* h, const float* grad_dev, int64_t field_stride
     return rc != CAFE_OK ? rc : status;
 }
 
-int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
-                          float* const* owner_grad, void* stream) {
+static int push_grads_impl(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                           float* const* owner_grad, int j_begin, int j_end, void* stream) {
     if (nfields_total < 1 || rows_local < 0 || nranks < 1 || nranks > CAFE_MAX_RANKS || rank < 0 || rank >= nranks || !owner_grad)
         return CAFE_ERR_ARG;
     if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
@@ -911,8 +976,20 @@ int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int 
     cudaStream_t st = (cudaStream_t)stream;
     CAFE_PROF(CAFE_P_OTHER, st);
     const int64_t threads = total_rows * (D / 4);
-    k_push_grads<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D, total_rows);
+    k_push_grads<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D, total_rows,
+                                                                   j_begin, j_end);
     return fail_cuda("cafe_shard_push_grads");
+}
+
+int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                          float* const* owner_grad, void* stream) {
+    return push_grads_impl(grad_blocked_dev, nfields_total, rows_local, D, nranks, rank, owner_grad, 0, 0x7fffffff, stream);
+}
+
+int cafe_shard_push_grads_fields(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                                 float* const* owner_grad, int j_begin, int j_end, void* stream) {
+    if (j_begin < 0 || j_end < j_begin) return CAFE_ERR_ARG;
+    return push_grads_impl(grad_blocked_dev, nfields_total, rows_local, D, nranks, rank, owner_grad, j_begin, j_end, stream);
 }
 
 }  // extern "C"

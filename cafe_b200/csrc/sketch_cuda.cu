@@ -1057,6 +1057,8 @@ struct CudaBackend {
         check(cudaEventRecord(pass_ev_join, pass_side));
         check(cudaStreamWaitEvent(stream, pass_ev_join, 0));
     }
+    cudaEvent_t gate_event = nullptr;   // see SketchEngine::set_gate
+    void wait_gate() { if (gate_event) check(cudaStreamWaitEvent(stream, gate_event, 0)); }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
     int32_t* diag_buf = nullptr;
     void diag_dump() {
@@ -1209,6 +1211,11 @@ void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t str
     CafeHandle* H = (CafeHandle*)h;
     H->eng.be.stream = stream;
     H->eng.presort(gid, n);
+}
+void cafe_internal_set_gate(void* h, int seg, cudaEvent_t ev) {
+    CafeHandle* H = (CafeHandle*)h;
+    H->eng.be.gate_event = ev;
+    H->eng.set_gate(ev ? seg : -1);
 }
 void cafe_internal_set_error(const char* msg) { g_last_error = msg; }
 

@@ -142,6 +142,10 @@ public:
         presorted_gid = gid; presorted_n = n;
     }
 
+    // The next insert_segments call may use the counts of segments >= seg only after the backend's gate
+    // event has fired on its stream (the caller is still producing them); -1 = no gate.
+    void set_gate(int seg) { gate_seg = seg; }
+
     // One batch_insert_val call per segment, in order (imp == null: batch_insert, unit counts).
     // mask[p] = the reference's per-lookup result; post_row[p] (optional) = hot row a query would
     // return for the id right after its own segment's call (0 = none).  parallel=false runs the
@@ -153,6 +157,8 @@ public:
         const int total = seg_off[nseg];
         if (total > 0 && (!gid || !mask)) return CAFE_ERR_ARG;
         last_status = CAFE_OK;
+        struct GateReset { int& g; ~GateReset() { g = -1; } } gate_reset{gate_seg};
+        if (gate_seg >= nseg) gate_seg = -1;
         int s = 0;
         while (s < nseg) {
             // a stretch of calls whose lookups fit the workspace is sorted by bucket once
@@ -175,6 +181,8 @@ public:
             }
             presorted_gid = nullptr;
             while (s < se) {
+                // counts of the calls from gate_seg on become valid only when the caller's gate opens
+                if (gate_seg >= 0 && s >= gate_seg) { be.wait_gate(); gate_seg = -1; }
                 call_boundary();
                 if (last_status == CAFE_ERR_CUDA) return last_status;
                 int e = s + 1;
@@ -182,7 +190,8 @@ public:
                     // fuse following calls while their boundaries are known to be uneventful: the decay
                     // clock is deterministic, the re-fit condition is checked after the fact
                     double d = decay_importance;
-                    const int maxe = std::min(se, s + std::max(1, std::min(window, (int)CAFE_MAX_SEGMENTS)));
+                    int maxe = std::min(se, s + std::max(1, std::min(window, (int)CAFE_MAX_SEGMENTS)));
+                    if (gate_seg >= 0 && s < gate_seg) maxe = std::min(maxe, gate_seg);   // a job ends at the gate
                     while (e < maxe) {
                         double d2 = d * alpha;
                         if (d2 > CAFE_DECAY_BASE) break;
@@ -291,6 +300,7 @@ public:
     }
 
 private:
+    int gate_seg = -1;
     bool cursors_advanced = false;
     const uint32_t* presorted_gid = nullptr;
     int presorted_n = 0;

@@ -130,6 +130,9 @@ class PeerBuffers:
         self.block_off = [rows * dim * sum(plan.counts[:r]) for r in range(plan.G)]
         self.flag = torch.zeros(1, device=device)
         self.gen = 0
+        with torch.cuda.device(device):
+            self.comm_stream = torch.cuda.Stream()        # the gradient exchange when it is issued in pieces
+            self.ev_first, self.ev_second = torch.cuda.Event(), torch.cuda.Event()
 
     def ptr_array(self, handle, elem_offset: int, elem_size: int):
         return (ctypes.c_void_p * self.plan.G)(*[int(p) + elem_offset * elem_size for p in handle.buffer_ptrs])
@@ -182,12 +185,35 @@ class _PeerFunction(torch.autograd.Function):
         with torch.no_grad(), torch.cuda.device(pb.grad.device):
             g = blocked_grad.reshape(-1).contiguous()
             f.backward_begin(gid, row, G * Bl, grp.insert_mode)   # sorts run beside the gradient exchange
-            # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
-            _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank, pb.ptr_array(pb.h_gown, 0, 4),
-                                                 _stream()), "cafe_shard_push_grads")
-            pb.fence()
-            # ... and every owner runs the ordinary fused backward on its local buffer [G*B_local, F_g, D]
-            grp.last_status = f.backward(pb.gown, D, Fg * D, own, gid, row, G * Bl, grp.lr, grp.insert_mode)
+            half = (plan.F // G) // 2     # same on every rank: owners' fields 0..half-1 travel first
+            if not model.pipeline_push or G == 1 or half < 1:
+                # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
+                _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank,
+                                                     pb.ptr_array(pb.h_gown, 0, 4), _stream()), "cafe_shard_push_grads")
+                pb.fence()
+                # ... and every owner runs the ordinary fused backward on its local buffer [G*B_local, F_g, D]
+                grp.last_status = f.backward(pb.gown, D, Fg * D, own, gid, row, G * Bl, grp.lr, grp.insert_mode)
+            else:
+                # The same in two pieces on a stream of its own: while the second piece crosses NVLink, the
+                # owners already compute the importance of the first piece's fields and insert them (the
+                # insert takes the fields in ascending order anyway); the gated backward waits for the
+                # second piece only when it gets to its fields.
+                main, comm = torch.cuda.current_stream(), pb.comm_stream
+                comm.wait_stream(main)
+                g.record_stream(comm)
+                owners = pb.ptr_array(pb.h_gown, 0, 4)
+                with torch.cuda.stream(comm):
+                    _lib.check(lib.cafe_shard_push_grads_fields(g.data_ptr(), plan.F, Bl, D, G, plan.rank, owners, 0, half,
+                                                                comm.cuda_stream), "cafe_shard_push_grads_fields")
+                    pb.fence()
+                    pb.ev_first.record(comm)
+                    _lib.check(lib.cafe_shard_push_grads_fields(g.data_ptr(), plan.F, Bl, D, G, plan.rank, owners, half,
+                                                                1 << 30, comm.cuda_stream), "cafe_shard_push_grads_fields")
+                    pb.fence()
+                    pb.ev_second.record(comm)
+                main.wait_event(pb.ev_first)
+                grp.last_status = f.backward_gated(pb.gown, D, Fg * D, own, gid, row, G * Bl, grp.lr, grp.insert_mode,
+                                                   half, pb.ev_second)
         return None, None, None
 
 
@@ -224,7 +250,7 @@ class ShardedSKEmbedding(torch.nn.Module):
 
     def __init__(self, num_categories, embedding_dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1,
                  sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None,
-                 exchange="peer", f_offsets=None):
+                 exchange="peer", f_offsets=None, pipeline_push=False):
         super().__init__()
         from .sk_embedding_bag import SKEmbeddingGroup
         world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -249,6 +275,7 @@ class ShardedSKEmbedding(torch.nn.Module):
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
         self.exchange = exchange
+        self.pipeline_push = bool(pipeline_push)   # gradient exchange in two pieces, the second beside the first's insert
         self.peer = None
         self._gbuf = self._imp = None
         if exchange == "peer":

@@ -110,6 +110,17 @@ class _FieldSet:
                 self.sketch.handle, gid.data_ptr(), row.data_ptr(), self.nf, B, self.hash_size, wp, hp, self.hotn,
                 self.dim, mode, _stream()), "cafe_embed_backward_begin")
 
+    def backward_gated(self, grad, field_stride, sample_stride, ids, gid, row, B, lr, mode, gate_field, gate_event):
+        """backward() whose gradient rows of the fields from gate_field on are complete only once gate_event
+        (a torch.cuda.Event recorded on another stream) has fired."""
+        wp, hp = self.ptrs()
+        with torch.cuda.device(grad.device):
+            return _lib.check(self.sketch.lib.cafe_embed_backward_gated(
+                self.sketch.handle, grad.data_ptr(), field_stride, sample_stride, ids.data_ptr(),
+                int(ids.dtype == torch.int64), gid.data_ptr(), row.data_ptr(), self.nf, B, self.f_offset, self.hash_size,
+                wp, hp, self.hotn, self.dim, float(lr), mode, int(gate_field), ctypes.c_void_p(gate_event.cuda_event),
+                _stream()), "cafe_embed_backward_gated")
+
     def backward(self, grad, field_stride, sample_stride, ids, gid, row, B, lr, mode, mask_out=None):
         wp, hp = self.ptrs()
         with torch.cuda.device(grad.device):

@@ -175,6 +175,22 @@ int cafe_shard_pull_importance(void* handle, const float* const* grad_rank, int 
  * ordinary cafe_embed_backward on its local buffer. */
 int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
                           float* const* owner_grad, void* stream);
+/* cafe_shard_push_grads for the owners' fields number j_begin .. j_end-1 only (j counts a field among its
+ * owner's fields), so that the exchange can be issued in pieces and the owners can start on the first piece
+ * while the next one is on its way. */
+int cafe_shard_push_grads_fields(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks,
+                                 int rank, float* const* owner_grad, int j_begin, int j_end, void* stream);
+/* cafe_embed_backward whose gradient rows of the fields from gate_field on are still being written when the call
+ * is made: they are complete once gate_event (a cudaEvent_t) has fired.  The fields before gate_field are
+ * processed at once; the importance of the late fields is computed behind the gate on a stream of the handle,
+ * and the insert, which takes the fields in ascending order like the reference's per-field calls
+ * (sk_embedding_bag.py:173-208 called per table), waits for it only when it gets there.  Results are those of
+ * cafe_embed_backward.  No counterpart in the reference (single GPU). */
+int cafe_embed_backward_gated(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                              const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev,
+                              int nfields, int B, const int64_t* f_offset, const int32_t* hash_size,
+                              float* const* weight_hash, float* weight_high, int hotn, int D, float lr, int insert_mode,
+                              int gate_field, void* gate_event, void* stream);
 /* cafe_embed_backward for a caller that already holds the importance array. */
 int cafe_embed_backward_imp(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
                             const float* imp_dev, const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev,

@@ -49,6 +49,7 @@ struct HostBackend {
         for (int i = 0; i < n; ++i) out[i] = mask[i] ? cafe_probe_hot(mb[cafe_hash(gid[i], n1)], gid[i]) : 0;
     }
     void sort_join(int) {}
+    void wait_gate() {}
     void diag_dump() {}
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
         (void)lane;

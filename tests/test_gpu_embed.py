@@ -262,3 +262,42 @@ def test_backward_head_start_is_only_a_head_start():
         assert torch.equal(a.weight_high, b.weight_high), f"step {step}: hot table"
         for f in range(F):
             assert torch.equal(a.weight_hash[f], b.weight_hash[f]), f"step {step}: hash table {f}"
+
+
+def test_gated_backward_waits_for_late_fields():
+    """cafe_embed_backward_gated: the gradient rows of the later fields are written by another stream, well
+    after the call has been made; the result must be the ordinary backward's, bit for bit."""
+    import torch
+    import cafe_b200
+    cards = [4000, 150000, 61, 700000, 2500, 90000]
+    F, D, B = len(cards), 32, 1024
+    mk = lambda: cafe_b200.SKEmbeddingGroup(cards, D, 0.01, 0.3, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=9)
+    a, b = mk(), mk()
+    a.eval(); b.eval()                          # no head start: the calls below drive the field set directly
+    rng = np.random.default_rng(21)
+    side = torch.cuda.Stream()
+    for step in range(8):
+        ids = torch.from_numpy(np.stack([zipf_ids(rng, n, B) for n in cards])).cuda()
+        g = torch.from_numpy((rng.standard_normal((B, F, D)) * 0.01).astype(np.float32)).cuda()
+        flat = ids.reshape(-1)
+        outs = []
+        for m in (a, b):
+            out = torch.empty(B, F, D, dtype=torch.float32, device="cuda")
+            gid, row = m._fields.forward(flat, out, D, F * D)
+            outs.append((gid, row))
+        b._fields.backward(g, D, F * D, flat, outs[1][0], outs[1][1], B, b.lr, b.insert_mode)
+        gate = 1 + step % (F - 1)
+        late = torch.full_like(g, float("nan"))             # what the backward must not read too early
+        late[:, :gate] = g[:, :gate]
+        ev = torch.cuda.Event()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            torch.cuda._sleep(3_000_000)                    # about 1.5 ms: the gated call is queued long before
+            late[:, gate:] = g[:, gate:]
+            ev.record(side)
+        a._fields.backward_gated(late, D, F * D, flat, outs[0][0], outs[0][1], B, a.lr, a.insert_mode, gate, ev)
+        torch.cuda.synchronize()
+        assert states_equal(a.sketch.state(), b.sketch.state()) == [], f"step {step}: sketch state"
+        assert torch.equal(a.weight_high, b.weight_high), f"step {step}: hot table"
+        for f in range(F):
+            assert torch.equal(a.weight_hash[f], b.weight_hash[f]), f"step {step}: hash table {f}"
