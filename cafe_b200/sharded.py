@@ -275,7 +275,9 @@ class ShardedSKEmbedding(torch.nn.Module):
         if exchange not in ("peer", "nccl"):
             raise ValueError("exchange must be 'peer' or 'nccl'")
         self.exchange = exchange
-        self.pipeline_push = bool(pipeline_push)   # gradient exchange in two pieces, the second beside the first's insert
+        # gradient exchange in two pieces, the second beside the first piece's insert.  Off by default: on two GPUs
+        # the job boundary it forces at the gate cost more than the hidden half of the transfer gave back.
+        self.pipeline_push = bool(pipeline_push)
         self.peer = None
         self._gbuf = self._imp = None
         if exchange == "peer":
