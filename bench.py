@@ -1,17 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the CAFE compressed-embedding hot path (sketch + forward + backward) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|micro|cfg3|weak26]
 
-One step = one pass of the hot path over one batch of the microbenchmark workload (26 fields x 40M
-ids, Zipf 1.05, batch 65536 x 26 int64 ids, fp32 dim 128, N(0, 0.01) gradients, CAFE settings
-compress 0.001 / hash-rate 0.3 / threshold 1 / alpha 1.0000005): fused query+gather forward, then
-importance -> sketch insert -> migration -> scatter/SGD.  Prints ONE JSON line (rank 0).
+One step = one pass of the hot path over one batch: fused query+gather forward, then importance ->
+sketch insert -> migration -> scatter/SGD.  Every step gets a batch of ids of its own (nothing is
+replayed) and a gradient buffer of its own.  Prints ONE JSON line (rank 0).
+
+Workloads (`--workload auto` picks `micro` on one GPU and `cfg3` on several):
+  micro   the HotSketch + SKEmbeddingBag microbenchmark: 26 fields x 40M ids, Zipf 1.05, batch 65536 x 26
+          int64 ids, fp32 dim 128, N(0, 0.01) gradients, compress 0.001 / hash-rate 0.3 / threshold 1 /
+          alpha 1.0000005;
+  cfg3    the Terabyte-shaped drifting workload: 26 fields with the Criteo-Terabyte cardinalities sharded by
+          field (round robin) over the GPUs, global batch 65536, dim 128, compress 0.0001 / hash-rate 0.2,
+          Zipf exponent drifting 1.05 -> 1.2 over 10k workload steps with 5 % of the ids re-permuted every
+          1k workload steps; one bench step advances the workload by --drift-stride steps;
+  weak26  every GPU brings 26 microbenchmark fields of its own (26*N fields), global batch 65536.
 
 `value` is measured with the ids already in HBM; `e2e` copies each step's ids from pinned host memory
-and reads a slice of the result back.  `--impl reference` times the reference's own CPU
-implementation of the same step (tricks/sketch.cpp compiled under oracle/_ref, or the C restatement
-when that library is absent, plus PyTorch CPU embedding bags) on the host cores.
+and reads a slice of the result back, on a sketch that starts from the same state and sees the same
+batches as `value`.  `--impl reference` times the reference's own CPU implementation of the same step on
+the same workload (tricks/sketch.cpp compiled under oracle/_ref, or the C restatement when that library
+is absent, plus PyTorch CPU embedding bags) on all host cores.
 """
 from __future__ import annotations
 
@@ -29,8 +39,8 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-CR, HR, THR, ADJ, ALPHA = 0.001, 0.3, 1, 1, 1.0000005
-DIM, BATCH, ZIPF_S, SEED = 128, 65536, 1.05, 2024
+THR, ADJ, ALPHA = 1, 1, 1.0000005
+DIM, BATCH, SEED = 128, 65536, 2024
 LR = 0.1
 METRIC = "cafe_embedding_ids_per_s"
 UNIT = "ids/s"
@@ -66,7 +76,7 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int, uuid=None, allow_smi=True):
         self.idx, self.nv, self.h, self.proc = gpu_index, None, None, None
-        self.samples, self.lines, self.on, self.t = [], [], False, None
+        self.samples, self.lines, self.on, self.t, self.stop = [], [], False, None, False
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -101,17 +111,19 @@ class ClockSampler:
 
     def _poll(self):
         nv = self.nv
-        while self.on:
-            try:
-                self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)),
-                                     int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))))
-            except Exception:
-                pass
+        while not self.stop:
+            if self.on:
+                try:
+                    self.samples.append((float(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)),
+                                         int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))))
+                except Exception:
+                    pass
             time.sleep(0.002)
 
+    # `with sampler:` may be entered several times: samples are taken only inside, one polling thread serves all
     def __enter__(self):
         self.on = True
-        if self.nv is not None:
+        if self.nv is not None and self.t is None:
             self.t = threading.Thread(target=self._poll, daemon=True)
             self.t.start()
         return self
@@ -120,6 +132,9 @@ class ClockSampler:
         if self.proc:
             time.sleep(0.06)
         self.on = False
+
+    def close(self):
+        self.stop = True
         if self.nv is not None and self.t is not None:
             self.t.join(timeout=1)
         if self.proc:
@@ -157,6 +172,76 @@ class ClockSampler:
 
 
 # -------------------------------------------------------------------------------------------------
+# workloads
+# -------------------------------------------------------------------------------------------------
+class Workload:
+    """One named workload: field cardinalities, CAFE sizing rates and the id stream (a batch per step)."""
+
+    def __init__(self, name: str, world: int, stride: int):
+        from cafe_b200 import sizing, synthetic as S
+        self.name, self.world, self.stride, self.S = name, world, stride, S
+        if name == "micro":
+            self.cards, self.cr, self.hr = list(S.MICRO_CARDS), 0.001, 0.3
+            self.offsets = sizing.field_offsets(self.cards)
+        elif name == "cfg3":
+            self.cards, self.cr, self.hr = list(S.TERABYTE_CARDS), 0.0001, 0.2
+            self.offsets = sizing.field_offsets(self.cards)
+        elif name == "weak26":
+            self.cards, self.cr, self.hr = list(S.MICRO_CARDS) * world, 0.001, 0.3
+            # 26*N*40M ids do not fit 31 bits: offsets are distinct within each rank only (ranks share no state)
+            self.offsets = [(f // world) * 40_000_000 for f in range(len(self.cards))]
+        else:
+            raise ValueError(name)
+        self.F = len(self.cards)
+        self.scaling = "weak" if name == "weak26" or world == 1 else "strong"
+
+    def ids(self, step: int, batch: int, rank: int = 0) -> np.ndarray:
+        """ids [F, batch] of the GLOBAL batch of `step` (weak26: of this rank's slice)."""
+        S = self.S
+        if self.name == "micro":
+            return S.batch_ids(self.cards, batch, 1.05, SEED, step)
+        if self.name == "cfg3":
+            return S.drift_batch_ids(self.cards, batch, SEED, step * self.stride)
+        return S.batch_ids(self.cards, batch, 1.05, SEED + 7919 * rank, step)
+
+    def config(self, batch: int) -> dict:
+        w = self.world
+        if self.name == "micro":
+            what = ("hotsketch+skembeddingbag microbenchmark: 26 fields x 40M ids, Zipf(1.05) permuted, "
+                    f"batch {batch} x 26 int64 ids, fp32 dim {DIM}, N(0,0.01) grads, compress 0.001, hash-rate 0.3, "
+                    "threshold 1, alpha 1.0000005; a fresh id batch and gradient every step")
+            par = "single GPU"
+        elif self.name == "cfg3":
+            what = ("Terabyte-shaped drifting workload: 26 fields with the Criteo-Terabyte cardinalities, "
+                    f"global batch {batch} x 26 int64 ids, fp32 dim {DIM}, N(0,0.01) grads, compress 0.0001, hash-rate 0.2, "
+                    "threshold 1, alpha 1.0000005; Zipf exponent 1.05 -> 1.2 over 10k workload steps, 5% of ids "
+                    f"re-permuted every 1k workload steps, one bench step = {self.stride} workload steps; a fresh id "
+                    "batch and gradient every step")
+            par = (f"field-sharded x{w}: 26 fields round robin over the GPUs (own sketch + tables per GPU), pooled rows and "
+                   "gradients exchanged through peer memory inside the gather / push kernels") if w > 1 else "single GPU"
+        else:
+            what = (f"26 microbenchmark fields per GPU ({26 * w} fields x 40M ids, Zipf 1.05), global batch {batch}, fp32 dim "
+                    f"{DIM}, compress 0.001, hash-rate 0.3, threshold 1; a fresh id batch and gradient every step")
+            par = f"field-sharded x{w}: 26 fields (own sketch + tables) per GPU, exchange through peer memory"
+        return {"workload": what, "name": self.name, "batch": batch, "fields": self.F, "dim": DIM,
+                "ids_per_step": batch * self.F, "parallelism": par,
+                "l2": "per-step streams (ids, pooled output, gradients: 1.7 GB) exceed L2; no flush needed",
+                "e2e_note": "ids come from pinned host memory every step and a slice of the pooled output is read back; "
+                            "gradients stay on the device, where a training loop's dense backward produces them"}
+
+
+def generate_batches(wl: Workload, steps, batch: int, rank: int = 0, cols=None):
+    """[np.ndarray [F, cols]] for the given workload steps, generated by a few host threads."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    def one(s):
+        a = wl.ids(s, batch, rank)
+        return np.ascontiguousarray(a if cols is None else a[:, cols[0]:cols[1]])
+    with ThreadPoolExecutor(max_workers=max(1, min(8, (os.cpu_count() or 2) // 2))) as ex:
+        return list(ex.map(one, steps))
+
+
+# -------------------------------------------------------------------------------------------------
 # reference CPU path (the baseline): reference sketch library + PyTorch CPU embedding bags
 # -------------------------------------------------------------------------------------------------
 class CpuReferencePath:
@@ -164,16 +249,20 @@ class CpuReferencePath:
     (tricks/sk_embedding_bag.py:119-152) -> autograd backward -> importance (:178-189) -> batch_insert_val
     (C) -> guarded migration (:199-208) -> torch.optim.SGD on sparse gradients (dlrm_s_pytorch.py:1658)."""
 
-    def __init__(self, cards, D, batch):
+    def __init__(self, wl: Workload, D, batch):
         import torch
         import torch.nn.functional as F
         from cafe_b200 import sizing
         from oracle import hotsketch as oh
+        # torch.distributed.run exports OMP_NUM_THREADS=1: the baseline gets every host core it may use regardless
+        ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        torch.set_num_threads(max(1, ncpu))
         self.torch, self.Fn = torch, F
+        cards = wl.cards
         self.cards, self.D, self.B = cards, D, batch
-        self.hotn = sizing.hot_rows(sum(cards), CR, HR, D)
-        self.hs = [sizing.hash_rows(n, CR, HR) for n in cards]
-        self.off = sizing.field_offsets(cards)
+        self.hotn = sizing.hot_rows(sum(cards), wl.cr, wl.hr, D)
+        self.hs = [sizing.hash_rows(n, wl.cr, wl.hr) for n in cards]
+        self.off = wl.offsets
         if oh.REF_SO.exists():
             self.sk, self.kind = oh.ReferenceSketch(self.hotn, THR, ADJ, ALPHA), "reference"
         else:
@@ -186,7 +275,7 @@ class CpuReferencePath:
         self.offsets = torch.arange(batch)
         self.threads = torch.get_num_threads()
 
-    def step(self, ids: np.ndarray, grad: "np.ndarray"):
+    def step(self, ids: np.ndarray, grad):
         torch, F = self.torch, self.Fn
         outs, gids, qs = [], [], []
         for f in range(len(self.cards)):
@@ -214,79 +303,102 @@ class CpuReferencePath:
         return outs
 
 
+def time_cpu_path(wl: Workload, batch: int, warm: int, steps: int):
+    """(ids/s, ms per step, path) of the reference's CPU step over fresh batches 0 .. warm+steps-1."""
+    import torch
+    path = CpuReferencePath(wl, DIM, batch)
+    ids = generate_batches(wl, range(warm + steps), batch)
+    ng = min(warm + steps, 4)   # gradients: a few distinct buffers (the host holds 0.9 GB each at full batch)
+    gg = torch.Generator().manual_seed(SEED)
+    grads = [torch.randn(batch, wl.F, DIM, generator=gg) * 0.01 for _ in range(ng)]
+    for s in range(warm):
+        path.step(ids[s], grads[s % ng])
+    t0 = time.perf_counter()
+    for s in range(warm, warm + steps):
+        path.step(ids[s], grads[s % ng])
+    dt = time.perf_counter() - t0
+    return steps * batch * wl.F / dt, 1e3 * dt / steps, path
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    import torch
-    from cafe_b200 import synthetic as S
-    cards = S.MICRO_CARDS
+    wl = Workload(args.workload, world, args.drift_stride)
     B = args.cpu_batch
-    path = CpuReferencePath(cards, DIM, B)
-    F = len(cards)
-    nb = 2
-    ids = [S.batch_ids(cards, B, ZIPF_S, SEED, s) for s in range(nb)]
-    grads = [torch.from_numpy(S.gradients(B, F, DIM, SEED, s)) for s in range(nb)]
-    for s in range(args.warmup):
-        path.step(ids[s % nb], grads[s % nb])
-    t0 = time.perf_counter()
-    for s in range(args.steps):
-        path.step(ids[s % nb], grads[s % nb])
-    dt = time.perf_counter() - t0
-    v = args.steps * B * F / dt
-    sample = f"{args.steps} steps of batch {B} x {F} fields after {args.warmup} warm-up steps (full batch is {BATCH})"
+    v, ms, path = time_cpu_path(wl, B, args.warmup, args.steps)
+    sample = (f"{args.steps} steps of batch {B} x {wl.F} fields after {args.warmup} warm-up steps, a fresh batch every step "
+              f"(sketch single-threaded as in the reference, torch CPU ops on {path.threads} threads)")
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(B, world=1),
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": wl.scaling,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": wl.config(B),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": path.threads, "kind": path.kind, "sample": sample,
                              "host_cpus": os.cpu_count()},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def workload_config(batch, world):
-    return {"workload": "hotsketch+skembeddingbag microbenchmark: 26 fields x 40M ids, Zipf(1.05) permuted, "
-                        f"batch {batch} x 26 int64 ids, fp32 dim {DIM}, N(0,0.01) grads, compress 0.001, hash-rate 0.3, "
-                        "threshold 1, alpha 1.0000005",
-            "batch": batch, "fields": 26 * world, "dim": DIM, "ids_per_step": batch * 26 * world,
-            "parallelism": (f"field-sharded x{world}: 26 fields (own sketch + tables) per GPU, global batch {batch}, pooled rows and "
-                            "gradients exchanged through peer memory inside the gather / push kernels") if world > 1 else "single GPU",
-            "l2": "per-step streams (ids, pooled output, gradients: 1.7 GB) exceed L2; no flush needed",
-            "e2e_note": "ids come from pinned host memory every step and a slice of the pooled output is read back; "
-                        "gradients stay on the device, where a training loop's dense backward produces them"}
-
-
-def cpu_baseline_leg(args):
+def cpu_baseline_leg(args, wl):
     """Bounded sample of the same workload through the reference's CPU path, on this host's cores."""
-    import torch
-    from cafe_b200 import synthetic as S
-    cards = S.MICRO_CARDS
-    B = args.cpu_batch
-    path = CpuReferencePath(cards, DIM, B)
-    F = len(cards)
-    ids = [S.batch_ids(cards, B, ZIPF_S, SEED, s) for s in range(2)]
-    grads = [torch.from_numpy(S.gradients(B, F, DIM, SEED, s)) for s in range(2)]
-    warm, steps = 2, args.cpu_steps
-    for s in range(warm):
-        path.step(ids[s % 2], grads[s % 2])
-    t0 = time.perf_counter()
-    for s in range(steps):
-        path.step(ids[s % 2], grads[s % 2])
-    dt = time.perf_counter() - t0
-    return {"value": steps * B * F / dt, "unit": UNIT, "cores": path.threads, "kind": path.kind,
-            "sample": f"{steps} steps of batch {B} x {F} fields after {warm} warm-up steps (sketch single-threaded as in the "
-                      f"reference, torch CPU ops on {path.threads} threads)", "ms_per_step": 1e3 * dt / steps,
-            "host_cpus": os.cpu_count()}
+    warm, steps = 1, args.cpu_steps
+    v, ms, path = time_cpu_path(wl, args.cpu_batch, warm, steps)
+    return {"value": v, "unit": UNIT, "cores": path.threads, "kind": path.kind,
+            "sample": f"{steps} steps of batch {args.cpu_batch} x {wl.F} fields after {warm} warm-up step, a fresh batch every "
+                      f"step (sketch single-threaded as in the reference, torch CPU ops on {path.threads} threads)",
+            "ms_per_step": ms, "host_cpus": os.cpu_count()}
 
 
 # -------------------------------------------------------------------------------------------------
 # our arm
 # -------------------------------------------------------------------------------------------------
+class SingleGpuRun:
+    """All fields of the workload on one GPU behind SKEmbeddingGroup."""
+
+    def __init__(self, wl, B, dev):
+        import cafe_b200
+        self.grp = cafe_b200.SKEmbeddingGroup(wl.cards, DIM, wl.cr, wl.hr, THR, ADJ, ALPHA, device=dev, max_batch=B, lr=LR,
+                                              seed=1, f_offsets=wl.offsets)
+        self.out = None
+
+    def step(self, ids_dev, grad):
+        self.out = self.grp(ids_dev)
+        self.out.backward(grad)
+
+    def result_slice(self):
+        return self.out.detach()[:16]
+
+    def grad_shape(self, B, wl):
+        return (B, wl.F, DIM)
+
+    def stats(self):
+        return self.grp.sketch.stats()
+
+
+class ShardedRun:
+    """Fields sharded over the ranks behind ShardedSKEmbedding; every rank feeds its slice of the global batch."""
+
+    def __init__(self, wl, B, dev, exchange):
+        from cafe_b200.sharded import ShardedSKEmbedding
+        self.model = ShardedSKEmbedding(wl.cards, DIM, wl.cr, wl.hr, THR, ADJ, ALPHA, device=dev, global_batch=B, lr=LR, seed=1,
+                                        exchange=exchange, f_offsets=wl.offsets)
+        self.out = None
+
+    def step(self, ids_dev, grad):
+        self.out = self.model(ids_dev)
+        self.out.backward(grad)
+
+    def result_slice(self):
+        return self.out.detach().reshape(-1)[:16 * DIM]
+
+    def grad_shape(self, B, wl):
+        return (B // wl.world * wl.F * DIM,)
+
+    def stats(self):
+        return self.model.group.sketch.stats()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch
-    import cafe_b200
     from cafe_b200 import profile as prof
-    from cafe_b200 import synthetic as S
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -295,41 +407,33 @@ def run_ours(args, rank, world, local_rank):
         import torch.distributed as dist
         import datetime
         # a short timeout: a rank that stops (an exception, a mismatch) ends the job instead of hanging it
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))
-    cards = S.MICRO_CARDS[:args.fields]
-    F, D, B = len(cards), DIM, args.batch
-    if world > 1:
-        # weak scaling of a field-sharded model: every GPU brings its own copy of the workload's 26 fields
-        # (26*N fields in all, rank g owns 26 of them with their sketch and tables), the global batch stays
-        # 65536 samples, so each field still sees the batch the metric is quoted on and every rank serves
-        # 26 x 65536 lookups per step, plus the exchange of its samples' rows with all other ranks
-        from cafe_b200.sharded import ShardedSKEmbedding
-        all_cards = cards * world
-        offs = [(f // world) * 40_000_000 for f in range(len(all_cards))]   # distinct within each rank, < 2**31
-        model = ShardedSKEmbedding(all_cards, D, CR, HR, THR, ADJ, ALPHA, device=dev, global_batch=B, lr=LR, seed=1,
-                                   exchange=args.exchange, f_offsets=offs)
-        step_fn, e2e_fn, ids_per_step = model.bench_closures(S, ZIPF_S, SEED)
-    else:
-        grp = cafe_b200.SKEmbeddingGroup(cards, D, CR, HR, THR, ADJ, ALPHA, device=dev, max_batch=B, lr=LR, seed=1)
-        nb = 4
-        host_ids = [torch.from_numpy(S.batch_ids(cards, B, ZIPF_S, SEED, s)).pin_memory() for s in range(nb)]
-        dev_ids = [h.to(dev) for h in host_ids]
-        g = torch.Generator(device=dev).manual_seed(SEED)
-        grads = [torch.randn(B, F, D, device=dev, generator=g) * 0.01 for _ in range(2)]
-        stage = torch.empty_like(dev_ids[0])
-        res_host = torch.empty(16, F, D, dtype=torch.float32).pin_memory()
-        ids_per_step = B * F
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    wl = Workload(args.workload, world, args.drift_stride)
+    B, W, K = args.batch, args.warmup, args.steps
+    Bl = B // world
+    cols = None if (world == 1 or wl.name == "weak26") else (rank * Bl, (rank + 1) * Bl)
+    gen_batch = Bl if wl.name == "weak26" else B
+    # steps 0 .. W+K-1 feed the warm-up and the timed region (the end-to-end measurement sees the same ones on a
+    # sketch built anew); W+K .. W+2K-1 feed the per-kernel timing pass
+    host_ids = [torch.from_numpy(a).pin_memory() for a in generate_batches(wl, range(W + 2 * K), gen_batch, rank, cols)]
+    dev_ids = [h.to(dev) for h in host_ids]
+    make = (lambda: SingleGpuRun(wl, B, dev)) if world == 1 else (lambda: ShardedRun(wl, B, dev, args.exchange))
+    run = make()
+    g = torch.Generator(device=dev).manual_seed(SEED + rank)
+    ng = min(W + K, 32)
+    grads = [torch.randn(run.grad_shape(B, wl), device=dev, generator=g) * 0.01 for _ in range(ng)]
+    stage = torch.empty_like(dev_ids[0])
+    res_host = torch.empty(16 * (wl.F if world == 1 else 1) * DIM, dtype=torch.float32).pin_memory()
+    ids_per_step = B * wl.F                       # whole job, all ranks together
+    h2d, d2h = host_ids[0].numel() * 8 * world, res_host.numel() * 4 * world
 
-        def step_fn(s):
-            out = grp(dev_ids[s % nb])
-            out.backward(grads[s % 2])
+    def step_fn(s):
+        run.step(dev_ids[s], grads[s % ng])
 
-        def e2e_fn(s):
-            stage.copy_(host_ids[s % nb], non_blocking=True)
-            out = grp(stage)
-            out.backward(grads[s % 2])
-            res_host.copy_(out.detach()[:16], non_blocking=True)
-        h2d, d2h = host_ids[0].numel() * 8, res_host.numel() * 4
+    def e2e_fn(s):
+        stage.copy_(host_ids[s], non_blocking=True)
+        run.step(stage, grads[s % ng])
+        res_host.copy_(run.result_slice().reshape(-1), non_blocking=True)
 
     def barrier():
         if dist is not None:
@@ -359,66 +463,96 @@ def run_ours(args, rank, world, local_rank):
     except Exception:
         uuid = None
     clk = ClockSampler(local_rank, uuid, allow_smi=(rank == 0))   # set up ahead of the warm-up; samples only inside `with`
-    for s in range(args.warmup):
+    for s in range(W):
         step_fn(s)
     barrier()
+    st0 = run.stats()
     l0 = prof.launch_count()
-    with clk:   # the clock samples cover both timed regions (resident inputs and end to end)
-        ms = timed(step_fn, args.steps, args.warmup)
-        step_ms_per_rank = [round(x / args.steps, 3) for x in timed.per_rank] if timed.per_rank else None
-        launches = prof.launch_count() - l0
-        total_ids = ids_per_step * (world if world > 1 else 1)
-        value = args.steps * total_ids / (ms / 1e3)
-
-        # end to end: ids from pinned host memory each step, result slice read back
-        for s in range(3):
-            e2e_fn(s)
-        ms_e2e = timed(e2e_fn, args.steps, 0)
-        e2e_value = args.steps * total_ids / (ms_e2e / 1e3)
+    with clk:   # the clock samples cover the two timed regions (resident inputs, end to end) and nothing else
+        ms = timed(step_fn, K, W)
+    step_ms_per_rank = [round(x / K, 3) for x in timed.per_rank] if timed.per_rank else None
+    launches = prof.launch_count() - l0
+    st1 = run.stats()
+    value = K * ids_per_step / (ms / 1e3)
+    # end to end: the same batches on a sketch and tables built anew and warmed up the same way, ids from pinned
+    # host memory each step, a slice of the result read back
+    run = None
+    torch.cuda.empty_cache()
+    run = make()
+    for s in range(W):
+        step_fn(s)
+    with clk:
+        ms_e2e = timed(e2e_fn, K, W)
+    e2e_value = K * ids_per_step / (ms_e2e / 1e3)
     clocks = clk.summary()
+    clk.close()
 
     # per-kernel times, live, with CUDA events on the launching stream (every rank runs the pass: the steps
     # contain collectives; rank 0 reports its own kernels)
     prof.read()
     prof.enable(True)
-    ms_prof = timed(step_fn, args.steps, args.warmup + args.steps)
+    ms_prof = timed(step_fn, K, W + K)
     slots = prof.read()
     prof.enable(False)
     rank_info = None
     if dist is not None:
         # how evenly the ranks are loaded: every rank's own kernel time per step (sum of its per-kernel times)
-        mine = torch.tensor([sum(v[0] for v in slots.values()) / args.steps], device=dev)
+        mine = torch.tensor([sum(v[0] for v in slots.values()) / K], device=dev)
         allr = [torch.zeros_like(mine) for _ in range(world)]
         dist.all_gather(allr, mine)
         names = sorted(slots.keys())
-        vec = torch.tensor([slots[k][0] / args.steps for k in names], device=dev, dtype=torch.float32)
+        vec = torch.tensor([slots[k][0] / K for k in names], device=dev, dtype=torch.float32)
         allv = [torch.zeros_like(vec) for _ in range(world)]
         dist.all_gather(allv, vec)
         per_slot = {k: [round(float(allv[r][i].item()), 3) for r in range(world)] for i, k in enumerate(names)
                     if max(float(allv[r][i].item()) for r in range(world)) >= 0.05}
-        rank_info = {"phase_ms_per_rank": per_slot, "step_ms": step_ms_per_rank, "own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
+        rank_info = {"phase_ms_per_rank": per_slot, "step_ms": step_ms_per_rank,
+                     "own_kernel_ms_per_step": [round(float(t.item()), 3) for t in allr],
                      "host_cpus": len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()}
+    single_ref = None
+    if dist is not None and wl.name == "cfg3" and not args.no_single_ref:
+        # strong-scaling context: the same workload un-sharded on ONE GPU (rank 0; the others wait), same steps
+        if rank == 0:
+            wl1 = Workload("cfg3", 1, args.drift_stride)
+            ids1 = [torch.from_numpy(a).to(dev) for a in generate_batches(wl1, range(W + K), B)]
+            one = SingleGpuRun(wl1, B, dev)
+            g1 = [torch.randn(B, wl1.F, DIM, device=dev, generator=g) * 0.01 for _ in range(min(W + K, 8))]
+            for s in range(W):
+                one.step(ids1[s], g1[s % len(g1)])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for s in range(W, W + K):
+                one.step(ids1[s], g1[s % len(g1)])
+            e1.record()
+            torch.cuda.synchronize()
+            ms1 = e0.elapsed_time(e1)
+            single_ref = {"value": K * ids_per_step / (ms1 / 1e3), "unit": UNIT, "ms_per_step": ms1 / K,
+                          "note": "the same workload and steps on one GPU (all 26 fields, one sketch), measured by rank 0 in "
+                                  "this run; value / (n_gpus * this) is the strong-scaling efficiency of the sharded run"}
+            del one, ids1, g1
+        barrier()
     line = None
     if rank == 0:
         peak, peak_kind = read_peaks()
-        phases = {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[1] / args.steps}
-                  for k, v in slots.items() if v[1] > 0}
-        cand = {k: v for k, v in slots.items() if alg_bytes(k, D) > 0 and v[1] > 0}
+        phases = {k: {"ms_per_step": v[0] / K, "launches_per_step": v[1] / K} for k, v in slots.items() if v[1] > 0}
+        rank_ids = ids_per_step / world if wl.name != "weak26" else ids_per_step / world   # lookups this rank serves per step
+        cand = {k: v for k, v in slots.items() if alg_bytes(k, DIM) > 0 and v[1] > 0}
         # the sketch passes run in three modes (all buckets / later rounds / final pass) that are timed in slots of
         # their own: the kernel is ranked by their sum and reported on its all-bucket launches
         group = {"main_pass": ("main_pass", "main_pass_later_rounds", "main_pass_final"),
                  "lru_pass": ("lru_pass", "lru_pass_later_rounds")}
-        rank = lambda k: sum(slots[g][0] for g in group.get(k, (k,)) if g in slots)
-        top = max(cand, key=rank) if cand else None
+        weight = lambda k: sum(slots[g_][0] for g_ in group.get(k, (k,)) if g_ in slots)
+        top = max(cand, key=weight) if cand else None
         roof = None
         if top:
             per_launch_ms = cand[top][0] / cand[top][1]
             # lookups one launch processes: the per-step kernels see every lookup of the step once; the
             # sketch passes run once or more per job over that job's window, and all windows of a step
-            # add up to the step's lookups, so an average launch covers ids_per_step / launches_per_step
-            launches_per_step = cand[top][1] / args.steps
-            units = ids_per_step / max(1.0, launches_per_step)
-            ach = alg_bytes(top, D) * units / (per_launch_ms / 1e3) / 1e9
+            # add up to the step's lookups, so an average launch covers (lookups per step) / (launches per step)
+            launches_per_step = cand[top][1] / K
+            units = rank_ids / max(1.0, launches_per_step)
+            ach = alg_bytes(top, DIM) * units / (per_launch_ms / 1e3) / 1e9
             traffic = None
             tp = ROOT / "profiles" / "traffic.json"
             if tp.exists():
@@ -427,27 +561,46 @@ def run_ours(args, rank, world, local_rank):
                     traffic = per_id * units if per_id else None
                 except Exception:
                     traffic = None
+            fused = FUSED_BYTES_PER_ID(DIM) * ids_per_step / (ms / K / 1e3) / 1e9 / world
             roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, D),
+                    "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, DIM),
                     "ms_per_launch": per_launch_ms, "ids_per_launch": units,
-                    "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(D),
-                                   "achieved": FUSED_BYTES_PER_ID(D) * total_ids / (ms / args.steps / 1e3) / 1e9 / max(world, 1),
-                                   "frac": FUSED_BYTES_PER_ID(D) * total_ids / (ms / args.steps / 1e3) / 1e9 / max(world, 1) / peak}}
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic", "config": workload_config(B, world),
-                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d if world == 1 else model.h2d_bytes,
-                        "d2h_bytes_per_step": d2h if world == 1 else model.d2h_bytes, "ms_per_step": ms_e2e / args.steps},
-                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "phases": phases,
+                    "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(DIM), "achieved": fused, "frac": fused / peak,
+                                   "note": "per GPU: whole-step algorithmic bytes / step time / n_gpus"}}
+        dl = st1["lookups"] - st0["lookups"]
+        mix = {"lookups": dl, "main_hit_frac": (st1["main_hits"] - st0["main_hits"]) / max(1, dl),
+               "lru_visit_frac": (st1["lru_visits"] - st0["lru_visits"]) / max(1, dl),
+               "rounds_per_step": (st1["rounds"] - st0["rounds"]) / K, "jobs_per_step": (st1["jobs"] - st0["jobs"]) / K,
+               "refits_per_step": (st1["resets"] - st0["resets"]) / K, "seq_fallbacks": st1["seq_fallbacks"] - st0["seq_fallbacks"],
+               "max_rounds": st1["max_rounds"], "note": "rank 0's sketch over the timed region of `value`"}
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": ms / K, "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "config": wl.config(B),
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / K},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "sketch_mix": mix, "phases": phases,
                 "phases_note": "per-kernel CUDA-event times of a separate pass with the side-stream overlap switched off",
-                "ms_per_step_profiled": ms_prof / args.steps}
+                "ms_per_step_profiled": ms_prof / K}
         if rank_info is not None:
             line["ranks"] = rank_info
-        if world == 1:
-            line["sketch"] = {k: v for k, v in grp.sketch.stats().items()}
+        if single_ref is not None:
+            line["single_gpu_same_workload"] = single_ref
+        if world > 1:
+            # bytes this rank stores into its peers per step and direction, against the time of the kernel that moves them
+            R = 4 * DIM
+            fg0 = len([f for f in range(wl.F) if f % world == 0])
+            out_fwd = (world - 1) / world * B * fg0 * R
+            out_bwd = (world - 1) / world * Bl * wl.F * R
+            nv = {"peak_measured_GBs": 770.0, "peak_nominal_GBs": 900.0, "unit": "GB/s per direction per GPU (rank 0)"}
+            if "embed_forward" in phases and phases["embed_forward"]["ms_per_step"] > 0:
+                nv["gather_remote_store_GBs"] = out_fwd / (phases["embed_forward"]["ms_per_step"] / 1e3) / 1e9
+            if "push_grads" in phases and phases["push_grads"]["ms_per_step"] > 0:
+                nv["grad_push_GBs"] = out_bwd / (phases["push_grads"]["ms_per_step"] / 1e3) / 1e9
+            nv["bytes_out_per_step"] = {"pooled_rows": out_fwd, "gradients": out_bwd}
+            line["nvlink"] = nv
         if world == 1 and not args.no_cpu_baseline:
             try:
-                line["cpu_baseline"] = cpu_baseline_leg(args)
+                line["cpu_baseline"] = cpu_baseline_leg(args, wl)
             except Exception as e:  # the baseline is informative; never lose the GPU number to it
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": repr(e)}
         print(json.dumps(line))
@@ -462,11 +615,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=BATCH, help="samples per GPU per step")
-    ap.add_argument("--cpu-batch", type=int, default=16384, help="batch of the CPU baseline sample")
-    ap.add_argument("--cpu-steps", type=int, default=3)
+    ap.add_argument("--workload", default="auto", choices=["auto", "micro", "cfg3", "weak26"])
+    ap.add_argument("--drift-stride", type=int, default=100, help="cfg3: workload steps per bench step")
+    ap.add_argument("--batch", type=int, default=BATCH, help="global batch (samples per step)")
+    ap.add_argument("--cpu-batch", type=int, default=BATCH, help="batch of the CPU reference path")
+    ap.add_argument("--cpu-steps", type=int, default=3, help="timed steps of the cpu_baseline leg of our arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--fields", type=int, default=26, help="use only the first N fields of the workload (experiments)")
+    ap.add_argument("--no-single-ref", action="store_true", help="cfg3 on several GPUs: skip the one-GPU run of the same workload")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU exchange of pooled rows / gradients")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -474,6 +629,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "auto":
+        args.workload = "micro" if world == 1 else "cfg3"
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:

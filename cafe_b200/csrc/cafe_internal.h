@@ -25,6 +25,7 @@ struct CafeEmbedWorkspace {
     uint32_t* key[2] = {nullptr, nullptr};   // [cap] unified row key, unsorted / sorted
     int32_t* pos[2] = {nullptr, nullptr};    // [cap] lookup position, unsorted / sorted
     float* partial = nullptr;    // [2 * ceil(cap/CAFE_CHUNK) * CAFE_MAX_DIM] partial row sums of chunk-spanning rows
+    int32_t* row_winner = nullptr;   // [hotn] migration: highest position that claims a hot row in this call (-1 between calls)
     void* cub_tmp = nullptr;
     size_t cub_bytes = 0;
     cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
@@ -55,7 +56,7 @@ enum {
     CAFE_P_FORWARD = 0, CAFE_P_NORM, CAFE_P_FIELDSUM, CAFE_P_IMPORTANCE, CAFE_P_LOOKUP_SORT, CAFE_P_MAIN, CAFE_P_SCAN,
     CAFE_P_LRU, CAFE_P_RESOLVE, CAFE_P_COMMIT, CAFE_P_REFIT, CAFE_P_MIGRATE, CAFE_P_ROWKEYS, CAFE_P_ROWSORT,
     CAFE_P_SCATTER, CAFE_P_FIXUP, CAFE_P_SEQ, CAFE_P_QUERY, CAFE_P_MEMSET, CAFE_P_OTHER, CAFE_P_MAIN_LATER, CAFE_P_MAIN_FINAL,
-    CAFE_P_LRU_LATER, CAFE_PROF_SLOTS
+    CAFE_P_LRU_LATER, CAFE_P_PUSH, CAFE_P_IDS, CAFE_PROF_SLOTS
 };
 bool cafe_prof_serialise();
 void cafe_prof_begin(int slot, cudaStream_t st);

@@ -67,15 +67,6 @@ struct CafeRoundResult {
     int32_t error;         // internal consistency problems seen (0 = none)
     int32_t n_main_hit;
     int32_t n_events;
-    int32_t n_active_main;   // diagnostics: long buckets replayed, and the most full-replay steps one of them took
-    int32_t max_slow_main;
-    int32_t n_active_lru;
-    int32_t max_feed_lru;
     int32_t list_cursor[3];  // work counters of the launches that go through the long-bucket lists (main, LRU, final pass)
     int32_t seg_real_delta[CAFE_MAX_SEGMENTS];  // change of real_n per segment
-    // diagnostics (experiment flag 128): per kernel phase, the longest warp and the sum over warps, in cycles;
-    // [0..3] main pass: hot-list warp, short phase, long phase, whole warp; [4..7] the same for the LRU pass
-    int32_t diag_max_cycles[8];
-    unsigned long long diag_sum_cycles[8];
-    int32_t diag_warps[8];
 };

@@ -165,20 +165,31 @@ __global__ void k_importance(const float* __restrict__ norm, const float* __rest
 // is in the main table right after its field's call gets its hash row copied into that hot row.
 // The hash row is addressed with the LOCAL id, as the reference does at :207.
 // ---------------------------------------------------------------------------------------------
+// Two lookups of one call can name the same hot row: an id of an early field is handed row r, a threshold
+// re-fit at a later field's call boundary takes r away again, and an id of that later field pops r.  The
+// reference migrates field by field, so the later copy is the one that stays.  Here all fields migrate in
+// one launch, so the lookups first claim their row (the highest position wins, k_migrate_claim) and only
+// the winner copies; it also returns the claim slot to -1 for the next call.
+__global__ void __launch_bounds__(256)
+k_migrate_claim(const int32_t* __restrict__ mask, const int32_t* __restrict__ post_row, int total, int32_t* __restrict__ winner) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < total && mask[p] != 0 && post_row[p] > 0) atomicMax(&winner[post_row[p]], p);
+}
 template <typename IdT>
 __global__ void __launch_bounds__(256)
 k_migrate(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids, const int32_t* __restrict__ mask,
-          const int32_t* __restrict__ post_row, int total, int32_t* __restrict__ n_migrated) {
+          const int32_t* __restrict__ post_row, int total, int32_t* __restrict__ winner, int32_t* __restrict__ n_migrated) {
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int64_t p = warp * 32 + lane;
     const float* src = nullptr;
     float* dst = nullptr;
-    if (p < total && mask[p] != 0 && post_row[p] > 0) {
+    if (p < total && mask[p] != 0 && post_row[p] > 0 && winner[post_row[p]] == (int32_t)p) {
         const int f = (int)(p / F.B);
         const int64_t local = (int64_t)ids[p];
         src = F.w_hash[f] + (size_t)(local % F.hash_size[f]) * F.D;
         dst = F.w_high + (size_t)post_row[p] * F.D;
+        winner[post_row[p]] = -1;
     }
     unsigned act = __ballot_sync(FULL, dst != nullptr);
     if (lane == 0 && act && n_migrated) atomicAdd(n_migrated, __popc(act));
@@ -427,7 +438,6 @@ k_pull_norm(const CafeRankBuffers src, int64_t field_stride, int64_t sample_stri
 // workspace
 // ---------------------------------------------------------------------------------------------
 int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
-    (void)hotn;
     ws->cap = cap;
     const size_t M = (size_t)cap;
     const size_t chunks = (M + CAFE_CHUNK - 1) / CAFE_CHUNK;
@@ -437,6 +447,8 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     A((void**)&ws->mask, 4 * M); A((void**)&ws->post_row, 4 * M);
     for (int i = 0; i < 2; ++i) { A((void**)&ws->key[i], 4 * M); A((void**)&ws->pos[i], 4 * M); }
     A((void**)&ws->partial, sizeof(float) * 2 * chunks * CAFE_MAX_DIM);
+    A((void**)&ws->row_winner, 4 * (size_t)(hotn > 0 ? hotn : 1));
+    if (e == cudaSuccess) e = cudaMemset(ws->row_winner, 0xff, 4 * (size_t)(hotn > 0 ? hotn : 1));   // -1: unclaimed
     size_t b = 0;
     cub::DeviceRadixSort::SortPairs(nullptr, b, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
                                     (int32_t*)nullptr, cap, 0, 32, (cudaStream_t)0);
@@ -453,7 +465,7 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
 
 void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
     void* ptrs[] = {ws->norm, ws->imp, ws->totals, ws->mask, ws->post_row, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1],
-                    ws->partial, ws->cub_tmp};
+                    ws->partial, ws->cub_tmp, ws->row_winner};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ws->side) { cudaStreamSynchronize(ws->side); cudaStreamDestroy(ws->side); }
     if (ws->ev_fork) cudaEventDestroy(ws->ev_fork);
@@ -646,10 +658,12 @@ int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t*
     if (total == 0) return CAFE_OK;
     if (!ids_dev || !mask_dev || !post_row_dev) return CAFE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
+    int32_t* winner = cafe_internal_ws(h)->row_winner;
     const int blocks = ((total + 31) / 32 + 7) / 8;
     CAFE_PROF(CAFE_P_MIGRATE, st);
-    if (ids_are_int64) k_migrate<int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
-    else k_migrate<int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, mask_dev, post_row_dev, total, n_migrated_dev);
+    k_migrate_claim<<<(total + 255) / 256, 256, 0, st>>>(mask_dev, post_row_dev, total, winner);
+    if (ids_are_int64) k_migrate<int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, mask_dev, post_row_dev, total, winner, n_migrated_dev);
+    else k_migrate<int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, mask_dev, post_row_dev, total, winner, n_migrated_dev);
     return fail_cuda("cafe_migrate");
 }
 
@@ -851,7 +865,7 @@ int cafe_shard_scatter_ids(const int64_t* ids_local_dev, int nfields_total, int 
     memset(&d, 0, sizeof(d));
     for (int r = 0; r < nranks; ++r) { if (!owner_ids[r]) return CAFE_ERR_ARG; d.base[r] = owner_ids[r]; }
     cudaStream_t st = (cudaStream_t)stream;
-    CAFE_PROF(CAFE_P_OTHER, st);
+    CAFE_PROF(CAFE_P_IDS, st);
     k_scatter_ids<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(ids_local_dev, nfields_total, rows_local, nranks, rank, d);
     return fail_cuda("cafe_shard_scatter_ids");
 }
@@ -974,7 +988,7 @@ static int push_grads_impl(const float* grad_blocked_dev, int nfields_total, int
     P.row_off[nranks] = (int32_t)off;
     if (off != total_rows || total_rows > 0x7fffffffLL) return CAFE_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
-    CAFE_PROF(CAFE_P_OTHER, st);
+    CAFE_PROF(CAFE_P_PUSH, st);
     const int64_t threads = total_rows * (D / 4);
     k_push_grads<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D, total_rows,
                                                                    j_begin, j_end);

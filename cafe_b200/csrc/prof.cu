@@ -14,7 +14,7 @@ static const char* kSlotNames[CAFE_PROF_SLOTS] = {
     "embed_forward", "grad_norm", "field_sum", "importance", "lookup_hash_sort", "main_pass", "miss_scan", "lru_pass",
     "fifo_resolve", "fifo_commit", "threshold_refit", "migrate", "row_keys", "row_sort", "scatter_chunks",
     "scatter_fixup", "seq_insert", "query", "memset", "other", "main_pass_later_rounds", "main_pass_final",
-    "lru_pass_later_rounds"};
+    "lru_pass_later_rounds", "push_grads", "scatter_ids"};
 
 struct Rec { int slot; cudaEvent_t e0, e1; };
 static bool g_on = false;

@@ -243,8 +243,6 @@ struct CafeJob {
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
     int32_t cand_active;   // the FIFO timeline changed in the previous round: buckets with ids waiting for a row replay
-    int32_t diag;          // timing experiments only (changes results): see k_main_pass
-    int32_t* diag_buf;     // [512][8] per hot-list warp of the main pass: cycles, length, groups, calm chunks, runs, run lookups, feeds, bucket
     int32_t long_main;     // device hint: main buckets with more lookups than this are fed by a whole warp
     int32_t long_lru;      // same for LRU buckets
     int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to

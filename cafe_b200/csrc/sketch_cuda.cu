@@ -132,13 +132,12 @@ __global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_le
     if (idx < CAFE_LIST_CAP - CAFE_HOT_CAP) { list[CAFE_HOT_CAP + idx] = k; flag[k] = 1; }
 }
 // next listed bucket for this warp (lane 0 owns it; -1 = none left); the cursor is zeroed with the round result
-__device__ __forceinline__ int cafe_next_listed(const CafeHot& H, int32_t* cursor, int nb, int* widx) {
+__device__ __forceinline__ int cafe_next_listed(const CafeHot& H, int32_t* cursor, int nb) {
     const int lane = threadIdx.x & 31;
     const int n_hot = min(H.count[0], CAFE_HOT_CAP), n_long = min(H.count[1], CAFE_LIST_CAP - CAFE_HOT_CAP);
     int w = 0;
     if (lane == 0) w = atomicAdd(cursor, 1);
     w = __shfl_sync(CAFE_FULL, w, 0);
-    *widx = w;
     if (w >= n_hot + n_long) return -1;
     return lane == 0 ? H.list[w < n_hot ? w : CAFE_HOT_CAP + (w - n_hot)] : nb;
 }
@@ -169,22 +168,15 @@ __device__ __forceinline__ int cafe_warp_exclusive(int n, int lane, int* total) 
     *total = __shfl_sync(CAFE_FULL, inc, 31);
     return inc - n;
 }
-__device__ __forceinline__ void cafe_diag_cycles(const CafeJob& J, int slot, long long dt) {
-    atomicMax(&J.res->diag_max_cycles[slot], (int)dt);
-    atomicAdd(&J.res->diag_sum_cycles[slot], (unsigned long long)dt);
-    atomicAdd(&J.res->diag_warps[slot], 1);
-}
 #define CAFE_STAGE_MAIN 128   // entries per tile and warp in the main pass
 
 // PART 0: one listed bucket, owned by lane 0 and fed by the whole warp; PART 1: a thread per bucket.
 template <int PART>
-__device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, const int widx, float (*s_c)[CAFE_STAGE_MAIN],
+__device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, float (*s_c)[CAFE_STAGE_MAIN],
                                                int (*s_p)[CAFE_STAGE_MAIN], uint32_t (*s_x)[CAFE_STAGE_MAIN],
                                                uint32_t (*s_kf)[CAFE_STAGE_MAIN]) {
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
-    const bool hot_warp = PART == 0;
-    const long long t_begin = (J.diag & 128) ? clock64() : 0;
     CafeMainReplay R;
     int i = 0, iend = 0;
     bool live = k < J.n1;
@@ -193,17 +185,13 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
         live = R.init(J, k, i);
         if (live) iend = J.start1[k + 1];
     }
-    if (J.diag) {   // timing experiments: leave out classes of buckets
-        const int len = iend - i;
-        if (((J.diag & 1) && len > 512) || ((J.diag & 2) && len > J.long_main && len <= 512) || ((J.diag & 4) && len <= J.long_main)) iend = i;
-    }
     const bool is_long = PART == 0 && live;
     if (PART == 1) {
         const bool is_short = live;
-        const int n_k = (is_short && !(J.diag & 8)) ? max(iend - i, 0) : 0;
+        const int n_k = is_short ? max(iend - i, 0) : 0;
         int T;
         const int pref = cafe_warp_exclusive(n_k, lane, &T);
-        bool done = !is_short || (J.diag & 16);
+        bool done = !is_short;
         for (int t0 = 0; t0 < T; t0 += CAFE_STAGE_MAIN) {
             const int tn = min(CAFE_STAGE_MAIN, T - t0);
 #pragma unroll
@@ -235,9 +223,6 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
             __syncwarp();
         }
     }
-    int slow = 0;
-    int d_groups = 0, d_calm = 0, d_runs = 0, d_runlen = 0;
-    const long long t_short = (J.diag & 128) ? clock64() : 0;
     unsigned m = PART == 0 ? __ballot_sync(CAFE_FULL, is_long) : 0u;
     while (m) {
         const int o = __ffs(m) - 1;
@@ -325,7 +310,6 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
                         }
                     }
                     gb += 128;
-                    ++d_groups;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         cp[q] = xp[q]; cx[q] = xx[q]; cc[q] = xc[q]; cok[q] = xok[q]; cof[q] = xof[q];
@@ -400,7 +384,6 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
                 }
                 __syncwarp();
                 last_calm = calm;
-                ++d_calm;
                 if (lane == o) {
 #pragma unroll
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
@@ -508,7 +491,6 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
                             }
                         }
                         if (done < run) hvalid = false;
-                        ++d_runs; d_runlen += done;
                         j += done;
                         advanced = true;
                     }
@@ -517,27 +499,14 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, co
                     const float cj = __shfl_sync(CAFE_FULL, c, j);
                     const uint32_t kj = __shfl_sync(CAFE_FULL, ok, j);
                     const uint32_t fj = __shfl_sync(CAFE_FULL, of, j);
-                    if (lane == o) { R.feed(J, pj, xj, cj, kj, fj); ++slow; }
+                    if (lane == o) R.feed(J, pj, xj, cj, kj, fj);
                     hvalid = false;   // the full replay step may have changed slots, rows or the next event
                     ++j;
                 }
             }
         }
     }
-    if (is_long) { atomicAdd(&J.res->n_active_main, 1); atomicMax(&J.res->max_slow_main, slow); }
-    const long long t_long = (J.diag & 128) ? clock64() : 0;
     if (live) R.finish(J);
-    if ((J.diag & 128) && lane == 0) {
-        const long long t_end = clock64();
-        if (hot_warp) {
-            cafe_diag_cycles(J, 0, t_end - t_begin);
-            if (J.diag_buf) {
-                int32_t* d = J.diag_buf + 8 * (widx & 511);
-                d[0] = (int)(t_end - t_begin); d[1] = iend - i; d[2] = d_groups; d[3] = d_calm; d[4] = d_runs; d[5] = d_runlen; d[6] = slow; d[7] = k;
-            }
-        }
-        else { cafe_diag_cycles(J, 1, t_short - t_begin); cafe_diag_cycles(J, 2, t_long - t_short); cafe_diag_cycles(J, 3, t_end - t_begin); }
-    }
 }
 template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
@@ -546,32 +515,24 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
     __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
-        cafe_main_body<1>(J, (k < J.n1 && !H.flag[k]) ? k : J.n1, 0, s_c, s_p, s_x, s_kf);
+        cafe_main_body<1>(J, (k < J.n1 && !H.flag[k]) ? k : J.n1, s_c, s_p, s_x, s_kf);
     } else {
         for (;;) {
-            int widx;
-            const int k = cafe_next_listed(H, &J.res->list_cursor[J.final_pass ? 2 : 0], J.n1, &widx);
+            const int k = cafe_next_listed(H, &J.res->list_cursor[J.final_pass ? 2 : 0], J.n1);
             if (k < 0) break;
-            cafe_main_body<0>(J, k, widx, s_c, s_p, s_x, s_kf);
+            cafe_main_body<0>(J, k, s_c, s_p, s_x, s_kf);
         }
     }
 }
 template <int PART>
 __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
     const int lane = threadIdx.x & 31;
-    const bool hot_warp = PART == 0;
-    const long long t_begin = (J.diag & 128) ? clock64() : 0;
     CafeLruReplay R;
     int jb = 0, jend = 0;
     bool live = k < J.n2;
     if (live) {
         live = R.init(J, k);
         if (live) { jb = J.beg2[k]; jend = J.start2[k + 1]; }
-    }
-    int slow = 0;
-    if (J.diag) {   // timing experiments: leave out classes of buckets
-        const int len = jend - jb;
-        if (((J.diag & 32) && len > J.long_lru) || ((J.diag & 64) && len <= J.long_lru)) jend = jb;
     }
     const bool is_long = PART == 0 && live;
     if (PART == 1 && live) {
@@ -601,7 +562,6 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
             }
         }
     }
-    const long long t_short = (J.diag & 128) ? clock64() : 0;
     unsigned m = PART == 0 ? __ballot_sync(CAFE_FULL, is_long) : 0u;
     while (m) {
         const int o = __ffs(m) - 1;
@@ -656,7 +616,7 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
                     const int pj = __shfl_sync(CAFE_FULL, p0[q], j);
                     const uint32_t xj = __shfl_sync(CAFE_FULL, x0[q], j);
                     const float cj = __shfl_sync(CAFE_FULL, c0[q], j);
-                    if (lane == o) { R.feed(J, pj, xj, cj); ++slow; }
+                    if (lane == o) R.feed(J, pj, xj, cj);
                 }
             }
 #pragma unroll
@@ -667,14 +627,7 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
             }
         }
     }
-    if (is_long) { atomicAdd(&J.res->n_active_lru, 1); atomicMax(&J.res->max_feed_lru, slow); }
-    const long long t_long = (J.diag & 128) ? clock64() : 0;
     if (live) R.finish(J);
-    if ((J.diag & 128) && lane == 0) {
-        const long long t_end = clock64();
-        if (hot_warp) cafe_diag_cycles(J, 4, t_end - t_begin);
-        else { cafe_diag_cycles(J, 5, t_short - t_begin); cafe_diag_cycles(J, 6, t_long - t_short); cafe_diag_cycles(J, 7, t_end - t_begin); }
-    }
 }
 template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
@@ -683,8 +636,7 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __gri
         cafe_lru_body<1>(J, (k < J.n2 && !H.flag[k]) ? k : J.n2);
     } else {
         for (;;) {
-            int widx;
-            const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2, &widx);
+            const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2);
             if (k < 0) break;
             cafe_lru_body<0>(J, k);
         }
@@ -1060,27 +1012,7 @@ struct CudaBackend {
     cudaEvent_t gate_event = nullptr;   // see SketchEngine::set_gate
     void wait_gate() { if (gate_event) check(cudaStreamWaitEvent(stream, gate_event, 0)); }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
-    int32_t* diag_buf = nullptr;
-    void diag_dump() {
-        if (!diag_buf) return;
-        std::vector<int32_t> h(512 * 8);
-        cudaMemcpy(h.data(), diag_buf, h.size() * 4, cudaMemcpyDeviceToHost);
-        std::vector<int> idx(512);
-        for (int q = 0; q < 512; ++q) idx[q] = q;
-        std::sort(idx.begin(), idx.end(), [&](int a, int b) { return h[8 * a] > h[8 * b]; });
-        for (int q = 0; q < 6; ++q) {
-            const int32_t* d = &h[8 * idx[q]];
-            fprintf(stderr, "     hot warp %3d: %7d cyc, %5d entries, %3d groups, %3d calm chunks, %4d runs (%5d lookups), %3d feeds, bucket %d\n",
-                    idx[q], d[0], d[1], d[2], d[3], d[4], d[5], d[6], d[7]);
-        }
-    }
-    void main_pass(const CafeJob& J0) {
-        CafeJob J = J0;
-        if (J.diag & 128) {
-            if (!diag_buf) cudaMalloc(&diag_buf, 512 * 8 * 4);
-            cudaMemsetAsync(diag_buf, 0, 512 * 8 * 4, stream);
-            J.diag_buf = diag_buf;
-        }
+    void main_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
         pass_fork();
         k_main_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(0));

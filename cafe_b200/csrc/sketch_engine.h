@@ -39,7 +39,6 @@ public:
     int q_size = 0;
     uint32_t ring_mask = 0;
     int round_cap = 48;
-    bool diag = getenv("CAFE_B200_DIAG") != nullptr;   // print per-round diagnostics to stderr
     double cross_rate = -1.0;         // threshold crossings per lookup seen in recent jobs (-1: unknown)
     int window = CAFE_MAX_SEGMENTS;   // upper bound on the segments fused into one job
     int last_status = CAFE_OK;
@@ -375,7 +374,6 @@ private:
         CafeJob J;
         memset(&J, 0, sizeof(J));
         cursors_advanced = false;
-        const int planned = nseg;
         J.gid = gid; J.imp = imp; J.M = M; J.begin = seg[0]; J.limit = seg[nseg]; J.nseg = nseg;
         for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i];
         for (int i = nseg + 1; i <= CAFE_MAX_SEGMENTS; ++i) J.seg_off[i] = INT32_MAX;
@@ -393,7 +391,6 @@ private:
         // otherwise be a serial tail: threshold = a few times the average load per bucket.
         J.long_main = std::max(16, (int)(4.0 * M / n1));
         J.long_lru = std::max(16, (int)(4.0 * M / n2));
-        J.diag = getenv("CAFE_B200_EXPERIMENT") ? atoi(getenv("CAFE_B200_EXPERIMENT")) : 0;
         ++stats.jobs;
         {
             const size_t span = (size_t)(J.limit - J.begin);
@@ -439,13 +436,6 @@ private:
             first = false;
             tl_changed_prev = R.tl_changed != 0;
             pb ^= 1;
-            if (diag) fprintf(stderr, "round %d begin %d limit %d first %d all %d changed %d: long main %d (max slow %d) long lru %d (max feeds %d) miss %d\n", rounds, J.begin, J.limit, J.first_round, J.all_active, R.changed, R.n_active_main, R.max_slow_main, R.n_active_lru, R.max_feed_lru, R.n_miss);
-            if (diag && (J.diag & 128)) {
-                be.diag_dump();
-                static const char* names[8] = {"main hot", "main short", "main long", "main warp", "lru hot", "lru short", "lru long", "lru warp"};
-                for (int q = 0; q < 8; ++q)
-                    if (R.diag_warps[q]) fprintf(stderr, "   %-10s warps %7d  max %8d cyc  mean %8.0f cyc\n", names[q], R.diag_warps[q], R.diag_max_cycles[q], (double)R.diag_sum_cycles[q] / R.diag_warps[q]);
-            }
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
             // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
             // per-segment deltas of a round that has not converged yet are estimates, but shrinking
@@ -496,11 +486,6 @@ private:
         if (J.limit > J.begin) {
             const double r = (double)grown / (J.limit - J.begin);
             cross_rate = cross_rate < 0 ? r : 0.5 * cross_rate + 0.5 * r;
-        }
-        if (diag) {
-            fprintf(stderr, "job real_n0 %d lim %d rate %.4f planned %d done %d deltas", real_n - grown, lim, cross_rate, planned, nseg);
-            for (int b = 0; b < nseg; ++b) fprintf(stderr, " %d", R.seg_real_delta[b]);
-            fprintf(stderr, "\n");
         }
         stats.main_hits += (int64_t)(J.limit - J.begin) - R.n_miss; stats.lru_visits += R.n_miss; stats.events += R.n_events;
         if (rounds > stats.max_rounds) stats.max_rounds = rounds;

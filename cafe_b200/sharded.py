@@ -115,7 +115,7 @@ class PeerBuffers:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
         grp = group if group is not None else dist.group.WORLD
-        self.plan, self.rows, self.dim = plan, rows, dim
+        self.plan, self.rows, self.dim, self.pg = plan, rows, dim, group
         fmax = max(plan.counts)
         self.ids = symm.empty(2 * fmax * plan.G * rows, dtype=torch.int64, device=device)
         self.pooled = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
@@ -137,9 +137,9 @@ class PeerBuffers:
     def ptr_array(self, handle, elem_offset: int, elem_size: int):
         return (ctypes.c_void_p * self.plan.G)(*[int(p) + elem_offset * elem_size for p in handle.buffer_ptrs])
 
-    def fence(self, group=None):
-        """All ranks have issued everything before this point on their streams (stream-ordered)."""
-        dist.all_reduce(self.flag, group=group)
+    def fence(self):
+        """All ranks of the group have issued everything before this point on their streams (stream-ordered)."""
+        dist.all_reduce(self.flag, group=self.pg)
 
 
 class _PeerFunction(torch.autograd.Function):
@@ -153,6 +153,10 @@ class _PeerFunction(torch.autograd.Function):
         lib = grp.sketch.lib
         F, Bl = ids.shape
         G, Fg, D = plan.G, grp.num_fields, grp.embedding_dim
+        training = bool(ctx.needs_input_grad[0])
+        if training and model._pending_backward:
+            raise RuntimeError("ShardedSKEmbedding (peer exchange): a second training forward before the backward of the "
+                               "previous one would overwrite the exchange buffers that backward still reads")
         pb.gen ^= 1
         gen_off = pb.gen * pb.ids_gen_elems
         with torch.cuda.device(ids.device):
@@ -170,6 +174,7 @@ class _PeerFunction(torch.autograd.Function):
                                                       row.data_ptr(), _stream()), "cafe_embed_forward_sharded")
             pb.fence()                                   # every consumer's pooled buffer is complete
         ctx.model, ctx.saved, ctx.Bl = model, (own, gid, row), Bl
+        model._pending_backward = training
         return pb.pooled
 
     @staticmethod
@@ -177,6 +182,7 @@ class _PeerFunction(torch.autograd.Function):
         from . import _lib
         from .sketch import _stream
         model = ctx.model
+        model._pending_backward = False
         plan, grp, pb = model.plan, model.group, model.peer
         lib = grp.sketch.lib
         own, gid, row = ctx.saved
@@ -222,13 +228,13 @@ class _ShardedFunction(torch.autograd.Function):
     def forward(ctx, anchor, model, ids):
         plan, grp = model.plan, model.group
         Bl = ids.shape[1]
-        own_ids = plan.exchange_ids(ids)
+        own_ids = plan.exchange_ids(ids, model.pg)
         flat = own_ids.reshape(-1)
         Fg, D = grp.num_fields, grp.embedding_dim
         pooled = torch.empty(plan.G * Bl, Fg, D, dtype=torch.float32, device=ids.device)
         gid, row = grp._fields.forward(flat, pooled, D, Fg * D)
         ctx.model, ctx.saved, ctx.Bl = model, (flat, gid, row), Bl
-        return plan.exchange_pooled(pooled)
+        return plan.exchange_pooled(pooled, model.pg)
 
     @staticmethod
     def backward(ctx, blocked_grad):
@@ -237,7 +243,7 @@ class _ShardedFunction(torch.autograd.Function):
         flat, gid, row = ctx.saved
         Fg, D = grp.num_fields, grp.embedding_dim
         grp._fields.backward_begin(gid, row, plan.G * ctx.Bl, grp.insert_mode)   # sorts run beside the exchange
-        g = plan.exchange_grads(blocked_grad.contiguous(), ctx.Bl, D)
+        g = plan.exchange_grads(blocked_grad.contiguous(), ctx.Bl, D, model.pg)
         with torch.no_grad():
             grp.last_status = grp._fields.backward(g, D, Fg * D, flat, gid, row, plan.G * ctx.Bl, grp.lr, grp.insert_mode)
         return None, None, None
@@ -246,7 +252,14 @@ class _ShardedFunction(torch.autograd.Function):
 class ShardedSKEmbedding(torch.nn.Module):
     """forward(ids [F, B_local]) -> rank-blocked pooled embeddings of this rank's batch slice
     (see FieldShardPlan.unblock for the [B_local, F, D] view); backward runs the fused update on the
-    owners.  Needs an initialised NCCL process group with one rank per GPU."""
+    owners.  Needs an initialised NCCL process group with one rank per GPU; `group` (default: all ranks)
+    is the set of ranks the fields are sharded over, and every exchange and fence runs on it.
+
+    With the peer exchange the tensor a training forward returns IS this rank's exchange buffer: it is valid
+    until the next forward() of this module, whose peers overwrite it by remote stores that autograd does not
+    see.  Therefore a second forward before the backward of a training forward raises (gradient accumulation
+    over several forwards and evaluation between a forward and its backward are not supported); a forward
+    under no_grad, between steps, returns a copy."""
 
     def __init__(self, num_categories, embedding_dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1,
                  sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None,
@@ -254,6 +267,10 @@ class ShardedSKEmbedding(torch.nn.Module):
         super().__init__()
         from .sk_embedding_bag import SKEmbeddingGroup
         world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if rank < 0:
+            raise ValueError("this rank is not a member of `group`")
+        self.pg = group
+        self._pending_backward = False
         cards = [int(n) for n in num_categories]
         self.num_categories = cards
         self.plan = FieldShardPlan(len(cards), world, rank)
@@ -291,41 +308,10 @@ class ShardedSKEmbedding(torch.nn.Module):
         if self.peer is not None:
             if ids.dtype != torch.int64 or ids.shape[1] != self.peer.rows:
                 raise ValueError("peer exchange: ids must be int64 [F, global_batch / world]")
+            if not torch.is_grad_enabled():
+                if self._pending_backward:
+                    raise RuntimeError("ShardedSKEmbedding (peer exchange): forward under no_grad between a training "
+                                       "forward and its backward would overwrite the buffers that backward reads")
+                return _PeerFunction.apply(self._anchor, self, ids).clone()
             return _PeerFunction.apply(self._anchor, self, ids)
         return _ShardedFunction.apply(self._anchor, self, ids)
-
-    # ---- benchmark plumbing ---------------------------------------------------------------------------
-    def bench_closures(self, S, zipf_s, seed):
-        """(step_fn, e2e_fn, ids_per_rank_step) for bench.py: every rank feeds its slice of the global
-        batch (all fields), gradients of the exchanged embeddings are synthetic N(0, 0.01)."""
-        plan, dev = self.plan, self.group.weight_high.device
-        Bl, D, F = self.global_batch // plan.G, self.embedding_dim, plan.F
-        cards = None
-        nb = 4
-        import numpy as np
-        from . import synthetic
-        cards = self.num_categories
-        host = [torch.from_numpy(S.batch_ids(cards, Bl, zipf_s, seed + 7919 * plan.rank, s)).pin_memory() for s in range(nb)]
-        devi = [h.to(dev) for h in host]
-        g = torch.Generator(device=dev).manual_seed(seed + plan.rank)
-        if self.peer is not None:
-            # the gradient of the exchanged rows is produced in place, in the buffer the owners pull from
-            self.peer.grad.copy_(torch.randn(Bl * F * D, device=dev, generator=g) * 0.01)
-            grads = [self.peer.grad, self.peer.grad]
-        else:
-            grads = [torch.randn(Bl * F * D, device=dev, generator=g) * 0.01 for _ in range(2)]
-        stage = torch.empty_like(devi[0])
-        res = torch.empty(16 * D, dtype=torch.float32).pin_memory()
-        self.h2d_bytes, self.d2h_bytes = host[0].numel() * 8 * plan.G, res.numel() * 4 * plan.G
-
-        def step_fn(s):
-            out = self(devi[s % nb])
-            out.backward(grads[s % 2])
-
-        def e2e_fn(s):
-            stage.copy_(host[s % nb], non_blocking=True)
-            out = self(stage)
-            out.backward(grads[s % 2])
-            res.copy_(out.detach()[:16 * D], non_blocking=True)
-
-        return step_fn, e2e_fn, Bl * F

@@ -72,6 +72,45 @@ def batch_ids(cards, batch: int, s: float, seed: int, step: int, dtype=np.int64)
     return out
 
 
+def drift_exponent(step: int, s0: float = 1.05, s1: float = 1.2, horizon: int = 10_000) -> float:
+    """Zipf exponent of the drifting workload: linear from s0 at step 0 to s1 at `horizon`, constant afterwards."""
+    return s0 + (s1 - s0) * min(max(step, 0), horizon) / float(horizon)
+
+
+def drift_remap(ids: np.ndarray, n: int, seed: int, field: int, epochs: int, den: int = 20) -> np.ndarray:
+    """The re-permutations of the drifting workload applied to ids of one field.
+
+    Epoch j (j = 1..epochs) re-permutes, among themselves, the ids whose remainder modulo `den` equals a
+    seeded residue c_j: 1/den of the id space (5 % for den = 20) moves, everything else stays.  Each epoch
+    is a bijection of [0, n) (a Feistel permutation of the quotients within one residue class), so the
+    composition is one too and no table is needed for 40M-id fields."""
+    x = ids.astype(np.int64, copy=True)
+    if n < 2 * den:
+        return x
+    for j in range(1, epochs + 1):
+        c = int(_mix(np.array([j], np.uint64), seed * 7919 + field * 131 + 17)[0] % np.uint64(den))
+        cnt = (n - c + den - 1) // den            # ids in [0, n) with id % den == c
+        sel = (x % den) == c
+        if cnt > 1 and sel.any():
+            x[sel] = feistel_permute(x[sel] // den, int(cnt), seed * 1000 + field * 37 + 5000 + j) * den + c
+    return x
+
+
+def drift_batch_ids(cards, batch: int, seed: int, step: int, s0: float = 1.05, s1: float = 1.2, horizon: int = 10_000,
+                    period: int = 1000, den: int = 20, dtype=np.int64) -> np.ndarray:
+    """ids [F, batch] of the drifting Terabyte-shaped workload: the Zipf exponent moves from s0 to s1 over
+    `horizon` steps and, every `period` steps, 1/den of every field's ids are re-permuted (drift_remap), so
+    that ids leave and enter the hot set while training runs."""
+    s = drift_exponent(step, s0, s1, horizon)
+    out = np.empty((len(cards), batch), dtype)
+    for f, n in enumerate(cards):
+        rng = np.random.Generator(np.random.Philox(key=[seed, 0], counter=[0, 0, step, f]))
+        u = rng.random(batch)
+        base = feistel_permute(zipf_ranks(u, int(n), s), int(n), seed * 1000 + f)
+        out[f] = drift_remap(base, int(n), seed, f, step // period, den).astype(dtype)
+    return out
+
+
 def dense_features(batch: int, seed: int, step: int, num: int = 13) -> np.ndarray:
     """log(1 + round(Exp(mean 20))) as fp32, the dense side of the Criteo-shaped configurations."""
     rng = np.random.Generator(np.random.Philox(key=[seed, 1], counter=[0, 0, step, 0]))

@@ -13,11 +13,12 @@
 #       so that reset()'s address tie-break (sketch.cpp:79-96) is the canonical order
 #       main-before-LRU, bucket, slot instead of depending on the heap layout;
 #   P4  make the class members visible to the state-dump shim (ref_shim.inc) appended below.
-# Usage: build_ref.sh [reference_root]   (default: ref_root below; exits 0 and builds nothing when the
-# reference checkout is absent, e.g. on a machine that only runs the prebuilt library).
+# Usage: build_ref.sh [reference_root]   (default: $CAFE_REFERENCE_ROOT, else the directory `reference`
+# beside this repository; exits 0 and builds nothing when the reference checkout is absent, e.g. on a
+# machine that only runs the prebuilt library).
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-ref_root="${1:-/root/reference}"
+ref_root="${1:-${CAFE_REFERENCE_ROOT:-$here/../../reference}}"
 src="$ref_root/tricks/sketch.cpp"
 out_dir="$here/_ref"
 if [ ! -f "$src" ]; then

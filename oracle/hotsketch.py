@@ -36,7 +36,7 @@ def build(force: bool = False) -> None:
     if force or not ORACLE_SO.exists() or ORACLE_SO.stat().st_mtime < (_HERE / "hotsketch_oracle.c").stat().st_mtime:
         subprocess.run(["make", "-s", "-C", str(_HERE), str(ORACLE_SO)], check=True)
     if force or not REF_SO.exists():
-        subprocess.run(["bash", str(_HERE / "build_ref.sh")], check=True, stdout=subprocess.DEVNULL)
+        subprocess.run(["bash", str(_HERE / "build_ref.sh"), str(reference_root())], check=True, stdout=subprocess.DEVNULL)
 
 
 def _ptr(a: np.ndarray, typ):
@@ -157,24 +157,38 @@ class _MutedStdout:
         os.close(self._null)
 
 
+def reference_root() -> Path:
+    """Where the reference checkout is looked for: $CAFE_REFERENCE_ROOT, else a directory named
+    `reference` beside this repository."""
+    env = os.environ.get("CAFE_REFERENCE_ROOT")
+    return Path(env) if env else _HERE.parent.parent / "reference"
+
+
 def ref_available() -> bool:
-    if not REF_SO.exists() and Path("/root/reference/tricks/sketch.cpp").exists():
+    if not REF_SO.exists() and (reference_root() / "tricks" / "sketch.cpp").exists():
         build()
     return REF_SO.exists()
 
 
 class ReferenceSketch:
-    """The compiled reference.  Its state is process-global, so every instance loads a private copy
-    of the shared library (a temp-file copy), which gives independent sketches in one process."""
+    """The compiled reference.  Its state is process-global, so a process's first instance loads
+    oracle/_ref/libsketch_ref.so itself and every further one a private temp-file copy of it, which
+    gives independent sketches in one process."""
+
+    _direct_used = False
 
     def __init__(self, lim: int, thr: float, adjust: int = 1, alpha: float = 1.0000005):
         if not ref_available():
             raise RuntimeError("oracle/_ref/libsketch_ref.so has not been built (reference checkout absent)")
-        fd, self._tmp = tempfile.mkstemp(suffix=".so", prefix="sketch_ref_")
-        os.close(fd)
-        shutil.copyfile(REF_SO, self._tmp)
-        self._lib = lib = ctypes.CDLL(self._tmp)
-        os.unlink(self._tmp)
+        if not ReferenceSketch._direct_used:
+            ReferenceSketch._direct_used = True
+            self._lib = lib = ctypes.CDLL(str(REF_SO))
+        else:
+            fd, self._tmp = tempfile.mkstemp(suffix=".so", prefix="sketch_ref_")
+            os.close(fd)
+            shutil.copyfile(REF_SO, self._tmp)
+            self._lib = lib = ctypes.CDLL(self._tmp)
+            os.unlink(self._tmp)
         lib.init.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_double]
         lib.init.restype = None
         for name in ("batch_query", "batch_insert"):

@@ -18,9 +18,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent.parent))
-sys.path.insert(0, "/root/reference")
+from oracle.hotsketch import ReferenceSketch, reference_root  # noqa: E402
 
-from oracle.hotsketch import ReferenceSketch  # noqa: E402
+sys.path.insert(0, str(reference_root()))   # $CAFE_REFERENCE_ROOT, else `reference` beside the repository
 from tricks.sk_embedding_bag import SKEmbeddingBag as RefBag  # noqa: E402
 
 STATE_KEYS = ["main_val", "main_cnt", "main_dic", "main_flip", "lru_val", "lru_cnt", "lru_dic", "lru_t", "lru_flip",

@@ -50,7 +50,6 @@ struct HostBackend {
     }
     void sort_join(int) {}
     void wait_gate() {}
-    void diag_dump() {}
     void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
         (void)lane;
         sort_lookups_impl(gid, M, nb, ord, start);

@@ -1,6 +1,6 @@
-"""Fused training steps at the shapes of the named configurations (scaled to what the CPU oracle finishes in
-seconds): Kaggle-shaped 26 fields / dim 16 / batch 128, and the Avazu-shaped large-hot-table regime
-(compress 0.1, hash-rate 0.7, 9 sketch fields).  Same bars as tests/test_gpu_embed.py."""
+"""Fused training steps at the shapes and batch sizes of the named configurations: Kaggle-shaped 26 fields / dim 16 /
+batch 128, the Avazu-shaped large-hot-table regime (compress 0.1, hash-rate 0.7, 9 sketch fields, batch 4096) and
+the Terabyte-shaped one (dim 128, batch 2048).  Same bars as tests/test_gpu_embed.py."""
 import numpy as np
 import pytest
 
@@ -47,9 +47,9 @@ def test_avazu_shape_large_hot_table_regime():
     from cafe_b200 import sizing, synthetic as S
     cards = [n for n in S.AVAZU_CARDS if sizing.is_sketch_field(n, 0.1)]
     assert len(cards) == 9
-    run_steps(cards, 16, 0.1, 0.7, 512, 12, 1.0)
+    run_steps(cards, 16, 0.1, 0.7, 4096, 8, 1.0)
 
 
 def test_terabyte_shape_dim128():
     from cafe_b200 import synthetic as S
-    run_steps(S.TERABYTE_CARDS, 128, 0.001, 0.3, 256, 10, 1.1)
+    run_steps(S.TERABYTE_CARDS, 128, 0.001, 0.3, 2048, 8, 1.1)

@@ -301,3 +301,34 @@ def test_gated_backward_waits_for_late_fields():
         assert torch.equal(a.weight_high, b.weight_high), f"step {step}: hot table"
         for f in range(F):
             assert torch.equal(a.weight_hash[f], b.weight_hash[f]), f"step {step}: hash table {f}"
+
+
+def test_two_fields_claim_one_hot_row_in_one_step():
+    """A threshold re-fit between two fields' calls of one step takes a hot row from an id of the earlier field and an
+    id of the later field pops it: both lookups are reported newly hot with the same row.  The reference migrates
+    field by field, so the later field's hash row is the one that stays in the hot table (the configuration below
+    reaches this case within its 30 steps with the sequential oracle)."""
+    import torch
+    import cafe_b200
+    F, B, dom, D, lim = 8, 128, 2000, 16, 60
+    cards = [dom] * F
+    grp = cafe_b200.SKEmbeddingGroup(cards, D, 0.01, 0.3, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=3, hotn=lim)
+    sk = OracleSketch(lim, 1, 1, 1.0000005)
+    orc = ModuleOracle(sk, grp.weight_high.detach().cpu().numpy(), [w.detach().cpu().numpy() for w in grp.weight_hash],
+                       grp.f_offsets, grp.hash_sizes)
+    rng = np.random.default_rng(0)
+    for step in range(30):
+        ids = np.stack([np.minimum(rng.zipf(1.2, B) - 1, dom - 1) for _ in range(F)]).astype(np.int64)
+        imp = (rng.random((F, B)) * 2).astype(np.float32)
+        # gradient rows whose norms are the wanted importances times a constant: both sides get the kernel's floats
+        grad = np.zeros((B, F, D), np.float32)
+        grad[:, :, 0] = imp.T * 0.01
+        out = grp(torch.from_numpy(ids))
+        orc.forward(ids)
+        g = torch.from_numpy(grad).cuda()
+        impk = grp._fields.importance(g, D, F * D, B).view(F, B).cpu().numpy()
+        out.backward(g)
+        masks, _ = orc.backward(ids, grad, grp.lr, importance=impk)
+        assert states_equal(sk.state(), grp.sketch.state()) == [], f"step {step}"
+        close(grp.weight_high.detach().cpu().numpy(), orc.wh, f"step {step}: hot table")
+    assert grp.sketch.stats()["resets"] > 0

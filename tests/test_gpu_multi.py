@@ -1,5 +1,7 @@
-"""Exchange variants of the field-sharded module against each other on two GPUs (skipped with fewer)."""
+"""The field-sharded module on two GPUs (skipped with fewer): every shard against its own CPU oracle, and the
+exchange variants against each other (tests/multi_gpu_parity.py)."""
 import os
+import socket
 import subprocess
 import sys
 from pathlib import Path
@@ -9,13 +11,22 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-def test_exchange_variants_agree_on_two_gpus():
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_shards_match_their_oracles_and_exchange_variants_agree_on_two_gpus():
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     script = Path(__file__).resolve().parent / "multi_gpu_parity.py"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-                        "127.0.0.1", "--master-port", "29533", str(script)], env=env, capture_output=True, text=True, timeout=300)
+                        "127.0.0.1", "--master-port", str(_free_port()), str(script)], env=env, capture_output=True, text=True,
+                       timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "identical" in r.stdout

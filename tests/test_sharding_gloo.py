@@ -76,3 +76,42 @@ def test_plan_covers_every_field_once():
         assert seen == list(range(26))
         assert sorted(plans[0].blocked_order) == list(range(26))
         assert max(plans[0].counts) - min(plans[0].counts) <= 1
+
+
+def _subgroup_worker(rank, world, port, members, F, Bl, D, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sub = dist.new_group(ranks=members)   # every rank takes part in creating it
+        if rank not in members:
+            q.put((rank, True, True))
+            return
+        G, r = len(members), members.index(rank)
+        plan = FieldShardPlan(F, G, r)
+        g = torch.Generator().manual_seed(100 + r)
+        ids = torch.randint(0, 10_000, (F, Bl), generator=g)
+        own = plan.exchange_ids(ids, sub)
+        Fg = len(plan.local_fields)
+        pooled = torch.stack([fake_embed(f, own[j], D) for j, f in enumerate(plan.local_fields)], dim=1)
+        full = plan.unblock(plan.exchange_pooled(pooled.contiguous(), sub), Bl, D)
+        want = torch.stack([fake_embed(f, ids[f], D) for f in range(F)], dim=1)
+        got = plan.exchange_grads(plan.block(want * (r + 1)), Bl, D, sub)
+        scale = torch.arange(1, G + 1).repeat_interleave(Bl).float()[:, None, None]
+        q.put((rank, torch.equal(full, want), torch.equal(got, pooled * scale)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchanges_on_a_subgroup_of_the_job():
+    """Fields sharded over ranks 1 and 3 of a four-rank job: the exchanges run on that group only, and the other
+    ranks are not needed for them to finish."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_subgroup_worker, args=(r, 4, port, [1, 3], 7, 5, 4, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(4)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(a and b for _, a, b in res), res
