@@ -23,11 +23,11 @@ struct CafeEmbedWorkspace {
     int32_t* mask = nullptr;     // [cap] newly-hot flag per lookup
     int32_t* post_row = nullptr; // [cap] hot row after the lookup's own call
     uint32_t* key[2] = {nullptr, nullptr};   // [cap] unified row key, unsorted / sorted
-    int32_t* pos[2] = {nullptr, nullptr};    // [cap] lookup position, unsorted / sorted
+    int32_t* pos[2] = {nullptr, nullptr};    // [cap] lookup position: intermediate pass of the sort / sorted
     float* partial = nullptr;    // [2 * ceil(cap/CAFE_CHUNK) * CAFE_MAX_DIM] partial row sums of chunk-spanning rows
     int32_t* row_winner = nullptr;   // [hotn] migration: highest position that claims a hot row in this call (-1 between calls)
-    void* cub_tmp = nullptr;
-    size_t cub_bytes = 0;
+    uint32_t* key_tmp = nullptr;     // [cap] intermediate keys of the row sort
+    int32_t* sort_scratch = nullptr; // radix-sort histograms
     cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaStream_t late = nullptr;     // importance of fields whose gradients arrive behind a gate

@@ -9,10 +9,9 @@
 #include <stdio.h>
 #include <string.h>
 
-#include <cub/cub.cuh>
-
 #include "../../include/cafe_b200.h"
 #include "cafe_internal.h"
+#include "radix_sort.cuh"
 #include "sketch_core.cuh"
 
 struct CafeFields {
@@ -210,12 +209,11 @@ k_migrate(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids, con
 // results are deterministic.
 // ---------------------------------------------------------------------------------------------
 __global__ void k_row_keys(const __grid_constant__ CafeFields F, const int32_t* __restrict__ row, int total,
-                           uint32_t* __restrict__ key, int32_t* __restrict__ pos) {
+                           uint32_t* __restrict__ key) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= total) return;
     const int32_t r = row[p];
     key[p] = r < 0 ? (uint32_t)((-r) % F.hotn) : (uint32_t)(F.hotn + F.hash_base[p / F.B] + r);
-    pos[p] = p;
 }
 
 __device__ __forceinline__ float* row_ptr(const CafeFields& F, uint32_t key, int pos) {
@@ -449,11 +447,8 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     A((void**)&ws->partial, sizeof(float) * 2 * chunks * CAFE_MAX_DIM);
     A((void**)&ws->row_winner, 4 * (size_t)(hotn > 0 ? hotn : 1));
     if (e == cudaSuccess) e = cudaMemset(ws->row_winner, 0xff, 4 * (size_t)(hotn > 0 ? hotn : 1));   // -1: unclaimed
-    size_t b = 0;
-    cub::DeviceRadixSort::SortPairs(nullptr, b, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
-                                    (int32_t*)nullptr, cap, 0, 32, (cudaStream_t)0);
-    ws->cub_bytes = b + 1024;
-    A(&ws->cub_tmp, ws->cub_bytes);
+    A((void**)&ws->key_tmp, 4 * M);
+    A((void**)&ws->sort_scratch, 4 * cafe_rs_scratch_elems(cap));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_join, cudaEventDisableTiming);
@@ -465,7 +460,7 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
 
 void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
     void* ptrs[] = {ws->norm, ws->imp, ws->totals, ws->mask, ws->post_row, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1],
-                    ws->partial, ws->cub_tmp, ws->row_winner};
+                    ws->partial, ws->key_tmp, ws->sort_scratch, ws->row_winner};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ws->side) { cudaStreamSynchronize(ws->side); cudaStreamDestroy(ws->side); }
     if (ws->ev_fork) cudaEventDestroy(ws->ev_fork);
@@ -672,13 +667,16 @@ int cafe_migrate(void* h, const void* ids_dev, int ids_are_int64, const int32_t*
 // caller run the first part on the workspace's side stream while the sketch insert runs on the main one.
 static int scatter_prepare(CafeEmbedWorkspace* ws, const CafeFields& F, const int32_t* row_dev, int total, int hotn,
                            cudaStream_t st) {
-    { CAFE_PROF(CAFE_P_ROWKEYS, st); k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0], ws->pos[0]); }
+    { CAFE_PROF(CAFE_P_ROWKEYS, st); k_row_keys<<<(total + 255) / 256, 256, 0, st>>>(F, row_dev, total, ws->key[0]); }
     int bits = 1;
     while ((1ll << bits) < (int64_t)hotn + F.hash_base[F.nfields]) ++bits;
-    size_t b = ws->cub_bytes;
     cudaError_t e;
     { CAFE_PROF(CAFE_P_ROWSORT, st);
-      e = cub::DeviceRadixSort::SortPairs(ws->cub_tmp, b, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1], total, 0, bits, st); }
+      // (row key, position) pairs, stable: a row's lookups stay in batch order, which fixes the order of the additions
+      CafeKeySource src;
+      src.key = ws->key[0]; src.gid = nullptr; src.nb = 0;
+      e = cafe_radix_sort(src, nullptr, ws->key_tmp, ws->pos[0], ws->key[1], ws->pos[1], total, bits, ws->sort_scratch, nullptr,
+                          nullptr, st); }
     if (e != cudaSuccess) { cafe_internal_set_error(cudaGetErrorString(e)); return CAFE_ERR_CUDA; }
     return CAFE_OK;
 }

@@ -202,7 +202,11 @@ CAFE_HD int cafe_seq_insert(CafeSeqState& S, uint32_t x, float count) {
 // =================================================================================================
 // Parallel form.
 // =================================================================================================
-struct alignas(16) CafeFn { int32_t a, b, np, nmiss; };   // FIFO size transfer s -> max(s + a, b); pushes and main-table misses so far
+struct alignas(16) CafeFn { int32_t a, b, np, pad; };   // FIFO size transfer s -> max(s + a, b); pushes so far
+
+// The FIFO timeline is kept sparse: one entry per op (a candidate pop or a push), in op-slot order.
+#define CAFE_TL_BLOCK 1024    // positions (resp. ops) handled by one block of the timeline kernels
+#define CAFE_TL_GROUP 64      // positions per entry of the coarse index into the op list
 
 // per-lookup result flags (one byte written by the main pass, one by the LRU pass)
 enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE_F_GOT = 16 };
@@ -225,6 +229,12 @@ struct CafeJob {
     const int32_t* ord2;
     const int32_t* start2;   // [n2+1]
     const int32_t* beg2;     // [n2]
+    // ids and counts permuted into the two orders (sgid1[i] = gid[ord1[i]], ...; simp* null for unit counts): the
+    // replay kernels read them beside the positions instead of gathering them by position
+    const uint32_t* sgid1;
+    const float* simp1;
+    const uint32_t* sgid2;
+    const float* simp2;
     // batch-start state (read) and the image the rounds write
     const CafeMainBucket* main_in;
     CafeMainBucket* main_out;
@@ -255,18 +265,22 @@ struct CafeJob {
     uint8_t* mstate;         // [n1] CAFE_S_* of the main bucket's last replay
     uint8_t* mark2;          // [n2] 1 = the main pass of this round changed an input of this LRU bucket
     uint8_t* lstate;         // [n2] CAFE_S_* of the LRU bucket's last replay
-    const int32_t* tl_size_old;   // [2M] FIFO size before each op slot (previous round)
-    const int32_t* tl_rank_old;   // [2M] successful pops before each op slot
-    const uint32_t* pushbuf_old;  // pushes in slot order
-    int32_t* tl_size_new;
-    int32_t* tl_rank_new;
-    uint32_t* pushbuf_new;
+    // FIFO timeline believed by this round = the one the previous round produced, as a list of ops
+    // (candidate pops and pushes) in op-slot order; the resolve step rewrites it in place
+    int32_t* tl_slot;        // [2M] op slot (2p or 2p+1) of every op, ascending
+    int32_t* tl_info;        // [2M] 0 = candidate pop, > 0 = push of this hot row
+    int32_t* tl_size;        // [2M] FIFO size before the op
+    int32_t* tl_rank;        // [2M] successful pops before the op
+    int32_t* tl_grp;         // [M / CAFE_TL_GROUP + 2] first op at or after position begin + CAFE_TL_GROUP * g
+    int32_t* tl_head;        // [4] number of ops, FIFO size and successful pops after the last op, pushes
+    uint32_t* pushbuf;       // [M] pushed rows in op order
+    int32_t* tl_blk;         // [2 * blocks] scratch: ops and main-table misses per block of CAFE_TL_BLOCK positions
+    CafeFn* tl_agg;          // [blocks of CAFE_TL_BLOCK ops] scratch: composed transfer function per block
+    int32_t* nmiss;          // [M] at commit: main-table misses up to and including each position
     // per-lookup results, kept between rounds
     uint8_t* mflag;      // [M] CAFE_F_* written by the main pass
     uint8_t* lflag;      // [M] CAFE_F_* written by the LRU pass for lookups that missed the main table
     int32_t* ins_res;    // [M] result of the event of this position when its target replayed it: 0 ok, -1 failed, >0 failed and pushed this row
-    // scratch
-    CafeFn* op_fn;       // [M] FIFO-size transfer function of the position, then its inclusive scan
     // outputs
     int32_t* mask;       // [M] 1 = this lookup was handed a hot row (the reference's insert result)
     int32_t* post_row;   // [M] hot row of the id at the end of its segment (0 = not hot in the main table)
@@ -279,15 +293,31 @@ CAFE_HD uint32_t cafe_eff_flag(const CafeJob& J, int p) {
     return (m & CAFE_F_MISS) ? ((uint32_t)J.lflag[p] | CAFE_F_MISS) : m;
 }
 
+// Believed FIFO size and number of successful pops before op slot `slot`: those before the first op of
+// the previous round's list at or after the slot (no op lies in between), or the list's end values.
+CAFE_HD void cafe_fifo_before(const CafeJob& J, int64_t slot, int32_t* size, int32_t* rank) {
+    if (J.first_round) { *size = J.q_size; *rank = 0; return; }
+    const int32_t n = J.tl_head[0];
+    const int32_t g = (int32_t)(((slot >> 1) - J.begin) / CAFE_TL_GROUP);
+    int32_t j = J.tl_grp[g];
+    const int32_t hi = J.tl_grp[g + 1];
+    while (j < hi && (int64_t)J.tl_slot[j] < slot) ++j;
+    if (j < n) { *size = J.tl_size[j]; *rank = J.tl_rank[j]; }
+    else { *size = J.tl_head[1]; *rank = J.tl_head[2]; }
+}
+CAFE_HD bool cafe_fifo_nonempty(const CafeJob& J, int64_t slot) {
+    int32_t size, rank;
+    cafe_fifo_before(J, slot, &size, &rank);
+    return size > 0;
+}
 // Belief about a pop at op slot `slot`: would the FIFO be non-empty, and which row is at its front.
 CAFE_HD bool cafe_would_pop(const CafeJob& J, int64_t slot, int32_t* id) {
     int32_t size, rank;
-    if (J.first_round) { size = J.q_size; rank = 0; }
-    else { size = J.tl_size_old[slot]; rank = J.tl_rank_old[slot]; }
+    cafe_fifo_before(J, slot, &size, &rank);
     *id = 0;
     if (size <= 0) return false;
     if (rank < J.q_size) *id = (int32_t)J.ring[(J.q_head + (uint32_t)rank) & J.ring_mask];
-    else if (rank - J.q_size < J.M) *id = (int32_t)J.pushbuf_old[rank - J.q_size];
+    else if (rank - J.q_size < J.M) *id = (int32_t)J.pushbuf[rank - J.q_size];
     else { CAFE_ATOMIC_OR(&J.res->error, 4); return false; }
     return true;
 }
@@ -332,8 +362,9 @@ struct CafeMainReplay {
     int cand_p[CAFE_CAND];
     uint32_t cand_x[CAFE_CAND];
 
-    // returns false if the bucket does not need to be replayed this round
-    CAFE_HD bool init(const CafeJob& J, int k_, int i_start) {
+    // returns false if the bucket does not need to be replayed this round; `pre` = the bucket's batch-start
+    // image if the caller has loaded it already
+    CAFE_HD bool init(const CafeJob& J, int k_, int i_start, const CafeMainBucket* pre = nullptr) {
         k = k_;
         cond_now = false;
         if (!J.first_round) {
@@ -348,7 +379,7 @@ struct CafeMainReplay {
                                              : (J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0);
             if (!active) return false;
         }
-        b = J.main_in[k];
+        b = pre ? *pre : J.main_in[k];
         evhead = J.first_round ? -1 : J.head[k];
         p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
         touched = cand = dirty = false;
@@ -482,7 +513,7 @@ struct CafeLruReplay {
     int k, n_ev;
     bool touched, cand, cond_now;
 
-    CAFE_HD bool init(const CafeJob& J, int k_) {
+    CAFE_HD bool init(const CafeJob& J, int k_, const CafeLruBucket* pre = nullptr) {
         k = k_;
         cond_now = false;
         if (!J.first_round) {
@@ -491,7 +522,7 @@ struct CafeLruReplay {
             const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
             if (!(J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0)) return false;
         }
-        b = J.lru_in[k];
+        b = pre ? *pre : J.lru_in[k];
         n_ev = 0;
         touched = cand = false;
         return true;
@@ -611,7 +642,7 @@ CAFE_HD void cafe_lru_tconvert(const CafeJob& J, int k) {
     CafeLruBucket& b = J.lru_out[k];
 #pragma unroll
     for (int q = 0; q < CAFE_SLOTS; ++q)
-        if (b.t[q] > J.t0) b.t[q] = J.t0 + J.op_fn[b.t[q] - J.t0 - 1].nmiss;   // misses up to and including that position
+        if (b.t[q] > J.t0) b.t[q] = J.t0 + J.nmiss[b.t[q] - J.t0 - 1];   // misses up to and including that position
 }
 // at commit: the reference's per-lookup insert result
 CAFE_HD void cafe_finalize_position(const CafeJob& J, int p) {
@@ -621,7 +652,9 @@ CAFE_HD void cafe_finalize_position(const CafeJob& J, int p) {
 // ---- round step 3: the FIFO timeline ---------------------------------------------------------------
 // Each position owns two op slots (2p, 2p+1).  An op is a candidate pop or a push; the FIFO size
 // evolves as s -> max(s + a, b) per op (pop: a=-1,b=0; push: a=+1,b=-inf), a family closed under
-// composition, so sizes come from one scan; ranks of successful pops and of pushes from a second.
+// composition, so sizes come from one scan; the number of successful pops before an op follows from
+// size = q_size + pushes - pops.  Few positions carry an op, so the ops are first compacted into a
+// list (count per block of positions, then emit at the block's offset) and only the list is scanned.
 #define CAFE_NEG_INF (-(1 << 29))
 struct CafeOps { int op0, op1; int32_t id0, id1; };   // op: 0 none, 1 pop, 2 push
 
@@ -640,11 +673,7 @@ CAFE_HD CafeOps cafe_ops_of(const CafeJob& J, int p) {
     }
     return o;
 }
-CAFE_HD void cafe_op_fn(int op, int32_t* a, int32_t* b) {
-    if (op == 1) { *a = -1; *b = 0; }
-    else if (op == 2) { *a = 1; *b = CAFE_NEG_INF; }
-    else { *a = 0; *b = CAFE_NEG_INF; }
-}
+CAFE_HD int cafe_ops_count(const CafeOps& o) { return (o.op0 != 0) + (o.op1 != 0); }
 // (a2,b2) after (a1,b1)
 CAFE_HD void cafe_compose(int32_t a1, int32_t b1, int32_t a2, int32_t b2, int32_t* a, int32_t* b) {
     int32_t bb = b1 + a2;
@@ -652,60 +681,64 @@ CAFE_HD void cafe_compose(int32_t a1, int32_t b1, int32_t a2, int32_t b2, int32_
     *a = a1 + a2;
     *b = bb > b2 ? bb : b2;
 }
+CAFE_HD CafeFn cafe_fn_identity() { CafeFn f; f.a = 0; f.b = CAFE_NEG_INF; f.np = 0; f.pad = 0; return f; }
+CAFE_HD CafeFn cafe_fn_then(const CafeFn& f, const CafeFn& g) {   // g after f
+    CafeFn r;
+    cafe_compose(f.a, f.b, g.a, g.b, &r.a, &r.b);
+    r.np = f.np + g.np;
+    r.pad = 0;
+    return r;
+}
 CAFE_HD int32_t cafe_apply_fn(int32_t a, int32_t b, int32_t s) { int32_t v = s + a; return v > b ? v : b; }
-
-// 3a: transfer function of position p
-CAFE_HD CafeFn cafe_resolve_fn(const CafeJob& J, int p) {
-    CafeOps o = cafe_ops_of(J, p);
-    int32_t a0, b0, a1, b1;
+// transfer function of one list entry
+CAFE_HD CafeFn cafe_fn_of_info(int32_t info) {
     CafeFn f;
-    cafe_op_fn(o.op0, &a0, &b0);
-    cafe_op_fn(o.op1, &a1, &b1);
-    cafe_compose(a0, b0, a1, b1, &f.a, &f.b);
-    f.np = (o.op0 == 2) + (o.op1 == 2);
-    f.nmiss = (J.mflag[p] & CAFE_F_MISS) ? 1 : 0;
+    if (info == 0) { f.a = -1; f.b = 0; f.np = 0; }
+    else { f.a = 1; f.b = CAFE_NEG_INF; f.np = 1; }
+    f.pad = 0;
     return f;
 }
-CAFE_HD void cafe_resolve_ops(const CafeJob& J, int p) { J.op_fn[p] = cafe_resolve_fn(J, p); }
-// 3b (after the inclusive scan of the transfer functions): write the timeline, compare with the consumed
-// one.  Successful pops so far follow from sizes and pushes: size = q_size + pushes - pops.
-CAFE_HD void cafe_resolve_write(const CafeJob& J, int p) {
-    CafeOps o = cafe_ops_of(J, p);
-    int32_t s = J.q_size, npush = 0;
-    if (p != J.begin) { const CafeFn pf = J.op_fn[p - 1]; s = cafe_apply_fn(pf.a, pf.b, J.q_size); npush = pf.np; }
-    int32_t rank = J.q_size + npush - s;
-    const int32_t rank_before = rank, push_before = npush;
-    int32_t sz[2], rk[2];
-    sz[0] = s; rk[0] = rank;
+// 3a: ops of position p go to list entries j, j+1, ...; the list is updated in place, and an entry that
+// differs from what the previous round left there means the timeline this round consumed has changed
+// (the first round consumed none: its change test is in cafe_tl_finish_op)
+CAFE_HD void cafe_tl_emit(const CafeJob& J, int p, const CafeOps& o, int32_t j, int32_t n_old) {
     bool diff = false;
-    if (o.op0 == 1) { if (s > 0) { ++rank; --s; } }
-    else if (o.op0 == 2) {
-        if (!J.first_round && J.pushbuf_old[npush] != (uint32_t)o.id0) diff = true;
-        J.pushbuf_new[npush++] = (uint32_t)o.id0; ++s;
+    if (o.op0 != 0) {
+        const int32_t slot = 2 * p, info = o.op0 == 2 ? o.id0 : 0;
+        if (!J.first_round && (j >= n_old || J.tl_slot[j] != slot || J.tl_info[j] != info)) diff = true;
+        J.tl_slot[j] = slot; J.tl_info[j] = info;
+        ++j;
     }
-    sz[1] = s; rk[1] = rank;
-    if (o.op1 == 2) {
-        if (!J.first_round && J.pushbuf_old[npush] != (uint32_t)o.id1) diff = true;
-        J.pushbuf_new[npush++] = (uint32_t)o.id1;
+    if (o.op1 != 0) {
+        const int32_t slot = 2 * p + 1, info = o.op1 == 2 ? o.id1 : 0;
+        if (!J.first_round && (j >= n_old || J.tl_slot[j] != slot || J.tl_info[j] != info)) diff = true;
+        J.tl_slot[j] = slot; J.tl_info[j] = info;
     }
-    if (J.first_round) {
-        diff = diff || sz[0] != J.q_size || sz[1] != J.q_size || rk[0] != 0 || rk[1] != 0 || o.op0 == 2 || o.op1 == 2;
-    } else {
-        diff = diff || J.tl_size_old[2 * (int64_t)p] != sz[0] || J.tl_size_old[2 * (int64_t)p + 1] != sz[1] ||
-               J.tl_rank_old[2 * (int64_t)p] != rk[0] || J.tl_rank_old[2 * (int64_t)p + 1] != rk[1];
-    }
-    J.tl_size_new[2 * (int64_t)p] = sz[0];
-    J.tl_size_new[2 * (int64_t)p + 1] = sz[1];
-    J.tl_rank_new[2 * (int64_t)p] = rk[0];
-    J.tl_rank_new[2 * (int64_t)p + 1] = rk[1];
     if (diff) { J.res->changed = 1; J.res->tl_changed = 1; }
-    if (p == J.limit - 1) {
-        // totals: prefix up to p plus p's own outcomes
-        int32_t my_pops = 0, my_push = 0, s2 = sz[0];
-        if (o.op0 == 1) { if (s2 > 0) { ++my_pops; --s2; } } else if (o.op0 == 2) { ++my_push; ++s2; }
-        if (o.op1 == 1) { if (s2 > 0) { ++my_pops; } } else if (o.op1 == 2) { ++my_push; }
-        J.res->n_pop_ok = rank_before + my_pops;
-        J.res->n_push = push_before + my_push;
+}
+// after the last position: the list's length (a different length is a change too)
+CAFE_HD void cafe_tl_set_count(const CafeJob& J, int32_t n_new, int32_t n_old) {
+    if (!J.first_round && n_new != n_old) { J.res->changed = 1; J.res->tl_changed = 1; }
+    J.tl_head[0] = n_new;
+    if (n_new == 0) { J.tl_head[1] = J.q_size; J.tl_head[2] = 0; J.tl_head[3] = 0; J.res->n_pop_ok = 0; J.res->n_push = 0; }
+}
+// 3b: list entry j of n, given the composition `before` of all entries ahead of it
+CAFE_HD void cafe_tl_finish_op(const CafeJob& J, int32_t j, int32_t n, const CafeFn& before) {
+    const int32_t info = J.tl_info[j];
+    const int32_t s = cafe_apply_fn(before.a, before.b, J.q_size);
+    const int32_t rank = J.q_size + before.np - s;
+    J.tl_size[j] = s;
+    J.tl_rank[j] = rank;
+    if (info != 0) J.pushbuf[before.np] = (uint32_t)info;
+    // the first round believed an untouched FIFO everywhere: a push or a successful pop contradicts that
+    if (J.first_round && (info != 0 || s > 0)) { J.res->changed = 1; J.res->tl_changed = 1; }
+    if (j == n - 1) {
+        const CafeFn after = cafe_fn_then(before, cafe_fn_of_info(info));
+        const int32_t s_end = cafe_apply_fn(after.a, after.b, J.q_size);
+        const int32_t pops = J.q_size + after.np - s_end;
+        J.tl_head[1] = s_end; J.tl_head[2] = pops; J.tl_head[3] = after.np;
+        J.res->n_pop_ok = pops;
+        J.res->n_push = after.np;
     }
 }
 

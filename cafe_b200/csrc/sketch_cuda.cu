@@ -15,6 +15,7 @@
 
 #include "../../include/cafe_b200.h"
 #include "cafe_internal.h"
+#include "radix_sort.cuh"
 #include "sketch_engine.h"
 
 #define CAFE_TPB 256
@@ -78,14 +79,6 @@ __global__ void k_post_query(const CafeMainBucket* __restrict__ mb, int n1, cons
     out[i] = r;
 }
 
-__global__ void k_hash_keys(const uint32_t* __restrict__ gid, int M, int nb, uint32_t* __restrict__ key,
-                            int32_t* __restrict__ pos) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= M) return;
-    key[i] = (uint32_t)cafe_hash(gid[i], nb);
-    pos[i] = i;
-}
-
 // start[k] = first sorted index whose key is >= k, for k in [0, nb]
 __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb, int32_t* __restrict__ start) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -93,6 +86,15 @@ __global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb
     const int lo = (i == 0) ? 0 : (int)skey[i - 1] + 1;
     const int hi = (i == M) ? nb : (int)skey[i];
     for (int k = lo; k <= hi; ++k) start[k] = i;
+}
+
+// counts in bucket order, so that the replay kernels stream them beside the sorted positions and ids
+__global__ void k_gather_counts(const float* __restrict__ imp, const int32_t* __restrict__ ord1, const int32_t* __restrict__ ord2,
+                                int M, float* __restrict__ simp1, float* __restrict__ simp2) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= M) return;
+    simp1[i] = imp[ord1[i]];
+    simp2[i] = imp[ord2[i]];
 }
 
 // Buckets with at most CAFE_LONG lookups are replayed by their own thread.  Longer ones (the ids at
@@ -172,7 +174,7 @@ __device__ __forceinline__ int cafe_warp_exclusive(int n, int lane, int* total) 
 
 // PART 0: one listed bucket, owned by lane 0 and fed by the whole warp; PART 1: a thread per bucket.
 template <int PART>
-__device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, float (*s_c)[CAFE_STAGE_MAIN],
+__device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& H, const int k, float (*s_c)[CAFE_STAGE_MAIN],
                                                int (*s_p)[CAFE_STAGE_MAIN], uint32_t (*s_x)[CAFE_STAGE_MAIN],
                                                uint32_t (*s_kf)[CAFE_STAGE_MAIN]) {
     const int lane = threadIdx.x & 31;
@@ -180,7 +182,19 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
     CafeMainReplay R;
     int i = 0, iend = 0;
     bool live = k < J.n1;
-    if (live) {
+    if (PART == 1) {
+        // everything the thread needs to start is requested at once: whether its bucket is on the long-bucket
+        // list, the range of its lookups and, in a round that replays every bucket, the bucket itself
+        CafeMainBucket pre;
+        int listed = 0, e1 = 0;
+        if (live) {
+            listed = H.flag[k]; i = J.beg1[k]; e1 = J.start1[k + 1];
+            if (J.all_active) pre = J.main_in[k];
+        }
+        live = live && !listed;
+        if (live) live = R.init(J, k, i, J.all_active ? &pre : nullptr);
+        if (live) iend = e1;
+    } else if (live) {
         i = J.beg1[k];
         live = R.init(J, k, i);
         if (live) iend = J.start1[k + 1];
@@ -204,11 +218,10 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
                 uint32_t x = 0, kf = CAFE_EV_NONE;
                 float c = 1.0f;
                 if (e < t0 + tn) {
-                    p = J.ord1[iL + (e - pL)];
-                    if (p < J.limit) {
-                        x = J.gid[p]; c = cafe_count_of(J, p);
-                        kf = cafe_old_kind(J, p) | (cafe_old_mflag(J, p) << 8);
-                    }
+                    const int idx = iL + (e - pL);   // position, id and count come from the same sorted index
+                    p = J.ord1[idx]; x = J.sgid1[idx];
+                    if (J.simp1) c = J.simp1[idx];
+                    if (!J.first_round && p < J.limit) kf = cafe_old_kind(J, p) | (cafe_old_mflag(J, p) << 8);
                 }
                 s_p[wib][r * 32 + lane] = p; s_x[wib][r * 32 + lane] = x; s_c[wib][r * 32 + lane] = c; s_kf[wib][r * 32 + lane] = kf;
             }
@@ -238,11 +251,8 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
         int p_n2 = (s + 32 + lane < e) ? J.ord1[s + 32 + lane] : INT32_MAX;
         uint32_t x_nx = 0, ok_nx = CAFE_EV_NONE, of_nx = 0;
         float c_nx = 1.0f;
-        bool av_nx = false;
-        if (p_nx < J.limit) {
-            x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx);
-            av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
-        }
+        if (s + lane < e) { x_nx = J.sgid1[s + lane]; if (J.simp1) c_nx = J.simp1[s + lane]; }
+        if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
         bool last_calm = false;   // the previous chunk went through the calm whole-chunk path
         for (int base = s; base < e && !stop; base += 32) {
             if (last_calm && e - base >= 128) {
@@ -269,9 +279,9 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     cx[q] = 0; cok[q] = CAFE_EV_NONE; cof[q] = 0; cc[q] = 1.0f;
-                    if (cp[q] < J.limit) {
-                        cx[q] = J.gid[cp[q]]; cc[q] = cafe_count_of(J, cp[q]); cok[q] = cafe_old_kind(J, cp[q]); cof[q] = cafe_old_mflag(J, cp[q]);
-                    }
+                    const int i0 = gb + 32 * q + lane;
+                    if (i0 < e) { cx[q] = J.sgid1[i0]; if (J.simp1) cc[q] = J.simp1[i0]; }
+                    if (cp[q] < J.limit) { cok[q] = cafe_old_kind(J, cp[q]); cof[q] = cafe_old_mflag(J, cp[q]); }
                 }
                 for (;;) {
                     bool good = true;
@@ -283,9 +293,9 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
                         const int i2 = gb + 256 + 32 * q + lane;
                         n2p[q] = i2 < e ? J.ord1[i2] : INT32_MAX;
                         xx[q] = 0; xok[q] = CAFE_EV_NONE; xof[q] = 0; xc[q] = 1.0f;
-                        if (xp[q] < J.limit) {
-                            xx[q] = J.gid[xp[q]]; xc[q] = cafe_count_of(J, xp[q]); xok[q] = cafe_old_kind(J, xp[q]); xof[q] = cafe_old_mflag(J, xp[q]);
-                        }
+                        const int i1 = gb + 128 + 32 * q + lane;
+                        if (i1 < e) { xx[q] = J.sgid1[i1]; if (J.simp1) xc[q] = J.simp1[i1]; }
+                        if (xp[q] < J.limit) { xok[q] = cafe_old_kind(J, xp[q]); xof[q] = cafe_old_mflag(J, xp[q]); }
                     }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) s_c[wib][32 * q + lane] = cc[q];
@@ -326,8 +336,6 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
                     if (base >= e) break;
                     // hand the loaded lookups back to the chunk pipeline
                     p_nx = cp[0]; x_nx = cx[0]; c_nx = cc[0]; ok_nx = cok[0]; of_nx = cof[0];
-                    av_nx = false;
-                    if (p_nx < J.limit) av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
                     p_n2 = cp[1];
                 }
             }
@@ -335,14 +343,11 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
             const int p = p_nx;
             const uint32_t x = x_nx, ok = ok_nx, of = of_nx;
             const float c = c_nx;
-            const bool av = av_nx;
             p_nx = p_n2;
             p_n2 = (base + 64 + lane < e) ? J.ord1[base + 64 + lane] : INT32_MAX;
-            x_nx = 0; ok_nx = CAFE_EV_NONE; of_nx = 0; c_nx = 1.0f; av_nx = false;
-            if (p_nx < J.limit) {
-                x_nx = J.gid[p_nx]; c_nx = cafe_count_of(J, p_nx); ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx);
-                av_nx = J.first_round ? (J.q_size > 0) : (J.tl_size_old[2 * (int64_t)p_nx] > 0);
-            }
+            x_nx = 0; ok_nx = CAFE_EV_NONE; of_nx = 0; c_nx = 1.0f;
+            if (base + 32 + lane < e) { x_nx = J.sgid1[base + 32 + lane]; if (J.simp1) c_nx = J.simp1[base + 32 + lane]; }
+            if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
             const int n = min(32, e - base);
             // Whole chunk = 32 more lookups of the id the previous step dealt with, whose slot owns a hot
             // row: add the 32 counts in order, write 32 flags, nothing else can happen.
@@ -460,7 +465,9 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const int k, fl
                     const bool in_run = lane >= j && lane < j + run;
                     const bool has_row = ms >= 0 && ((rowmask >> ms) & 1) != 0;
                     const bool cd = !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
-                    const unsigned blocked = __ballot_sync(CAFE_FULL, in_run && cd && av);   // ... that could succeed
+                    // ... that could succeed: the FIFO is believed non-empty at its op slot (looked up only for candidates)
+                    const bool av = in_run && cd && cafe_fifo_nonempty(J, 2 * (int64_t)p);
+                    const unsigned blocked = __ballot_sync(CAFE_FULL, av);
                     const int done = blocked ? (__ffs(blocked) - 1 - j) : run;
                     if (done > 0) {
                         const bool in_done = lane >= j && lane < j + done;
@@ -515,45 +522,54 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
     __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
-        cafe_main_body<1>(J, (k < J.n1 && !H.flag[k]) ? k : J.n1, s_c, s_p, s_x, s_kf);
+        cafe_main_body<1>(J, H, k < J.n1 ? k : J.n1, s_c, s_p, s_x, s_kf);
     } else {
         for (;;) {
             const int k = cafe_next_listed(H, &J.res->list_cursor[J.final_pass ? 2 : 0], J.n1);
             if (k < 0) break;
-            cafe_main_body<0>(J, k, s_c, s_p, s_x, s_kf);
+            cafe_main_body<0>(J, H, k, s_c, s_p, s_x, s_kf);
         }
     }
 }
 template <int PART>
-__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
+__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k) {
     const int lane = threadIdx.x & 31;
     CafeLruReplay R;
     int jb = 0, jend = 0;
     bool live = k < J.n2;
-    if (live) {
+    if (PART == 1) {
+        // as in the main pass: list flag, range and (when every bucket replays) the bucket are requested together
+        CafeLruBucket pre;
+        int listed = 0, b1 = 0, e1 = 0;
+        if (live) {
+            listed = H.flag[k]; b1 = J.beg2[k]; e1 = J.start2[k + 1];
+            if (J.all_active) pre = J.lru_in[k];
+        }
+        live = live && !listed;
+        if (live) live = R.init(J, k, J.all_active ? &pre : nullptr);
+        if (live) { jb = b1; jend = e1; }
+    } else if (live) {
         live = R.init(J, k);
         if (live) { jb = J.beg2[k]; jend = J.start2[k + 1]; }
     }
     const bool is_long = PART == 0 && live;
     if (PART == 1 && live) {
         // Most entries of an LRU bucket are lookups that hit the main table.  Eight entries at a time:
-        // their positions, then their flags, are loaded together, so a thread waits for two load
-        // latencies per eight entries instead of two per entry.
+        // their positions, ids and counts (consecutive in the sorted order) are requested together, then the
+        // flags of those positions, so a thread waits for two load latencies per eight entries.
         bool done = false;
         for (int j = jb; j < jend && !done; j += 8) {
             int pq[8];
             uint32_t fq[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q) pq[q] = (j + q < jend) ? J.ord2[j + q] : INT32_MAX;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) fq[q] = (pq[q] < J.limit) ? (uint32_t)J.mflag[pq[q]] : 0u;
             uint32_t xq[8];
             float cq[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {   // ids and counts of the misses among them, again all at once
-                xq[q] = 0; cq[q] = 1.0f;
-                if (fq[q] & CAFE_F_MISS) { xq[q] = J.gid[pq[q]]; cq[q] = cafe_count_of(J, pq[q]); }
+            for (int q = 0; q < 8; ++q) {
+                pq[q] = INT32_MAX; xq[q] = 0; cq[q] = 1.0f;
+                if (j + q < jend) { pq[q] = J.ord2[j + q]; xq[q] = J.sgid2[j + q]; if (J.simp2) cq[q] = J.simp2[j + q]; }
             }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) fq[q] = (pq[q] < J.limit) ? (uint32_t)J.mflag[pq[q]] : 0u;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
                 if (done) break;
@@ -592,7 +608,7 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
 #pragma unroll
         for (int q = 0; q < GL; ++q) {
             x0[q] = 0; c0[q] = 1.0f;
-            if (f0[q] & CAFE_F_MISS) { x0[q] = J.gid[p0[q]]; c0[q] = cafe_count_of(J, p0[q]); }
+            if (f0[q] & CAFE_F_MISS) { x0[q] = J.sgid2[s + 32 * q + lane]; if (J.simp2) c0[q] = J.simp2[s + 32 * q + lane]; }
         }
         for (int base = s; base < e && !stop; base += 32 * GL) {
 #pragma unroll
@@ -601,7 +617,10 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const int k) {
                 p3[q] = i3 < e ? J.ord2[i3] : INT32_MAX;
                 f2[q] = p2[q] < J.limit ? (uint32_t)J.mflag[p2[q]] : 0u;
                 x1[q] = 0; c1[q] = 1.0f;
-                if (f1[q] & CAFE_F_MISS) { x1[q] = J.gid[p1[q]]; c1[q] = cafe_count_of(J, p1[q]); }
+                if (f1[q] & CAFE_F_MISS) {   // (p1 was read at this index of the sorted order)
+                    const int i1 = base + 32 * GL + 32 * q + lane;
+                    x1[q] = J.sgid2[i1]; if (J.simp2) c1[q] = J.simp2[i1];
+                }
             }
 #pragma unroll
             for (int q = 0; q < GL; ++q) {
@@ -633,12 +652,12 @@ template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
-        cafe_lru_body<1>(J, (k < J.n2 && !H.flag[k]) ? k : J.n2);
+        cafe_lru_body<1>(J, H, k < J.n2 ? k : J.n2);
     } else {
         for (;;) {
             const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2);
             if (k < 0) break;
-            cafe_lru_body<0>(J, k);
+            cafe_lru_body<0>(J, H, k);
         }
     }
 }
@@ -659,29 +678,198 @@ __global__ void k_commit_tables(const __grid_constant__ CafeJob J, int32_t* beg1
     }
     if (k < J.n1) beg1[k] = cafe_advance_cursor(J.ord1, beg1[k], J.start1[k + 1], J.limit);
 }
-// per-segment threshold crossings and the number of LRU visits: block-wide sums, one atomic per
-// block and counter (a block of consecutive positions lies in one segment except at boundaries)
-__global__ void __launch_bounds__(CAFE_TPB) k_resolve_write(const __grid_constant__ CafeJob J) {
-    __shared__ int s_cross, s_miss;
-    const int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
-    if (p < J.limit) cafe_resolve_write(J, p);
-    const int first = J.begin + blockIdx.x * blockDim.x;
-    const int last = min(first + (int)blockDim.x, J.limit) - 1;
-    if (threadIdx.x == 0) { s_cross = 0; s_miss = 0; }
-    __syncthreads();
-    int c = 0, mi = 0;
-    if (p < J.limit) cafe_position_counts(J, p, &c, &mi);
-    const int seg_first = cafe_segment_of(J, first), seg_last = cafe_segment_of(J, last);
-    const unsigned mc = __ballot_sync(CAFE_FULL, c != 0), mm = __ballot_sync(CAFE_FULL, mi != 0);
-    if ((threadIdx.x & 31) == 0) {
-        if (mm) atomicAdd(&s_miss, __popc(mm));
-        if (mc && seg_first == seg_last) atomicAdd(&s_cross, __popc(mc));
+// ---- FIFO timeline (round step 3), sparse -------------------------------------------------------
+// A block of CAFE_TL_THREADS threads handles CAFE_TL_BLOCK consecutive positions (resp. list entries),
+// CAFE_TL_PER consecutive ones per thread, so that a scan over threads is a scan in position order.
+#define CAFE_TL_THREADS 256
+#define CAFE_TL_PER (CAFE_TL_BLOCK / CAFE_TL_THREADS)
+
+// exclusive prefix of v over the block's threads (in thread order) and the block total
+__device__ __forceinline__ int cafe_block_exclusive_sum(int v, int* total, int* s_warp) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(CAFE_FULL, inc, d);
+        if (lane >= d) inc += t;
     }
-    if (seg_first != seg_last && c) atomicAdd(&J.res->seg_real_delta[cafe_segment_of(J, p)], c);
+    if (lane == 31) s_warp[w] = inc;
+    __syncthreads();
+    int before = 0, all = 0;
+#pragma unroll
+    for (int q = 0; q < CAFE_TL_THREADS / 32; ++q) { const int t = s_warp[q]; if (q < w) before += t; all += t; }
+    __syncthreads();
+    *total = all;
+    return before + inc - v;
+}
+// the same for the FIFO-size transfer functions (composition is associative but not commutative:
+// earlier entries are always the left operand)
+__device__ __forceinline__ CafeFn cafe_block_exclusive_fn(const CafeFn& v, CafeFn* total, CafeFn* s_warp) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    CafeFn inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        CafeFn t;
+        t.a = __shfl_up_sync(CAFE_FULL, inc.a, d); t.b = __shfl_up_sync(CAFE_FULL, inc.b, d);
+        t.np = __shfl_up_sync(CAFE_FULL, inc.np, d); t.pad = 0;
+        if (lane >= d) inc = cafe_fn_then(t, inc);
+    }
+    CafeFn exc;   // composition of the earlier lanes of this warp
+    exc.a = __shfl_up_sync(CAFE_FULL, inc.a, 1); exc.b = __shfl_up_sync(CAFE_FULL, inc.b, 1);
+    exc.np = __shfl_up_sync(CAFE_FULL, inc.np, 1); exc.pad = 0;
+    if (lane == 0) exc = cafe_fn_identity();
+    if (lane == 31) s_warp[w] = inc;
+    __syncthreads();
+    CafeFn before = cafe_fn_identity(), all = cafe_fn_identity();
+#pragma unroll
+    for (int q = 0; q < CAFE_TL_THREADS / 32; ++q) {
+        const CafeFn t = s_warp[q];
+        if (q < w) before = cafe_fn_then(before, t);
+        all = cafe_fn_then(all, t);
+    }
+    __syncthreads();
+    *total = all;
+    return cafe_fn_then(before, exc);
+}
+
+// 3a, first half: ops and main-table misses per block of positions; per-segment threshold crossings and the
+// number of LRU visits as block-wide sums, one atomic per block and counter (a block of consecutive
+// positions lies in one segment except at boundaries)
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_count(const __grid_constant__ CafeJob J) {
+    __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    __shared__ int s_cross;
+    const int first = J.begin + blockIdx.x * CAFE_TL_BLOCK;
+    const int last = min(first + CAFE_TL_BLOCK, J.limit) - 1;
+    if (blockIdx.x == 0 && threadIdx.x == 0) J.tl_blk[2 * gridDim.x] = J.tl_head[0];   // the old list's length, for k_tl_emit
+    if (threadIdx.x == 0) s_cross = 0;
+    __syncthreads();
+    const int seg_first = cafe_segment_of(J, first), seg_last = cafe_segment_of(J, last);
+    int ops = 0, miss = 0, cross = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        const int p = first + threadIdx.x * CAFE_TL_PER + i;
+        if (p >= J.limit) break;
+        ops += cafe_ops_count(cafe_ops_of(J, p));
+        int c, mi;
+        cafe_position_counts(J, p, &c, &mi);
+        miss += mi;
+        if (c) { if (seg_first == seg_last) ++cross; else atomicAdd(&J.res->seg_real_delta[cafe_segment_of(J, p)], 1); }
+    }
+    int tot_ops, tot_miss;
+    cafe_block_exclusive_sum(ops, &tot_ops, s_warp);
+    cafe_block_exclusive_sum(miss, &tot_miss, s_warp);
+    if (cross) atomicAdd(&s_cross, cross);
     __syncthreads();
     if (threadIdx.x == 0) {
+        J.tl_blk[2 * blockIdx.x] = tot_ops;
+        J.tl_blk[2 * blockIdx.x + 1] = tot_miss;
         if (s_cross) atomicAdd(&J.res->seg_real_delta[seg_first], s_cross);
-        if (s_miss) atomicAdd(&J.res->n_miss, s_miss);
+        if (tot_miss) atomicAdd(&J.res->n_miss, tot_miss);
+    }
+}
+// sum of the per-block counts (kind 0: ops, 1: misses) of the blocks ahead of this one
+__device__ __forceinline__ int cafe_tl_blocks_before(const CafeJob& J, int kind, int* s_warp) {
+    int v = 0;
+    for (int q = threadIdx.x; q < (int)blockIdx.x; q += CAFE_TL_THREADS) v += J.tl_blk[2 * q + kind];
+    int tot;
+    cafe_block_exclusive_sum(v, &tot, s_warp);
+    return tot;
+}
+// 3a, second half: the ops go to their places in the list (updated in place, compared with the old entries)
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_emit(const __grid_constant__ CafeJob J) {
+    __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    const int first = J.begin + blockIdx.x * CAFE_TL_BLOCK;
+    const int32_t n_old = J.tl_blk[2 * gridDim.x];
+    const int base = cafe_tl_blocks_before(J, 0, s_warp);
+    CafeOps o[CAFE_TL_PER];
+    int cnt = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        const int p = first + threadIdx.x * CAFE_TL_PER + i;
+        o[i].op0 = o[i].op1 = 0;
+        if (p < J.limit) { o[i] = cafe_ops_of(J, p); cnt += cafe_ops_count(o[i]); }
+    }
+    int tot;
+    int j = base + cafe_block_exclusive_sum(cnt, &tot, s_warp);
+    const int p0 = first + threadIdx.x * CAFE_TL_PER;
+    if (p0 < J.limit && (p0 - J.begin) % CAFE_TL_GROUP == 0) J.tl_grp[(p0 - J.begin) / CAFE_TL_GROUP] = j;
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        const int p = p0 + i;
+        if (p >= J.limit) break;
+        cafe_tl_emit(J, p, o[i], j, n_old);
+        j += cafe_ops_count(o[i]);
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+        J.tl_grp[(J.limit - J.begin + CAFE_TL_GROUP - 1) / CAFE_TL_GROUP] = base + tot;
+        cafe_tl_set_count(J, base + tot, n_old);
+    }
+}
+// 3b, first half: composed transfer function of every block of list entries
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_aggregate(const __grid_constant__ CafeJob J) {
+    __shared__ CafeFn s_warp[CAFE_TL_THREADS / 32];
+    const int32_t n = J.tl_head[0];
+    const int base = blockIdx.x * CAFE_TL_BLOCK;
+    if (base >= n) return;
+    CafeFn v = cafe_fn_identity();
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        const int j = base + threadIdx.x * CAFE_TL_PER + i;
+        if (j < n) v = cafe_fn_then(v, cafe_fn_of_info(J.tl_info[j]));
+    }
+    CafeFn tot;
+    cafe_block_exclusive_fn(v, &tot, s_warp);
+    if (threadIdx.x == 0) J.tl_agg[blockIdx.x] = tot;
+}
+// 3b, second half: FIFO size and successful pops before every list entry, the pushed rows in order, totals
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_finish(const __grid_constant__ CafeJob J) {
+    __shared__ CafeFn s_warp[CAFE_TL_THREADS / 32];
+    __shared__ CafeFn s_before;
+    const int32_t n = J.tl_head[0];
+    const int base = blockIdx.x * CAFE_TL_BLOCK;
+    if (base >= n) return;
+    if (threadIdx.x == 0) {
+        CafeFn f = cafe_fn_identity();
+        for (int q = 0; q < (int)blockIdx.x; ++q) f = cafe_fn_then(f, J.tl_agg[q]);
+        s_before = f;
+    }
+    __syncthreads();
+    const int j0 = base + threadIdx.x * CAFE_TL_PER;
+    CafeFn v = cafe_fn_identity();
+    int32_t info[CAFE_TL_PER];
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        info[i] = (j0 + i < n) ? J.tl_info[j0 + i] : 0;
+        if (j0 + i < n) v = cafe_fn_then(v, cafe_fn_of_info(info[i]));
+    }
+    CafeFn tot;
+    CafeFn before = cafe_fn_then(s_before, cafe_block_exclusive_fn(v, &tot, s_warp));
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        if (j0 + i >= n) break;
+        cafe_tl_finish_op(J, j0 + i, n, before);
+        before = cafe_fn_then(before, cafe_fn_of_info(info[i]));
+    }
+}
+// at commit: main-table misses up to and including every position of the job (the LRU clock numbering)
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_miss_prefix(const __grid_constant__ CafeJob J) {
+    __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    const int first = J.begin + blockIdx.x * CAFE_TL_BLOCK;
+    const int base = cafe_tl_blocks_before(J, 1, s_warp);
+    const int p0 = first + threadIdx.x * CAFE_TL_PER;
+    int m[CAFE_TL_PER], cnt = 0;
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        m[i] = (p0 + i < J.limit && (J.mflag[p0 + i] & CAFE_F_MISS)) ? 1 : 0;
+        cnt += m[i];
+    }
+    int tot;
+    int run = base + cafe_block_exclusive_sum(cnt, &tot, s_warp);
+#pragma unroll
+    for (int i = 0; i < CAFE_TL_PER; ++i) {
+        if (p0 + i >= J.limit) break;
+        run += m[i];
+        J.nmiss[p0 + i] = run;
     }
 }
 __global__ void k_commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
@@ -698,21 +886,6 @@ __global__ void k_seq_insert(CafeSeqState* Sd, const uint32_t* __restrict__ gid,
     for (int i = 0; i < n; ++i) mask[i] = cafe_seq_insert(S, gid[i], imp ? imp[i] : 1.0f);
     *Sd = S;
 }
-
-// input iterators of the two FIFO scans: values are computed from the per-lookup flags on the fly
-struct FnOfIndex {
-    CafeJob J;
-    __host__ __device__ __forceinline__ CafeFn operator()(const int& i) const { return cafe_resolve_fn(J, J.begin + i); }
-};
-struct FnCompose {
-    __host__ __device__ __forceinline__ CafeFn operator()(const CafeFn& f, const CafeFn& g) const {
-        CafeFn r;
-        cafe_compose(f.a, f.b, g.a, g.b, &r.a, &r.b);
-        r.np = f.np + g.np;
-        r.nmiss = f.nmiss + g.nmiss;
-        return r;
-    }
-};
 
 __global__ void k_advance_cursors(const int32_t* __restrict__ ord, const int32_t* __restrict__ start, int32_t* beg, int nb,
                                   int limit) {
@@ -807,10 +980,10 @@ struct CudaBackend {
     // lane 0 sorts on `stream`; lanes 1 and 2 on side streams with buffers of their own, forked from
     // and joined to `stream`
     static const int LANES = 3;
-    void* sort_tmp[LANES] = {nullptr, nullptr, nullptr};
-    size_t sort_bytes = 0;
-    uint32_t *key_in[LANES] = {nullptr, nullptr, nullptr}, *key_out[LANES] = {nullptr, nullptr, nullptr};
-    int32_t* pos_in[LANES] = {nullptr, nullptr, nullptr};
+    // per lane: scratch of the radix sort, intermediate pairs, sorted keys
+    int32_t* sort_scratch[LANES] = {nullptr, nullptr, nullptr};
+    uint32_t *key_tmp[LANES] = {nullptr, nullptr, nullptr}, *key_out[LANES] = {nullptr, nullptr, nullptr};
+    int32_t* pos_tmp[LANES] = {nullptr, nullptr, nullptr};
     cudaStream_t side[LANES] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_fork[LANES] = {nullptr, nullptr, nullptr}, ev_join[LANES] = {nullptr, nullptr, nullptr};
     bool side_pending[LANES] = {false, false, false};
@@ -831,10 +1004,10 @@ struct CudaBackend {
             if (side[i]) { cudaStreamSynchronize(side[i]); cudaStreamDestroy(side[i]); }
             if (ev_fork[i]) cudaEventDestroy(ev_fork[i]);
             if (ev_join[i]) cudaEventDestroy(ev_join[i]);
-            if (sort_tmp[i]) cudaFree(sort_tmp[i]);
-            if (key_in[i]) cudaFree(key_in[i]);
+            if (sort_scratch[i]) cudaFree(sort_scratch[i]);
+            if (key_tmp[i]) cudaFree(key_tmp[i]);
             if (key_out[i]) cudaFree(key_out[i]);
-            if (pos_in[i]) cudaFree(pos_in[i]);
+            if (pos_tmp[i]) cudaFree(pos_tmp[i]);
         }
         if (scan64) cudaFree(scan64);
         for (int i = 0; i < 2; ++i) { if (hot_list[i]) cudaFree(hot_list[i]); if (hot_count[i]) cudaFree(hot_count[i]); if (hot_flag[i]) cudaFree(hot_flag[i]); }
@@ -896,20 +1069,14 @@ struct CudaBackend {
     bool prepare(int cap_, int n1, int n2) {
         cap = cap_;
         for (int i = 0; i < LANES; ++i) {
-            check(cudaMalloc(&key_in[i], 4 * (size_t)cap));
+            check(cudaMalloc(&key_tmp[i], 4 * (size_t)cap));
             check(cudaMalloc(&key_out[i], 4 * (size_t)cap));
-            check(cudaMalloc(&pos_in[i], 4 * (size_t)cap));
+            check(cudaMalloc(&pos_tmp[i], 4 * (size_t)cap));
+            check(cudaMalloc(&sort_scratch[i], 4 * cafe_rs_scratch_elems(cap)));
             if (i == 0) continue;
             check(cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking));
             check(cudaEventCreateWithFlags(&ev_fork[i], cudaEventDisableTiming));
             check(cudaEventCreateWithFlags(&ev_join[i], cudaEventDisableTiming));
-        }
-        {
-            size_t sb = 0;
-            cub::DeviceRadixSort::SortPairs(nullptr, sb, (uint32_t*)nullptr, (uint32_t*)nullptr, (int32_t*)nullptr,
-                                            (int32_t*)nullptr, cap, 0, 32, stream);
-            sort_bytes = sb + 1024;
-            for (int i = 0; i < LANES; ++i) check(cudaMalloc(&sort_tmp[i], sort_bytes));
         }
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
@@ -930,8 +1097,6 @@ struct CudaBackend {
         need = b > need ? b : need;
         cub::DeviceScan::InclusiveSum(nullptr, b, (int32_t*)nullptr, (int32_t*)nullptr, nsort, stream);
         need = b > need ? b : need;
-        cub::DeviceScan::InclusiveScan(nullptr, b, (CafeFn*)nullptr, (CafeFn*)nullptr, FnCompose(), nsort, stream);
-        need = b > need ? b : need;
         cub_bytes = need * 2 + 1024;
         check(cudaMalloc(&cub_tmp, cub_bytes));
         return ok();
@@ -950,7 +1115,7 @@ struct CudaBackend {
     static int bits_for(int nb) { int b = 1; while ((1ll << b) < nb) ++b; return b; }
 
     // positions ordered by (bucket, position): stable LSD radix sort of the bucket index
-    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
+    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, uint32_t* sgid, int32_t* start, int32_t* beg, int lane) {
         cudaStream_t st = stream;
         if (lane != 0 && cafe_prof_serialise()) lane = -lane;   // the lane's buffers, the caller's stream
         if (lane > 0) {
@@ -962,11 +1127,11 @@ struct CudaBackend {
         lane = lane < 0 ? -lane : lane;
         {
         CAFE_PROF(CAFE_P_LOOKUP_SORT, st);
-        k_hash_keys<<<cafe_blocks(M), CAFE_TPB, 0, st>>>(gid, M, nb, key_in[lane], pos_in[lane]);
-        check_launch();
-        size_t b = sort_bytes;
-        check(cub::DeviceRadixSort::SortPairs(sort_tmp[lane], b, key_in[lane], key_out[lane], pos_in[lane], ord, M, 0,
-                                              bits_for(nb), st));
+        // the keys are the hashes of the ids (computed in the first pass); the last pass also writes the ids in sorted order
+        CafeKeySource src;
+        src.key = nullptr; src.gid = gid; src.nb = nb;
+        check(cafe_radix_sort(src, nullptr, key_tmp[lane], pos_tmp[lane], key_out[lane], ord, M, bits_for(nb), sort_scratch[lane],
+                              gid, sgid, st));
         k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start);
         check_launch();
         const int t = (nb == hot_nb[0]) ? 0 : 1;
@@ -982,6 +1147,11 @@ struct CudaBackend {
             check(cudaEventRecord(ev_join[lane], side[lane]));
             side_pending[lane] = true;
         }
+    }
+    void gather_counts(const float* imp, const int32_t* ord1, const int32_t* ord2, int M, float* simp1, float* simp2) {
+        CAFE_PROF(CAFE_P_LOOKUP_SORT, stream);
+        k_gather_counts<<<cafe_blocks(M), CAFE_TPB, 0, stream>>>(imp, ord1, ord2, M, simp1, simp2);
+        check_launch();
     }
     // makes `stream` wait for the sorts outstanding on the side lanes (no-op when there are none)
     void sort_join(int which) {
@@ -1030,6 +1200,7 @@ struct CudaBackend {
     void finalize(const CafeJob& J) {
         CAFE_PROF(CAFE_P_COMMIT, stream);
         const int cnt = J.limit - J.begin;
+        k_miss_prefix<<<cafe_blocks(cnt, CAFE_TL_BLOCK), CAFE_TL_THREADS, 0, stream>>>(J);
         k_finalize_positions<<<cafe_blocks(cnt), CAFE_TPB, 0, stream>>>(J);
         check_launch();
         k_commit_tables<<<cafe_blocks(J.n1 > J.n2 ? J.n1 : J.n2), CAFE_TPB, 0, stream>>>(J, const_cast<int32_t*>(J.beg1),
@@ -1048,12 +1219,13 @@ struct CudaBackend {
     void resolve(const CafeJob& J) {
         CAFE_PROF(CAFE_P_RESOLVE, stream);
         const int cnt = J.limit - J.begin;
-        const int g = cafe_blocks(cnt);
-        FnOfIndex f1; f1.J = J;
-        cub::TransformInputIterator<CafeFn, FnOfIndex, cub::CountingInputIterator<int>> in1(cub::CountingInputIterator<int>(0), f1);
-        size_t b = cub_bytes;
-        check(cub::DeviceScan::InclusiveScan(cub_tmp, b, in1, J.op_fn + J.begin, FnCompose(), cnt, stream));
-        k_resolve_write<<<g, CAFE_TPB, 0, stream>>>(J);
+        const int g = cafe_blocks(cnt, CAFE_TL_BLOCK);
+        k_tl_count<<<g, CAFE_TL_THREADS, 0, stream>>>(J);
+        k_tl_emit<<<g, CAFE_TL_THREADS, 0, stream>>>(J);
+        // the list has at most two entries per position; blocks beyond its real length return at once
+        const int go = cafe_blocks(2 * (int64_t)cnt, CAFE_TL_BLOCK);
+        k_tl_aggregate<<<go, CAFE_TL_THREADS, 0, stream>>>(J);
+        k_tl_finish<<<go, CAFE_TL_THREADS, 0, stream>>>(J);
         check_launch();
     }
     void commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,

@@ -76,6 +76,8 @@ public:
         // workspace of the parallel insert
         size_t M = (size_t)cap;
         ord1 = (int32_t*)be.alloc(4 * M); ord2 = (int32_t*)be.alloc(4 * M);
+        sgid1 = (uint32_t*)be.alloc(4 * M); sgid2 = (uint32_t*)be.alloc(4 * M);
+        simp1 = (float*)be.alloc(4 * M); simp2 = (float*)be.alloc(4 * M);
         start1 = (int32_t*)be.alloc(4 * ((size_t)n1 + 1)); start2 = (int32_t*)be.alloc(4 * ((size_t)n2 + 1));
         beg1 = (int32_t*)be.alloc(4 * (size_t)n1); beg2 = (int32_t*)be.alloc(4 * (size_t)n2);
         ev = (CafeEvent*)be.alloc(sizeof(CafeEvent) * M);
@@ -91,13 +93,15 @@ public:
         mstate = (uint8_t*)be.alloc((size_t)n1);
         lstate = (uint8_t*)be.alloc((size_t)n2);
         mflag = (uint8_t*)be.alloc(M); lflag = (uint8_t*)be.alloc(M);
-        for (int i = 0; i < 2; ++i) {
-            tl_size[i] = (int32_t*)be.alloc(8 * M);
-            tl_rank[i] = (int32_t*)be.alloc(8 * M);
-            pushbuf[i] = (uint32_t*)be.alloc(4 * M);
-        }
+        tl_slot = (int32_t*)be.alloc(8 * M); tl_info = (int32_t*)be.alloc(8 * M);
+        tl_size = (int32_t*)be.alloc(8 * M); tl_rank = (int32_t*)be.alloc(8 * M);
+        tl_grp = (int32_t*)be.alloc(4 * (M / CAFE_TL_GROUP + 2));
+        tl_head = (int32_t*)be.alloc(4 * 4);
+        pushbuf = (uint32_t*)be.alloc(4 * M);
+        tl_blk = (int32_t*)be.alloc(4 * 2 * (M / CAFE_TL_BLOCK + 2));
+        tl_agg = (CafeFn*)be.alloc(sizeof(CafeFn) * (2 * M / CAFE_TL_BLOCK + 2));
+        nmiss = (int32_t*)be.alloc(4 * M);
         ins_res = (int32_t*)be.alloc(4 * M);
-        op_fn = (CafeFn*)be.alloc(sizeof(CafeFn) * M);
         seq_dev = (CafeSeqState*)be.alloc(sizeof(CafeSeqState));
         size_t ncand = (size_t)(n1 + n2) * CAFE_SLOTS;
         cand_key[0] = (uint32_t*)be.alloc(4 * ncand); cand_key[1] = (uint32_t*)be.alloc(4 * ncand);
@@ -105,11 +109,11 @@ public:
         cand_cnt = (int32_t*)be.alloc(4 * ((size_t)n1 + n2 + 1));
         reset_out = (int32_t*)be.alloc(4 * 8);
         if (!be.prepare(cap, n1, n2)) return CAFE_ERR_CUDA;
-        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !ins_res || !op_fn ||
+        if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !ins_res ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
-        for (int i = 0; i < 2; ++i)
-            if (!tl_size[i] || !tl_rank[i] || !pushbuf[i]) return CAFE_ERR_CUDA;
+        if (!sgid1 || !sgid2 || !simp1 || !simp2) return CAFE_ERR_CUDA;
+        if (!tl_slot || !tl_info || !tl_size || !tl_rank || !tl_grp || !tl_head || !pushbuf || !tl_blk || !tl_agg || !nmiss) return CAFE_ERR_CUDA;
         ready = true;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
     }
@@ -136,8 +140,8 @@ public:
         presorted_gid = nullptr;
         if (ready) be.sort_join(-1);   // a null gid withdraws an earlier presort
         if (!ready || !gid || n <= 0 || n > cap) return;
-        be.sort_lookups(gid, n, n1, ord1, start1, beg1, 1);
-        be.sort_lookups(gid, n, n2, ord2, start2, beg2, 2);
+        be.sort_lookups(gid, n, n1, ord1, sgid1, start1, beg1, 1);
+        be.sort_lookups(gid, n, n2, ord2, sgid2, start2, beg2, 2);
         presorted_gid = gid; presorted_n = n;
     }
 
@@ -175,10 +179,15 @@ public:
                 be.sort_join(-1);   // a head start for other arrays may still be writing the orders
                 // the LRU table's order is first needed by the first LRU pass: it is built on a side
                 // lane of the backend while the main table's order and first pass proceed
-                be.sort_lookups(g, mtot, n2, ord2, start2, beg2, 2);
-                be.sort_lookups(g, mtot, n1, ord1, start1, beg1, 0);
+                be.sort_lookups(g, mtot, n2, ord2, sgid2, start2, beg2, 2);
+                be.sort_lookups(g, mtot, n1, ord1, sgid1, start1, beg1, 0);
             }
             presorted_gid = nullptr;
+            if (parallel && mtot > 0 && im) {   // counts in the two bucket orders, beside the sorted positions and ids
+                if (gate_seg >= 0) { be.wait_gate(); gate_seg = -1; }   // every count must exist before it is permuted
+                be.sort_join(-1);
+                be.gather_counts(im, ord1, ord2, mtot, simp1, simp2);
+            }
             while (s < se) {
                 // counts of the calls from gate_seg on become valid only when the caller's gate opens
                 if (gate_seg >= 0 && s >= gate_seg) { be.wait_gate(); gate_seg = -1; }
@@ -309,15 +318,17 @@ private:
     CafeLruBucket* lrub[2] = {nullptr, nullptr};
     uint32_t* ring = nullptr;
     int32_t *ord1 = nullptr, *ord2 = nullptr, *start1 = nullptr, *start2 = nullptr, *beg1 = nullptr, *beg2 = nullptr;
+    uint32_t *sgid1 = nullptr, *sgid2 = nullptr;   // ids in the order of ord1 / ord2
+    float *simp1 = nullptr, *simp2 = nullptr;      // counts in the order of ord1 / ord2
     CafeEvent* ev = nullptr;
     int32_t* head = nullptr;
     int32_t* nxt = nullptr;
     uint8_t *mark_own = nullptr, *mstate = nullptr, *mark2 = nullptr, *lstate = nullptr, *mflag = nullptr, *lflag = nullptr;
-    int32_t* tl_size[2] = {nullptr, nullptr};
-    int32_t* tl_rank[2] = {nullptr, nullptr};
-    uint32_t* pushbuf[2] = {nullptr, nullptr};
+    int32_t *tl_slot = nullptr, *tl_info = nullptr, *tl_size = nullptr, *tl_rank = nullptr, *tl_grp = nullptr, *tl_head = nullptr;
+    int32_t *tl_blk = nullptr, *nmiss = nullptr;
+    uint32_t* pushbuf = nullptr;
+    CafeFn* tl_agg = nullptr;
     int32_t* ins_res = nullptr;
-    CafeFn* op_fn = nullptr;
     CafeRoundResult* res_dev = nullptr;
     size_t off_mark2 = 0, off_res = 0, span_clear = 0;
     CafeSeqState* seq_dev = nullptr;
@@ -328,8 +339,8 @@ private:
 
     void release() {
         if (!ready && !mainb[0]) return;
-        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mflag, lflag, tl_size[0], tl_size[1], tl_rank[0], tl_rank[1], pushbuf[0], pushbuf[1],
-                        ins_res, op_fn, seq_dev, cand_key[0], cand_key[1],
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, sgid1, sgid2, simp1, simp2, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mflag, lflag, tl_slot, tl_info, tl_size, tl_rank, tl_grp, tl_head, pushbuf, tl_blk, tl_agg, nmiss,
+                        ins_res, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
         mainb[0] = mainb[1] = nullptr; lrub[0] = lrub[1] = nullptr;
@@ -378,12 +389,15 @@ private:
         for (int i = 0; i <= nseg; ++i) J.seg_off[i] = seg[i];
         for (int i = nseg + 1; i <= CAFE_MAX_SEGMENTS; ++i) J.seg_off[i] = INT32_MAX;
         J.ord1 = ord1; J.start1 = start1; J.beg1 = beg1; J.ord2 = ord2; J.start2 = start2; J.beg2 = beg2;
+        J.sgid1 = sgid1; J.sgid2 = sgid2; J.simp1 = imp ? simp1 : nullptr; J.simp2 = imp ? simp2 : nullptr;
         J.n1 = n1; J.n2 = n2; J.thr = thr; J.gflip = gflip; J.t0 = t;
         J.ring = ring; J.ring_mask = ring_mask; J.q_head = q_head; J.q_size = q_size;
         J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
         J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
         J.ev = ev; J.head = head; J.nxt = nxt; J.mark_own = mark_own; J.mstate = mstate; J.mark2 = mark2; J.lstate = lstate;
-        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res; J.op_fn = op_fn;
+        J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res;
+        J.tl_slot = tl_slot; J.tl_info = tl_info; J.tl_size = tl_size; J.tl_rank = tl_rank; J.tl_grp = tl_grp; J.tl_head = tl_head;
+        J.pushbuf = pushbuf; J.tl_blk = tl_blk; J.tl_agg = tl_agg; J.nmiss = nmiss;
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
@@ -402,7 +416,6 @@ private:
         CafeRoundResult R;
         int rounds = 0;
         bool truncated = false, shortened = false, tl_changed_prev = true;
-        int pb = 0;   // index of the FIFO timeline consumed this round
         bool first = true;
         for (;;) {
             if (rounds >= round_cap) {
@@ -419,8 +432,6 @@ private:
             J.cand_active = (first || tl_changed_prev) ? 1 : 0;
             J.final_pass = 0;
             shortened = false;
-            J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
-            J.tl_size_new = tl_size[pb ^ 1]; J.tl_rank_new = tl_rank[pb ^ 1]; J.pushbuf_new = pushbuf[pb ^ 1];
             if (!first) {   // (the first round's mark2 + round result were cleared with the job's arrays)
                 be.fills(head, 0xff, 4 * (size_t)n1, mark_own, 0, span_clear);   // mark_own + mark2 + round result
                 be.route(J);
@@ -435,7 +446,6 @@ private:
             ++rounds; ++stats.rounds;
             first = false;
             tl_changed_prev = R.tl_changed != 0;
-            pb ^= 1;
             if (R.error) return last_status = CAFE_ERR_CAPACITY;
             // A threshold re-fit is due at the first inner boundary where real_n exceeds 1.2*lim.  The
             // per-segment deltas of a round that has not converged yet are estimates, but shrinking
@@ -462,9 +472,8 @@ private:
             if (R.changed) continue;
             break;
         }
-        // converged: the timeline just produced (index pb) equals the one consumed
+        // converged: the timeline just produced equals the one consumed
         J.first_round = 0; J.all_active = 0; J.cand_active = 1;
-        J.tl_size_old = tl_size[pb]; J.tl_rank_old = tl_rank[pb]; J.pushbuf_old = pushbuf[pb];
         if (post_row) {
             be.fills(post_row + J.begin, 0, 4 * (size_t)(J.limit - J.begin), head, 0xff, 4 * (size_t)n1, mark_own, 0, (size_t)n1);
             be.route(J);
@@ -474,7 +483,7 @@ private:
         }
         be.finalize(J);   // per-lookup results, LRU clock values, cursors of the sorted order
         cursors_advanced = true;
-        if (R.n_push > 0) be.commit_queue(ring, ring_mask, q_head, q_size, R.n_pop_ok, pushbuf[pb], R.n_push);
+        if (R.n_push > 0) be.commit_queue(ring, ring_mask, q_head, q_size, R.n_pop_ok, pushbuf, R.n_push);
         cur ^= 1;
         q_head += (uint32_t)R.n_pop_ok;
         q_size += R.n_push - R.n_pop_ok;

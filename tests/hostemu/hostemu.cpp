@@ -50,10 +50,14 @@ struct HostBackend {
     }
     void sort_join(int) {}
     void wait_gate() {}
-    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start, int32_t* beg, int lane) {
+    void sort_lookups(const uint32_t* gid, int M, int nb, int32_t* ord, uint32_t* sgid, int32_t* start, int32_t* beg, int lane) {
         (void)lane;
         sort_lookups_impl(gid, M, nb, ord, start);
+        for (int i = 0; i < M; ++i) sgid[i] = gid[ord[i]];
         memcpy(beg, start, 4 * (size_t)nb);
+    }
+    void gather_counts(const float* imp, const int32_t* ord1, const int32_t* ord2, int M, float* simp1, float* simp2) {
+        for (int i = 0; i < M; ++i) { simp1[i] = imp[ord1[i]]; simp2[i] = imp[ord2[i]]; }
     }
     void sort_lookups_impl(const uint32_t* gid, int M, int nb, int32_t* ord, int32_t* start) {
         std::vector<int32_t> key((size_t)M);
@@ -76,7 +80,12 @@ struct HostBackend {
     }
     // per-lookup results and the LRU clock numbering, once the rounds have converged
     void finalize(const CafeJob& J) {
-        for (int p = J.begin; p < J.limit; ++p) cafe_finalize_position(J, p);
+        int32_t misses = 0;
+        for (int p = J.begin; p < J.limit; ++p) {
+            cafe_finalize_position(J, p);
+            misses += (J.mflag[p] & CAFE_F_MISS) ? 1 : 0;
+            J.nmiss[p] = misses;
+        }
         for (int k = 0; k < J.n2; ++k) cafe_lru_tconvert(J, k);
         advance_cursors(J.ord1, J.start1, const_cast<int32_t*>(J.beg1), J.n1, J.limit);
         advance_cursors(J.ord2, J.start2, const_cast<int32_t*>(J.beg2), J.n2, J.limit);
@@ -86,15 +95,22 @@ struct HostBackend {
         else for (int k = 0; k < J.n2; ++k) cafe_lru_pass_bucket(J, k);
     }
     void resolve(const CafeJob& J) {
-        for (int p = J.begin; p < J.limit; ++p) cafe_resolve_ops(J, p);
-        for (int p = J.begin + 1; p < J.limit; ++p) {
-            CafeFn r;
-            cafe_compose(J.op_fn[p - 1].a, J.op_fn[p - 1].b, J.op_fn[p].a, J.op_fn[p].b, &r.a, &r.b);
-            r.np = J.op_fn[p - 1].np + J.op_fn[p].np;
-            r.nmiss = J.op_fn[p - 1].nmiss + J.op_fn[p].nmiss;
-            J.op_fn[p] = r;
+        // list the ops in slot order, updating the previous round's list in place
+        const int32_t n_old = J.tl_head[0];
+        int32_t j = 0;
+        for (int p = J.begin; p < J.limit; ++p) {
+            if ((p - J.begin) % CAFE_TL_GROUP == 0) J.tl_grp[(p - J.begin) / CAFE_TL_GROUP] = j;
+            const CafeOps o = cafe_ops_of(J, p);
+            cafe_tl_emit(J, p, o, j, n_old);
+            j += cafe_ops_count(o);
         }
-        for (int p = J.limit - 1; p >= J.begin; --p) cafe_resolve_write(J, p);
+        J.tl_grp[(J.limit - J.begin + CAFE_TL_GROUP - 1) / CAFE_TL_GROUP] = j;
+        cafe_tl_set_count(J, j, n_old);
+        CafeFn before = cafe_fn_identity();
+        for (int32_t i = 0; i < j; ++i) {
+            cafe_tl_finish_op(J, i, j, before);
+            before = cafe_fn_then(before, cafe_fn_of_info(J.tl_info[i]));
+        }
         for (int p = J.begin; p < J.limit; ++p) {
             int c, m;
             cafe_position_counts(J, p, &c, &m);

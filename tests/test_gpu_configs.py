@@ -1,6 +1,8 @@
 """Fused training steps at the shapes and batch sizes of the named configurations: Kaggle-shaped 26 fields / dim 16 /
 batch 128, the Avazu-shaped large-hot-table regime (compress 0.1, hash-rate 0.7, 9 sketch fields, batch 4096) and
-the Terabyte-shaped one (dim 128, batch 2048).  Same bars as tests/test_gpu_embed.py."""
+the Terabyte-shaped one (dim 128, batch 2048).  Bars as in tests/test_gpu_embed.py, with an absolute floor of 1e-6 on
+table rows and pooled rows: at these batch sizes a hot id's row sums hundreds of gradient rows, in a different order
+on the two sides, and elements whose sum nearly cancels cannot meet a purely relative bound."""
 import numpy as np
 import pytest
 
@@ -23,16 +25,16 @@ def run_steps(cards, D, cr, hr, B, steps, s_zipf):
         ids = S.batch_ids(cards, B, s_zipf, 7, s)
         out = grp(torch.from_numpy(ids))
         ref = orc.forward(ids)
-        np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=1e-5, atol=1e-7)
+        np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=1e-5, atol=1e-6)
         grad = S.gradients(B, F, D, 7, s)
         g = torch.from_numpy(grad).cuda()
         imp = grp._fields.importance(g, D, F * D, B).view(F, B).cpu().numpy()
         out.backward(g)
         orc.backward(ids, grad, grp.lr, importance=imp)
         assert states_equal(sk.state(), grp.sketch.state()) == [], f"step {s}"
-        np.testing.assert_allclose(grp.weight_high.detach().cpu().numpy(), orc.wh, rtol=1e-5, atol=1e-7)
+        np.testing.assert_allclose(grp.weight_high.detach().cpu().numpy(), orc.wh, rtol=1e-5, atol=1e-6)
     for f in range(F):
-        np.testing.assert_allclose(grp.weight_hash[f].detach().cpu().numpy(), orc.wc[f], rtol=1e-5, atol=1e-7)
+        np.testing.assert_allclose(grp.weight_hash[f].detach().cpu().numpy(), orc.wc[f], rtol=1e-5, atol=1e-6)
     return grp.sketch.stats()
 
 

@@ -14,7 +14,7 @@ from oracle.module_oracle import ModuleOracle
 pytestmark = pytest.mark.gpu
 
 
-def fused_steps(cards, D, cr, hr, B, steps, ids_of_step, seed=11):
+def fused_steps(cards, D, cr, hr, B, steps, ids_of_step, seed=11, atol=1e-6):
     import torch
     import cafe_b200
     grp = cafe_b200.SKEmbeddingGroup(cards, D, cr, hr, 1, 1, 1.0000005, device="cuda", max_batch=B, lr=0.1, seed=seed)
@@ -27,7 +27,7 @@ def fused_steps(cards, D, cr, hr, B, steps, ids_of_step, seed=11):
         ids = ids_of_step(s)
         out = grp(torch.from_numpy(ids))
         ref = orc.forward(ids)
-        np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=1e-5, atol=1e-6, err_msg=f"step {s}: pooled rows")
+        np.testing.assert_allclose(out.detach().cpu().numpy(), ref, rtol=1e-5, atol=atol, err_msg=f"step {s}: pooled rows")
         rows = grp.last_rows.cpu().numpy()
         for f in range(F):
             hot, rh, rc = orc.rows[f]
@@ -40,9 +40,9 @@ def fused_steps(cards, D, cr, hr, B, steps, ids_of_step, seed=11):
         del out, g
         orc.backward(ids, grad, grp.lr, importance=imp)
         assert states_equal(sk.state(), grp.sketch.state()) == [], f"step {s}: sketch state"
-        np.testing.assert_allclose(grp.weight_high.detach().cpu().numpy(), orc.wh, rtol=1e-5, atol=1e-6, err_msg=f"step {s}: hot table")
+        np.testing.assert_allclose(grp.weight_high.detach().cpu().numpy(), orc.wh, rtol=1e-5, atol=atol, err_msg=f"step {s}: hot table")
     for f in range(F):
-        np.testing.assert_allclose(grp.weight_hash[f].detach().cpu().numpy(), orc.wc[f], rtol=1e-5, atol=1e-6,
+        np.testing.assert_allclose(grp.weight_hash[f].detach().cpu().numpy(), orc.wc[f], rtol=1e-5, atol=atol,
                                    err_msg=f"hash table {f}")
     return grp.sketch.stats()
 
@@ -96,8 +96,13 @@ def test_sharding_configuration_sketch_regime():
 
 
 def test_sharding_configuration_fused_steps():
-    """configs[3] un-sharded (all 26 Terabyte fields on one GPU), global batch 65536, dim 128: two fused steps."""
+    """configs[3] un-sharded (all 26 Terabyte fields on one GPU), global batch 65536, dim 128: two fused steps.
+
+    The tables are tiny here (at most 800 hash rows per field, 13 733 hot rows), so one row sums the gradient rows
+    of up to several thousand lookups of a 65536-id call.  Each side adds them in fp32 in its own order; with partial
+    sums near 1 and K of a few thousand, sqrt(K) * 2^-24 * |partial sum| per side is several 1e-6, hence the absolute
+    floor of 2e-5 beside the 1e-5 relative bound."""
     from cafe_b200 import synthetic as S
     cards = S.TERABYTE_CARDS
-    st = fused_steps(cards, 128, 0.0001, 0.2, 65536, 2, lambda s: S.drift_batch_ids(cards, 65536, 2024, 1000 * s))
+    st = fused_steps(cards, 128, 0.0001, 0.2, 65536, 2, lambda s: S.drift_batch_ids(cards, 65536, 2024, 1000 * s), atol=2e-5)
     assert st["seq_fallbacks"] == 0
