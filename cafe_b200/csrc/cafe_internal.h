@@ -11,7 +11,7 @@
 
 struct CafeSketchView {
     const CafeMainBucket* main;
-    int n1, lim, cap;
+    int n1, n2, lim, cap;
 };
 
 // Device buffers of the embedding path, sized once per handle for `cap` lookups.
@@ -27,6 +27,9 @@ struct CafeEmbedWorkspace {
     float* partial = nullptr;    // [2 * ceil(cap/CAFE_CHUNK) * CAFE_MAX_DIM] partial row sums of chunk-spanning rows
     int32_t* row_winner = nullptr;   // [hotn] migration: highest position that claims a hot row in this call (-1 between calls)
     uint32_t* key_tmp = nullptr;     // [cap] intermediate keys of the row sort
+    uint32_t* bucket_key[2] = {nullptr, nullptr};   // [cap] main / LRU bucket of every lookup, left by cafe_embed_resolve ...
+    const uint32_t* keys_of = nullptr;              // ... for the lookups whose global ids are in this array
+    int keys_total = 0;
     int32_t* sort_scratch = nullptr; // radix-sort histograms
     cudaStream_t side = nullptr;     // runs the scatter's key sort beside the sketch insert
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -46,7 +49,8 @@ CafeEmbedWorkspace* cafe_internal_ws(void* h);
 int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const int* seg_off, int nseg, int32_t* mask,
                          int32_t* post_row, int mode, cudaStream_t stream);
 // starts the insert's bucket sorts of `gid` beside whatever the caller queues next on `stream`
-void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t stream);
+// (key1 / key2: the lookups' main / LRU bucket numbers if the caller has them, else null)
+void cafe_internal_presort(void* h, const uint32_t* gid, int n, const uint32_t* key1, const uint32_t* key2, cudaStream_t stream);
 // counts of segments >= seg of the next cafe_internal_insert are valid once `ev` has fired (null: no gate)
 void cafe_internal_set_gate(void* h, int seg, cudaEvent_t ev);
 void cafe_internal_set_error(const char* msg);

@@ -98,6 +98,70 @@ k_embed_forward(const __grid_constant__ CafeFields F, const IdT* __restrict__ id
     }
 }
 
+// The forward in two kernels, for training: k_embed_resolve does the sketch probe only (global id, row code,
+// and the two bucket numbers the insert will sort by), k_embed_gather copies the rows named by the codes.
+// Between the two the caller can start the backward's sorts, which need nothing but the first kernel's
+// outputs, so that they run beside the gather instead of after it.
+template <typename IdT>
+__global__ void __launch_bounds__(256)
+k_embed_resolve(const __grid_constant__ CafeFields F, const IdT* __restrict__ ids, const CafeMainBucket* __restrict__ mb,
+                int n1, int n2, uint32_t* __restrict__ gid_out, int32_t* __restrict__ row_out, uint32_t* __restrict__ key1_out,
+                uint32_t* __restrict__ key2_out, int total) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= total) return;
+    const int f = p / F.B;
+    const uint32_t x = (uint32_t)((int64_t)ids[p] + (int64_t)F.f_offset[f]);
+    const int32_t k1 = cafe_hash(x, n1);
+    const CafeMainBucket* bk = &mb[k1];
+    const uint4 v = *reinterpret_cast<const uint4*>(bk->val);
+    const int4 d = *reinterpret_cast<const int4*>(bk->dic);
+    int32_t r = 0;
+    if (v.w == x && d.w != 0) r = d.w;
+    if (v.z == x && d.z != 0) r = d.z;
+    if (v.y == x && d.y != 0) r = d.y;
+    if (v.x == x && d.x != 0) r = d.x;
+    gid_out[p] = x;
+    row_out[p] = r ? -r : (int32_t)(x % (uint32_t)F.hash_size[f]);
+    if (key1_out) { key1_out[p] = (uint32_t)k1; key2_out[p] = (uint32_t)cafe_hash(x, n2); }
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+k_embed_gather(const __grid_constant__ CafeFields F, const int32_t* __restrict__ row, const CafeRankBuffers out,
+               int64_t field_stride, int64_t sample_stride, int total) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t p = warp * 32 + lane;
+    const float* src = nullptr;
+    float* dst = nullptr;
+    if (p < total) {
+        const int f = (int)(p / F.B);
+        const int b = (int)(p - (int64_t)f * F.B);
+        const int32_t code = row[p];
+        src = code < 0 ? F.w_high + (size_t)((-code) % F.hotn) * F.D : F.w_hash[f] + (size_t)code * F.D;
+        const int dr = b / out.rows_per_rank;   // rank that consumes this sample
+        dst = out.base[dr] + f * field_stride + (b - dr * out.rows_per_rank) * sample_stride;
+    }
+    constexpr int RPI = 32 / G;   // rows moved per warp iteration
+    constexpr int U = 4;
+    const int sub = lane / G, c = (lane % G) * 4;
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += RPI * U) {
+        float4 val[U];
+        float* d_[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int j = j0 + u * RPI + sub;
+            const float* s = shfl_ptr(src, j);
+            d_[u] = shfl_ptr(dst, j);
+            if (s) val[u] = ld_row(s + c);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (d_[u]) st_stream(d_[u] + c, val[u]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // importance (sk_embedding_bag.py:178-189): per-lookup L2 norm of its gradient row, scaled by
 // N / (sum of the field's norms).
@@ -448,6 +512,7 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     A((void**)&ws->row_winner, 4 * (size_t)(hotn > 0 ? hotn : 1));
     if (e == cudaSuccess) e = cudaMemset(ws->row_winner, 0xff, 4 * (size_t)(hotn > 0 ? hotn : 1));   // -1: unclaimed
     A((void**)&ws->key_tmp, 4 * M);
+    A((void**)&ws->bucket_key[0], 4 * M); A((void**)&ws->bucket_key[1], 4 * M);
     A((void**)&ws->sort_scratch, 4 * cafe_rs_scratch_elems(cap));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
@@ -460,7 +525,7 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
 
 void cafe_embed_ws_free(CafeEmbedWorkspace* ws) {
     void* ptrs[] = {ws->norm, ws->imp, ws->totals, ws->mask, ws->post_row, ws->key[0], ws->key[1], ws->pos[0], ws->pos[1],
-                    ws->partial, ws->key_tmp, ws->sort_scratch, ws->row_winner};
+                    ws->partial, ws->key_tmp, ws->sort_scratch, ws->row_winner, ws->bucket_key[0], ws->bucket_key[1]};
     for (void* p : ptrs) if (p) cudaFree(p);
     if (ws->side) { cudaStreamSynchronize(ws->side); cudaStreamDestroy(ws->side); }
     if (ws->ev_fork) cudaEventDestroy(ws->ev_fork);
@@ -556,6 +621,80 @@ int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfie
     return launch_forward(F, ids_dev, ids_are_int64, V, ob, out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total, D, st);
 }
 
+
+int cafe_embed_resolve(void* h, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
+                       const int32_t* hash_size, int hotn, uint32_t* gid_out_dev, int32_t* row_out_dev, void* stream) {
+    if (!h || nfields < 1 || nfields > CAFE_MAX_SEGMENTS || B < 0 || !f_offset || !hash_size) return CAFE_ERR_ARG;
+    const int64_t total64 = (int64_t)nfields * B;
+    if (total64 > 0x7fffffffLL) return CAFE_ERR_CAPACITY;
+    if (total64 == 0) return CAFE_OK;
+    if (!ids_dev || !gid_out_dev || !row_out_dev) return CAFE_ERR_ARG;
+    CafeFields F;
+    memset(&F, 0, sizeof(F));
+    F.nfields = nfields; F.B = B; F.hotn = hotn;
+    for (int f = 0; f < nfields; ++f) {
+        if (hash_size[f] < 1) return CAFE_ERR_ARG;
+        F.f_offset[f] = (uint32_t)f_offset[f]; F.hash_size[f] = hash_size[f];
+    }
+    CafeSketchView V = cafe_internal_view(h);
+    if (hotn != V.lim) return CAFE_ERR_ARG;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    const int total = (int)total64;
+    // the bucket numbers are kept for the insert's sorts when the lookups fit the workspace
+    const bool keep = total <= ws->cap;
+    uint32_t* k1 = keep ? ws->bucket_key[0] : nullptr;
+    uint32_t* k2 = keep ? ws->bucket_key[1] : nullptr;
+    ws->keys_of = keep ? gid_out_dev : nullptr;
+    ws->keys_total = keep ? total : 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    CAFE_PROF(CAFE_P_QUERY, st);
+    const int blocks = (total + 255) / 256;
+    if (ids_are_int64) k_embed_resolve<int64_t><<<blocks, 256, 0, st>>>(F, (const int64_t*)ids_dev, V.main, V.n1, V.n2, gid_out_dev, row_out_dev, k1, k2, total);
+    else k_embed_resolve<int32_t><<<blocks, 256, 0, st>>>(F, (const int32_t*)ids_dev, V.main, V.n1, V.n2, gid_out_dev, row_out_dev, k1, k2, total);
+    return fail_cuda("cafe_embed_resolve");
+}
+
+static int gather_impl(void* h, const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                       float* weight_high, int hotn, int D, const CafeRankBuffers& ob, int64_t out_field_stride,
+                       int64_t out_sample_stride, cudaStream_t st) {
+    CafeFields F;
+    int64_t zero_off[CAFE_MAX_SEGMENTS] = {0};
+    int rc = fill_fields(&F, nfields, B, D, hotn, zero_off, hash_size, weight_hash, weight_high);
+    if (rc != CAFE_OK) return rc;
+    const int total = nfields * B;
+    if (total == 0) return CAFE_OK;
+    if (!h || !row_dev || out_field_stride % 4 || out_sample_stride % 4) return CAFE_ERR_ARG;
+    const int warps = (total + 31) / 32;
+    const int blocks = (warps + 7) / 8;
+    CAFE_PROF(CAFE_P_FORWARD, st);
+    DISPATCH_G(D, (k_embed_gather<G><<<blocks, 256, 0, st>>>(F, row_dev, ob, out_field_stride, out_sample_stride, total)));
+    return fail_cuda("cafe_embed_gather");
+}
+
+int cafe_embed_gather(void* h, const int32_t* row_dev, int nfields, int B, const int32_t* hash_size, float* const* weight_hash,
+                      float* weight_high, int hotn, int D, float* out_dev, int64_t out_field_stride, int64_t out_sample_stride,
+                      void* stream) {
+    if (nfields * (int64_t)B > 0 && (!out_dev || !aligned16(out_dev))) return CAFE_ERR_ARG;
+    CafeRankBuffers ob;
+    memset(&ob, 0, sizeof(ob));
+    ob.base[0] = out_dev;
+    ob.rows_per_rank = B > 0 ? B : 1;
+    return gather_impl(h, row_dev, nfields, B, hash_size, weight_hash, weight_high, hotn, D, ob, out_field_stride, out_sample_stride,
+                       (cudaStream_t)stream);
+}
+
+int cafe_embed_gather_sharded(void* h, const int32_t* row_dev, int nfields, int B, const int32_t* hash_size,
+                              float* const* weight_hash, float* weight_high, int hotn, int D, float* const* out_rank, int nranks,
+                              int rows_per_rank, int64_t out_field_stride, int64_t out_sample_stride, void* stream) {
+    if (!out_rank || nranks < 1 || nranks > CAFE_MAX_RANKS || rows_per_rank < 1) return CAFE_ERR_ARG;
+    if ((int64_t)rows_per_rank * nranks != B) return CAFE_ERR_ARG;
+    CafeRankBuffers ob;
+    memset(&ob, 0, sizeof(ob));
+    for (int r = 0; r < nranks; ++r) { if (!out_rank[r] || !aligned16(out_rank[r])) return CAFE_ERR_ARG; ob.base[r] = out_rank[r]; }
+    ob.rows_per_rank = rows_per_rank;
+    return gather_impl(h, row_dev, nfields, B, hash_size, weight_hash, weight_high, hotn, D, ob, out_field_stride, out_sample_stride,
+                       (cudaStream_t)stream);
+}
 
 int cafe_grad_importance(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields, int B,
                          int D, float* imp_out_dev, void* stream) {
@@ -746,7 +885,11 @@ static int backward_side_work(void* h, CafeEmbedWorkspace* ws, const CafeFields&
     if (begun) return CAFE_OK;
     int rc = scatter_prepare_aside(ws, FS, row_dev, total, hotn, st);
     if (rc != CAFE_OK) return rc;
-    if (insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, gid_dev, total, st);
+    if (insert_mode != CAFE_INSERT_SEQUENTIAL) {
+        // bucket numbers left by cafe_embed_resolve for exactly these lookups save the sorts their hashing
+        const bool have = ws->keys_of == gid_dev && ws->keys_total == total;
+        cafe_internal_presort(h, gid_dev, total, have ? ws->bucket_key[0] : nullptr, have ? ws->bucket_key[1] : nullptr, st);
+    }
     return CAFE_OK;
 }
 static int scatter_join(CafeEmbedWorkspace* ws, cudaStream_t st) {
@@ -810,7 +953,7 @@ static int embed_backward_impl(void* h, const float* grad_dev, int64_t field_str
         if (rc == CAFE_OK) cafe_internal_set_gate(h, gate_field, ws->ev_late);
     }
     if (rc != CAFE_OK) {
-        cafe_internal_presort(h, nullptr, 0, st);   // withdraws the sorts started above
+        cafe_internal_presort(h, nullptr, 0, nullptr, nullptr, st);   // withdraws the sorts started above
         scatter_join(ws, st);
         return rc;
     }

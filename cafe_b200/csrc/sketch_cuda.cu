@@ -984,6 +984,7 @@ struct CudaBackend {
     int32_t* sort_scratch[LANES] = {nullptr, nullptr, nullptr};
     uint32_t *key_tmp[LANES] = {nullptr, nullptr, nullptr}, *key_out[LANES] = {nullptr, nullptr, nullptr};
     int32_t* pos_tmp[LANES] = {nullptr, nullptr, nullptr};
+    const uint32_t* given_key[LANES] = {nullptr, nullptr, nullptr};   // bucket numbers the caller already has (else hashed here)
     cudaStream_t side[LANES] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_fork[LANES] = {nullptr, nullptr, nullptr}, ev_join[LANES] = {nullptr, nullptr, nullptr};
     bool side_pending[LANES] = {false, false, false};
@@ -1129,7 +1130,7 @@ struct CudaBackend {
         CAFE_PROF(CAFE_P_LOOKUP_SORT, st);
         // the keys are the hashes of the ids (computed in the first pass); the last pass also writes the ids in sorted order
         CafeKeySource src;
-        src.key = nullptr; src.gid = gid; src.nb = nb;
+        src.key = given_key[lane]; src.gid = gid; src.nb = nb;
         check(cafe_radix_sort(src, nullptr, key_tmp[lane], pos_tmp[lane], key_out[lane], ord, M, bits_for(nb), sort_scratch[lane],
                               gid, sgid, st));
         k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start);
@@ -1300,7 +1301,7 @@ static int finish(CafeHandle* H, int rc, const char* where) {
 CafeSketchView cafe_internal_view(void* h) {
     CafeHandle* H = (CafeHandle*)h;
     CafeSketchView v;
-    v.main = H->eng.main_table(); v.n1 = H->eng.n1; v.lim = H->eng.lim; v.cap = H->eng.capacity();
+    v.main = H->eng.main_table(); v.n1 = H->eng.n1; v.n2 = H->eng.n2; v.lim = H->eng.lim; v.cap = H->eng.capacity();
     return v;
 }
 CafeEmbedWorkspace* cafe_internal_ws(void* h) { return &((CafeHandle*)h)->ws; }
@@ -1311,10 +1312,13 @@ int cafe_internal_insert(void* h, const uint32_t* gid, const float* imp, const i
     int rc = H->eng.insert_segments(gid, imp, seg_off, nseg, mask, post_row, mode != CAFE_INSERT_SEQUENTIAL);
     return finish(H, rc, "cafe_sketch_insert");
 }
-void cafe_internal_presort(void* h, const uint32_t* gid, int n, cudaStream_t stream) {
+void cafe_internal_presort(void* h, const uint32_t* gid, int n, const uint32_t* key1, const uint32_t* key2, cudaStream_t stream) {
     CafeHandle* H = (CafeHandle*)h;
     H->eng.be.stream = stream;
+    H->eng.be.given_key[1] = key1;   // consumed by the two sort_lookups calls of presort
+    H->eng.be.given_key[2] = key2;
     H->eng.presort(gid, n);
+    H->eng.be.given_key[1] = H->eng.be.given_key[2] = nullptr;
 }
 void cafe_internal_set_gate(void* h, int seg, cudaEvent_t ev) {
     CafeHandle* H = (CafeHandle*)h;

@@ -169,9 +169,20 @@ class _PeerFunction(torch.autograd.Function):
             f = grp._fields
             wp, hp = f.ptrs()
             out_rank = pb.ptr_array(pb.h_pooled, pb.block_off[plan.rank], 4)
-            _lib.check(lib.cafe_embed_forward_sharded(grp.sketch.handle, own.data_ptr(), 1, Fg, G * Bl, f.f_offset, f.hash_size,
-                                                      wp, hp, f.hotn, D, out_rank, G, Bl, D, Fg * D, gid.data_ptr(),
-                                                      row.data_ptr(), _stream()), "cafe_embed_forward_sharded")
+            if training:
+                # sketch probe, then the backward's sorts on the side streams, then the gather with the exchange as
+                # its epilogue: the sorts run beside the gather and the dense model
+                _lib.check(lib.cafe_embed_resolve(grp.sketch.handle, own.data_ptr(), 1, Fg, G * Bl, f.f_offset, f.hash_size,
+                                                  f.hotn, gid.data_ptr(), row.data_ptr(), _stream()), "cafe_embed_resolve")
+                f.backward_begin(gid, row, G * Bl, grp.insert_mode)
+                _lib.check(lib.cafe_embed_gather_sharded(grp.sketch.handle, row.data_ptr(), Fg, G * Bl, f.hash_size, wp, hp,
+                                                         f.hotn, D, out_rank, G, Bl, D, Fg * D, _stream()),
+                           "cafe_embed_gather_sharded")
+            else:
+                _lib.check(lib.cafe_embed_forward_sharded(grp.sketch.handle, own.data_ptr(), 1, Fg, G * Bl, f.f_offset,
+                                                          f.hash_size, wp, hp, f.hotn, D, out_rank, G, Bl, D, Fg * D,
+                                                          gid.data_ptr(), row.data_ptr(), _stream()),
+                           "cafe_embed_forward_sharded")
             pb.fence()                                   # every consumer's pooled buffer is complete
         ctx.model, ctx.saved, ctx.Bl = model, (own, gid, row), Bl
         model._pending_backward = training
@@ -189,8 +200,7 @@ class _PeerFunction(torch.autograd.Function):
         G, Fg, D, Bl = plan.G, grp.num_fields, grp.embedding_dim, ctx.Bl
         f = grp._fields
         with torch.no_grad(), torch.cuda.device(pb.grad.device):
-            g = blocked_grad.reshape(-1).contiguous()
-            f.backward_begin(gid, row, G * Bl, grp.insert_mode)   # sorts run beside the gradient exchange
+            g = blocked_grad.reshape(-1).contiguous()   # (the backward's sorts were started by the forward)
             half = (plan.F // G) // 2     # same on every rank: owners' fields 0..half-1 travel first
             if not model.pipeline_push or G == 1 or half < 1:
                 # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
@@ -232,7 +242,10 @@ class _ShardedFunction(torch.autograd.Function):
         flat = own_ids.reshape(-1)
         Fg, D = grp.num_fields, grp.embedding_dim
         pooled = torch.empty(plan.G * Bl, Fg, D, dtype=torch.float32, device=ids.device)
-        gid, row = grp._fields.forward(flat, pooled, D, Fg * D)
+        if ctx.needs_input_grad[0] and flat.numel() > 0:
+            gid, row = grp._fields.forward_training(flat, pooled, D, Fg * D, grp.insert_mode)   # starts the backward's sorts
+        else:
+            gid, row = grp._fields.forward(flat, pooled, D, Fg * D)
         ctx.model, ctx.saved, ctx.Bl = model, (flat, gid, row), Bl
         return plan.exchange_pooled(pooled, model.pg)
 
@@ -242,7 +255,6 @@ class _ShardedFunction(torch.autograd.Function):
         plan, grp = model.plan, model.group
         flat, gid, row = ctx.saved
         Fg, D = grp.num_fields, grp.embedding_dim
-        grp._fields.backward_begin(gid, row, plan.G * ctx.Bl, grp.insert_mode)   # sorts run beside the exchange
         g = plan.exchange_grads(blocked_grad.contiguous(), ctx.Bl, D, model.pg)
         with torch.no_grad():
             grp.last_status = grp._fields.backward(g, D, Fg * D, flat, gid, row, plan.G * ctx.Bl, grp.lr, grp.insert_mode)

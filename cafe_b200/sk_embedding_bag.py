@@ -78,6 +78,26 @@ class _FieldSet:
                                               row.data_ptr(), _stream()), "cafe_embed_forward")
         return gid, row
 
+    def forward_training(self, ids: torch.Tensor, out: torch.Tensor, field_stride: int, sample_stride: int, mode: int):
+        """forward() in two kernels with the backward's head start in between: the sketch probe first, then the
+        bucket sorts of the insert and the row sort of the scatter are started on the library's side streams, and
+        the row gather runs beside them.  Same results as forward()."""
+        lib, sk = self.sketch.lib, self.sketch
+        B = ids.numel() // self.nf
+        gid = torch.empty(ids.numel(), dtype=torch.int32, device=ids.device)
+        row = torch.empty(ids.numel(), dtype=torch.int32, device=ids.device)
+        wp, hp = self.ptrs()
+        with torch.cuda.device(ids.device):
+            _lib.check(lib.cafe_embed_resolve(sk.handle, ids.data_ptr(), int(ids.dtype == torch.int64), self.nf, B,
+                                              self.f_offset, self.hash_size, self.hotn, gid.data_ptr(), row.data_ptr(),
+                                              _stream()), "cafe_embed_resolve")
+            _lib.check(lib.cafe_embed_backward_begin(sk.handle, gid.data_ptr(), row.data_ptr(), self.nf, B, self.hash_size,
+                                                     wp, hp, self.hotn, self.dim, mode, _stream()), "cafe_embed_backward_begin")
+            _lib.check(lib.cafe_embed_gather(sk.handle, row.data_ptr(), self.nf, B, self.hash_size, wp, hp, self.hotn,
+                                             self.dim, out.data_ptr(), field_stride, sample_stride, _stream()),
+                       "cafe_embed_gather")
+        return gid, row
+
     def importance(self, grad: torch.Tensor, field_stride: int, sample_stride: int, B: int) -> torch.Tensor:
         imp = torch.empty(self.nf * B, dtype=torch.float32, device=grad.device)
         with torch.cuda.device(grad.device):
@@ -282,12 +302,15 @@ class _GroupFunction(torch.autograd.Function):
         F, B = ids.shape
         out = torch.empty(B, F, group.embedding_dim, dtype=torch.float32, device=ids.device)
         flat = ids.reshape(-1)
-        gid, row = group._fields.forward(flat, out, group.embedding_dim, F * group.embedding_dim)
+        if group.training and ctx.needs_input_grad[0] and flat.numel() > 0:
+            # the backward's sorts start right behind the sketch probe and overlap the gather and whatever runs
+            # before the backward
+            gid, row = group._fields.forward_training(flat, out, group.embedding_dim, F * group.embedding_dim, group.insert_mode)
+        else:
+            gid, row = group._fields.forward(flat, out, group.embedding_dim, F * group.embedding_dim)
         ctx.group = group
         ctx.saved = (flat, gid, row, B)
         group.last_rows = row.view(F, B)
-        if group.training and ctx.needs_input_grad[0] and flat.numel() > 0:
-            group._fields.backward_begin(gid, row, B, group.insert_mode)   # overlaps whatever runs before the backward
         return out
 
     @staticmethod

@@ -96,6 +96,17 @@ int cafe_embed_forward(void* handle, const void* ids_dev, int ids_are_int64, int
                        float* out_dev, int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
                        int32_t* row_out_dev, void* stream);
 
+/* cafe_embed_forward in two calls, for training.  cafe_embed_resolve is the query part alone
+ * (tricks/sk_embedding_bag.py:101-113: global ids and row codes; it also keeps each lookup's bucket numbers
+ * for the insert's sorts), cafe_embed_gather the two embedding_bag gathers and the where (:131-150) from the
+ * row codes.  Between the two a caller can issue cafe_embed_backward_begin, whose sorts then run beside the
+ * gather.  Results are identical to cafe_embed_forward. */
+int cafe_embed_resolve(void* handle, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
+                       const int32_t* hash_size, int hotn, uint32_t* gid_out_dev, int32_t* row_out_dev, void* stream);
+int cafe_embed_gather(void* handle, const int32_t* row_dev, int nfields, int B, const int32_t* hash_size,
+                      float* const* weight_hash, float* weight_high, int hotn, int D, float* out_dev,
+                      int64_t out_field_stride, int64_t out_sample_stride, void* stream);
+
 /* Replaces the importance arithmetic of insert_grad (tricks/sk_embedding_bag.py:178-189):
  * imp[p] = ||grad row p||_2 * B / sum over the field of the norms. */
 int cafe_grad_importance(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride, int nfields,
@@ -163,6 +174,11 @@ int cafe_embed_forward_sharded(void* handle, const void* ids_dev, int ids_are_in
                                float* weight_high, int hotn, int D, float* const* out_rank, int nranks, int rows_per_rank,
                                int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
                                int32_t* row_out_dev, void* stream);
+/* cafe_embed_gather with the same epilogue: the row of sample b goes to out_rank[b / rows_per_rank]. */
+int cafe_embed_gather_sharded(void* handle, const int32_t* row_dev, int nfields, int B, const int32_t* hash_size,
+                              float* const* weight_hash, float* weight_high, int hotn, int D, float* const* out_rank,
+                              int nranks, int rows_per_rank, int64_t out_field_stride, int64_t out_sample_stride,
+                              void* stream);
 /* The transpose for gradients, fused with cafe_grad_importance: the owner reads the gradient row of
  * sample b from grad_rank[b / rows_per_rank], writes it to local_grad_dev ([nranks*rows, nfields, D]
  * through the strides) and produces the importance array. */
