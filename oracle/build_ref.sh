@@ -38,3 +38,16 @@ mkdir -p "$out_dir"
     cat "$here/ref_shim.inc"
 } | g++ -x c++ - -fPIC -shared --std=c++17 -O3 -o "$out_dir/libsketch_ref.so"
 echo "built $out_dir/libsketch_ref.so"
+
+# The one-stage sketch of the artifact tree (ArtifactEvaluation/embeddings/sketch.cpp), the same way: its static
+# result arrays enlarged (:7), members made visible to the state-dump shim (ref_shim_sigmod.inc), nothing else.
+src2="$ref_root/ArtifactEvaluation/embeddings/sketch.cpp"
+if [ -f "$src2" ]; then
+    {
+        sed -e 's/int ins\[16384\], que\[16384\];/int ins[1 << 22], que[1 << 22];/' \
+            -e 's/private:/public:/' \
+            "$src2"
+        cat "$here/ref_shim_sigmod.inc"
+    } | g++ -x c++ - -fPIC -shared --std=c++17 -O3 -fopenmp -o "$out_dir/libsketch_sigmod_ref.so"
+    echo "built $out_dir/libsketch_sigmod_ref.so"
+fi
