@@ -7,7 +7,8 @@ command in the message.  There is no CPU path.
 from __future__ import annotations
 
 __all__ = ["HotSketch", "SKEmbeddingBag", "SKEmbeddingGroup", "attach_optimizer", "sizing", "synthetic", "CafeError",
-           "INSERT_PARALLEL", "INSERT_SEQUENTIAL", "load_library", "profile"]
+           "INSERT_PARALLEL", "INSERT_SEQUENTIAL", "load_library", "profile", "SigmodSketch", "SigmodSKEmbeddingBag",
+           "dlrm_harness", "sharded"]
 
 INSERT_PARALLEL, INSERT_SEQUENTIAL = 0, 1
 
@@ -28,10 +29,14 @@ def __getattr__(name):
         load_library()
         from . import sk_embedding_bag
         return getattr(sk_embedding_bag, name)
+    if name in ("SigmodSketch", "SigmodSKEmbeddingBag"):
+        load_library()
+        from . import sigmod
+        return getattr(sigmod, name)
     if name == "CafeError":
         from ._lib import CafeError
         return CafeError
-    if name in ("sizing", "synthetic", "profile", "sharded"):
+    if name in ("sizing", "synthetic", "profile", "sharded", "dlrm_harness", "sigmod"):
         import importlib
         return importlib.import_module(f".{name}", __name__)
     raise AttributeError(f"module 'cafe_b200' has no attribute {name!r}")

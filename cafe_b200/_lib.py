@@ -65,6 +65,16 @@ SIGNATURES = {
                                           POINTER(_vp), _vp, c_int, c_int, c_float, c_int, c_int, _vp, _vp]),
     "cafe_embed_backward_imp": (c_int, [_vp, _vp, c_int64, c_int64, _vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                         POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
+    "cafe_sigmod_create": (c_int, [POINTER(_vp), c_int, c_int, c_double, c_int]),
+    "cafe_sigmod_destroy": (c_int, [_vp]),
+    "cafe_sigmod_query": (c_int, [_vp, _vp, c_int, _vp, _vp]),
+    "cafe_sigmod_insert": (c_int, [_vp, _vp, _vp, c_int, _vp, _vp]),
+    "cafe_sigmod_update": (c_int, [_vp, _vp]),
+    "cafe_sigmod_resolve": (c_int, [_vp, _vp, c_int, c_int64, c_int, c_int, _vp, _vp, _vp]),
+    "cafe_sigmod_post_rows": (c_int, [_vp, _vp, _vp, c_int, _vp, _vp]),
+    "cafe_sigmod_dump": (c_int, [_vp, _u32p, _f32p, _i32p, _u32p, _i64p, POINTER(c_double), _vp]),
+    "cafe_sigmod_load": (c_int, [_vp, _u32p, _f32p, _i32p, c_int64, c_double, _vp]),
+    "cafe_workspace_create": (c_int, [POINTER(_vp), c_int, c_int]),
     "cafe_profile_slots": (c_int, []),
     "cafe_profile_slot_name": (c_char_p, [c_int]),
     "cafe_profile_enable": (c_int, [c_int]),

@@ -1352,6 +1352,23 @@ int cafe_sketch_create(void** out, int hotn, float threshold, int adjust_thres, 
     return CAFE_OK;
 }
 
+// The per-handle workspace of the embedding entry points (importance, migration, scatter) without a CAFE+ sketch,
+// for callers that bring a sketch of another kind (cafe_sigmod_*).  Destroyed with cafe_sketch_destroy.
+int cafe_workspace_create(void** out, int hotn, int max_lookups) {
+    if (!out) return CAFE_ERR_ARG;
+    *out = nullptr;
+    if (hotn < 1 || max_lookups < 1) return CAFE_ERR_ARG;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("cafe_workspace_create", e); return CAFE_ERR_CUDA; }
+    CafeHandle* H = new CafeHandle();
+    H->device = dev;
+    int rc = cafe_embed_ws_init(&H->ws, max_lookups, hotn);
+    if (rc != CAFE_OK) { delete H; return rc; }
+    *out = H;
+    return CAFE_OK;
+}
+
 int cafe_sketch_destroy(void* h) {
     CAFE_H(h);
     cudaDeviceSynchronize();

@@ -214,6 +214,42 @@ int cafe_embed_backward_imp(void* handle, const float* grad_dev, int64_t field_s
                             float* const* weight_hash, float* weight_high, int hotn, int D, float lr, int insert_mode,
                             int32_t* mask_out_dev, void* stream);
 
+/* ---- the one-stage HotSketch of the artifact tree, device ABI -----------------------------------------
+ * Replaces class SS of ArtifactEvaluation/embeddings/sketch.cpp (the sketch of the SIGMOD'24 paper; the
+ * reference keeps one per field in ss[26], :151, selected by the `idx` argument of its entry points --
+ * here every sketch is a handle).  Device pointers, caller-owned outputs, no synchronisation except in
+ * dump / load. */
+/* init(n, Threshold, dr, idx), sketch.cpp:228-230: lim buckets, rows 1..lim-1 free. */
+int cafe_sigmod_create(void** handle_out, int lim, int threshold, double decay_rate, int max_lookups);
+int cafe_sigmod_destroy(void* handle);
+/* batch_query, sketch.cpp:124-130: out[i] = -row if the id holds a hot row, else (int32)id. */
+int cafe_sigmod_query(void* handle, const uint32_t* gid_dev, int n, int32_t* out_dev, void* stream);
+/* batch_insert_val / batch_insert (imp_dev null), sketch.cpp:131-149: decay check, then Insert per lookup in
+ * order; mask_out_dev[i] = 1 where the lookup was handed a hot row. */
+int cafe_sigmod_insert(void* handle, const uint32_t* gid_dev, const float* imp_dev, int n, int32_t* mask_out_dev,
+                       void* stream);
+/* update(idx), sketch.cpp:61-75, 222-225: rebuild the free-row FIFO from the rows the buckets hold. */
+int cafe_sigmod_update(void* handle, void* stream);
+/* The query of SKEmbeddingBag.forward (ArtifactEvaluation/embeddings/sk_embedding_bag.py:77-88, 95-118) for one
+ * field: global ids and row codes (-hot row, or global id % hash_size) for cafe_embed_gather / cafe_scatter_sgd. */
+int cafe_sigmod_resolve(void* handle, const void* ids_dev, int ids_are_int64, int64_t f_offset, int hash_size, int n,
+                        uint32_t* gid_out_dev, int32_t* row_out_dev, void* stream);
+/* The post-insert query of insert_grad (sk_embedding_bag.py:173-180): hot row of every lookup with mask 1
+ * (0 elsewhere), the post_row input of cafe_migrate. */
+int cafe_sigmod_post_rows(void* handle, const uint32_t* gid_dev, const int32_t* mask_dev, int n, int32_t* post_row_out_dev,
+                          void* stream);
+/* State export / import with host arrays (val, cnt, dic: 4 * lim each; queue: lim; scalars[0..2] = rows handed
+ * out, FIFO length, decays).  The reference saves nothing and calls update() after loading the model
+ * (ArtifactEvaluation/main.py); load restores the buckets and rebuilds the FIFO the same way. */
+int cafe_sigmod_dump(void* handle, uint32_t* val, float* cnt, int32_t* dic, uint32_t* queue, int64_t* scalars, double* tot,
+                     void* stream);
+int cafe_sigmod_load(void* handle, const uint32_t* val, const float* cnt, const int32_t* dic, int64_t num, double tot,
+                     void* stream);
+/* Workspace of the embedding entry points (cafe_grad_importance, cafe_embed_gather, cafe_migrate, cafe_scatter_sgd)
+ * for a model whose sketch is not the CAFE+ one: a handle without a sketch.  No counterpart in the reference
+ * (its modules allocate through torch).  Destroy with cafe_sketch_destroy. */
+int cafe_workspace_create(void** handle_out, int hotn, int max_lookups);
+
 /* ---- the reference's own ctypes ABI, host pointers (tricks/sketch.cpp:300-327) ------------------
  * Same names, argument meaning and result convention (pointer to a library-owned int array that is
  * valid until the next call), so that the reference's Python can bind this library in place of its
