@@ -42,6 +42,7 @@ SIGNATURES = {
     "cafe_sketch_load": (c_int, [_vp, _u32p, _f32p, _i32p, _u8p, _u32p, _f32p, _i32p, _i32p, _u8p, _u32p, c_int, _vp]),
     "cafe_embed_forward": (c_int, [_vp, _vp, c_int, c_int, c_int, _i64p, _i32p, POINTER(_vp), _vp, c_int, c_int, _vp,
                                    c_int64, c_int64, _vp, _vp, _vp]),
+    "cafe_records_to_batch": (c_int, [_vp, c_int, c_int, _vp, c_int, _vp, _vp, _vp]),
     "cafe_embed_resolve": (c_int, [_vp, _vp, c_int, c_int, c_int, _i64p, _i32p, c_int, _vp, _vp, _vp]),
     "cafe_embed_gather": (c_int, [_vp, _vp, c_int, c_int, _i32p, POINTER(_vp), _vp, c_int, c_int, _vp, c_int64, c_int64, _vp]),
     "cafe_embed_gather_sharded": (c_int, [_vp, _vp, c_int, c_int, _i32p, POINTER(_vp), _vp, c_int, c_int, POINTER(_vp), c_int,

@@ -497,6 +497,37 @@ k_pull_norm(const CafeRankBuffers src, int64_t field_stride, int64_t sample_stri
 }
 
 // ---------------------------------------------------------------------------------------------
+// Input records -> batch.  The reference's preprocessed datasets store the categorical features sample-major
+// (processed_sparse_sep.bin: int32 [N, F], ArtifactEvaluation/load_data.py:44-66; the same layout for the Kaggle
+// / Terabyte / Avazu memmaps of dlrm_data_pytorch.py:643-649) and its collate functions turn a block of rows into
+// one int64 index vector per field on the host (dlrm_data_pytorch.py:395-437: X_cat[:, i] for every field, labels
+// as float [B, 1]).  Here the block of rows is copied to the device as it lies on disk and transposed there:
+// a 32 x 32 tile goes through shared memory so that both the reads (along a sample's fields) and the writes
+// (along a field's samples) are coalesced.
+// ---------------------------------------------------------------------------------------------
+template <typename OutT>
+__global__ void __launch_bounds__(256) k_records_to_fields(const int32_t* __restrict__ rows, int B, int F, OutT* __restrict__ ids) {
+    __shared__ int32_t tile[32][33];
+    const int b0 = blockIdx.x * 32, f0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8 threads
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int b = b0 + r, f = f0 + tx;
+        if (b < B && f < F) tile[r][tx] = rows[(int64_t)b * F + f];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int f = f0 + r, b = b0 + tx;
+        if (b < B && f < F) ids[(int64_t)f * B + b] = (OutT)tile[tx][r];
+    }
+}
+__global__ void k_labels_to_float(const int32_t* __restrict__ label, int B, float* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) out[i] = (float)label[i];
+}
+
+// ---------------------------------------------------------------------------------------------
 // workspace
 // ---------------------------------------------------------------------------------------------
 int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
@@ -621,6 +652,21 @@ int cafe_embed_forward(void* h, const void* ids_dev, int ids_are_int64, int nfie
     return launch_forward(F, ids_dev, ids_are_int64, V, ob, out_field_stride, out_sample_stride, gid_out_dev, row_out_dev, total, D, st);
 }
 
+
+int cafe_records_to_batch(const int32_t* sparse_rows_dev, int B, int F, void* ids_out_dev, int ids_are_int64,
+                          const int32_t* label_dev, float* label_out_dev, void* stream) {
+    if (B < 0 || F < 1) return CAFE_ERR_ARG;
+    if (B == 0) return CAFE_OK;
+    if (!sparse_rows_dev || !ids_out_dev) return CAFE_ERR_ARG;
+    if ((label_dev == nullptr) != (label_out_dev == nullptr)) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    CAFE_PROF(CAFE_P_OTHER, st);
+    const dim3 grid((unsigned)((B + 31) / 32), (unsigned)((F + 31) / 32));
+    if (ids_are_int64) k_records_to_fields<int64_t><<<grid, 256, 0, st>>>(sparse_rows_dev, B, F, (int64_t*)ids_out_dev);
+    else k_records_to_fields<int32_t><<<grid, 256, 0, st>>>(sparse_rows_dev, B, F, (int32_t*)ids_out_dev);
+    if (label_dev) k_labels_to_float<<<(B + 255) / 256, 256, 0, st>>>(label_dev, B, label_out_dev);
+    return fail_cuda("cafe_records_to_batch");
+}
 
 int cafe_embed_resolve(void* h, const void* ids_dev, int ids_are_int64, int nfields, int B, const int64_t* f_offset,
                        const int32_t* hash_size, int hotn, uint32_t* gid_out_dev, int32_t* row_out_dev, void* stream) {

@@ -253,8 +253,6 @@ struct CafeJob {
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
     int32_t cand_active;   // the FIFO timeline changed in the previous round: buckets with ids waiting for a row replay
-    int32_t long_main;     // device hint: main buckets with more lookups than this are fed by a whole warp
-    int32_t long_lru;      // same for LRU buckets
     int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to
                            // record post_row; nothing else is written
     // beliefs: the promotion event of every position, kept in place and updated by the LRU pass
@@ -362,23 +360,23 @@ struct CafeMainReplay {
     int cand_p[CAFE_CAND];
     uint32_t cand_x[CAFE_CAND];
 
+    // does bucket k have to be replayed in this (not first) round?  `cond` receives whether events land in it.
+    static CAFE_HD bool wanted(const CafeJob& J, int k, bool* cond) {
+        const uint32_t st = J.mstate[k];
+        // cond: events land here, so results depend on beliefs that may be withdrawn later (one more
+        // replay after the last such round returns the bucket to its belief-free result); an id waiting
+        // for a row makes the results depend on the FIFO timeline only, which needs a replay exactly when
+        // the timeline changed
+        *cond = J.head[k] >= 0 || J.mark_own[k] != 0;
+        const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
+        return J.final_pass ? (st & CAFE_S_DIRTY) != 0 : (J.all_active || *cond || waiting || (st & CAFE_S_COND) != 0);
+    }
     // returns false if the bucket does not need to be replayed this round; `pre` = the bucket's batch-start
     // image if the caller has loaded it already
     CAFE_HD bool init(const CafeJob& J, int k_, int i_start, const CafeMainBucket* pre = nullptr) {
         k = k_;
         cond_now = false;
-        if (!J.first_round) {
-            const uint32_t st = J.mstate[k];
-            // cond_now: events land here, so results depend on beliefs that may be withdrawn later (one more
-            // replay after the last such round returns the bucket to its belief-free result); an id waiting
-            // for a row makes the results depend on the FIFO timeline only, which needs a replay exactly when
-            // the timeline changed
-            cond_now = J.head[k] >= 0 || J.mark_own[k] != 0;
-            const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
-            const bool active = J.final_pass ? (st & CAFE_S_DIRTY) != 0
-                                             : (J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0);
-            if (!active) return false;
-        }
+        if (!J.first_round && !wanted(J, k, &cond_now)) return false;
         b = pre ? *pre : J.main_in[k];
         evhead = J.first_round ? -1 : J.head[k];
         p_ev = (evhead < 0) ? INT32_MAX : cafe_next_event(J, evhead, -1);
@@ -513,15 +511,16 @@ struct CafeLruReplay {
     int k, n_ev;
     bool touched, cand, cond_now;
 
+    static CAFE_HD bool wanted(const CafeJob& J, int k, bool* cond) {
+        const uint32_t st = J.lstate[k];
+        *cond = J.mark2[k] != 0;
+        const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
+        return J.all_active || *cond || waiting || (st & CAFE_S_COND) != 0;
+    }
     CAFE_HD bool init(const CafeJob& J, int k_, const CafeLruBucket* pre = nullptr) {
         k = k_;
         cond_now = false;
-        if (!J.first_round) {
-            const uint32_t st = J.lstate[k];
-            cond_now = J.mark2[k] != 0;
-            const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
-            if (!(J.all_active || cond_now || waiting || (st & CAFE_S_COND) != 0)) return false;
-        }
+        if (!J.first_round && !wanted(J, k, &cond_now)) return false;
         b = pre ? *pre : J.lru_in[k];
         n_ev = 0;
         touched = cand = false;

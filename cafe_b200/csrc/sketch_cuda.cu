@@ -108,7 +108,8 @@ __global__ void k_gather_counts(const float* __restrict__ imp, const int32_t* __
 // the tail starts at once and overlaps with everything else; the other blocks skip listed buckets.
 #define CAFE_HOT_LEN 256      // a bucket with more lookups than this is listed in the first region (taken first)
 #define CAFE_HOT_CAP 512      // size of that region
-#define CAFE_LIST_CAP (CAFE_HOT_CAP + 32768)   // the second region lists the other long buckets
+// (the second region, behind it, has room for every bucket of the table: with a small sketch and large calls every
+// bucket is long)
 #define CAFE_LIST_BLOCKS (148 * 4)              // blocks of the launch that works through the list
 // Long buckets (more lookups in the sorted stretch than a few times the average) are listed at sort
 // time and replayed by a warp each, in a launch of their own that runs beside the thread-per-bucket
@@ -119,9 +120,10 @@ struct CafeHot {
     const int32_t* list;
     const int32_t* count;
     const uint8_t* flag;
+    int32_t cap2;   // capacity of the second region
 };
-__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int long_len, int32_t* list, int32_t* count,
-                           uint8_t* flag) {
+__global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int long_len, int cap2, int32_t* list,
+                           int32_t* count, uint8_t* flag) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= nb) return;
     const int len = start[k + 1] - start[k];
@@ -131,12 +133,12 @@ __global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_le
         if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; return; }
     }
     const int idx = atomicAdd(&count[1], 1);
-    if (idx < CAFE_LIST_CAP - CAFE_HOT_CAP) { list[CAFE_HOT_CAP + idx] = k; flag[k] = 1; }
+    if (idx < cap2) { list[CAFE_HOT_CAP + idx] = k; flag[k] = 1; }
 }
 // next listed bucket for this warp (lane 0 owns it; -1 = none left); the cursor is zeroed with the round result
 __device__ __forceinline__ int cafe_next_listed(const CafeHot& H, int32_t* cursor, int nb) {
     const int lane = threadIdx.x & 31;
-    const int n_hot = min(H.count[0], CAFE_HOT_CAP), n_long = min(H.count[1], CAFE_LIST_CAP - CAFE_HOT_CAP);
+    const int n_hot = min(H.count[0], CAFE_HOT_CAP), n_long = min(H.count[1], H.cap2);
     int w = 0;
     if (lane == 0) w = atomicAdd(cursor, 1);
     w = __shfl_sync(CAFE_FULL, w, 0);
@@ -531,6 +533,41 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
         }
     }
 }
+// Later rounds and the final pass replay only a small share of the buckets.  One warp scans a chunk of consecutive
+// buckets for the ones that are wanted (coalesced reads of the per-bucket state), queues them in shared memory
+// and then replays them 32 at a time, a bucket per lane: every lane of every replay has work, where the
+// thread-per-bucket launch would drag whole warps along for two or three live lanes.
+#define CAFE_SCAN_MAIN 256   // buckets scanned per warp
+#define CAFE_SCAN_LRU 64
+__global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];
+    __shared__ int s_p[4][CAFE_STAGE_MAIN];
+    __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
+    __shared__ int s_q[4][CAFE_SCAN_MAIN];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int lo = (blockIdx.x * 4 + wib) * CAFE_SCAN_MAIN;
+    constexpr int ITS = CAFE_SCAN_MAIN / 32;
+    bool act[ITS];
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const int k = lo + it * 32 + lane;
+        act[it] = false;
+        if (k < J.n1) { bool cond; act[it] = CafeMainReplay::wanted(J, k, &cond) && !H.flag[k]; }
+    }
+    int nq = 0;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const unsigned m = __ballot_sync(CAFE_FULL, act[it]);
+        if (act[it]) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
+        nq += __popc(m);
+    }
+    __syncwarp();
+    for (int q0 = 0; q0 < nq; q0 += 32) {
+        const int k = q0 + lane < nq ? s_q[wib][q0 + lane] : J.n1;
+        cafe_main_body<1>(J, H, k, s_c, s_p, s_x, s_kf);
+    }
+}
+
 template <int PART>
 __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k) {
     const int lane = threadIdx.x & 31;
@@ -659,6 +696,31 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __gri
             if (k < 0) break;
             cafe_lru_body<0>(J, H, k);
         }
+    }
+}
+__global__ void __launch_bounds__(128, 6) k_lru_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ int s_q[4][CAFE_SCAN_LRU];
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int lo = (blockIdx.x * 4 + wib) * CAFE_SCAN_LRU;
+    constexpr int ITS = CAFE_SCAN_LRU / 32;
+    bool act[ITS];
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const int k = lo + it * 32 + lane;
+        act[it] = false;
+        if (k < J.n2) { bool cond; act[it] = CafeLruReplay::wanted(J, k, &cond) && !H.flag[k]; }
+    }
+    int nq = 0;
+#pragma unroll
+    for (int it = 0; it < ITS; ++it) {
+        const unsigned m = __ballot_sync(CAFE_FULL, act[it]);
+        if (act[it]) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
+        nq += __popc(m);
+    }
+    __syncwarp();
+    for (int q0 = 0; q0 < nq; q0 += 32) {
+        const int k = q0 + lane < nq ? s_q[wib][q0 + lane] : J.n2;
+        cafe_lru_body<1>(J, H, k);
     }
 }
 __global__ void k_route(const __grid_constant__ CafeJob J) {
@@ -805,50 +867,54 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_emit(const __grid_consta
         cafe_tl_set_count(J, base + tot, n_old);
     }
 }
-// 3b, first half: composed transfer function of every block of list entries
+// 3b, first half: composed transfer function of every block of list entries (the list is usually short: a
+// fixed small grid walks over its blocks)
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_aggregate(const __grid_constant__ CafeJob J) {
     __shared__ CafeFn s_warp[CAFE_TL_THREADS / 32];
     const int32_t n = J.tl_head[0];
-    const int base = blockIdx.x * CAFE_TL_BLOCK;
-    if (base >= n) return;
-    CafeFn v = cafe_fn_identity();
+    for (int blk = blockIdx.x; blk * CAFE_TL_BLOCK < n; blk += gridDim.x) {
+        const int base = blk * CAFE_TL_BLOCK;
+        CafeFn v = cafe_fn_identity();
 #pragma unroll
-    for (int i = 0; i < CAFE_TL_PER; ++i) {
-        const int j = base + threadIdx.x * CAFE_TL_PER + i;
-        if (j < n) v = cafe_fn_then(v, cafe_fn_of_info(J.tl_info[j]));
+        for (int i = 0; i < CAFE_TL_PER; ++i) {
+            const int j = base + threadIdx.x * CAFE_TL_PER + i;
+            if (j < n) v = cafe_fn_then(v, cafe_fn_of_info(J.tl_info[j]));
+        }
+        CafeFn tot;
+        cafe_block_exclusive_fn(v, &tot, s_warp);
+        if (threadIdx.x == 0) J.tl_agg[blk] = tot;
     }
-    CafeFn tot;
-    cafe_block_exclusive_fn(v, &tot, s_warp);
-    if (threadIdx.x == 0) J.tl_agg[blockIdx.x] = tot;
 }
 // 3b, second half: FIFO size and successful pops before every list entry, the pushed rows in order, totals
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_tl_finish(const __grid_constant__ CafeJob J) {
     __shared__ CafeFn s_warp[CAFE_TL_THREADS / 32];
     __shared__ CafeFn s_before;
     const int32_t n = J.tl_head[0];
-    const int base = blockIdx.x * CAFE_TL_BLOCK;
-    if (base >= n) return;
-    if (threadIdx.x == 0) {
-        CafeFn f = cafe_fn_identity();
-        for (int q = 0; q < (int)blockIdx.x; ++q) f = cafe_fn_then(f, J.tl_agg[q]);
-        s_before = f;
-    }
-    __syncthreads();
-    const int j0 = base + threadIdx.x * CAFE_TL_PER;
-    CafeFn v = cafe_fn_identity();
-    int32_t info[CAFE_TL_PER];
+    for (int blk = blockIdx.x; blk * CAFE_TL_BLOCK < n; blk += gridDim.x) {
+        const int base = blk * CAFE_TL_BLOCK;
+        if (threadIdx.x == 0) {
+            CafeFn f = cafe_fn_identity();
+            for (int q = 0; q < blk; ++q) f = cafe_fn_then(f, J.tl_agg[q]);
+            s_before = f;
+        }
+        __syncthreads();
+        const int j0 = base + threadIdx.x * CAFE_TL_PER;
+        CafeFn v = cafe_fn_identity();
+        int32_t info[CAFE_TL_PER];
 #pragma unroll
-    for (int i = 0; i < CAFE_TL_PER; ++i) {
-        info[i] = (j0 + i < n) ? J.tl_info[j0 + i] : 0;
-        if (j0 + i < n) v = cafe_fn_then(v, cafe_fn_of_info(info[i]));
-    }
-    CafeFn tot;
-    CafeFn before = cafe_fn_then(s_before, cafe_block_exclusive_fn(v, &tot, s_warp));
+        for (int i = 0; i < CAFE_TL_PER; ++i) {
+            info[i] = (j0 + i < n) ? J.tl_info[j0 + i] : 0;
+            if (j0 + i < n) v = cafe_fn_then(v, cafe_fn_of_info(info[i]));
+        }
+        CafeFn tot;
+        CafeFn before = cafe_fn_then(s_before, cafe_block_exclusive_fn(v, &tot, s_warp));
 #pragma unroll
-    for (int i = 0; i < CAFE_TL_PER; ++i) {
-        if (j0 + i >= n) break;
-        cafe_tl_finish_op(J, j0 + i, n, before);
-        before = cafe_fn_then(before, cafe_fn_of_info(info[i]));
+        for (int i = 0; i < CAFE_TL_PER; ++i) {
+            if (j0 + i >= n) break;
+            cafe_tl_finish_op(J, j0 + i, n, before);
+            before = cafe_fn_then(before, cafe_fn_of_info(info[i]));
+        }
+        __syncthreads();
     }
 }
 // at commit: main-table misses up to and including every position of the job (the LRU clock numbering)
@@ -1082,7 +1148,7 @@ struct CudaBackend {
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
         for (int i = 0; i < 2; ++i) {
-            check(cudaMalloc(&hot_list[i], 4 * CAFE_LIST_CAP));
+            check(cudaMalloc(&hot_list[i], 4 * ((size_t)CAFE_HOT_CAP + (size_t)hot_nb[i])));
             check(cudaMalloc(&hot_count[i], 8));
             check(cudaMalloc(&hot_flag[i], (size_t)hot_nb[i]));
             check(cudaMemsetAsync(hot_count[i], 0, 8, stream));
@@ -1138,9 +1204,13 @@ struct CudaBackend {
         const int t = (nb == hot_nb[0]) ? 0 : 1;
         check(cudaMemsetAsync(hot_count[t], 0, 8, st));
         check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, st));
-        const int hot_len = std::max(CAFE_HOT_LEN, (int)(16.0 * M / nb));
-        const int long_len = std::max(16, (int)(4.0 * M / nb));
-        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, long_len, hot_list[t], hot_count[t], hot_flag[t]);
+        // A warp feeding one long bucket leaves 31 lanes idle while it loads, so it pays where that bucket would
+        // otherwise be a serial tail of the thread-per-bucket launch: more lookups than a few times the average
+        // load -- but never more than 64, beyond which one thread's serial replay is the tail whatever the average
+        // (a sketch of a few thousand rows fed 65536-id calls has hundreds of lookups in EVERY bucket).
+        const int hot_len = std::max(CAFE_HOT_LEN, std::min((int)(16.0 * M / nb), 4096));
+        const int long_len = std::max(16, std::min((int)(4.0 * M / nb), 64));
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, long_len, nb, hot_list[t], hot_count[t], hot_flag[t]);
         check_launch();
         check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
         }
@@ -1182,13 +1252,14 @@ struct CudaBackend {
     }
     cudaEvent_t gate_event = nullptr;   // see SketchEngine::set_gate
     void wait_gate() { if (gate_event) check(cudaStreamWaitEvent(stream, gate_event, 0)); }
-    CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; return h; }
+    CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; h.cap2 = hot_nb[t]; return h; }
     void main_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
         pass_fork();
         k_main_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(0));
         check_launch();
-        k_main_pass<1><<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
+        if (J.all_active) k_main_pass<1><<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
+        else k_main_pass_sparse<<<cafe_blocks(J.n1, 4 * CAFE_SCAN_MAIN), 128, 0, stream>>>(J, hot(0));
         pass_join();
         check_launch();
     }
@@ -1213,7 +1284,8 @@ struct CudaBackend {
         pass_fork();
         k_lru_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(1));
         check_launch();
-        k_lru_pass<1><<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
+        if (J.all_active) k_lru_pass<1><<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
+        else k_lru_pass_sparse<<<cafe_blocks(J.n2, 4 * CAFE_SCAN_LRU), 128, 0, stream>>>(J, hot(1));
         pass_join();
         check_launch();
     }
@@ -1223,8 +1295,8 @@ struct CudaBackend {
         const int g = cafe_blocks(cnt, CAFE_TL_BLOCK);
         k_tl_count<<<g, CAFE_TL_THREADS, 0, stream>>>(J);
         k_tl_emit<<<g, CAFE_TL_THREADS, 0, stream>>>(J);
-        // the list has at most two entries per position; blocks beyond its real length return at once
-        const int go = cafe_blocks(2 * (int64_t)cnt, CAFE_TL_BLOCK);
+        // the list has at most two entries per position, usually far fewer: a small grid walks over its blocks
+        const int go = std::min(cafe_blocks(2 * (int64_t)cnt, CAFE_TL_BLOCK), 148);
         k_tl_aggregate<<<go, CAFE_TL_THREADS, 0, stream>>>(J);
         k_tl_finish<<<go, CAFE_TL_THREADS, 0, stream>>>(J);
         check_launch();

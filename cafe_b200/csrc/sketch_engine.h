@@ -401,10 +401,6 @@ private:
         J.mask = mask;
         J.post_row = post_row;
         J.res = res_dev;
-        // A warp feeding one long bucket leaves 31 lanes idle, so it only pays when that bucket would
-        // otherwise be a serial tail: threshold = a few times the average load per bucket.
-        J.long_main = std::max(16, (int)(4.0 * M / n1));
-        J.long_lru = std::max(16, (int)(4.0 * M / n2));
         ++stats.jobs;
         {
             const size_t span = (size_t)(J.limit - J.begin);

