@@ -618,6 +618,11 @@ def run_ours(args, rank, world, local_rank):
                 nv["grad_push_GBs"] = out_bwd / (phases["push_grads"]["ms_per_step"] / 1e3) / 1e9
             nv["bytes_out_per_step"] = {"pooled_rows": out_fwd, "gradients": out_bwd}
             line["nvlink"] = nv
+        if world == 1 and not args.no_dlrm:
+            try:
+                line["dlrm_samples_per_s"] = dlrm_figures()
+            except Exception as e:   # informative only
+                line["dlrm_samples_per_s"] = {"error": repr(e)}
         if world == 1 and not args.no_cpu_baseline:
             try:
                 line["cpu_baseline"] = cpu_baseline_leg(args, wl)
@@ -627,6 +632,25 @@ def run_ours(args, rank, world, local_rank):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def dlrm_figures():
+    """The metric's second figure on one GPU: samples/s of whole training steps (dense side on stock PyTorch, the
+    CAFE embedding path from this library) at the three model configurations, on seeded synthetic data."""
+    from cafe_b200 import dlrm_harness as H
+    out = {}
+    for name, argv in (("kaggle_dlrm_dim16_batch128", ["--data-set", "kaggle", "--mini-batch-size", "128", "--compress-rate", "0.001",
+                                                        "--hash-rate", "0.3", "--nbatches", "150"]),
+                       ("terabyte_dlrm_dim128_batch2048", ["--data-set", "terabyte", "--mini-batch-size", "2048", "--compress-rate",
+                                                           "0.001", "--hash-rate", "0.3", "--nbatches", "60"]),
+                       ("avazu_dcn_dim16_batch4096", ["--data-set", "avazu", "--model", "dcn", "--mini-batch-size", "4096",
+                                                      "--compress-rate", "0.1", "--hash-rate", "0.7", "--nbatches", "60"])):
+        r = H.run(H.make_parser().parse_args(["--sketch-flag", "--sketch-alpha", "1.0000005", "--warmup-batches", "20"] + argv))
+        out[name] = {"samples_per_s": r["samples_per_s"], "ms_per_step": r["ms_per_step"], "sketch_fields": r["sketch_fields"],
+                     "plain_fields": r["plain_fields"], "loss_last": r["loss_last"]}
+    out["note"] = ("whole training steps: stock-PyTorch MLPs / interaction / loss / SGD around the library's embedding path; "
+                   "ids arrive as host tensors every step")
+    return out
 
 
 def main():
@@ -641,6 +665,7 @@ def main():
     ap.add_argument("--cpu-batch", type=int, default=BATCH, help="batch of the CPU reference path")
     ap.add_argument("--cpu-steps", type=int, default=3, help="timed steps of the cpu_baseline leg of our arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-dlrm", action="store_true", help="skip the DLRM / DCN samples-per-second figures")
     ap.add_argument("--no-single-ref", action="store_true", help="cfg3 on several GPUs: skip the one-GPU run of the same workload")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU exchange of pooled rows / gradients")
     args = ap.parse_args()

@@ -469,7 +469,8 @@ struct CafeMainReplay {
                 }
             }
         } else {
-            if (J.final_pass) note_cand(p, x);
+            // final pass: only a lookup that was handed a row (in the LRU stage) needs its post-insert row
+            if (J.final_pass) { if (J.lflag[p] & CAFE_F_GOT) note_cand(p, x); }
             else {
                 if (old_flag != CAFE_F_MISS) J.mflag[p] = CAFE_F_MISS;   // goes to the LRU stage; that pass writes lflag
                 if (!J.first_round && !(old_flag & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor

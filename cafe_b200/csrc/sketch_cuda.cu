@@ -421,6 +421,10 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                 // the first lookup that could take a row; that one goes through the full replay.
                 // (several ids of one bucket may alternate: every lane finds the slot of its own id, and the
                 // counts of each slot are added in order by that slot's own chain)
+                // Lookups of ids that sit in no slot ride along: a main-table miss changes nothing in the bucket
+                // (it goes to the LRU stage; whatever it causes comes back as an event at its own position, which
+                // bounds the run), so its lane only writes its flags -- unless the lookup carries an own-promotion
+                // event or, in the final pass, was handed a row in the LRU stage: those take the full replay.
                 uint32_t bv0 = 0, bv1 = 0, bv2 = 0, bv3 = 0;
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
                 int rowmask = 0, bound = 0, tch = 0;
@@ -442,14 +446,17 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     rowmask = __shfl_sync(CAFE_FULL, rowmask, o);
                     bound = __shfl_sync(CAFE_FULL, bound, o);
                     ms = (x == bv0) ? 0 : (x == bv1) ? 1 : (x == bv2) ? 2 : (x == bv3) ? 3 : -1;
-                    const bool mine = lane >= j && lane < n && ms >= 0 && p < bound;
+                    bool pure = lane >= j && lane < n && ms < 0 && p < bound && ok != CAFE_EV_OWN;
+                    if (pure && J.final_pass && (J.lflag[p] & CAFE_F_GOT) != 0) pure = false;
+                    const bool mine = lane >= j && lane < n && p < bound && (ms >= 0 || pure);
                     const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
                     if (run < 0) run = 32 - j;    // all remaining lanes qualify
                     if (run > 0) {
                         const int slot_j = __shfl_sync(CAFE_FULL, ms, j);
                         const bool one_id = (__ballot_sync(CAFE_FULL, lane >= j && lane < j + run && x != xj) == 0);
-                        hvalid = one_id; hx = xj; hslot = slot_j; hrow = ((rowmask >> slot_j) & 1) != 0; hbound = bound;
+                        hvalid = one_id && slot_j >= 0; hx = xj; hslot = slot_j < 0 ? 0 : slot_j;
+                        hrow = slot_j >= 0 && ((rowmask >> slot_j) & 1) != 0; hbound = bound;
                     }
                 }
                 if (run >= 2) {
@@ -459,6 +466,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     for (int u = j; u < j + run; ++u) {
                         const float cu = __shfl_sync(CAFE_FULL, c, u);
                         const int su = __shfl_sync(CAFE_FULL, ms, u);
+                        if (su < 0) continue;   // a miss riding along (warp-uniform)
                         float t = (su == 0) ? a0 : (su == 1) ? a1 : (su == 2) ? a2 : a3;
                         t = t + cu;
                         if (su == 0) a0 = t; else if (su == 1) a1 = t; else if (su == 2) a2 = t; else a3 = t;
@@ -466,7 +474,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     }
                     const bool in_run = lane >= j && lane < j + run;
                     const bool has_row = ms >= 0 && ((rowmask >> ms) & 1) != 0;
-                    const bool cd = !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
+                    const bool cd = ms >= 0 && !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
                     // ... that could succeed: the FIFO is believed non-empty at its op slot (looked up only for candidates)
                     const bool av = in_run && cd && cafe_fifo_nonempty(J, 2 * (int64_t)p);
                     const unsigned blocked = __ballot_sync(CAFE_FULL, av);
@@ -490,7 +498,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                             R.i_cur += done;
                             if (any_cand) R.cand = true;
                         }
-                        if (!J.final_pass && in_done) {
+                        if (!J.final_pass && in_done && ms >= 0) {
                             const bool cr = (my_acc >= J.thr && my_acc - c < J.thr);   // sketch.cpp:218
                             const uint32_t nf = (cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0);
                             if (nf != of) J.mflag[p] = (uint8_t)nf;
@@ -498,6 +506,10 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                                 if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
                                 if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                             }
+                        }
+                        if (!J.final_pass && in_done && ms < 0) {   // goes to the LRU stage; that pass writes lflag
+                            if (of != CAFE_F_MISS) J.mflag[p] = CAFE_F_MISS;
+                            if (!J.first_round && !(of & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor
                         }
                         if (done < run) hvalid = false;
                         j += done;
@@ -539,26 +551,25 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
 // thread-per-bucket launch would drag whole warps along for two or three live lanes.
 #define CAFE_SCAN_MAIN 256   // buckets scanned per warp
 #define CAFE_SCAN_LRU 64
-__global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H) {
+__global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H, const int its) {
     __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];
     __shared__ int s_p[4][CAFE_STAGE_MAIN];
     __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
     __shared__ int s_q[4][CAFE_SCAN_MAIN];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int lo = (blockIdx.x * 4 + wib) * CAFE_SCAN_MAIN;
-    constexpr int ITS = CAFE_SCAN_MAIN / 32;
-    bool act[ITS];
+    const int lo = (blockIdx.x * 4 + wib) * its * 32;   // a warp scans its * 32 buckets (its <= CAFE_SCAN_MAIN / 32)
+    unsigned act = 0;
 #pragma unroll
-    for (int it = 0; it < ITS; ++it) {
+    for (int it = 0; it < CAFE_SCAN_MAIN / 32; ++it) {
         const int k = lo + it * 32 + lane;
-        act[it] = false;
-        if (k < J.n1) { bool cond; act[it] = CafeMainReplay::wanted(J, k, &cond) && !H.flag[k]; }
+        if (it < its && k < J.n1) { bool cond; if (CafeMainReplay::wanted(J, k, &cond) && !H.flag[k]) act |= 1u << it; }
     }
     int nq = 0;
 #pragma unroll
-    for (int it = 0; it < ITS; ++it) {
-        const unsigned m = __ballot_sync(CAFE_FULL, act[it]);
-        if (act[it]) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
+    for (int it = 0; it < CAFE_SCAN_MAIN / 32; ++it) {
+        const bool a = (act >> it) & 1u;
+        const unsigned m = __ballot_sync(CAFE_FULL, a);
+        if (a) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
         nq += __popc(m);
     }
     __syncwarp();
@@ -698,23 +709,22 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __gri
         }
     }
 }
-__global__ void __launch_bounds__(128, 6) k_lru_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H) {
+__global__ void __launch_bounds__(128, 6) k_lru_pass_sparse(const __grid_constant__ CafeJob J, const CafeHot H, const int its) {
     __shared__ int s_q[4][CAFE_SCAN_LRU];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int lo = (blockIdx.x * 4 + wib) * CAFE_SCAN_LRU;
-    constexpr int ITS = CAFE_SCAN_LRU / 32;
-    bool act[ITS];
+    const int lo = (blockIdx.x * 4 + wib) * its * 32;
+    unsigned act = 0;
 #pragma unroll
-    for (int it = 0; it < ITS; ++it) {
+    for (int it = 0; it < CAFE_SCAN_LRU / 32; ++it) {
         const int k = lo + it * 32 + lane;
-        act[it] = false;
-        if (k < J.n2) { bool cond; act[it] = CafeLruReplay::wanted(J, k, &cond) && !H.flag[k]; }
+        if (it < its && k < J.n2) { bool cond; if (CafeLruReplay::wanted(J, k, &cond) && !H.flag[k]) act |= 1u << it; }
     }
     int nq = 0;
 #pragma unroll
-    for (int it = 0; it < ITS; ++it) {
-        const unsigned m = __ballot_sync(CAFE_FULL, act[it]);
-        if (act[it]) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
+    for (int it = 0; it < CAFE_SCAN_LRU / 32; ++it) {
+        const bool a = (act >> it) & 1u;
+        const unsigned m = __ballot_sync(CAFE_FULL, a);
+        if (a) s_q[wib][nq + __popc(m & ((1u << lane) - 1u))] = lo + it * 32 + lane;
         nq += __popc(m);
     }
     __syncwarp();
@@ -1253,13 +1263,21 @@ struct CudaBackend {
     cudaEvent_t gate_event = nullptr;   // see SketchEngine::set_gate
     void wait_gate() { if (gate_event) check(cudaStreamWaitEvent(stream, gate_event, 0)); }
     CafeHot hot(int t) const { CafeHot h; h.list = hot_list[t]; h.count = hot_count[t]; h.flag = hot_flag[t]; h.cap2 = hot_nb[t]; return h; }
+    // buckets a warp of a sparse launch scans, in units of 32: enough warps to fill the GPU first, long scans second
+    static int scan_its(int nb, int most) {
+        const int its = (int)((nb + 148 * 16 * 32 - 1) / (148 * 16 * 32));
+        return its < 1 ? 1 : (its > most ? most : its);
+    }
     void main_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
         pass_fork();
         k_main_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(0));
         check_launch();
         if (J.all_active) k_main_pass<1><<<cafe_blocks(J.n1, 128), 128, 0, stream>>>(J, hot(0));
-        else k_main_pass_sparse<<<cafe_blocks(J.n1, 4 * CAFE_SCAN_MAIN), 128, 0, stream>>>(J, hot(0));
+        else {
+            const int its = scan_its(J.n1, CAFE_SCAN_MAIN / 32);
+            k_main_pass_sparse<<<cafe_blocks(J.n1, 4 * 32 * its), 128, 0, stream>>>(J, hot(0), its);
+        }
         pass_join();
         check_launch();
     }
@@ -1285,7 +1303,10 @@ struct CudaBackend {
         k_lru_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(1));
         check_launch();
         if (J.all_active) k_lru_pass<1><<<cafe_blocks(J.n2, 128), 128, 0, stream>>>(J, hot(1));
-        else k_lru_pass_sparse<<<cafe_blocks(J.n2, 4 * CAFE_SCAN_LRU), 128, 0, stream>>>(J, hot(1));
+        else {
+            const int its = scan_its(J.n2, CAFE_SCAN_LRU / 32);
+            k_lru_pass_sparse<<<cafe_blocks(J.n2, 4 * 32 * its), 128, 0, stream>>>(J, hot(1), its);
+        }
         pass_join();
         check_launch();
     }
