@@ -213,6 +213,9 @@ enum { CAFE_F_MISS = 1, CAFE_F_POP0 = 2, CAFE_F_POP1 = 4, CAFE_F_CROSS = 8, CAFE
 // per-bucket replay state kept between rounds
 enum { CAFE_S_COND = 1, CAFE_S_CAND = 2, CAFE_S_DIRTY = 4 };   // DIRTY: a row was handed out or an event landed
 
+// what a main bucket remembers of its last long stretch of lookups of one hot id (CUDA list launch only)
+struct alignas(16) CafeCalmMemo { int32_t serial, i0, i1, p_last; uint32_t acc_in, acc_out, x; int32_t slot; };
+
 struct CafeJob {
     // the lookups
     const uint32_t* gid;     // [M] global ids
@@ -249,6 +252,8 @@ struct CafeJob {
     uint32_t ring_mask;
     uint32_t q_head;
     int32_t q_size;
+    int32_t serial;          // number of this job within its sketch (never 0)
+    CafeCalmMemo* memo1;     // [n1] or null
     // round control
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)

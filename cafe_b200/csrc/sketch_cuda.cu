@@ -269,6 +269,21 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                 }
                 acc = __shfl_sync(CAFE_FULL, acc, o);
                 int gb = base;
+                // A stretch that an earlier round of this job has already added up from the same count gives the
+                // same sum again: the bucket remembers its last long stretch (where it began and ended, the count
+                // it started from and arrived at) and later rounds and the final pass jump over it.  The lookups'
+                // flags were left clean by the round that walked the stretch, and only this bucket writes them.
+                const int kb = __shfl_sync(CAFE_FULL, k, o);
+                const uint32_t acc_in = __float_as_uint(acc);
+                if (J.memo1) {
+                    const CafeCalmMemo mm = J.memo1[kb];
+                    if (mm.serial == J.serial && mm.i0 == base && mm.acc_in == acc_in && mm.x == hx && mm.slot == hslot &&
+                        mm.p_last < hbound && mm.i1 <= e) {
+                        acc = __uint_as_float(mm.acc_out);
+                        gb = mm.i1;
+                    }
+                }
+                const int g_start = gb;
                 int cp[4], xp[4], n2p[4];
                 uint32_t cx[4], cok[4], cof[4], xx[4], xok[4], xof[4];
                 float cc[4], xc[4];
@@ -329,6 +344,12 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     }
                 }
                 if (gb != base) {
+                    if (J.memo1 && g_start == base && gb - base >= 512 && lane == 0) {   // (walked, not jumped: remember it)
+                        CafeCalmMemo mm;
+                        mm.serial = J.serial; mm.i0 = base; mm.i1 = gb; mm.p_last = J.ord1[gb - 1];
+                        mm.acc_in = acc_in; mm.acc_out = __float_as_uint(acc); mm.x = hx; mm.slot = hslot;
+                        J.memo1[kb] = mm;
+                    }
                     if (lane == o) {
 #pragma unroll
                         for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
@@ -948,6 +969,84 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_miss_prefix(const __grid_co
         J.nmiss[p0 + i] = run;
     }
 }
+// ---- LRU pass over compacted miss lists --------------------------------------------------------------
+// When a small sketch is fed large calls, an LRU bucket's sorted stretch holds thousands of lookups of which
+// most hit the main table (all lookups of a hot id lie in one LRU bucket).  Walking them just to skip them
+// then dominates the pass, so the lookups that missed the main table in this round are first compacted, in
+// the order of the LRU sort (count per block, then emit at the block's offset, as for the FIFO timeline), and
+// each bucket replays its slice of the compacted list, a warp per bucket.
+struct CafeMissList {
+    int32_t* pre;    // [M + 1] misses among the sorted entries before entry i (pre[M] = all of them)
+    int32_t* list;   // [M]     sorted-order indices of the misses
+    int32_t* blk;    // [blocks] misses per block of CAFE_TL_BLOCK sorted entries
+};
+__device__ __forceinline__ int cafe_entry_missed(const CafeJob& J, int i) {
+    const int p = J.ord2[i];
+    return (p >= J.begin && p < J.limit && (J.mflag[p] & CAFE_F_MISS)) ? 1 : 0;
+}
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_count(const __grid_constant__ CafeJob J, const CafeMissList L) {
+    __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < CAFE_TL_PER; ++q) {
+        const int i = blockIdx.x * CAFE_TL_BLOCK + threadIdx.x * CAFE_TL_PER + q;
+        if (i < J.M) c += cafe_entry_missed(J, i);
+    }
+    int tot;
+    cafe_block_exclusive_sum(c, &tot, s_warp);
+    if (threadIdx.x == 0) L.blk[blockIdx.x] = tot;
+}
+__global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_emit(const __grid_constant__ CafeJob J, const CafeMissList L) {
+    __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    int v = 0;
+    for (int q = threadIdx.x; q < (int)blockIdx.x; q += CAFE_TL_THREADS) v += L.blk[q];
+    int base;
+    cafe_block_exclusive_sum(v, &base, s_warp);
+    const int i0 = blockIdx.x * CAFE_TL_BLOCK + threadIdx.x * CAFE_TL_PER;
+    int m[CAFE_TL_PER], c = 0;
+#pragma unroll
+    for (int q = 0; q < CAFE_TL_PER; ++q) { m[q] = (i0 + q < J.M) ? cafe_entry_missed(J, i0 + q) : 0; c += m[q]; }
+    int tot;
+    int j = base + cafe_block_exclusive_sum(c, &tot, s_warp);
+#pragma unroll
+    for (int q = 0; q < CAFE_TL_PER; ++q) {
+        if (i0 + q >= J.M) break;
+        L.pre[i0 + q] = j;
+        if (m[q]) L.list[j++] = i0 + q;
+    }
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) L.pre[J.M] = base + tot;
+}
+__global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant__ CafeJob J, const CafeMissList L) {
+    const int lane = threadIdx.x & 31;
+    const int nwarps = gridDim.x * (blockDim.x >> 5);
+    for (int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); k < J.n2; k += nwarps) {
+        CafeLruReplay R;
+        int live = 0, jb = 0, jend = 0;
+        if (lane == 0) {
+            live = R.init(J, k) ? 1 : 0;
+            if (live) { jb = L.pre[J.start2[k]]; jend = L.pre[J.start2[k + 1]]; }
+        }
+        live = __shfl_sync(CAFE_FULL, live, 0);
+        if (!live) continue;
+        jb = __shfl_sync(CAFE_FULL, jb, 0); jend = __shfl_sync(CAFE_FULL, jend, 0);
+        // a chunk of 32 misses is loaded while the previous one is replayed (by lane 0, in order)
+        int p_nx = 0; uint32_t x_nx = 0; float c_nx = 1.0f;
+        if (jb + lane < jend) { const int i = L.list[jb + lane]; p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i]; }
+        for (int base = jb; base < jend; base += 32) {
+            const int p = p_nx; const uint32_t x = x_nx; const float c = c_nx;
+            c_nx = 1.0f;
+            if (base + 32 + lane < jend) { const int i = L.list[base + 32 + lane]; p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i]; }
+            const int n = min(32, jend - base);
+            for (int t = 0; t < n; ++t) {
+                const int pj = __shfl_sync(CAFE_FULL, p, t);
+                const uint32_t xj = __shfl_sync(CAFE_FULL, x, t);
+                const float cj = __shfl_sync(CAFE_FULL, c, t);
+                if (lane == 0) R.feed(J, pj, xj, cj);
+            }
+        }
+        if (lane == 0) R.finish(J);
+    }
+}
 __global__ void k_commit_queue(uint32_t* ring, uint32_t mask, uint32_t q_head, int32_t q_size, int32_t n_pop_ok,
                                const uint32_t* __restrict__ pushbuf, int n_push) {
     int j = blockIdx.x * blockDim.x + threadIdx.x;
@@ -1061,6 +1160,8 @@ struct CudaBackend {
     uint32_t *key_tmp[LANES] = {nullptr, nullptr, nullptr}, *key_out[LANES] = {nullptr, nullptr, nullptr};
     int32_t* pos_tmp[LANES] = {nullptr, nullptr, nullptr};
     const uint32_t* given_key[LANES] = {nullptr, nullptr, nullptr};   // bucket numbers the caller already has (else hashed here)
+    CafeMissList miss = {nullptr, nullptr, nullptr};   // compacted misses of the LRU pass (small sketch, large calls)
+    CafeCalmMemo* memo1 = nullptr;   // [n1] last long calm stretch of every main bucket (see the list launch of the main pass)
     cudaStream_t side[LANES] = {nullptr, nullptr, nullptr};
     cudaEvent_t ev_fork[LANES] = {nullptr, nullptr, nullptr}, ev_join[LANES] = {nullptr, nullptr, nullptr};
     bool side_pending[LANES] = {false, false, false};
@@ -1087,6 +1188,10 @@ struct CudaBackend {
             if (pos_tmp[i]) cudaFree(pos_tmp[i]);
         }
         if (scan64) cudaFree(scan64);
+        if (memo1) cudaFree(memo1);
+        if (miss.pre) cudaFree(miss.pre);
+        if (miss.list) cudaFree(miss.list);
+        if (miss.blk) cudaFree(miss.blk);
         for (int i = 0; i < 2; ++i) { if (hot_list[i]) cudaFree(hot_list[i]); if (hot_count[i]) cudaFree(hot_count[i]); if (hot_flag[i]) cudaFree(hot_flag[i]); }
         if (pinned) cudaFreeHost(pinned);
     }
@@ -1157,6 +1262,11 @@ struct CudaBackend {
         }
         check(cudaMallocHost(&pinned, 4096));
         hot_nb[0] = n1; hot_nb[1] = n2;
+        check(cudaMalloc(&miss.pre, 4 * ((size_t)cap + 1)));
+        check(cudaMalloc(&miss.list, 4 * (size_t)cap));
+        check(cudaMalloc(&miss.blk, 4 * ((size_t)cap / CAFE_TL_BLOCK + 2)));
+        check(cudaMalloc(&memo1, sizeof(CafeCalmMemo) * (size_t)n1));
+        check(cudaMemsetAsync(memo1, 0, sizeof(CafeCalmMemo) * (size_t)n1, stream));
         for (int i = 0; i < 2; ++i) {
             check(cudaMalloc(&hot_list[i], 4 * ((size_t)CAFE_HOT_CAP + (size_t)hot_nb[i])));
             check(cudaMalloc(&hot_count[i], 8));
@@ -1268,7 +1378,9 @@ struct CudaBackend {
         const int its = (int)((nb + 148 * 16 * 32 - 1) / (148 * 16 * 32));
         return its < 1 ? 1 : (its > most ? most : its);
     }
-    void main_pass(const CafeJob& J) {
+    void main_pass(const CafeJob& J0) {
+        CafeJob J = J0;
+        J.memo1 = memo1;
         CAFE_PROF_DYN(J.final_pass ? CAFE_P_MAIN_FINAL : (J.all_active ? CAFE_P_MAIN : CAFE_P_MAIN_LATER), stream);
         pass_fork();
         k_main_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(0));
@@ -1299,6 +1411,16 @@ struct CudaBackend {
     }
     void lru_pass(const CafeJob& J) {
         CAFE_PROF_DYN(J.all_active ? CAFE_P_LRU : CAFE_P_LRU_LATER, stream);
+        if (J.sgid2 && (int64_t)J.M >= 256 * (int64_t)J.n2) {
+            // hundreds of sorted entries per LRU bucket, most of them main-table hits: replay compacted miss lists
+            const int g = cafe_blocks(J.M, CAFE_TL_BLOCK);
+            k_lru_miss_count<<<g, CAFE_TL_THREADS, 0, stream>>>(J, miss);
+            k_lru_miss_emit<<<g, CAFE_TL_THREADS, 0, stream>>>(J, miss);
+            const int blocks = std::min(cafe_blocks(J.n2, 4), 148 * 8);
+            k_lru_pass_compact<<<blocks, 128, 0, stream>>>(J, miss);
+            check_launch();
+            return;
+        }
         pass_fork();
         k_lru_pass<0><<<CAFE_LIST_BLOCKS, 128, 0, pass_side>>>(J, hot(1));
         check_launch();

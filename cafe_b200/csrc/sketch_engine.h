@@ -309,6 +309,7 @@ public:
 
 private:
     int gate_seg = -1;
+    int32_t job_serial = 0;
     bool cursors_advanced = false;
     const uint32_t* presorted_gid = nullptr;
     int presorted_n = 0;
@@ -402,6 +403,8 @@ private:
         J.post_row = post_row;
         J.res = res_dev;
         ++stats.jobs;
+        if (++job_serial <= 0) job_serial = 1;
+        J.serial = job_serial;
         {
             const size_t span = (size_t)(J.limit - J.begin);
             be.fills(ins_res + J.begin, 0, 4 * span, mflag + J.begin, 0, span,

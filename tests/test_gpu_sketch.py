@@ -93,6 +93,15 @@ def test_heavy_duplicates():
     drive(100, 1, 1.1, 30, 600, 40, 3)
 
 
+def test_small_sketch_large_calls():
+    """Hundreds of lookups per bucket and call (the LRU pass then replays compacted miss lists, every main bucket is
+    fed by a warp, and long stretches of one hot id are remembered between rounds)."""
+    st = drive(60, 1, 1.2, 24, 2000, 300, 2)
+    assert st["resets"] > 0 and st["seq_fallbacks"] == 0
+    drive(400, 2, 1.0000005, 12, 40000, 3000, 3, seed=11)
+    drive(300, 1, 1.0000005, 8, 60000, 40, 2, seed=12)      # a 40-id domain: stretches of thousands of lookups of one id
+
+
 def test_round_cap_fallback_is_exact():
     st = drive(200, 1, 1.3, 40, 96, 3000, 4, round_cap=2)
     assert st["seq_fallbacks"] > 0
