@@ -302,9 +302,12 @@ CAFE_HD void cafe_fifo_before(const CafeJob& J, int64_t slot, int32_t* size, int
     if (J.first_round) { *size = J.q_size; *rank = 0; return; }
     const int32_t n = J.tl_head[0];
     const int32_t g = (int32_t)(((slot >> 1) - J.begin) / CAFE_TL_GROUP);
-    int32_t j = J.tl_grp[g];
-    const int32_t hi = J.tl_grp[g + 1];
-    while (j < hi && (int64_t)J.tl_slot[j] < slot) ++j;
+    // first op at or after the slot among the group's ops (up to two per position: binary search)
+    int32_t j = J.tl_grp[g], hi = J.tl_grp[g + 1];
+    while (j < hi) {
+        const int32_t mid = (j + hi) >> 1;
+        if ((int64_t)J.tl_slot[mid] < slot) j = mid + 1; else hi = mid;
+    }
     if (j < n) { *size = J.tl_size[j]; *rank = J.tl_rank[j]; }
     else { *size = J.tl_head[1]; *rank = J.tl_head[2]; }
 }
@@ -536,12 +539,14 @@ struct CafeLruReplay {
 #pragma unroll
         for (int q = 0; q < CAFE_SLOTS; ++q) if (q == slot) { b.val[q] = v; b.cnt[q] = c; b.dic[q] = d; b.t[q] = tt; }
     }
-    CAFE_HD void emit(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic) {
+    // `pre_ev` / `pre_ins`: the event and the ins_res the previous round left for this position, if the caller has
+    // loaded them already (a warp loads them for 32 misses at once); null = read here
+    CAFE_HD void emit(const CafeJob& J, int p, uint32_t kind, uint32_t x, float cnt, int32_t dic, const CafeEvent* pre_ev) {
         if (J.first_round) {
             if (kind == CAFE_EV_NONE) return;   // events of the window are cleared before the first round
             J.res->changed = 1;
         } else {
-            const CafeEvent o = J.ev[p];
+            const CafeEvent o = pre_ev ? *pre_ev : J.ev[p];
             bool same;
             if (kind == CAFE_EV_NONE) same = (o.kind == CAFE_EV_NONE);
             else same = (o.kind == kind && o.x == x && o.dic == dic && cafe_float_bits(o.cnt) == cafe_float_bits(cnt));
@@ -554,7 +559,8 @@ struct CafeLruReplay {
         J.ev[p] = e;
     }
     // a lookup at position p (ascending) that missed the main table
-    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c) {
+    CAFE_HD void feed(const CafeJob& J, int p, uint32_t x, float c, const CafeEvent* pre_ev = nullptr,
+                      const int32_t* pre_ins = nullptr) {
         if (!touched) { cafe_touch(b, J.gflip); touched = true; }
         const int32_t tp = J.t0 + 1 + p;
         int hit = -1, vic = -1, t_min = 1000000000;
@@ -581,13 +587,13 @@ struct CafeLruReplay {
             }
             if (cn >= J.thr) {
                 ++n_ev;
-                emit(J, p, CAFE_EV_OWN, x, cn, dic0);
+                emit(J, p, CAFE_EV_OWN, x, cn, dic0, pre_ev);
                 // the main pass of this round replayed the event this position carried before the round
-                if (!J.first_round && J.ins_res[p] != 0) nf &= ~(uint32_t)CAFE_F_GOT;
+                if (!J.first_round && (pre_ins ? *pre_ins : J.ins_res[p]) != 0) nf &= ~(uint32_t)CAFE_F_GOT;
                 set(hit, 0u, 0.0f, 0, 0);   // the slot is cleared whether or not the promotion succeeded
             } else {
                 set(hit, x, cn, dic0, tp);
-                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0, pre_ev);
             }
         } else {
             if (vic < 0) { CAFE_ATOMIC_OR(&J.res->error, 2); vic = 0; }
@@ -598,9 +604,9 @@ struct CafeLruReplay {
             for (int q = 0; q < CAFE_SLOTS; ++q) if (q == vic) { vval = b.val[q]; vcnt = b.cnt[q]; vdic = b.dic[q]; }
             if (vdic != 0 || vcnt >= 5.0f) {
                 ++n_ev;
-                emit(J, p, CAFE_EV_VICTIM, vval, vcnt, vdic);
+                emit(J, p, CAFE_EV_VICTIM, vval, vcnt, vdic, pre_ev);
             } else {
-                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0);
+                emit(J, p, CAFE_EV_NONE, 0, 0.0f, 0, pre_ev);
             }
             int32_t ndic = 0;
             if (1.0f >= J.thr && 1.0f - c < J.thr) nf |= CAFE_F_CROSS;

@@ -1029,19 +1029,33 @@ __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant_
         live = __shfl_sync(CAFE_FULL, live, 0);
         if (!live) continue;
         jb = __shfl_sync(CAFE_FULL, jb, 0); jend = __shfl_sync(CAFE_FULL, jend, 0);
-        // a chunk of 32 misses is loaded while the previous one is replayed (by lane 0, in order)
-        int p_nx = 0; uint32_t x_nx = 0; float c_nx = 1.0f;
-        if (jb + lane < jend) { const int i = L.list[jb + lane]; p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i]; }
+        // a chunk of 32 misses -- position, id, count and what the previous round left for the position -- is loaded
+        // while the previous chunk is replayed (by lane 0, in order)
+        int p_nx = 0, i_nx = 0; uint32_t x_nx = 0; float c_nx = 1.0f;
+        CafeEvent e_nx; e_nx.x = 0; e_nx.cnt = 0.f; e_nx.dic = 0; e_nx.kind = CAFE_EV_NONE;
+        if (jb + lane < jend) {
+            const int i = L.list[jb + lane];
+            p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i];
+            if (!J.first_round) { e_nx = J.ev[p_nx]; i_nx = J.ins_res[p_nx]; }
+        }
         for (int base = jb; base < jend; base += 32) {
-            const int p = p_nx; const uint32_t x = x_nx; const float c = c_nx;
+            const int p = p_nx, ins = i_nx; const uint32_t x = x_nx; const float c = c_nx; const CafeEvent ev = e_nx;
             c_nx = 1.0f;
-            if (base + 32 + lane < jend) { const int i = L.list[base + 32 + lane]; p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i]; }
+            if (base + 32 + lane < jend) {
+                const int i = L.list[base + 32 + lane];
+                p_nx = J.ord2[i]; x_nx = J.sgid2[i]; if (J.simp2) c_nx = J.simp2[i];
+                if (!J.first_round) { e_nx = J.ev[p_nx]; i_nx = J.ins_res[p_nx]; }
+            }
             const int n = min(32, jend - base);
             for (int t = 0; t < n; ++t) {
                 const int pj = __shfl_sync(CAFE_FULL, p, t);
                 const uint32_t xj = __shfl_sync(CAFE_FULL, x, t);
                 const float cj = __shfl_sync(CAFE_FULL, c, t);
-                if (lane == 0) R.feed(J, pj, xj, cj);
+                CafeEvent ej;
+                ej.x = __shfl_sync(CAFE_FULL, ev.x, t); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, t);
+                ej.dic = __shfl_sync(CAFE_FULL, ev.dic, t); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, t);
+                const int32_t ij = __shfl_sync(CAFE_FULL, ins, t);
+                if (lane == 0) R.feed(J, pj, xj, cj, &ej, &ij);
             }
         }
         if (lane == 0) R.finish(J);
