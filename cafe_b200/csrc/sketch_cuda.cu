@@ -255,9 +255,13 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
         float c_nx = 1.0f;
         if (s + lane < e) { x_nx = J.sgid1[s + lane]; if (J.simp1) c_nx = J.simp1[s + lane]; }
         if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
-        bool last_calm = false;   // the previous chunk went through the calm whole-chunk path
+        // Number of chunks in a row that went through the calm whole-chunk path.  Every eighth one looks 512 lookups
+        // ahead (one id, one position); if that lookup still belongs to the stretch, the next chunk starts the
+        // four-chunk path below.  Shorter stretches stay on the chunk path, which needs no start-up loads.
+        int calm_streak = 0, far_at = -1, far_p = INT32_MAX;
+        uint32_t far_x = 0;
         for (int base = s; base < e && !stop; base += 32) {
-            if (last_calm && e - base >= 128) {
+            if (far_at == base && far_x == hx && far_p < hbound && e - base >= 128) {
                 // A long calm stretch (the head ids of a skewed field have thousands of lookups per call)
                 // goes four chunks at a time: every lane holds four lookups, the conditions of the calm
                 // whole-chunk path are checked for all 128, and the 128 counts are added in order by one
@@ -362,7 +366,8 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     p_n2 = cp[1];
                 }
             }
-            last_calm = false;
+            const int streak_in = calm_streak;
+            calm_streak = 0;
             const int p = p_nx;
             const uint32_t x = x_nx, ok = ok_nx, of = of_nx;
             const float c = c_nx;
@@ -411,7 +416,10 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     }
                 }
                 __syncwarp();
-                last_calm = calm;
+                calm_streak = calm ? streak_in + 1 : 0;
+                if (calm && (calm_streak & 7) == 0 && base + 32 + 511 < e) {
+                    far_at = base + 32; far_x = J.sgid1[far_at + 511]; far_p = J.ord1[far_at + 511];
+                }
                 if (lane == o) {
 #pragma unroll
                     for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hslot) R.b.cnt[q] = acc;
@@ -483,16 +491,26 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                 if (run >= 2) {
                     a0 = __shfl_sync(CAFE_FULL, a0, o); a1 = __shfl_sync(CAFE_FULL, a1, o);
                     a2 = __shfl_sync(CAFE_FULL, a2, o); a3 = __shfl_sync(CAFE_FULL, a3, o);
-                    float my_acc = 0.f;
-                    for (int u = j; u < j + run; ++u) {
-                        const float cu = __shfl_sync(CAFE_FULL, c, u);
-                        const int su = __shfl_sync(CAFE_FULL, ms, u);
-                        if (su < 0) continue;   // a miss riding along (warp-uniform)
-                        float t = (su == 0) ? a0 : (su == 1) ? a1 : (su == 2) ? a2 : a3;
-                        t = t + cu;
-                        if (su == 0) a0 = t; else if (su == 1) a1 = t; else if (su == 2) a2 = t; else a3 = t;
-                        if (lane == u) my_acc = t;
+                    // Every lane adds up the counts of its own slot's lookups from the run's start to itself, in
+                    // order, starting from the slot's count: the same additions in the same order as the replay,
+                    // without a cross-lane chain.  The 32 counts are read back from shared memory as 8 broadcast
+                    // 16-byte loads; `same` has a bit for every lane of the run whose id sits in this lane's slot.
+                    float my_acc = (ms == 0) ? a0 : (ms == 1) ? a1 : (ms == 2) ? a2 : a3;
+                    const unsigned same = __match_any_sync(CAFE_FULL, ms) & (0xffffffffu << j) & (0xffffffffu >> (31 - lane));
+                    s_c[wib][lane] = c;
+                    __syncwarp();
+                    {
+                        const float4* cv = reinterpret_cast<const float4*>(s_c[wib]);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 t = cv[q];
+                            if (same & (1u << (4 * q))) my_acc = my_acc + t.x;
+                            if (same & (2u << (4 * q))) my_acc = my_acc + t.y;
+                            if (same & (4u << (4 * q))) my_acc = my_acc + t.z;
+                            if (same & (8u << (4 * q))) my_acc = my_acc + t.w;
+                        }
                     }
+                    __syncwarp();
                     const bool in_run = lane >= j && lane < j + run;
                     const bool has_row = ms >= 0 && ((rowmask >> ms) & 1) != 0;
                     const bool cd = ms >= 0 && !has_row && my_acc >= J.thr;   // pop candidate (sketch.cpp:221) ...
@@ -600,8 +618,104 @@ __global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_consta
     }
 }
 
+// Replays the main-table misses held by the lanes of `mm` (one lookup per lane, positions ascending with the lane) into
+// the LRU bucket that lane `o` owns.  Consecutive misses whose ids all sit in the bucket and whose counts stay below
+// the threshold only add to their slots' counts and refresh the slots' clocks (sketch.cpp:236-249 without the
+// promotion): such a run is applied by the warp at once -- every lane adds up the counts of its own slot's lookups
+// from the run's start to itself, in order -- and ends before the first lookup that reaches the threshold or whose id
+// is not in the bucket; that one goes through the full replay on the owner lane.  `kind` is the kind of the event the
+// previous round left at the lane's position (unused in a first round); `ev` / `ins` are passed to the full replay
+// when the caller holds them (HAVE_EV).
+template <bool HAVE_EV>
+__device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruReplay& R, unsigned mm, const int o, const int lane,
+                                                    const int p, const uint32_t x, const float c, const uint32_t kind,
+                                                    const CafeEvent& ev, const int32_t ins, float* s_c) {
+    while (mm) {
+        const int j = __ffs(mm) - 1;
+        bool applied = false;
+        if (mm & (mm - 1)) {   // at least two misses left
+            int tch = 0;
+            uint32_t v0 = 0, v1 = 0, v2 = 0, v3 = 0;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            if (lane == o) {
+                tch = R.touched ? 1 : 0;
+                v0 = R.b.val[0]; v1 = R.b.val[1]; v2 = R.b.val[2]; v3 = R.b.val[3];
+                a0 = R.b.cnt[0]; a1 = R.b.cnt[1]; a2 = R.b.cnt[2]; a3 = R.b.cnt[3];
+            }
+            tch = __shfl_sync(CAFE_FULL, tch, o);
+            if (tch) {
+                v0 = __shfl_sync(CAFE_FULL, v0, o); v1 = __shfl_sync(CAFE_FULL, v1, o);
+                v2 = __shfl_sync(CAFE_FULL, v2, o); v3 = __shfl_sync(CAFE_FULL, v3, o);
+                const int ms = (x == v0) ? 0 : (x == v1) ? 1 : (x == v2) ? 2 : (x == v3) ? 3 : -1;   // lowest matching slot
+                const unsigned bad = mm & ~__ballot_sync(CAFE_FULL, ms >= 0);
+                const unsigned runm = bad ? (mm & ((1u << (__ffs(bad) - 1)) - 1u)) : mm;
+                if (runm & (runm - 1)) {
+                    a0 = __shfl_sync(CAFE_FULL, a0, o); a1 = __shfl_sync(CAFE_FULL, a1, o);
+                    a2 = __shfl_sync(CAFE_FULL, a2, o); a3 = __shfl_sync(CAFE_FULL, a3, o);
+                    float my_acc = (ms == 0) ? a0 : (ms == 1) ? a1 : (ms == 2) ? a2 : a3;
+                    const unsigned same = __match_any_sync(CAFE_FULL, ms) & runm & (0xffffffffu >> (31 - lane));
+                    s_c[lane] = c;
+                    __syncwarp();
+                    {
+                        const float4* cv = reinterpret_cast<const float4*>(s_c);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const float4 t = cv[q];
+                            if (same & (1u << (4 * q))) my_acc = my_acc + t.x;
+                            if (same & (2u << (4 * q))) my_acc = my_acc + t.y;
+                            if (same & (4u << (4 * q))) my_acc = my_acc + t.z;
+                            if (same & (8u << (4 * q))) my_acc = my_acc + t.w;
+                        }
+                    }
+                    __syncwarp();
+                    const bool in_run = (runm >> lane) & 1u;
+                    const unsigned hot = __ballot_sync(CAFE_FULL, in_run && my_acc >= J.thr);
+                    const unsigned dm = hot ? (runm & ((1u << (__ffs(hot) - 1)) - 1u)) : runm;
+                    if (dm) {
+                        const bool in_done = (dm >> lane) & 1u;
+                        const unsigned l0 = __ballot_sync(CAFE_FULL, in_done && ms == 0), l1 = __ballot_sync(CAFE_FULL, in_done && ms == 1);
+                        const unsigned l2 = __ballot_sync(CAFE_FULL, in_done && ms == 2), l3 = __ballot_sync(CAFE_FULL, in_done && ms == 3);
+                        const int w0 = l0 ? 31 - __clz(l0) : 0, w1 = l1 ? 31 - __clz(l1) : 0;
+                        const int w2 = l2 ? 31 - __clz(l2) : 0, w3 = l3 ? 31 - __clz(l3) : 0;
+                        const float e0 = __shfl_sync(CAFE_FULL, my_acc, w0), e1 = __shfl_sync(CAFE_FULL, my_acc, w1);
+                        const float e2 = __shfl_sync(CAFE_FULL, my_acc, w2), e3 = __shfl_sync(CAFE_FULL, my_acc, w3);
+                        const int q0 = __shfl_sync(CAFE_FULL, p, w0), q1 = __shfl_sync(CAFE_FULL, p, w1);
+                        const int q2 = __shfl_sync(CAFE_FULL, p, w2), q3 = __shfl_sync(CAFE_FULL, p, w3);
+                        if (lane == o) {
+                            if (l0) { R.b.cnt[0] = e0; R.b.t[0] = J.t0 + 1 + q0; }
+                            if (l1) { R.b.cnt[1] = e1; R.b.t[1] = J.t0 + 1 + q1; }
+                            if (l2) { R.b.cnt[2] = e2; R.b.t[2] = J.t0 + 1 + q2; }
+                            if (l3) { R.b.cnt[3] = e3; R.b.t[3] = J.t0 + 1 + q3; }
+                        }
+                        if (in_done) {   // a hit below the threshold: no flags, no event
+                            if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                            J.lflag[p] = 0;
+                        }
+                        mm &= ~dm;
+                        applied = true;
+                    }
+                }
+            }
+        }
+        if (!applied) {
+            mm &= mm - 1;
+            const int pj = __shfl_sync(CAFE_FULL, p, j);
+            const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
+            const float cj = __shfl_sync(CAFE_FULL, c, j);
+            if (HAVE_EV) {
+                CafeEvent ej;
+                ej.x = __shfl_sync(CAFE_FULL, ev.x, j); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, j);
+                ej.dic = __shfl_sync(CAFE_FULL, ev.dic, j); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, j);
+                const int32_t ij = __shfl_sync(CAFE_FULL, ins, j);
+                if (lane == o) R.feed(J, pj, xj, cj, &ej, &ij);
+            } else {
+                if (lane == o) R.feed(J, pj, xj, cj);
+            }
+        }
+    }
+}
 template <int PART>
-__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k) {
+__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k, float* s_c) {
     const int lane = threadIdx.x & 31;
     CafeLruReplay R;
     int jb = 0, jend = 0;
@@ -660,8 +774,10 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
         // hit the main table; a group without misses costs eight ballots.
         constexpr int GL = 8;
         int p0[GL], p1[GL], p2[GL], p3[GL];
-        uint32_t f0[GL], f1[GL], f2[GL], x0[GL], x1[GL];
+        uint32_t f0[GL], f1[GL], f2[GL], x0[GL], x1[GL], k0[GL], k1[GL];   // k: kind of the event left at a miss's position
         float c0[GL], c1[GL];
+        CafeEvent no_ev;
+        no_ev.x = 0; no_ev.cnt = 0.f; no_ev.dic = 0; no_ev.kind = CAFE_EV_NONE;
 #pragma unroll
         for (int q = 0; q < GL; ++q) {
             const int i0 = s + 32 * q + lane, i1 = i0 + 32 * GL, i2 = i1 + 32 * GL;
@@ -676,8 +792,11 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
         }
 #pragma unroll
         for (int q = 0; q < GL; ++q) {
-            x0[q] = 0; c0[q] = 1.0f;
-            if (f0[q] & CAFE_F_MISS) { x0[q] = J.sgid2[s + 32 * q + lane]; if (J.simp2) c0[q] = J.simp2[s + 32 * q + lane]; }
+            x0[q] = 0; c0[q] = 1.0f; k0[q] = CAFE_EV_NONE;
+            if (f0[q] & CAFE_F_MISS) {
+                x0[q] = J.sgid2[s + 32 * q + lane]; if (J.simp2) c0[q] = J.simp2[s + 32 * q + lane];
+                if (!J.first_round) k0[q] = J.ev[p0[q]].kind;
+            }
         }
         for (int base = s; base < e && !stop; base += 32 * GL) {
 #pragma unroll
@@ -685,10 +804,11 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
                 const int i3 = base + 3 * 32 * GL + 32 * q + lane;
                 p3[q] = i3 < e ? J.ord2[i3] : INT32_MAX;
                 f2[q] = p2[q] < J.limit ? (uint32_t)J.mflag[p2[q]] : 0u;
-                x1[q] = 0; c1[q] = 1.0f;
+                x1[q] = 0; c1[q] = 1.0f; k1[q] = CAFE_EV_NONE;
                 if (f1[q] & CAFE_F_MISS) {   // (p1 was read at this index of the sorted order)
                     const int i1 = base + 32 * GL + 32 * q + lane;
                     x1[q] = J.sgid2[i1]; if (J.simp2) c1[q] = J.simp2[i1];
+                    if (!J.first_round) k1[q] = J.ev[p1[q]].kind;
                 }
             }
 #pragma unroll
@@ -697,19 +817,12 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
                 const int idx = base + 32 * q + lane;
                 // positions ascend inside a bucket: once one lane sees the limit, later entries are beyond it too
                 stop = __any_sync(CAFE_FULL, idx < e && p0[q] >= J.limit);
-                unsigned mm = __ballot_sync(CAFE_FULL, (f0[q] & CAFE_F_MISS) != 0);
-                while (mm) {
-                    const int j = __ffs(mm) - 1;
-                    mm &= mm - 1;
-                    const int pj = __shfl_sync(CAFE_FULL, p0[q], j);
-                    const uint32_t xj = __shfl_sync(CAFE_FULL, x0[q], j);
-                    const float cj = __shfl_sync(CAFE_FULL, c0[q], j);
-                    if (lane == o) R.feed(J, pj, xj, cj);
-                }
+                const unsigned mm = __ballot_sync(CAFE_FULL, (f0[q] & CAFE_F_MISS) != 0);
+                cafe_lru_feed_lanes<false>(J, R, mm, o, lane, p0[q], x0[q], c0[q], k0[q], no_ev, 0, s_c);
             }
 #pragma unroll
             for (int q = 0; q < GL; ++q) {
-                p0[q] = p1[q]; f0[q] = f1[q]; x0[q] = x1[q]; c0[q] = c1[q];
+                p0[q] = p1[q]; f0[q] = f1[q]; x0[q] = x1[q]; c0[q] = c1[q]; k0[q] = k1[q];
                 p1[q] = p2[q]; f1[q] = f2[q];
                 p2[q] = p3[q];
             }
@@ -719,14 +832,15 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
 }
 template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
+    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up (list launch only)
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
-        cafe_lru_body<1>(J, H, k < J.n2 ? k : J.n2);
+        cafe_lru_body<1>(J, H, k < J.n2 ? k : J.n2, nullptr);
     } else {
         for (;;) {
             const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2);
             if (k < 0) break;
-            cafe_lru_body<0>(J, H, k);
+            cafe_lru_body<0>(J, H, k, s_c[threadIdx.x >> 5]);
         }
     }
 }
@@ -751,7 +865,7 @@ __global__ void __launch_bounds__(128, 6) k_lru_pass_sparse(const __grid_constan
     __syncwarp();
     for (int q0 = 0; q0 < nq; q0 += 32) {
         const int k = q0 + lane < nq ? s_q[wib][q0 + lane] : J.n2;
-        cafe_lru_body<1>(J, H, k);
+        cafe_lru_body<1>(J, H, k, nullptr);
     }
 }
 __global__ void k_route(const __grid_constant__ CafeJob J) {
@@ -1017,6 +1131,7 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_emit(const __grid_
     if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) L.pre[J.M] = base + tot;
 }
 __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant__ CafeJob J, const CafeMissList L) {
+    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up
     const int lane = threadIdx.x & 31;
     const int nwarps = gridDim.x * (blockDim.x >> 5);
     for (int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); k < J.n2; k += nwarps) {
@@ -1030,7 +1145,7 @@ __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant_
         if (!live) continue;
         jb = __shfl_sync(CAFE_FULL, jb, 0); jend = __shfl_sync(CAFE_FULL, jend, 0);
         // a chunk of 32 misses -- position, id, count and what the previous round left for the position -- is loaded
-        // while the previous chunk is replayed (by lane 0, in order)
+        // while the previous chunk is replayed
         int p_nx = 0, i_nx = 0; uint32_t x_nx = 0; float c_nx = 1.0f;
         CafeEvent e_nx; e_nx.x = 0; e_nx.cnt = 0.f; e_nx.dic = 0; e_nx.kind = CAFE_EV_NONE;
         if (jb + lane < jend) {
@@ -1047,16 +1162,8 @@ __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant_
                 if (!J.first_round) { e_nx = J.ev[p_nx]; i_nx = J.ins_res[p_nx]; }
             }
             const int n = min(32, jend - base);
-            for (int t = 0; t < n; ++t) {
-                const int pj = __shfl_sync(CAFE_FULL, p, t);
-                const uint32_t xj = __shfl_sync(CAFE_FULL, x, t);
-                const float cj = __shfl_sync(CAFE_FULL, c, t);
-                CafeEvent ej;
-                ej.x = __shfl_sync(CAFE_FULL, ev.x, t); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, t);
-                ej.dic = __shfl_sync(CAFE_FULL, ev.dic, t); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, t);
-                const int32_t ij = __shfl_sync(CAFE_FULL, ins, t);
-                if (lane == 0) R.feed(J, pj, xj, cj, &ej, &ij);
-            }
+            cafe_lru_feed_lanes<true>(J, R, n == 32 ? 0xffffffffu : ((1u << n) - 1u), 0, lane, p, x, c, ev.kind, ev, ins,
+                                      s_c[threadIdx.x >> 5]);
         }
         if (lane == 0) R.finish(J);
     }
