@@ -255,9 +255,11 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
         float c_nx = 1.0f;
         if (s + lane < e) { x_nx = J.sgid1[s + lane]; if (J.simp1) c_nx = J.simp1[s + lane]; }
         if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
-        // Number of chunks in a row that went through the calm whole-chunk path.  Every eighth one looks 512 lookups
-        // ahead (one id, one position); if that lookup still belongs to the stretch, the next chunk starts the
-        // four-chunk path below.  Shorter stretches stay on the chunk path, which needs no start-up loads.
+        // Number of chunks in a row that went through the calm whole-chunk path.  A calm chunk that ends on a multiple
+        // of 256 entries of the bucket looks 512 lookups ahead (one id, one position); if that lookup still belongs
+        // to the stretch, the next chunk starts the four-chunk path below.  Shorter stretches stay on the chunk path,
+        // which needs no start-up loads.  (Starting points on a fixed grid: a later round that differs in the lookups
+        // before the stretch still starts at the same entry and finds what the earlier round remembered.)
         int calm_streak = 0, far_at = -1, far_p = INT32_MAX;
         uint32_t far_x = 0;
         for (int base = s; base < e && !stop; base += 32) {
@@ -417,7 +419,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                 }
                 __syncwarp();
                 calm_streak = calm ? streak_in + 1 : 0;
-                if (calm && (calm_streak & 7) == 0 && base + 32 + 511 < e) {
+                if (calm && calm_streak >= 2 && ((base + 32 - s) & 255) == 0 && base + 32 + 511 < e) {
                     far_at = base + 32; far_x = J.sgid1[far_at + 511]; far_p = J.ord1[far_at + 511];
                 }
                 if (lane == o) {
@@ -619,98 +621,130 @@ __global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_consta
 }
 
 // Replays the main-table misses held by the lanes of `mm` (one lookup per lane, positions ascending with the lane) into
-// the LRU bucket that lane `o` owns.  Consecutive misses whose ids all sit in the bucket and whose counts stay below
-// the threshold only add to their slots' counts and refresh the slots' clocks (sketch.cpp:236-249 without the
-// promotion): such a run is applied by the warp at once -- every lane adds up the counts of its own slot's lookups
-// from the run's start to itself, in order -- and ends before the first lookup that reaches the threshold or whose id
-// is not in the bucket; that one goes through the full replay on the owner lane.  `kind` is the kind of the event the
-// previous round left at the lane's position (unused in a first round); `ev` / `ins` are passed to the full replay
-// when the caller holds them (HAVE_EV).
+// an LRU bucket.  Every lane of the warp holds the same copy of the bucket's replay state R and runs the same
+// steps, so nothing has to travel between lanes except the lookup itself.  The two common outcomes are handled in
+// line: a hit that stays below the threshold (count and clock of the slot change, sketch.cpp:236-249 without the
+// promotion) and a miss whose victim leaves no trace (no row, count below 5, no free row to ask for:
+// sketch.cpp:252-268).  Both write no flags and clear the event of the position; the lane that holds the lookup
+// does those writes.  Everything else -- promotions, victims with a row, candidates for a free row -- goes through
+// the full replay on lane `o`, whose state is then copied to the other lanes.  Before a lookup is taken on its own, the
+// warp checks whether it starts a run of hits: consecutive misses of the list whose ids all sit in the bucket.  Such a
+// run is applied at once, up to the first lookup that reaches the threshold: every lane adds up the counts of its own
+// slot's lookups from the run's start to itself, in order (the same additions as the replay makes), and the last
+// lookup of every slot leaves the slot's count and clock.  `kind` is the kind of the event the previous round left at
+// the lane's position (unused in a first round); `ev` / `ins` are handed to the full replay when the caller has
+// loaded them (HAVE_EV); `s_c` is room for 32 counts of this warp in shared memory.  `gate` (kept by the caller per
+// bucket) holds back the check for runs after it has failed: buckets whose misses rarely come as runs of hits
+// then pay for the check on every ninth lookup at most.
+struct CafeRunGate { int skip = 0, len = 0; };
 template <bool HAVE_EV>
 __device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruReplay& R, unsigned mm, const int o, const int lane,
                                                     const int p, const uint32_t x, const float c, const uint32_t kind,
-                                                    const CafeEvent& ev, const int32_t ins, float* s_c) {
+                                                    const CafeEvent& ev, const int32_t ins, float* s_c, CafeRunGate& gate) {
     while (mm) {
         const int j = __ffs(mm) - 1;
-        bool applied = false;
-        if (mm & (mm - 1)) {   // at least two misses left
-            int tch = 0;
-            uint32_t v0 = 0, v1 = 0, v2 = 0, v3 = 0;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            if (lane == o) {
-                tch = R.touched ? 1 : 0;
-                v0 = R.b.val[0]; v1 = R.b.val[1]; v2 = R.b.val[2]; v3 = R.b.val[3];
-                a0 = R.b.cnt[0]; a1 = R.b.cnt[1]; a2 = R.b.cnt[2]; a3 = R.b.cnt[3];
-            }
-            tch = __shfl_sync(CAFE_FULL, tch, o);
-            if (tch) {
-                v0 = __shfl_sync(CAFE_FULL, v0, o); v1 = __shfl_sync(CAFE_FULL, v1, o);
-                v2 = __shfl_sync(CAFE_FULL, v2, o); v3 = __shfl_sync(CAFE_FULL, v3, o);
-                const int ms = (x == v0) ? 0 : (x == v1) ? 1 : (x == v2) ? 2 : (x == v3) ? 3 : -1;   // lowest matching slot
-                const unsigned bad = mm & ~__ballot_sync(CAFE_FULL, ms >= 0);
-                const unsigned runm = bad ? (mm & ((1u << (__ffs(bad) - 1)) - 1u)) : mm;
-                if (runm & (runm - 1)) {
-                    a0 = __shfl_sync(CAFE_FULL, a0, o); a1 = __shfl_sync(CAFE_FULL, a1, o);
-                    a2 = __shfl_sync(CAFE_FULL, a2, o); a3 = __shfl_sync(CAFE_FULL, a3, o);
-                    float my_acc = (ms == 0) ? a0 : (ms == 1) ? a1 : (ms == 2) ? a2 : a3;
-                    const unsigned same = __match_any_sync(CAFE_FULL, ms) & runm & (0xffffffffu >> (31 - lane));
-                    s_c[lane] = c;
-                    __syncwarp();
-                    {
-                        const float4* cv = reinterpret_cast<const float4*>(s_c);
+        if (gate.skip > 0) --gate.skip;
+        else if (R.touched && (mm & (mm - 1))) {
+            const int ms = (x == R.b.val[0]) ? 0 : (x == R.b.val[1]) ? 1 : (x == R.b.val[2]) ? 2 : (x == R.b.val[3]) ? 3 : -1;
+            const unsigned bad = mm & ~__ballot_sync(CAFE_FULL, ms >= 0);
+            const unsigned runm = bad ? (mm & ((1u << (__ffs(bad) - 1)) - 1u)) : mm;
+            if (runm & (runm - 1)) {   // at least two hits in a row
+                float my_acc = (ms == 0) ? R.b.cnt[0] : (ms == 1) ? R.b.cnt[1] : (ms == 2) ? R.b.cnt[2] : R.b.cnt[3];
+                const unsigned same = __match_any_sync(CAFE_FULL, ms) & runm & (0xffffffffu >> (31 - lane));
+                s_c[lane] = c;
+                __syncwarp();
+                {
+                    const float4* cv = reinterpret_cast<const float4*>(s_c);
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            const float4 t = cv[q];
-                            if (same & (1u << (4 * q))) my_acc = my_acc + t.x;
-                            if (same & (2u << (4 * q))) my_acc = my_acc + t.y;
-                            if (same & (4u << (4 * q))) my_acc = my_acc + t.z;
-                            if (same & (8u << (4 * q))) my_acc = my_acc + t.w;
-                        }
-                    }
-                    __syncwarp();
-                    const bool in_run = (runm >> lane) & 1u;
-                    const unsigned hot = __ballot_sync(CAFE_FULL, in_run && my_acc >= J.thr);
-                    const unsigned dm = hot ? (runm & ((1u << (__ffs(hot) - 1)) - 1u)) : runm;
-                    if (dm) {
-                        const bool in_done = (dm >> lane) & 1u;
-                        const unsigned l0 = __ballot_sync(CAFE_FULL, in_done && ms == 0), l1 = __ballot_sync(CAFE_FULL, in_done && ms == 1);
-                        const unsigned l2 = __ballot_sync(CAFE_FULL, in_done && ms == 2), l3 = __ballot_sync(CAFE_FULL, in_done && ms == 3);
-                        const int w0 = l0 ? 31 - __clz(l0) : 0, w1 = l1 ? 31 - __clz(l1) : 0;
-                        const int w2 = l2 ? 31 - __clz(l2) : 0, w3 = l3 ? 31 - __clz(l3) : 0;
-                        const float e0 = __shfl_sync(CAFE_FULL, my_acc, w0), e1 = __shfl_sync(CAFE_FULL, my_acc, w1);
-                        const float e2 = __shfl_sync(CAFE_FULL, my_acc, w2), e3 = __shfl_sync(CAFE_FULL, my_acc, w3);
-                        const int q0 = __shfl_sync(CAFE_FULL, p, w0), q1 = __shfl_sync(CAFE_FULL, p, w1);
-                        const int q2 = __shfl_sync(CAFE_FULL, p, w2), q3 = __shfl_sync(CAFE_FULL, p, w3);
-                        if (lane == o) {
-                            if (l0) { R.b.cnt[0] = e0; R.b.t[0] = J.t0 + 1 + q0; }
-                            if (l1) { R.b.cnt[1] = e1; R.b.t[1] = J.t0 + 1 + q1; }
-                            if (l2) { R.b.cnt[2] = e2; R.b.t[2] = J.t0 + 1 + q2; }
-                            if (l3) { R.b.cnt[3] = e3; R.b.t[3] = J.t0 + 1 + q3; }
-                        }
-                        if (in_done) {   // a hit below the threshold: no flags, no event
-                            if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
-                            J.lflag[p] = 0;
-                        }
-                        mm &= ~dm;
-                        applied = true;
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 t = cv[q];
+                        if (same & (1u << (4 * q))) my_acc = my_acc + t.x;
+                        if (same & (2u << (4 * q))) my_acc = my_acc + t.y;
+                        if (same & (4u << (4 * q))) my_acc = my_acc + t.z;
+                        if (same & (8u << (4 * q))) my_acc = my_acc + t.w;
                     }
                 }
+                __syncwarp();
+                const bool in_run = (runm >> lane) & 1u;
+                const unsigned hot = __ballot_sync(CAFE_FULL, in_run && my_acc >= J.thr);
+                const unsigned dm = hot ? (runm & ((1u << (__ffs(hot) - 1)) - 1u)) : runm;
+                if (dm) {
+                    const bool in_done = (dm >> lane) & 1u;
+#pragma unroll
+                    for (int q = 0; q < CAFE_SLOTS; ++q) {
+                        const unsigned lq = __ballot_sync(CAFE_FULL, in_done && ms == q);
+                        const int w = lq ? 31 - __clz(lq) : 0;   // the slot's last lookup of the run
+                        const float eq = __shfl_sync(CAFE_FULL, my_acc, w);
+                        const int pq = __shfl_sync(CAFE_FULL, p, w);
+                        if (lq) { R.b.cnt[q] = eq; R.b.t[q] = J.t0 + 1 + pq; }
+                    }
+                    if (in_done) {   // a hit below the threshold: no flags, no event
+                        if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                        J.lflag[p] = 0;
+                    }
+                    mm &= ~dm;
+                    gate.len = 0;
+                    continue;
+                }
+            }
+            gate.len = gate.len == 0 ? 1 : (gate.len >= 8 ? 8 : 2 * gate.len);
+            gate.skip = gate.len;
+        }
+        mm &= mm - 1;
+        const int pj = __shfl_sync(CAFE_FULL, p, j);
+        const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
+        const float cj = __shfl_sync(CAFE_FULL, c, j);
+        if (!R.touched) { cafe_touch(R.b, J.gflip); R.touched = true; }
+        const int32_t tp = J.t0 + 1 + pj;
+        int hit = -1, vic = -1, t_min = 1000000000;
+#pragma unroll
+        for (int q = 0; q < CAFE_SLOTS; ++q) {
+            if (hit < 0) {
+                if (R.b.val[q] == xj) hit = q;
+                else if (t_min > R.b.t[q]) { t_min = R.b.t[q]; vic = q; }
             }
         }
-        if (!applied) {
-            mm &= mm - 1;
-            const int pj = __shfl_sync(CAFE_FULL, p, j);
-            const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
-            const float cj = __shfl_sync(CAFE_FULL, c, j);
-            if (HAVE_EV) {
-                CafeEvent ej;
-                ej.x = __shfl_sync(CAFE_FULL, ev.x, j); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, j);
-                ej.dic = __shfl_sync(CAFE_FULL, ev.dic, j); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, j);
-                const int32_t ij = __shfl_sync(CAFE_FULL, ins, j);
-                if (lane == o) R.feed(J, pj, xj, cj, &ej, &ij);
-            } else {
-                if (lane == o) R.feed(J, pj, xj, cj);
+        bool fast = false;
+        if (hit >= 0) {
+            float cnt0 = 0.f;
+#pragma unroll
+            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hit) cnt0 = R.b.cnt[q];
+            const float cn = cnt0 + cj;
+            if (!(cn >= J.thr)) {
+#pragma unroll
+                for (int q = 0; q < CAFE_SLOTS; ++q) if (q == hit) { R.b.cnt[q] = cn; R.b.t[q] = tp; }
+                fast = true;
             }
+        } else if (vic >= 0 && !(1.0f >= J.thr)) {
+            float vcnt = 0.f;
+            int32_t vdic = 0;
+#pragma unroll
+            for (int q = 0; q < CAFE_SLOTS; ++q) if (q == vic) { vcnt = R.b.cnt[q]; vdic = R.b.dic[q]; }
+            if (vdic == 0 && !(vcnt >= 5.0f)) {
+                R.set(vic, xj, 1.0f, 0, tp);
+                fast = true;
+            }
+        }
+        if (fast) {
+            if (lane == j) {
+                if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                J.lflag[p] = 0;
+            }
+            continue;
+        }
+        if (HAVE_EV) {
+            CafeEvent ej;
+            ej.x = __shfl_sync(CAFE_FULL, ev.x, j); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, j);
+            ej.dic = __shfl_sync(CAFE_FULL, ev.dic, j); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, j);
+            const int32_t ij = __shfl_sync(CAFE_FULL, ins, j);
+            if (lane == o) R.feed(J, pj, xj, cj, &ej, &ij);
+        } else {
+            if (lane == o) R.feed(J, pj, xj, cj);
+        }
+#pragma unroll
+        for (int q = 0; q < CAFE_SLOTS; ++q) {
+            R.b.val[q] = __shfl_sync(CAFE_FULL, R.b.val[q], o); R.b.cnt[q] = __shfl_sync(CAFE_FULL, R.b.cnt[q], o);
+            R.b.dic[q] = __shfl_sync(CAFE_FULL, R.b.dic[q], o); R.b.t[q] = __shfl_sync(CAFE_FULL, R.b.t[q], o);
         }
     }
 }
@@ -767,6 +801,10 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
         m &= m - 1;
         const int s = __shfl_sync(CAFE_FULL, jb, o), e = __shfl_sync(CAFE_FULL, jend, o);
         bool stop = false;
+        // every lane gets its own copy of the bucket's replay state (reads only); lane o writes the result back
+        CafeLruReplay W;
+        W.init(J, __shfl_sync(CAFE_FULL, k, o));
+        CafeRunGate gate;
         // Three-stage pipeline at a granularity of eight chunks (256 entries, eight per lane): positions
         // are requested three groups ahead, the flags of those positions two groups ahead, ids and counts
         // of the misses among them one group ahead, so that every load has a whole iteration to arrive
@@ -818,7 +856,7 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
                 // positions ascend inside a bucket: once one lane sees the limit, later entries are beyond it too
                 stop = __any_sync(CAFE_FULL, idx < e && p0[q] >= J.limit);
                 const unsigned mm = __ballot_sync(CAFE_FULL, (f0[q] & CAFE_F_MISS) != 0);
-                cafe_lru_feed_lanes<false>(J, R, mm, o, lane, p0[q], x0[q], c0[q], k0[q], no_ev, 0, s_c);
+                cafe_lru_feed_lanes<false>(J, W, mm, o, lane, p0[q], x0[q], c0[q], k0[q], no_ev, 0, s_c, gate);
             }
 #pragma unroll
             for (int q = 0; q < GL; ++q) {
@@ -827,12 +865,13 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
                 p2[q] = p3[q];
             }
         }
+        if (lane == o) W.finish(J);
     }
-    if (live) R.finish(J);
+    if (PART == 1 && live) R.finish(J);
 }
 template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
-    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up (list launch only)
+    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of a run being added up (list launch only)
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
         cafe_lru_body<1>(J, H, k < J.n2 ? k : J.n2, nullptr);
@@ -1131,19 +1170,14 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_emit(const __grid_
     if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) L.pre[J.M] = base + tot;
 }
 __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant__ CafeJob J, const CafeMissList L) {
-    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of the chunk being added up
+    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of a run being added up
     const int lane = threadIdx.x & 31;
     const int nwarps = gridDim.x * (blockDim.x >> 5);
     for (int k = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); k < J.n2; k += nwarps) {
-        CafeLruReplay R;
-        int live = 0, jb = 0, jend = 0;
-        if (lane == 0) {
-            live = R.init(J, k) ? 1 : 0;
-            if (live) { jb = L.pre[J.start2[k]]; jend = L.pre[J.start2[k + 1]]; }
-        }
-        live = __shfl_sync(CAFE_FULL, live, 0);
-        if (!live) continue;
-        jb = __shfl_sync(CAFE_FULL, jb, 0); jend = __shfl_sync(CAFE_FULL, jend, 0);
+        CafeLruReplay R;   // the same in every lane
+        if (!R.init(J, k)) continue;
+        const int jb = L.pre[J.start2[k]], jend = L.pre[J.start2[k + 1]];
+        CafeRunGate gate;
         // a chunk of 32 misses -- position, id, count and what the previous round left for the position -- is loaded
         // while the previous chunk is replayed
         int p_nx = 0, i_nx = 0; uint32_t x_nx = 0; float c_nx = 1.0f;
@@ -1163,7 +1197,7 @@ __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant_
             }
             const int n = min(32, jend - base);
             cafe_lru_feed_lanes<true>(J, R, n == 32 ? 0xffffffffu : ((1u << n) - 1u), 0, lane, p, x, c, ev.kind, ev, ins,
-                                      s_c[threadIdx.x >> 5]);
+                                      s_c[threadIdx.x >> 5], gate);
         }
         if (lane == 0) R.finish(J);
     }
