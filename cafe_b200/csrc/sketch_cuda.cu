@@ -620,77 +620,230 @@ __global__ void __launch_bounds__(128, 6) k_main_pass_sparse(const __grid_consta
     }
 }
 
-// Replays the main-table misses held by the lanes of `mm` (one lookup per lane, positions ascending with the lane) into
-// an LRU bucket.  Every lane of the warp holds the same copy of the bucket's replay state R and runs the same
-// steps, so nothing has to travel between lanes except the lookup itself.  The two common outcomes are handled in
-// line: a hit that stays below the threshold (count and clock of the slot change, sketch.cpp:236-249 without the
-// promotion) and a miss whose victim leaves no trace (no row, count below 5, no free row to ask for:
-// sketch.cpp:252-268).  Both write no flags and clear the event of the position; the lane that holds the lookup
-// does those writes.  Everything else -- promotions, victims with a row, candidates for a free row -- goes through
-// the full replay on lane `o`, whose state is then copied to the other lanes.  Before a lookup is taken on its own, the
-// warp checks whether it starts a run of hits: consecutive misses of the list whose ids all sit in the bucket.  Such a
-// run is applied at once, up to the first lookup that reaches the threshold: every lane adds up the counts of its own
-// slot's lookups from the run's start to itself, in order (the same additions as the replay makes), and the last
-// lookup of every slot leaves the slot's count and clock.  `kind` is the kind of the event the previous round left at
-// the lane's position (unused in a first round); `ev` / `ins` are handed to the full replay when the caller has
-// loaded them (HAVE_EV); `s_c` is room for 32 counts of this warp in shared memory.  `gate` (kept by the caller per
-// bucket) holds back the check for runs after it has failed: buckets whose misses rarely come as runs of hits
-// then pay for the check on every ninth lookup at most.
+// ---- LRU stage, a chunk of misses at a time -----------------------------------------------------------------------
+// The lanes [a, n) of a warp hold consecutive main-table misses of one LRU bucket (one lookup per lane, positions
+// ascending with the lane); every lane holds the same copy R of the bucket's replay state.
+//
+// cafe_lru_apply_chunk applies as many leading lookups as have one of the two plain outcomes -- a hit that stays below
+// the threshold (count and clock of the slot change, sketch.cpp:236-249 without the promotion) or a miss whose victim
+// leaves no trace (no row, count below 5, no free row to ask for: sketch.cpp:252-268) -- all at once, and returns the
+// first lane it did not apply.  While only such lookups happen the bucket is a plain LRU stack of depth 4, so what a
+// lookup meets does not depend on how the earlier ones were classified, only on which ids were used how recently:
+//   1. lane j's lookup is the latest use of its id as seen from lane i if j < i and the id does not occur in between;
+//      every lane collects those lanes in a bit mask (the next lane with the same id, from a match over the warp, is
+//      passed around through shared memory).  The bucket's own slots follow in order of their clocks, as far as their
+//      ids have not been used in the chunk; empty slots count as entries.
+//   2. a lookup hits if fewer than four distinct entries were used since the last use of its id (counted in the
+//      mask, plus more recent untouched slots if the id was last used before the chunk); otherwise it replaces the
+//      fourth most recent entry;
+//   3. the count an entry has after a lookup is 1 at the miss that created it (or the slot's count if it was in the
+//      bucket already) plus the counts of its later lookups, added in order by the lane itself;
+//   4. the run ends before the first hit that reaches the threshold and the first miss whose victim has a row or a
+//      count of 5 or more;
+//   5. the slot an entry sits in is the slot of the entry it replaced: pointers from lane to lane, resolved by
+//      pointer doubling; the entries that are most recent after the last applied lookup are written into their
+//      slots, and every applied lane clears the flags and the event of its position.
+// Returns `a` when nothing can be applied (the first lookup needs the full replay, or an id is 0 and would match an
+// empty slot, or a lookup of count 1 could ask for a free row).  `s_c`: 32 words of this warp in shared memory.
+__device__ __forceinline__ int cafe_lru_apply_chunk(const CafeJob& J, CafeLruReplay& R, const int a, const int n, const int lane,
+                                                    const int p, const uint32_t x, const float c, const uint32_t kind,
+                                                    float* s_c) {
+    const bool act = lane >= a && lane < n;
+    if (1.0f >= J.thr) return a;
+    if (__any_sync(CAFE_FULL, act && x == 0u)) return a;
+    // the bucket's slots from most to least recently used; equal clocks: the lower slot is replaced first
+    int Ls0 = 0, Ls1 = 0, Ls2 = 0, Ls3 = 0;
+    uint32_t Lv0 = 0, Lv1 = 0, Lv2 = 0, Lv3 = 0;
+    bool t_ok = true;
+#pragma unroll
+    for (int s = 0; s < CAFE_SLOTS; ++s) {
+        int rk = 0;
+#pragma unroll
+        for (int u = 0; u < CAFE_SLOTS; ++u)
+            if (u != s) rk += (R.b.t[u] > R.b.t[s] || (R.b.t[u] == R.b.t[s] && u > s)) ? 1 : 0;
+        if (rk == 0) { Ls0 = s; Lv0 = R.b.val[s]; }
+        if (rk == 1) { Ls1 = s; Lv1 = R.b.val[s]; }
+        if (rk == 2) { Ls2 = s; Lv2 = R.b.val[s]; }
+        if (rk == 3) { Ls3 = s; Lv3 = R.b.val[s]; }
+        t_ok = t_ok && R.b.t[s] < 1000000000;
+    }
+    if (!t_ok) return a;
+    const unsigned rangem = ((n >= 32 ? 0u : (1u << n)) - 1u) & ~((1u << a) - 1u);
+    const unsigned lt = (1u << lane) - 1u;
+    // 1. latest uses before this lane
+    const unsigned same = __match_any_sync(CAFE_FULL, x) & rangem;   // lanes of the chunk with this lane's id
+    const unsigned prevm = same & lt;
+    const int pv = prevm ? 31 - __clz(prevm) : -1;                   // the previous lookup of this id
+    const unsigned nextm = same & ~lt & ~(1u << lane);
+    reinterpret_cast<int*>(s_c)[lane] = act ? (nextm ? __ffs(nextm) - 1 : 32) : -1;
+    __syncwarp();
+    unsigned mask = 0;   // bit j: lane j < this lane holds the latest use of its id before this lane
+    {
+        const int4* nv = reinterpret_cast<const int4*>(s_c);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int4 t = nv[q];
+            if (t.x >= lane) mask |= 1u << (4 * q);
+            if (t.y >= lane) mask |= 2u << (4 * q);
+            if (t.z >= lane) mask |= 4u << (4 * q);
+            if (t.w >= lane) mask |= 8u << (4 * q);
+        }
+    }
+    __syncwarp();
+    mask &= lt;
+    const int D = __popc(mask);
+    // slots of the bucket whose ids have not been used in the chunk before this lane
+    const bool U0 = (__ballot_sync(CAFE_FULL, act && x == Lv0) & lt) == 0u, U1 = (__ballot_sync(CAFE_FULL, act && x == Lv1) & lt) == 0u;
+    const bool U2 = (__ballot_sync(CAFE_FULL, act && x == Lv2) & lt) == 0u, U3 = (__ballot_sync(CAFE_FULL, act && x == Lv3) & lt) == 0u;
+    // 2. hit or miss
+    const int ms = (x == R.b.val[0]) ? 0 : (x == R.b.val[1]) ? 1 : (x == R.b.val[2]) ? 2 : (x == R.b.val[3]) ? 3 : -1;
+    bool hit = false;
+    if (pv >= 0) hit = __popc(mask & ~((2u << pv) - 1u)) <= 3;
+    else if (ms >= 0) {
+        const int qx = ms == Ls0 ? 0 : ms == Ls1 ? 1 : ms == Ls2 ? 2 : 3;
+        const int newer = D + ((qx > 0 && U0) ? 1 : 0) + ((qx > 1 && U1) ? 1 : 0) + ((qx > 2 && U2) ? 1 : 0);
+        hit = newer <= 3;
+    }
+    // the entry a miss replaces: the fourth most recent one
+    int vw = 0;   // >= 0: last used by that lane; < 0: slot -1 - vw of the bucket as it was
+    if (D >= 4) {
+        unsigned t = mask;
+        t &= ~(1u << (31 - __clz(t))); t &= ~(1u << (31 - __clz(t))); t &= ~(1u << (31 - __clz(t)));
+        vw = 31 - __clz(t);
+    } else {
+        const int want = 4 - D;   // the want-th untouched slot in clock order
+        int seen = 0, vs = 0;
+        if (U0) { ++seen; if (seen == want) vs = Ls0; }
+        if (U1) { ++seen; if (seen == want) vs = Ls1; }
+        if (U2) { ++seen; if (seen == want) vs = Ls2; }
+        if (U3) { ++seen; if (seen == want) vs = Ls3; }
+        vw = -1 - vs;
+    }
+    // 3. the entry's count after this lookup
+    const unsigned misses = __ballot_sync(CAFE_FULL, act && !hit);
+    const unsigned upto = same & (lt | (1u << lane));
+    const unsigned sm = upto & misses;
+    const int m = sm ? 31 - __clz(sm) : -1;   // the miss that created the entry (this lane itself if it misses)
+    const unsigned chain = m >= 0 ? (upto & ~((2u << m) - 1u)) : upto;
+    float my_acc = 1.0f;
+    int32_t my_dic = 0;
+    if (m < 0) {
+        my_acc = (ms == 0) ? R.b.cnt[0] : (ms == 1) ? R.b.cnt[1] : (ms == 2) ? R.b.cnt[2] : R.b.cnt[3];
+        my_dic = (ms == 0) ? R.b.dic[0] : (ms == 1) ? R.b.dic[1] : (ms == 2) ? R.b.dic[2] : R.b.dic[3];
+    }
+    s_c[lane] = c;
+    __syncwarp();
+    {
+        const float4* cv = reinterpret_cast<const float4*>(s_c);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float4 t = cv[q];
+            if (chain & (1u << (4 * q))) my_acc = my_acc + t.x;
+            if (chain & (2u << (4 * q))) my_acc = my_acc + t.y;
+            if (chain & (4u << (4 * q))) my_acc = my_acc + t.z;
+            if (chain & (8u << (4 * q))) my_acc = my_acc + t.w;
+        }
+    }
+    __syncwarp();
+    // 4. where the run ends
+    const float vc_l = __shfl_sync(CAFE_FULL, my_acc, vw >= 0 ? vw : 0);
+    const int32_t vd_l = __shfl_sync(CAFE_FULL, my_dic, vw >= 0 ? vw : 0);
+    bool plain;
+    if (hit) plain = !(my_acc >= J.thr) && (m >= 0 || ms >= 0);
+    else {
+        const int vs = -1 - vw;
+        const float vc = vw >= 0 ? vc_l : (vs == 0 ? R.b.cnt[0] : vs == 1 ? R.b.cnt[1] : vs == 2 ? R.b.cnt[2] : R.b.cnt[3]);
+        const int32_t vd = vw >= 0 ? vd_l : (vs == 0 ? R.b.dic[0] : vs == 1 ? R.b.dic[1] : vs == 2 ? R.b.dic[2] : R.b.dic[3]);
+        plain = vd == 0 && !(vc >= 5.0f);
+    }
+    const unsigned bad = __ballot_sync(CAFE_FULL, act && !plain);
+    const int f = bad ? __ffs(bad) - 1 : n;
+    if (f <= a) return a;
+    // 5. the slot of every lane's entry: that of the entry it replaced (a miss) or of the miss that created it (a hit)
+    int code = hit ? (m >= 0 ? m : -1 - ms) : vw;   // >= 0: the same slot as that lane's entry; < 0: slot -1 - code
+#pragma unroll
+    for (int it = 0; it < 5; ++it) {
+        const int nx = __shfl_sync(CAFE_FULL, code, code >= 0 ? code : 0);
+        if (code >= 0) code = nx;
+    }
+    const int slot = -1 - code;
+    // the entries of the chunk among the four most recent after the last applied lookup: that lookup's own, and the
+    // three latest uses of other ids before it (slots of the bucket that are still among the four keep their values)
+    const int last = f - 1;
+    unsigned others = mask & ~(pv >= 0 ? (1u << pv) : 0u);
+    int W1 = -1, W2 = -1, W3 = -1;
+    if (others) { W1 = 31 - __clz(others); others &= ~(1u << W1); }
+    if (others) { W2 = 31 - __clz(others); others &= ~(1u << W2); }
+    if (others) { W3 = 31 - __clz(others); }
+    W1 = __shfl_sync(CAFE_FULL, W1, last); W2 = __shfl_sync(CAFE_FULL, W2, last); W3 = __shfl_sync(CAFE_FULL, W3, last);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int W = q == 0 ? last : q == 1 ? W1 : q == 2 ? W2 : W3;
+        const int k = W >= 0 ? W : 0;
+        const uint32_t ex = __shfl_sync(CAFE_FULL, x, k);
+        const float ec = __shfl_sync(CAFE_FULL, my_acc, k);
+        const int32_t ed = __shfl_sync(CAFE_FULL, my_dic, k);
+        const int ep = __shfl_sync(CAFE_FULL, p, k);
+        const int es = __shfl_sync(CAFE_FULL, slot, k);
+        if (W >= 0) R.set(es, ex, ec, ed, J.t0 + 1 + ep);
+    }
+    if (lane >= a && lane < f) {   // no flags, no event
+        if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+        J.lflag[p] = 0;
+    }
+    return f;
+}
+
+// One lookup (lane j's) through the full replay on lane `o`, whose state is then copied to the other lanes.  `ev` /
+// `ins` are what the previous round left at the lanes' positions, if the caller has loaded them (HAVE_EV).
+template <bool HAVE_EV>
+__device__ __forceinline__ void cafe_lru_feed_full(const CafeJob& J, CafeLruReplay& R, const int j, const int o, const int lane,
+                                                   const int pj, const uint32_t xj, const float cj, const CafeEvent& ev,
+                                                   const int32_t ins) {
+    if (HAVE_EV) {
+        CafeEvent ej;
+        ej.x = __shfl_sync(CAFE_FULL, ev.x, j); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, j);
+        ej.dic = __shfl_sync(CAFE_FULL, ev.dic, j); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, j);
+        const int32_t ij = __shfl_sync(CAFE_FULL, ins, j);
+        if (lane == o) R.feed(J, pj, xj, cj, &ej, &ij);
+    } else {
+        if (lane == o) R.feed(J, pj, xj, cj);
+    }
+#pragma unroll
+    for (int q = 0; q < CAFE_SLOTS; ++q) {
+        R.b.val[q] = __shfl_sync(CAFE_FULL, R.b.val[q], o); R.b.cnt[q] = __shfl_sync(CAFE_FULL, R.b.cnt[q], o);
+        R.b.dic[q] = __shfl_sync(CAFE_FULL, R.b.dic[q], o); R.b.t[q] = __shfl_sync(CAFE_FULL, R.b.t[q], o);
+    }
+}
+
+// Replays the misses held by lanes [0, n) into the bucket: chunks of plain lookups at once where that pays (at least
+// four lookups left; after an attempt that applied fewer than two, the next `gate.len` lookups go one by one), single
+// lookups otherwise -- the two plain outcomes in line on every lane's copy of the state, the rest through the full
+// replay.  `kind` is the kind of the event the previous round left at the lane's position (unused in a first
+// round); `s_c` is room for 32 counts of this warp in shared memory.
 struct CafeRunGate { int skip = 0, len = 0; };
 template <bool HAVE_EV>
-__device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruReplay& R, unsigned mm, const int o, const int lane,
+__device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruReplay& R, const int n, const int o, const int lane,
                                                     const int p, const uint32_t x, const float c, const uint32_t kind,
                                                     const CafeEvent& ev, const int32_t ins, float* s_c, CafeRunGate& gate) {
-    while (mm) {
-        const int j = __ffs(mm) - 1;
+    int a = 0;
+    while (a < n) {
         if (gate.skip > 0) --gate.skip;
-        else if (R.touched && (mm & (mm - 1))) {
-            const int ms = (x == R.b.val[0]) ? 0 : (x == R.b.val[1]) ? 1 : (x == R.b.val[2]) ? 2 : (x == R.b.val[3]) ? 3 : -1;
-            const unsigned bad = mm & ~__ballot_sync(CAFE_FULL, ms >= 0);
-            const unsigned runm = bad ? (mm & ((1u << (__ffs(bad) - 1)) - 1u)) : mm;
-            if (runm & (runm - 1)) {   // at least two hits in a row
-                float my_acc = (ms == 0) ? R.b.cnt[0] : (ms == 1) ? R.b.cnt[1] : (ms == 2) ? R.b.cnt[2] : R.b.cnt[3];
-                const unsigned same = __match_any_sync(CAFE_FULL, ms) & runm & (0xffffffffu >> (31 - lane));
-                s_c[lane] = c;
-                __syncwarp();
-                {
-                    const float4* cv = reinterpret_cast<const float4*>(s_c);
-#pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const float4 t = cv[q];
-                        if (same & (1u << (4 * q))) my_acc = my_acc + t.x;
-                        if (same & (2u << (4 * q))) my_acc = my_acc + t.y;
-                        if (same & (4u << (4 * q))) my_acc = my_acc + t.z;
-                        if (same & (8u << (4 * q))) my_acc = my_acc + t.w;
-                    }
-                }
-                __syncwarp();
-                const bool in_run = (runm >> lane) & 1u;
-                const unsigned hot = __ballot_sync(CAFE_FULL, in_run && my_acc >= J.thr);
-                const unsigned dm = hot ? (runm & ((1u << (__ffs(hot) - 1)) - 1u)) : runm;
-                if (dm) {
-                    const bool in_done = (dm >> lane) & 1u;
-#pragma unroll
-                    for (int q = 0; q < CAFE_SLOTS; ++q) {
-                        const unsigned lq = __ballot_sync(CAFE_FULL, in_done && ms == q);
-                        const int w = lq ? 31 - __clz(lq) : 0;   // the slot's last lookup of the run
-                        const float eq = __shfl_sync(CAFE_FULL, my_acc, w);
-                        const int pq = __shfl_sync(CAFE_FULL, p, w);
-                        if (lq) { R.b.cnt[q] = eq; R.b.t[q] = J.t0 + 1 + pq; }
-                    }
-                    if (in_done) {   // a hit below the threshold: no flags, no event
-                        if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
-                        J.lflag[p] = 0;
-                    }
-                    mm &= ~dm;
-                    gate.len = 0;
-                    continue;
-                }
+        else if (R.touched && n - a >= 4) {
+            const int f = cafe_lru_apply_chunk(J, R, a, n, lane, p, x, c, kind, s_c);
+            if (f - a >= 2) gate.len = 0;
+            else { gate.len = gate.len == 0 ? 1 : (gate.len >= 8 ? 8 : 2 * gate.len); gate.skip = gate.len; }
+            if (f > a) {
+                a = f;
+                if (a >= n) break;
+                // the lookup the chunk stopped at needs the full replay
+                cafe_lru_feed_full<HAVE_EV>(J, R, a, o, lane, __shfl_sync(CAFE_FULL, p, a), __shfl_sync(CAFE_FULL, x, a),
+                                            __shfl_sync(CAFE_FULL, c, a), ev, ins);
+                ++a;
+                continue;
             }
-            gate.len = gate.len == 0 ? 1 : (gate.len >= 8 ? 8 : 2 * gate.len);
-            gate.skip = gate.len;
         }
-        mm &= mm - 1;
+        const int j = a++;
         const int pj = __shfl_sync(CAFE_FULL, p, j);
         const uint32_t xj = __shfl_sync(CAFE_FULL, x, j);
         const float cj = __shfl_sync(CAFE_FULL, c, j);
@@ -732,24 +885,13 @@ __device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruRep
             }
             continue;
         }
-        if (HAVE_EV) {
-            CafeEvent ej;
-            ej.x = __shfl_sync(CAFE_FULL, ev.x, j); ej.cnt = __shfl_sync(CAFE_FULL, ev.cnt, j);
-            ej.dic = __shfl_sync(CAFE_FULL, ev.dic, j); ej.kind = __shfl_sync(CAFE_FULL, ev.kind, j);
-            const int32_t ij = __shfl_sync(CAFE_FULL, ins, j);
-            if (lane == o) R.feed(J, pj, xj, cj, &ej, &ij);
-        } else {
-            if (lane == o) R.feed(J, pj, xj, cj);
-        }
-#pragma unroll
-        for (int q = 0; q < CAFE_SLOTS; ++q) {
-            R.b.val[q] = __shfl_sync(CAFE_FULL, R.b.val[q], o); R.b.cnt[q] = __shfl_sync(CAFE_FULL, R.b.cnt[q], o);
-            R.b.dic[q] = __shfl_sync(CAFE_FULL, R.b.dic[q], o); R.b.t[q] = __shfl_sync(CAFE_FULL, R.b.t[q], o);
-        }
+        cafe_lru_feed_full<HAVE_EV>(J, R, j, o, lane, pj, xj, cj, ev, ins);
     }
 }
+// per warp of the list launch: the misses of a group of eight chunks, and room for the counts a chunk adds up
+struct alignas(16) CafeLruStage { float sum[32]; int p[256]; uint32_t x[256]; float c[256]; uint32_t k[256]; };
 template <int PART>
-__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k, float* s_c) {
+__device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H, const int k, CafeLruStage* st) {
     const int lane = threadIdx.x & 31;
     CafeLruReplay R;
     int jb = 0, jend = 0;
@@ -849,15 +991,32 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
                     if (!J.first_round) k1[q] = J.ev[p1[q]].kind;
                 }
             }
+            // the group's misses are queued in shared memory, in order, and replayed 32 at a time
+            int nq = 0;
 #pragma unroll
             for (int q = 0; q < GL; ++q) {
                 if (stop) break;   // warp-uniform
                 const int idx = base + 32 * q + lane;
                 // positions ascend inside a bucket: once one lane sees the limit, later entries are beyond it too
                 stop = __any_sync(CAFE_FULL, idx < e && p0[q] >= J.limit);
-                const unsigned mm = __ballot_sync(CAFE_FULL, (f0[q] & CAFE_F_MISS) != 0);
-                cafe_lru_feed_lanes<false>(J, W, mm, o, lane, p0[q], x0[q], c0[q], k0[q], no_ev, 0, s_c, gate);
+                const bool missed = (f0[q] & CAFE_F_MISS) != 0;
+                const unsigned mm = __ballot_sync(CAFE_FULL, missed);
+                if (missed) {
+                    const int at = nq + __popc(mm & ((1u << lane) - 1u));
+                    st->p[at] = p0[q]; st->x[at] = x0[q]; st->c[at] = c0[q]; st->k[at] = k0[q];
+                }
+                nq += __popc(mm);
             }
+            __syncwarp();
+            for (int q0 = 0; q0 < nq; q0 += 32) {
+                const int n = min(32, nq - q0);
+                int pp = 0;
+                uint32_t xx = 0, kk = CAFE_EV_NONE;
+                float cc = 1.0f;
+                if (lane < n) { pp = st->p[q0 + lane]; xx = st->x[q0 + lane]; cc = st->c[q0 + lane]; kk = st->k[q0 + lane]; }
+                cafe_lru_feed_lanes<false>(J, W, n, o, lane, pp, xx, cc, kk, no_ev, 0, st->sum, gate);
+            }
+            __syncwarp();
 #pragma unroll
             for (int q = 0; q < GL; ++q) {
                 p0[q] = p1[q]; f0[q] = f1[q]; x0[q] = x1[q]; c0[q] = c1[q]; k0[q] = k1[q];
@@ -871,7 +1030,7 @@ __device__ __forceinline__ void cafe_lru_body(const CafeJob& J, const CafeHot& H
 }
 template <int PART>
 __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __grid_constant__ CafeJob J, const CafeHot H) {
-    __shared__ __align__(16) float s_c[4][32];   // per warp: the counts of a run being added up (list launch only)
+    __shared__ CafeLruStage st[PART == 0 ? 4 : 1];   // (list launch only)
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
         cafe_lru_body<1>(J, H, k < J.n2 ? k : J.n2, nullptr);
@@ -879,7 +1038,7 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_lru_pass(const __gri
         for (;;) {
             const int k = cafe_next_listed(H, &J.res->list_cursor[1], J.n2);
             if (k < 0) break;
-            cafe_lru_body<0>(J, H, k, s_c[threadIdx.x >> 5]);
+            cafe_lru_body<0>(J, H, k, &st[threadIdx.x >> 5]);
         }
     }
 }
@@ -1196,7 +1355,7 @@ __global__ void __launch_bounds__(128) k_lru_pass_compact(const __grid_constant_
                 if (!J.first_round) { e_nx = J.ev[p_nx]; i_nx = J.ins_res[p_nx]; }
             }
             const int n = min(32, jend - base);
-            cafe_lru_feed_lanes<true>(J, R, n == 32 ? 0xffffffffu : ((1u << n) - 1u), 0, lane, p, x, c, ev.kind, ev, ins,
+            cafe_lru_feed_lanes<true>(J, R, n, 0, lane, p, x, c, ev.kind, ev, ins,
                                       s_c[threadIdx.x >> 5], gate);
         }
         if (lane == 0) R.finish(J);

@@ -102,6 +102,18 @@ def test_small_sketch_large_calls():
     drive(300, 1, 1.0000005, 8, 60000, 40, 2, seed=12)      # a 40-id domain: stretches of thousands of lookups of one id
 
 
+def test_few_lru_buckets_thousands_of_misses_each():
+    """Thresholds above 1 and sketches of a few dozen to a few hundred slots fed tens of thousands of lookups per call:
+    every LRU bucket sees hundreds to thousands of main-table misses per call, which the warps replay a chunk of 32
+    at a time (hits, misses, replaced entries that come back, empty slots, ids equal to 0, unit and random counts)."""
+    drive(100, 3, 1.0000005, 10, 30000, 2000, 2, seed=21)
+    drive(60, 2, 1.2, 12, 20000, 500, 3, seed=22, unit=True)
+    drive(358, 1, 1.0000005, 12, 65536, 300000, 6, seed=23)     # a shard of small fields: 6 fields x 65536 on 358 slots
+    drive(100, 3, 1.1, 6, 30000, 2000, 2, seed=24, zero_ids=True)
+    drive(40, 4, 1.0000005, 8, 5000, 60, 2, seed=25)            # a 60-id domain on 4 LRU buckets: mostly hits
+    drive(2000, 2, 1.0000005, 6, 65536, 5000000, 3, seed=26)
+
+
 def test_round_cap_fallback_is_exact():
     st = drive(200, 1, 1.3, 40, 96, 3000, 4, round_cap=2)
     assert st["seq_fallbacks"] > 0
