@@ -64,6 +64,9 @@ SIGNATURES = {
     "cafe_shard_push_grads_fields": (c_int, [_vp, c_int, c_int, c_int, c_int, c_int, POINTER(_vp), c_int, c_int, _vp]),
     "cafe_embed_backward_gated": (c_int, [_vp, _vp, c_int64, c_int64, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                           POINTER(_vp), _vp, c_int, c_int, c_float, c_int, c_int, _vp, _vp]),
+    "cafe_shard_push_norms": (c_int, [_vp, c_int, c_int, c_int, c_int, c_int, POINTER(_vp), _vp, _vp]),
+    "cafe_embed_backward_norms": (c_int, [_vp, _vp, c_int64, c_int64, _vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
+                                          POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
     "cafe_embed_backward_imp": (c_int, [_vp, _vp, c_int64, c_int64, _vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                         POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
     "cafe_sigmod_create": (c_int, [POINTER(_vp), c_int, c_int, c_double, c_int]),

@@ -439,22 +439,79 @@ __global__ void __launch_bounds__(256)
 k_push_grads(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rank, int rows, int D, int64_t total_rows,
              int j_begin, int j_end) {
     const int lanes = D / 4;                       // lanes per row (16-byte vectors)
+    // A grid of a few blocks per SM walks the rows: the transfer is bound by NVLink, not by the number of threads in
+    // flight, and a launch that filled every SM would hold back the small kernels of the sketch insert that run
+    // beside it on another stream.
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total_rows * lanes; t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t q0 = t / lanes;
+        const int c = (int)(t % lanes) * 4;
+        // Every rank starts with the block of the owner after itself and goes round: at any moment the ranks
+        // store into different owners, so no owner's NVLink ingress has to take all of them at once.
+        int64_t q = q0 + P.row_off[(rank + 1) % nranks];
+        if (q >= total_rows) q -= total_rows;
+        int g = 0;
+        while (g + 1 < nranks && q >= P.row_off[g + 1]) ++g;
+        const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
+        const int fg = P.fields_of[g];
+        const int64_t b = local / fg, j = local - b * fg;
+        if (j < j_begin || j >= j_end) continue;   // only the owners' fields number j_begin .. j_end-1 go in this launch
+        const float4 v = ld_stream(grad + q * D + c);
+        *reinterpret_cast<float4*>(P.base[g] + (((int64_t)rank * rows + b) * fg + j) * D + c) = v;
+    }
+}
+
+// The norms of the same rows, sent ahead of them: the sketch insert needs only the per-lookup L2 norms, which are a
+// 128th of the rows' bytes, so the owners can start inserting while the rows themselves are still crossing NVLink.
+// Arithmetic and lane layout are those of k_grad_norm (which the owner would run on the delivered rows): a group of G
+// lanes squares and adds the same 16-byte pieces in the same butterfly, so the owner gets the bits it would compute.
+// Owner g's norm array is [F_g, nranks*rows] (field-major, as k_field_sum and k_importance read it).  The norms are
+// first written to a local staging array in the order they will have at the owners (per owner g a block [F_g, rows]);
+// k_send_norms then copies every block's field rows with consecutive lanes on consecutive floats, so the remote
+// stores leave as full 128-byte lines instead of one 4-byte store per lookup.
+template <int G>
+__global__ void __launch_bounds__(256)
+k_push_norms(const float* __restrict__ grad, const CafePushPlan P, int nranks, int rows, int64_t total_rows,
+             float* __restrict__ staged) {
+    constexpr int U = 4;
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t q0 = t / lanes;
-    const int c = (int)(t % lanes) * 4;
-    if (q0 >= total_rows) return;
-    // Every rank starts with the block of the owner after itself and goes round: at any moment the ranks
-    // store into different owners, so no owner's NVLink ingress has to take all of them at once.
-    int64_t q = q0 + P.row_off[(rank + 1) % nranks];
-    if (q >= total_rows) q -= total_rows;
+    const int64_t q0 = (t / G) * U;
+    const int c = (int)(t % G) * 4;
+    float s[U];
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q0 + u < total_rows) v[u] = ld_stream(grad + (q0 + u) * (int64_t)(G * 4) + c);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        s[u] = v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+#pragma unroll
+        for (int o = G / 2; o > 0; o >>= 1) s[u] += __shfl_xor_sync(FULL, s[u], o);
+    }
+    if (c == 0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t q = q0 + u;
+            if (q >= total_rows) break;
+            int g = 0;
+            while (g + 1 < nranks && q >= P.row_off[g + 1]) ++g;
+            const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
+            const int fg = P.fields_of[g];
+            const int64_t b = local / fg, j = local - b * fg;
+            staged[P.row_off[g] + j * rows + b] = sqrtf(s[u]);
+        }
+    }
+}
+__global__ void __launch_bounds__(256)
+k_send_norms(const float* __restrict__ staged, const CafePushPlan P, int nranks, int rank, int rows, int64_t total_rows) {
+    const int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (q >= total_rows) return;
     int g = 0;
     while (g + 1 < nranks && q >= P.row_off[g + 1]) ++g;
-    const int64_t local = q - P.row_off[g];        // row inside block g: b * F_g + j
-    const int fg = P.fields_of[g];
-    const int64_t b = local / fg, j = local - b * fg;
-    if (j < j_begin || j >= j_end) return;   // only the owners' fields number j_begin .. j_end-1 go in this launch
-    const float4 v = ld_stream(grad + q * D + c);
-    *reinterpret_cast<float4*>(P.base[g] + (((int64_t)rank * rows + b) * fg + j) * D + c) = v;
+    const int64_t local = q - P.row_off[g];        // inside block g: j * rows + b
+    const int64_t j = local / rows, b = local - j * rows;
+    P.base[g][j * ((int64_t)nranks * rows) + (int64_t)rank * rows + b] = staged[q];
 }
 
 template <int G>
@@ -1177,9 +1234,75 @@ static int push_grads_impl(const float* grad_blocked_dev, int nfields_total, int
     cudaStream_t st = (cudaStream_t)stream;
     CAFE_PROF(CAFE_P_PUSH, st);
     const int64_t threads = total_rows * (D / 4);
-    k_push_grads<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D, total_rows,
-                                                                   j_begin, j_end);
+    const int64_t blocks = (threads + 255) / 256;
+    k_push_grads<<<(unsigned)(blocks < 148 * 8 ? blocks : 148 * 8), 256, 0, st>>>(grad_blocked_dev, P, nranks, rank, rows_local, D,
+                                                                                 total_rows, j_begin, j_end);
     return fail_cuda("cafe_shard_push_grads");
+}
+
+int cafe_shard_push_norms(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                          float* const* owner_norm, float* staging_dev, void* stream) {
+    if (nfields_total < 1 || rows_local < 0 || nranks < 1 || nranks > CAFE_MAX_RANKS || rank < 0 || rank >= nranks || !owner_norm ||
+        !staging_dev)
+        return CAFE_ERR_ARG;
+    if (!(D == 16 || D == 32 || D == 64 || D == 128)) return CAFE_ERR_UNSUPPORTED;
+    const int64_t total_rows = (int64_t)nfields_total * rows_local;
+    if (total_rows == 0) return CAFE_OK;
+    if (!grad_blocked_dev || !aligned16(grad_blocked_dev)) return CAFE_ERR_ARG;
+    CafePushPlan P;
+    memset(&P, 0, sizeof(P));
+    int64_t off = 0;
+    for (int g = 0; g < nranks; ++g) {
+        if (!owner_norm[g]) return CAFE_ERR_ARG;
+        P.base[g] = owner_norm[g];
+        P.fields_of[g] = nfields_total / nranks + (g < nfields_total % nranks ? 1 : 0);   // round-robin ownership
+        P.row_off[g] = (int32_t)off;
+        off += (int64_t)P.fields_of[g] * rows_local;
+    }
+    P.row_off[nranks] = (int32_t)off;
+    if (off != total_rows || total_rows > 0x7fffffffLL) return CAFE_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    CAFE_PROF(CAFE_P_NORM, st);
+    DISPATCH_G(D, (k_push_norms<G><<<(unsigned)(((total_rows + 3) / 4 * G + 255) / 256), 256, 0, st>>>(grad_blocked_dev, P, nranks,
+                   rows_local, total_rows, staging_dev)));
+    k_send_norms<<<(unsigned)((total_rows + 255) / 256), 256, 0, st>>>(staging_dev, P, nranks, rank, rows_local, total_rows);
+    return fail_cuda("cafe_shard_push_norms");
+}
+
+// cafe_embed_backward with the lookups' gradient norms already at hand (cafe_shard_push_norms) and the gradient rows
+// possibly still on their way: importance and the sketch insert run at once from the norms; the stream waits for
+// gate_event (null = the rows are there) only before the step that reads the rows, the SGD scatter.
+int cafe_embed_backward_norms(void* h, const float* grad_dev, int64_t field_stride, int64_t sample_stride, const float* norm_dev,
+                              const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev, const int32_t* row_dev,
+                              int nfields, int B, const int64_t* f_offset, const int32_t* hash_size, float* const* weight_hash,
+                              float* weight_high, int hotn, int D, float lr, int insert_mode, void* gate_event, void* stream) {
+    if (!h || !norm_dev) return CAFE_ERR_ARG;
+    CafeEmbedWorkspace* ws = cafe_internal_ws(h);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t total = (int64_t)nfields * B;
+    if (nfields < 1 || nfields > CAFE_MAX_SEGMENTS || total > ws->cap) return CAFE_ERR_CAPACITY;
+    if (total == 0) return CAFE_OK;
+    CafeFields FS;
+    int rc = scatter_check(h, &FS, grad_dev, field_stride, sample_stride, row_dev, nfields, B, hash_size, weight_hash,
+                           weight_high, hotn, D);
+    if (rc != CAFE_OK) return rc;
+    rc = backward_side_work(h, ws, FS, gid_dev, row_dev, (int)total, hotn, insert_mode, st);
+    if (rc != CAFE_OK) { scatter_join(ws, st); return rc; }
+    { CAFE_PROF(CAFE_P_FIELDSUM, st); k_field_sum<<<nfields, 1024, 0, st>>>(norm_dev, B, ws->totals); }
+    { CAFE_PROF(CAFE_P_IMPORTANCE, st); k_importance<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(norm_dev, ws->totals, B,
+                                                                                                    (int)total, ws->imp); }
+    int seg[CAFE_MAX_SEGMENTS + 1];
+    for (int f = 0; f <= nfields; ++f) seg[f] = f * B;
+    int status = cafe_internal_insert(h, gid_dev, ws->imp, seg, nfields, ws->mask, ws->post_row, insert_mode, st);
+    rc = scatter_join(ws, st);
+    if (status != CAFE_OK && status != CAFE_ERR_NOCONVERGE && status != CAFE_ERR_RESET_UNDERFLOW) return status;
+    if (rc != CAFE_OK) return rc;
+    rc = cafe_migrate(h, ids_dev, ids_are_int64, ws->mask, ws->post_row, nfields, B, f_offset, hash_size, weight_hash, weight_high,
+                      hotn, D, nullptr, stream);
+    if (rc != CAFE_OK) return rc;
+    if (gate_event && cudaStreamWaitEvent(st, (cudaEvent_t)gate_event, 0) != cudaSuccess) return fail_cuda("gate wait");
+    rc = scatter_apply(ws, FS, grad_dev, field_stride, sample_stride, (int)total, D, lr, st);
+    return rc != CAFE_OK ? rc : status;
 }
 
 int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,

@@ -121,18 +121,21 @@ class PeerBuffers:
         self.pooled = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
         self.grad = symm.empty(rows * plan.F * dim, dtype=torch.float32, device=device)
         self.gown = symm.empty(plan.G * rows * fmax * dim, dtype=torch.float32, device=device)   # as OWNER: gradients of its fields, global batch
+        self.nown = symm.empty(fmax * plan.G * rows, dtype=torch.float32, device=device)         # as OWNER: their L2 norms [F_g, B]
         self.h_ids = symm.rendezvous(self.ids, grp)
         self.h_pooled = symm.rendezvous(self.pooled, grp)
         self.h_grad = symm.rendezvous(self.grad, grp)
         self.h_gown = symm.rendezvous(self.gown, grp)
+        self.h_nown = symm.rendezvous(self.nown, grp)
         self.ids_gen_elems = fmax * plan.G * rows
         # offset (elements) of owner r's block inside every consumer's pooled / grad buffer
         self.block_off = [rows * dim * sum(plan.counts[:r]) for r in range(plan.G)]
+        self.nsend = torch.empty(rows * plan.F, dtype=torch.float32, device=device)   # norms of this rank's rows, staged
         self.flag = torch.zeros(1, device=device)
         self.gen = 0
         with torch.cuda.device(device):
             self.comm_stream = torch.cuda.Stream()        # the gradient exchange when it is issued in pieces
-            self.ev_first, self.ev_second = torch.cuda.Event(), torch.cuda.Event()
+            self.ev_first, self.ev_second, self.ev_grad = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
 
     def ptr_array(self, handle, elem_offset: int, elem_size: int):
         return (ctypes.c_void_p * self.plan.G)(*[int(p) + elem_offset * elem_size for p in handle.buffer_ptrs])
@@ -202,7 +205,26 @@ class _PeerFunction(torch.autograd.Function):
         with torch.no_grad(), torch.cuda.device(pb.grad.device):
             g = blocked_grad.reshape(-1).contiguous()   # (the backward's sorts were started by the forward)
             half = (plan.F // G) // 2     # same on every rank: owners' fields 0..half-1 travel first
-            if not model.pipeline_push or G == 1 or half < 1:
+            if model.push == "norms_first" and G > 1:
+                # The rows' L2 norms (4 bytes per lookup) go first; with them the owners run importance and the whole
+                # sketch insert while the rows themselves cross NVLink on a stream of their own.  Only the SGD scatter
+                # reads the rows, and only it waits for them.
+                main, comm = torch.cuda.current_stream(), pb.comm_stream
+                _lib.check(lib.cafe_shard_push_norms(g.data_ptr(), plan.F, Bl, D, G, plan.rank,
+                                                     pb.ptr_array(pb.h_nown, 0, 4), pb.nsend.data_ptr(), _stream()),
+                           "cafe_shard_push_norms")
+                pb.ev_grad.record(main)                     # (the rows start once the norms have left)
+                pb.fence()                                  # every owner holds the norms of the global batch
+                comm.wait_event(pb.ev_grad)
+                g.record_stream(comm)
+                with torch.cuda.stream(comm):
+                    _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank,
+                                                         pb.ptr_array(pb.h_gown, 0, 4), comm.cuda_stream), "cafe_shard_push_grads")
+                    pb.fence()                              # every owner holds the rows (issued second on every rank)
+                    pb.ev_second.record(comm)
+                grp.last_status = f.backward_norms(pb.gown, D, Fg * D, pb.nown, own, gid, row, G * Bl, grp.lr, grp.insert_mode,
+                                                   pb.ev_second)
+            elif not model.pipeline_push or G == 1 or half < 1:
                 # consumers store their gradient rows into the owners' buffers (remote stores over NVLink) ...
                 _lib.check(lib.cafe_shard_push_grads(g.data_ptr(), plan.F, Bl, D, G, plan.rank,
                                                      pb.ptr_array(pb.h_gown, 0, 4), _stream()), "cafe_shard_push_grads")
@@ -275,7 +297,7 @@ class ShardedSKEmbedding(torch.nn.Module):
 
     def __init__(self, num_categories, embedding_dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1,
                  sketch_alpha=1.0000005, device="cuda", global_batch=65536, lr=0.1, seed=None, group=None,
-                 exchange="peer", f_offsets=None, pipeline_push=False, hot_rows_by="fields"):
+                 exchange="peer", f_offsets=None, pipeline_push=False, hot_rows_by="fields", push="norms_first"):
         super().__init__()
         from .sk_embedding_bag import SKEmbeddingGroup
         world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -320,6 +342,11 @@ class ShardedSKEmbedding(torch.nn.Module):
         # gradient exchange in two pieces, the second beside the first piece's insert.  Off by default: on two GPUs
         # the job boundary it forces at the gate cost more than the hidden half of the transfer gave back.
         self.pipeline_push = bool(pipeline_push)
+        # "norms_first": the rows' norms travel ahead and the sketch insert runs beside the rows' transfer; "whole":
+        # rows first, then the ordinary backward (pipeline_push=True splits that into two pieces)
+        if push not in ("norms_first", "whole"):
+            raise ValueError("push must be 'norms_first' or 'whole'")
+        self.push = "whole" if self.pipeline_push else push
         self.peer = None
         self._gbuf = self._imp = None
         if exchange == "peer":

@@ -141,6 +141,18 @@ class _FieldSet:
                 wp, hp, self.hotn, self.dim, float(lr), mode, int(gate_field), ctypes.c_void_p(gate_event.cuda_event),
                 _stream()), "cafe_embed_backward_gated")
 
+    def backward_norms(self, grad, field_stride, sample_stride, norms, ids, gid, row, B, lr, mode, gate_event=None):
+        """backward() from per-lookup gradient norms that are already there ([F, B] fp32) while the gradient rows may
+        still be arriving: the stream waits for gate_event (a torch.cuda.Event, or None) only before the SGD scatter."""
+        wp, hp = self.ptrs()
+        with torch.cuda.device(grad.device):
+            return _lib.check(self.sketch.lib.cafe_embed_backward_norms(
+                self.sketch.handle, grad.data_ptr(), field_stride, sample_stride, norms.data_ptr(), ids.data_ptr(),
+                int(ids.dtype == torch.int64), gid.data_ptr(), row.data_ptr(), self.nf, B, self.f_offset, self.hash_size,
+                wp, hp, self.hotn, self.dim, float(lr), mode,
+                ctypes.c_void_p(gate_event.cuda_event) if gate_event is not None else None, _stream()),
+                "cafe_embed_backward_norms")
+
     def backward(self, grad, field_stride, sample_stride, ids, gid, row, B, lr, mode, mask_out=None):
         wp, hp = self.ptrs()
         with torch.cuda.device(grad.device):

@@ -205,6 +205,21 @@ int cafe_shard_push_grads(const float* grad_blocked_dev, int nfields_total, int 
  * while the next one is on its way. */
 int cafe_shard_push_grads_fields(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks,
                                  int rank, float* const* owner_grad, int j_begin, int j_end, void* stream);
+/* The L2 norms of the same rows, sent ahead of them (4 bytes per lookup): owner g receives them in owner_norm[g],
+ * laid out [F_g, nranks*rows].  Same arithmetic as the norm step of cafe_grad_importance on the delivered rows
+ * (sk_embedding_bag.py:178-184), so the owner gets the bits it would compute itself.  staging_dev: nfields_total *
+ * rows_local floats of this rank's own memory. */
+int cafe_shard_push_norms(const float* grad_blocked_dev, int nfields_total, int rows_local, int D, int nranks, int rank,
+                          float* const* owner_norm, float* staging_dev, void* stream);
+/* cafe_embed_backward from norms that are already there (cafe_shard_push_norms) while the gradient rows may still be
+ * on their way: importance (sk_embedding_bag.py:185-189), sketch insert and migration run at once; the stream waits
+ * for gate_event (a cudaEvent_t, or null) only before the SGD scatter, the one step that reads the rows.  Results
+ * are those of cafe_embed_backward on the delivered rows. */
+int cafe_embed_backward_norms(void* handle, const float* grad_dev, int64_t field_stride, int64_t sample_stride,
+                              const float* norm_dev, const void* ids_dev, int ids_are_int64, const uint32_t* gid_dev,
+                              const int32_t* row_dev, int nfields, int B, const int64_t* f_offset, const int32_t* hash_size,
+                              float* const* weight_hash, float* weight_high, int hotn, int D, float lr, int insert_mode,
+                              void* gate_event, void* stream);
 /* cafe_embed_backward whose gradient rows of the fields from gate_field on are still being written when the call
  * is made: they are complete once gate_event (a cudaEvent_t) has fired.  The fields before gate_field are
  * processed at once; the importance of the late fields is computed behind the gate on a stream of the handle,

@@ -32,8 +32,8 @@ def main():
     F, D, Bl, steps = 4 * world + 1, 32, 512, 6            # uneven field counts per rank on purpose
     cards = [3000 + 7919 * f for f in range(F)]
     models = {}
-    for name, kw in (("pieces", dict(exchange="peer", pipeline_push=True)), ("whole", dict(exchange="peer", pipeline_push=False)),
-                     ("nccl", dict(exchange="nccl"))):
+    for name, kw in (("pieces", dict(exchange="peer", pipeline_push=True)), ("whole", dict(exchange="peer", push="whole")),
+                     ("norms", dict(exchange="peer", push="norms_first")), ("nccl", dict(exchange="nccl"))):
         models[name] = ShardedSKEmbedding(cards, D, 0.02, 0.3, 1, 1, 1.0000005, device=dev, global_batch=Bl * world, lr=0.1,
                                           seed=5, **kw)
     ref = models["nccl"]
@@ -89,7 +89,7 @@ def main():
             if not np.allclose(grp.weight_hash[j].detach().cpu().numpy(), orc.wc[j], rtol=1e-5, atol=1e-7):
                 complain(f"step {step}: hash table of field {mine[j]} differs from the per-shard oracle")
         # ---- the exchange variants against each other
-        for name in ("pieces", "whole"):
+        for name in ("pieces", "whole", "norms"):
             m = models[name]
             same_out = outs[name].numel() == outs["nccl"].numel() and torch.equal(outs[name].reshape(-1), outs["nccl"].reshape(-1))
             diffs = states_equal(ref.group.sketch.state(), m.group.sketch.state())
@@ -101,7 +101,7 @@ def main():
     dist.all_reduce(t)
     if rank == 0:
         verdict = "identical" if int(t.item()) == 0 else f"{int(t.item())} mismatches"
-        line = f"multi-GPU parity on {world} GPUs ({steps} steps, per-shard oracle and three exchange variants): {verdict}"
+        line = f"multi-GPU parity on {world} GPUs ({steps} steps, per-shard oracle and four exchange variants): {verdict}"
         print(line, flush=True)
         if os.environ.get("CAFE_PARITY_REPORT"):
             Path(os.environ["CAFE_PARITY_REPORT"]).write_text(line + "\n")
