@@ -44,12 +44,26 @@ DIM, BATCH, SEED = 128, 65536, 2024
 LR = 0.1
 METRIC = "cafe_embedding_ids_per_s"
 UNIT = "ids/s"
-# algorithmic bytes per id of each kernel (R = 4*D bytes per row): what the kernel has to move
-def alg_bytes(slot: str, D: int) -> float:
+# Algorithmic bytes per id of each kernel (R = 4*D bytes per row): what the kernel has to move.  `u` is the share of
+# lookups that name a table row no earlier lookup of the step names (measured on the last timed batch): a row that
+# many lookups share has to be read once by the gather and read and written once by the scatter, while every lookup
+# has its own pooled row to write and its own gradient row to read.
+def alg_bytes(slot: str, D: int, u: float = 1.0) -> float:
     R = 4 * D
-    return {"embed_forward": 64 + 2 * R, "scatter_chunks": 3 * R + 8, "grad_norm": R + 4, "main_pass": 120,
+    return {"embed_forward": 64 + R + u * R, "scatter_chunks": R + 8 + 2 * u * R, "grad_norm": R + 4, "main_pass": 120,
             "lru_pass": 136, "row_sort": 16 * 3, "lookup_hash_sort": 16 * 3 * 2}.get(slot, 0.0)
-FUSED_BYTES_PER_ID = lambda D: 192 + 5 * 4 * D   # query 64 + gather 2R + scatter 3R+8 + insert 120
+FUSED_BYTES_PER_ID = lambda D, u=1.0: 192 + (2 + 3 * u) * 4 * D   # query 64 + gather R+uR + scatter R+8+2uR + insert 120
+
+
+def unique_row_share(codes) -> float:
+    """codes int32 [F, B] from SKEmbeddingGroup.row_codes: distinct table rows / lookups (hot rows are shared by all
+    fields, hash rows belong to their field)."""
+    import torch
+    F = codes.shape[0]
+    c = codes.to(torch.int64)
+    field = torch.arange(F, device=codes.device, dtype=torch.int64)[:, None]
+    key = torch.where(c < 0, c, (field << 32) | c)
+    return float(torch.unique(key).numel()) / max(1, key.numel())
 
 
 def read_peaks():
@@ -557,6 +571,13 @@ def run_ours(args, rank, world, local_rank):
         peak, peak_kind = read_peaks()
         phases = {k: {"ms_per_step": v[0] / K, "launches_per_step": v[1] / K} for k, v in slots.items() if v[1] > 0}
         rank_ids = ids_per_step / world if wl.name != "weak26" else ids_per_step / world   # lookups this rank serves per step
+        # share of distinct table rows among the lookups of the last timed batch (this rank's fields, global batch)
+        u_rows = 1.0   # (weak26: every lookup counted with a row of its own)
+        if wl.name != "weak26":
+            last = wl.ids(W + K - 1, B)
+            grp_ = run.grp if world == 1 else run.model.group
+            own = last if world == 1 else last[run.model.plan.local_fields]
+            u_rows = unique_row_share(grp_.row_codes(torch.from_numpy(np.ascontiguousarray(own)).to(dev)))
         cand = {k: v for k, v in slots.items() if alg_bytes(k, DIM) > 0 and v[1] > 0}
         # the sketch passes run in three modes (all buckets / later rounds / final pass) that are timed in slots of
         # their own: the kernel is ranked by their sum and reported on its all-bucket launches
@@ -572,7 +593,7 @@ def run_ours(args, rank, world, local_rank):
             # add up to the step's lookups, so an average launch covers (lookups per step) / (launches per step)
             launches_per_step = cand[top][1] / K
             units = rank_ids / max(1.0, launches_per_step)
-            ach = alg_bytes(top, DIM) * units / (per_launch_ms / 1e3) / 1e9
+            ach = alg_bytes(top, DIM, u_rows) * units / (per_launch_ms / 1e3) / 1e9
             traffic = None
             tp = ROOT / "profiles" / "traffic.json"
             if tp.exists():
@@ -581,11 +602,12 @@ def run_ours(args, rank, world, local_rank):
                     traffic = per_id * units if per_id else None
                 except Exception:
                     traffic = None
-            fused = FUSED_BYTES_PER_ID(DIM) * ids_per_step / (ms / K / 1e3) / 1e9 / world
+            fused = FUSED_BYTES_PER_ID(DIM, u_rows) * ids_per_step / (ms / K / 1e3) / 1e9 / world
             roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
-                    "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, DIM),
+                    "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, DIM, u_rows),
+                    "distinct_rows_per_lookup": u_rows,
                     "ms_per_launch": per_launch_ms, "ids_per_launch": units,
-                    "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(DIM), "achieved": fused, "frac": fused / peak,
+                    "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(DIM, u_rows), "achieved": fused, "frac": fused / peak,
                                    "note": "per GPU: whole-step algorithmic bytes / step time / n_gpus"}}
         dl = st1["lookups"] - st0["lookups"]
         mix = {"lookups": dl, "main_hit_frac": (st1["main_hits"] - st0["main_hits"]) / max(1, dl),

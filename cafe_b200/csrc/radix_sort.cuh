@@ -18,7 +18,7 @@
 #include "sketch_core.cuh"
 
 #define CAFE_RS_THREADS 256
-#define CAFE_RS_ITEMS 16
+#define CAFE_RS_ITEMS 8
 #define CAFE_RS_TILE (CAFE_RS_THREADS * CAFE_RS_ITEMS)
 #define CAFE_RS_MAX_BITS 10
 #define CAFE_RS_MAX_BINS (1 << CAFE_RS_MAX_BITS)

@@ -78,6 +78,18 @@ class _FieldSet:
                                               row.data_ptr(), _stream()), "cafe_embed_forward")
         return gid, row
 
+    def resolve(self, ids: torch.Tensor):
+        """The sketch probe alone: (gid, row) of ids [nf*B] as forward() would return them, no rows copied."""
+        lib, sk = self.sketch.lib, self.sketch
+        B = ids.numel() // self.nf
+        gid = torch.empty(ids.numel(), dtype=torch.int32, device=ids.device)
+        row = torch.empty(ids.numel(), dtype=torch.int32, device=ids.device)
+        with torch.cuda.device(ids.device):
+            _lib.check(lib.cafe_embed_resolve(sk.handle, ids.data_ptr(), int(ids.dtype == torch.int64), self.nf, B,
+                                              self.f_offset, self.hash_size, self.hotn, gid.data_ptr(), row.data_ptr(),
+                                              _stream()), "cafe_embed_resolve")
+        return gid, row
+
     def forward_training(self, ids: torch.Tensor, out: torch.Tensor, field_stride: int, sample_stride: int, mode: int):
         """forward() in two kernels with the backward's head start in between: the sketch probe first, then the
         bucket sorts of the insert and the row sort of the scatter are started on the library's side streams, and
@@ -400,6 +412,13 @@ class SKEmbeddingGroup(nn.Module):
             else:
                 st[k] = v
         self.sketch.load_state(st)
+
+    def row_codes(self, ids: torch.Tensor) -> torch.Tensor:
+        """int32 [num_fields, batch]: the table row every lookup of ids [num_fields, batch] reads right now: -r for row r
+        of the shared hot table, otherwise the row of the field's own hash table (sk_embedding_bag.py:141-153)."""
+        ids = _device_ids(ids, self.weight_high.device)
+        with torch.no_grad():
+            return self._fields.resolve(ids.reshape(-1))[1].view(self.num_fields, -1)
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         if ids.dim() != 2 or ids.shape[0] != self.num_fields:
