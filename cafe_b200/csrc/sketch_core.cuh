@@ -268,6 +268,16 @@ struct CafeJob {
     uint8_t* mstate;         // [n1] CAFE_S_* of the main bucket's last replay
     uint8_t* mark2;          // [n2] 1 = the main pass of this round changed an input of this LRU bucket
     uint8_t* lstate;         // [n2] CAFE_S_* of the LRU bucket's last replay
+    // Which buckets replay in a later round: those an input of which changed in the round before.  A main bucket's
+    // inputs are the events that land in it (an LRU replay that emits, changes or withdraws one marks the event's
+    // target) and the answers its requests for a free row get (the timeline step marks the bucket when an answer
+    // is, was or becomes "here is a row"; requests that found the FIFO empty and still do change nothing).  Marks
+    // for the next round go to mark_out1 while this round's main pass reads mark_in1 and every bucket clears its
+    // own entry there when it has replayed; the engine swaps the two per round.  LRU buckets: mark2 (above) for
+    // what the main pass of the same round changed, mark_c2 for the free-row answers, cleared the same way.
+    uint8_t* mark_in1;       // [n1]
+    uint8_t* mark_out1;      // [n1]
+    uint8_t* mark_c2;        // [n2]
     // FIFO timeline believed by this round = the one the previous round produced, as a list of ops
     // (candidate pops and pushes) in op-slot order; the resolve step rewrites it in place
     int32_t* tl_slot;        // [2M] op slot (2p or 2p+1) of every op, ascending
@@ -350,6 +360,15 @@ CAFE_HD void cafe_route_position(const CafeJob& J, int p) {
     else if (e.kind == CAFE_EV_OWN) J.mark_own[cafe_hash(e.x, J.n1)] = 1;
 }
 
+// the event of position p no longer exists (its lookup hits the main table now, or its LRU replay produces none):
+// the main bucket it would have landed in replays without it
+CAFE_HD void cafe_withdraw_event(const CafeJob& J, int p) {
+    const CafeEvent o = J.ev[p];
+    if (o.kind != CAFE_EV_NONE) J.mark_out1[cafe_hash(o.x, J.n1)] = 1;
+    J.ev[p].kind = CAFE_EV_NONE;
+    J.res->changed = 1;
+}
+
 // ---- round step 1: one main bucket ---------------------------------------------------------------
 // The replay of a bucket is a small state machine fed one own lookup at a time (feed), so that the
 // same code serves a thread that walks its bucket's lookups alone and a warp that loads a long
@@ -371,13 +390,8 @@ struct CafeMainReplay {
     // does bucket k have to be replayed in this (not first) round?  `cond` receives whether events land in it.
     static CAFE_HD bool wanted(const CafeJob& J, int k, bool* cond) {
         const uint32_t st = J.mstate[k];
-        // cond: events land here, so results depend on beliefs that may be withdrawn later (one more
-        // replay after the last such round returns the bucket to its belief-free result); an id waiting
-        // for a row makes the results depend on the FIFO timeline only, which needs a replay exactly when
-        // the timeline changed
-        *cond = J.head[k] >= 0 || J.mark_own[k] != 0;
-        const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
-        return J.final_pass ? (st & CAFE_S_DIRTY) != 0 : (J.all_active || *cond || waiting || (st & CAFE_S_COND) != 0);
+        *cond = J.head[k] >= 0 || J.mark_own[k] != 0;   // events land here
+        return J.final_pass ? (st & CAFE_S_DIRTY) != 0 : (J.all_active || J.mark_in1[k] != 0);
     }
     // returns false if the bucket does not need to be replayed this round; `pre` = the bucket's batch-start
     // image if the caller has loaded it already
@@ -472,7 +486,7 @@ struct CafeMainReplay {
                 // (no flag set) has nothing to store then; later rounds store what changed
                 if (nf != old_flag) J.mflag[p] = (uint8_t)nf;
                 if (!J.first_round) {
-                    if (old_kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                    if (old_kind != CAFE_EV_NONE) cafe_withdraw_event(J, p);
                     if (old_flag & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;   // its LRU bucket loses this visitor
                 }
             }
@@ -494,6 +508,7 @@ struct CafeMainReplay {
         drain_events(J, INT32_MAX);
         if (J.final_pass) { close_segment(J); return; }
         J.mstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0) | (dirty ? CAFE_S_DIRTY : 0));
+        J.mark_in1[k] = 0;
         J.main_out[k] = b;
     }
 };
@@ -523,8 +538,8 @@ struct CafeLruReplay {
     static CAFE_HD bool wanted(const CafeJob& J, int k, bool* cond) {
         const uint32_t st = J.lstate[k];
         *cond = J.mark2[k] != 0;
-        const bool waiting = (st & CAFE_S_CAND) != 0 && J.cand_active;
-        return J.all_active || *cond || waiting || (st & CAFE_S_COND) != 0;
+        (void)st;
+        return J.all_active || *cond || J.mark_c2[k] != 0;
     }
     CAFE_HD bool init(const CafeJob& J, int k_, const CafeLruBucket* pre = nullptr) {
         k = k_;
@@ -552,8 +567,10 @@ struct CafeLruReplay {
             else same = (o.kind == kind && o.x == x && o.dic == dic && cafe_float_bits(o.cnt) == cafe_float_bits(cnt));
             if (same) return;
             J.res->changed = 1;
+            if (o.kind != CAFE_EV_NONE) J.mark_out1[cafe_hash(o.x, J.n1)] = 1;   // the old event's target loses it
             if (kind == CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; return; }
         }
+        J.mark_out1[cafe_hash(x, J.n1)] = 1;   // the new event's target
         CafeEvent e;
         e.x = x; e.cnt = cnt; e.dic = dic; e.kind = kind;
         J.ev[p] = e;
@@ -623,6 +640,7 @@ struct CafeLruReplay {
     CAFE_HD void finish(const CafeJob& J) {
         if (n_ev) CAFE_ATOMIC_ADD(&J.res->n_events, n_ev);
         J.lstate[k] = (uint8_t)((cond_now ? CAFE_S_COND : 0) | (cand ? CAFE_S_CAND : 0));
+        J.mark_c2[k] = 0;
         J.lru_out[k] = b;
     }
 };
@@ -741,6 +759,15 @@ CAFE_HD void cafe_tl_finish_op(const CafeJob& J, int32_t j, int32_t n, const Caf
     J.tl_size[j] = s;
     J.tl_rank[j] = rank;
     if (info != 0) J.pushbuf[before.np] = (uint32_t)info;
+    else {
+        // a request for a free row: its bucket has to replay next round unless the answer was "none" and still is
+        const int p = J.tl_slot[j] >> 1;
+        const uint32_t f = cafe_eff_flag(J, p);
+        if (s > 0 || (f & CAFE_F_GOT)) {
+            if (f & CAFE_F_MISS) J.mark_c2[cafe_hash(J.gid[p], J.n2)] = 1;
+            else J.mark_out1[cafe_hash(J.gid[p], J.n1)] = 1;
+        }
+    }
     // the first round believed an untouched FIFO everywhere: a push or a successful pop contradicts that
     if (J.first_round && (info != 0 || s > 0)) { J.res->changed = 1; J.res->tl_changed = 1; }
     if (j == n - 1) {

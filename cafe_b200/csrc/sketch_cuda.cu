@@ -337,7 +337,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                         for (int q = 0; q < 4; ++q) {
                             if (cof[q] != 0) J.mflag[cp[q]] = 0;
                             if (!J.first_round) {
-                                if (cok[q] != CAFE_EV_NONE) { J.ev[cp[q]].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                                if (cok[q] != CAFE_EV_NONE) cafe_withdraw_event(J, cp[q]);
                                 if (cof[q] & CAFE_F_MISS) J.mark2[cafe_hash(cx[q], J.n2)] = 1;
                             }
                         }
@@ -432,7 +432,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     const uint32_t nf = cr ? CAFE_F_CROSS : 0;
                     if (nf != of) J.mflag[p] = (uint8_t)nf;
                     if (!J.first_round) {
-                        if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                        if (ok != CAFE_EV_NONE) cafe_withdraw_event(J, p);
                         if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                     }
                 }
@@ -544,7 +544,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                             const uint32_t nf = (cr ? CAFE_F_CROSS : 0) | (cd ? CAFE_F_POP0 : 0);
                             if (nf != of) J.mflag[p] = (uint8_t)nf;
                             if (!J.first_round) {
-                                if (ok != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                                if (ok != CAFE_EV_NONE) cafe_withdraw_event(J, p);
                                 if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
                             }
                         }
@@ -788,7 +788,7 @@ __device__ __forceinline__ int cafe_lru_apply_chunk(const CafeJob& J, CafeLruRep
         if (W >= 0) R.set(es, ex, ec, ed, J.t0 + 1 + ep);
     }
     if (lane >= a && lane < f) {   // no flags, no event
-        if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+        if (!J.first_round && kind != CAFE_EV_NONE) cafe_withdraw_event(J, p);
         J.lflag[p] = 0;
     }
     return f;
@@ -880,7 +880,7 @@ __device__ __forceinline__ void cafe_lru_feed_lanes(const CafeJob& J, CafeLruRep
         }
         if (fast) {
             if (lane == j) {
-                if (!J.first_round && kind != CAFE_EV_NONE) { J.ev[p].kind = CAFE_EV_NONE; J.res->changed = 1; }
+                if (!J.first_round && kind != CAFE_EV_NONE) cafe_withdraw_event(J, p);
                 J.lflag[p] = 0;
             }
             continue;

@@ -92,6 +92,11 @@ public:
         res_dev = mark_own ? (CafeRoundResult*)(mark_own + off_res) : nullptr;
         mstate = (uint8_t*)be.alloc((size_t)n1);
         lstate = (uint8_t*)be.alloc((size_t)n2);
+        mark_w1[0] = (uint8_t*)be.alloc(2 * (size_t)n1 + (size_t)n2);
+        mark_w1[1] = mark_w1[0] ? mark_w1[0] + n1 : nullptr;
+        mark_c2 = mark_w1[0] ? mark_w1[0] + 2 * (size_t)n1 : nullptr;
+        if (mark_w1[0]) be.memset(mark_w1[0], 0, 2 * (size_t)n1 + (size_t)n2);
+        mark_par = 0;
         mflag = (uint8_t*)be.alloc(M); lflag = (uint8_t*)be.alloc(M);
         tl_slot = (int32_t*)be.alloc(8 * M); tl_info = (int32_t*)be.alloc(8 * M);
         tl_size = (int32_t*)be.alloc(8 * M); tl_rank = (int32_t*)be.alloc(8 * M);
@@ -112,7 +117,7 @@ public:
         if (!ord1 || !ord2 || !start1 || !start2 || !beg1 || !beg2 || !mflag || !lflag || !ev || !head || !nxt || !mark_own || !mstate || !mark2 || !lstate || !ins_res ||
             !res_dev || !seq_dev || !cand_key[0] || !cand_key[1] || !cand_val[0] || !cand_val[1] || !cand_cnt || !reset_out)
             return CAFE_ERR_CUDA;
-        if (!sgid1 || !sgid2 || !simp1 || !simp2) return CAFE_ERR_CUDA;
+        if (!sgid1 || !sgid2 || !simp1 || !simp2 || !mark_w1[0]) return CAFE_ERR_CUDA;
         if (!tl_slot || !tl_info || !tl_size || !tl_rank || !tl_grp || !tl_head || !pushbuf || !tl_blk || !tl_agg || !nmiss) return CAFE_ERR_CUDA;
         ready = true;
         return be.ok() ? CAFE_OK : CAFE_ERR_CUDA;
@@ -325,6 +330,8 @@ private:
     int32_t* head = nullptr;
     int32_t* nxt = nullptr;
     uint8_t *mark_own = nullptr, *mstate = nullptr, *mark2 = nullptr, *lstate = nullptr, *mflag = nullptr, *lflag = nullptr;
+    uint8_t *mark_w1[2] = {nullptr, nullptr}, *mark_c2 = nullptr;   // see CafeJob::mark_in1
+    int mark_par = 0;
     int32_t *tl_slot = nullptr, *tl_info = nullptr, *tl_size = nullptr, *tl_rank = nullptr, *tl_grp = nullptr, *tl_head = nullptr;
     int32_t *tl_blk = nullptr, *nmiss = nullptr;
     uint32_t* pushbuf = nullptr;
@@ -340,7 +347,7 @@ private:
 
     void release() {
         if (!ready && !mainb[0]) return;
-        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, sgid1, sgid2, simp1, simp2, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mflag, lflag, tl_slot, tl_info, tl_size, tl_rank, tl_grp, tl_head, pushbuf, tl_blk, tl_agg, nmiss,
+        void* ptrs[] = {mainb[0], mainb[1], lrub[0], lrub[1], ring, sgid1, sgid2, simp1, simp2, ord1, ord2, start1, start2, beg1, beg2, ev, head, nxt, mark_own, mstate, lstate, mark_w1[0], mflag, lflag, tl_slot, tl_info, tl_size, tl_rank, tl_grp, tl_head, pushbuf, tl_blk, tl_agg, nmiss,
                         ins_res, seq_dev, cand_key[0], cand_key[1],
                         cand_val[0], cand_val[1], cand_cnt, reset_out};
         for (void* p : ptrs) if (p) be.free(p);
@@ -396,6 +403,7 @@ private:
         J.main_in = mainb[cur]; J.main_out = mainb[cur ^ 1];
         J.lru_in = lrub[cur]; J.lru_out = lrub[cur ^ 1];
         J.ev = ev; J.head = head; J.nxt = nxt; J.mark_own = mark_own; J.mstate = mstate; J.mark2 = mark2; J.lstate = lstate;
+        J.mark_in1 = mark_w1[mark_par]; J.mark_out1 = mark_w1[mark_par ^ 1]; J.mark_c2 = mark_c2;
         J.mflag = mflag; J.lflag = lflag; J.ins_res = ins_res;
         J.tl_slot = tl_slot; J.tl_info = tl_info; J.tl_size = tl_size; J.tl_rank = tl_rank; J.tl_grp = tl_grp; J.tl_head = tl_head;
         J.pushbuf = pushbuf; J.tl_blk = tl_blk; J.tl_agg = tl_agg; J.nmiss = nmiss;
@@ -427,6 +435,8 @@ private:
                 return rc == CAFE_OK ? CAFE_OK : rc;
             }
             J.first_round = first ? 1 : 0;
+            J.mark_in1 = mark_w1[mark_par]; J.mark_out1 = mark_w1[mark_par ^ 1];
+            mark_par ^= 1;   // what this round marks is what the next one reads
             J.all_active = (first || shortened) ? 1 : 0;
             J.cand_active = (first || tl_changed_prev) ? 1 : 0;
             J.final_pass = 0;
