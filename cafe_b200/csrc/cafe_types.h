@@ -67,6 +67,7 @@ struct CafeRoundResult {
     int32_t error;         // internal consistency problems seen (0 = none)
     int32_t n_main_hit;
     int32_t n_events;
+    int32_t miss_changed;  // the main pass of this round sent a lookup to the LRU stage that was not there before, or took one away
     int32_t list_cursor[3];  // work counters of the launches that go through the long-bucket lists (main, LRU, final pass)
     int32_t seg_real_delta[CAFE_MAX_SEGMENTS];  // change of real_n per segment
 };

@@ -487,7 +487,7 @@ struct CafeMainReplay {
                 if (nf != old_flag) J.mflag[p] = (uint8_t)nf;
                 if (!J.first_round) {
                     if (old_kind != CAFE_EV_NONE) cafe_withdraw_event(J, p);
-                    if (old_flag & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;   // its LRU bucket loses this visitor
+                    if (old_flag & CAFE_F_MISS) { J.mark2[cafe_hash(x, J.n2)] = 1; J.res->miss_changed = 1; }   // its LRU bucket loses this visitor
                 }
             }
         } else {
@@ -495,7 +495,7 @@ struct CafeMainReplay {
             if (J.final_pass) { if (J.lflag[p] & CAFE_F_GOT) note_cand(p, x); }
             else {
                 if (old_flag != CAFE_F_MISS) J.mflag[p] = CAFE_F_MISS;   // goes to the LRU stage; that pass writes lflag
-                if (!J.first_round && !(old_flag & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor
+                if (!J.first_round && !(old_flag & CAFE_F_MISS)) { J.mark2[cafe_hash(x, J.n2)] = 1; J.res->miss_changed = 1; }   // new visitor
             }
             if (old_kind == CAFE_EV_OWN) {   // believed: this lookup promotes its own id into this bucket
                 apply_event(J, p);

@@ -178,7 +178,7 @@ __device__ __forceinline__ int cafe_warp_exclusive(int n, int lane, int* total) 
 template <int PART>
 __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& H, const int k, float (*s_c)[CAFE_STAGE_MAIN],
                                                int (*s_p)[CAFE_STAGE_MAIN], uint32_t (*s_x)[CAFE_STAGE_MAIN],
-                                               uint32_t (*s_kf)[CAFE_STAGE_MAIN]) {
+                                               uint32_t (*s_kf)[CAFE_STAGE_MAIN], float (*s_d)[CAFE_STAGE_MAIN] = nullptr) {
     const int lane = threadIdx.x & 31;
     const int wib = threadIdx.x >> 5;
     CafeMainReplay R;
@@ -254,7 +254,8 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
         uint32_t x_nx = 0, ok_nx = CAFE_EV_NONE, of_nx = 0;
         float c_nx = 1.0f;
         if (s + lane < e) { x_nx = J.sgid1[s + lane]; if (J.simp1) c_nx = J.simp1[s + lane]; }
-        if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
+        // (the final pass asks of every miss whether the LRU stage handed it a row: that flag byte rides in bits 8-15)
+        if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); if (J.final_pass) of_nx |= (uint32_t)J.lflag[p_nx] << 8; }
         // Number of chunks in a row that went through the calm whole-chunk path.  A calm chunk that ends on a multiple
         // of 256 entries of the bucket looks 512 lookups ahead (one id, one position); if that lookup still belongs
         // to the stretch, the next chunk starts the four-chunk path below.  Shorter stretches stay on the chunk path,
@@ -290,65 +291,141 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     }
                 }
                 const int g_start = gb;
-                int cp[4], xp[4], n2p[4];
-                uint32_t cx[4], cok[4], cof[4], xx[4], xok[4], xof[4];
-                float cc[4], xc[4];
+                // Three sets of registers (A, B, C) take turns as the group being added up, the next one and the one after: positions, ids and counts of a group are requested two groups ahead, what depends on its positions
+                // (the event kind and flags the previous round left there) one group ahead, and no freshly requested
+                // register is touched before its group comes up for its check, a group and a half later.
+                // The chain of 128 additions is the only serial part of a group.  The counts of a group are checked and
+                // parked in shared memory one group ahead (two buffers), against a bound taken once (the count at the
+                // start: counts only grow, so an addend below it is below every later count too).
+                int Ap[4], Bp[4], Cp[4];
+                uint32_t Ax[4], Bx[4], Cx[4], Aok[4], Bok[4], Cok[4], Aof[4], Bof[4], Cof[4];
+                float Ac[4], Bc[4], Cc[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int i0 = gb + 32 * q + lane, i1 = i0 + 128;
-                    cp[q] = i0 < e ? J.ord1[i0] : INT32_MAX;
-                    xp[q] = i1 < e ? J.ord1[i1] : INT32_MAX;
+                    Ap[q] = i0 < e ? J.ord1[i0] : INT32_MAX;
+                    Bp[q] = i1 < e ? J.ord1[i1] : INT32_MAX;
+                    Ax[q] = 0; Ac[q] = 1.0f; Bx[q] = 0; Bc[q] = 1.0f;
+                    if (i0 < e) { Ax[q] = J.sgid1[i0]; if (J.simp1) Ac[q] = J.simp1[i0]; }
+                    if (i1 < e) { Bx[q] = J.sgid1[i1]; if (J.simp1) Bc[q] = J.simp1[i1]; }
+                    Cp[q] = INT32_MAX; Cx[q] = 0; Cc[q] = 1.0f; Cok[q] = CAFE_EV_NONE; Cof[q] = 0; Bok[q] = CAFE_EV_NONE; Bof[q] = 0;
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    cx[q] = 0; cok[q] = CAFE_EV_NONE; cof[q] = 0; cc[q] = 1.0f;
-                    const int i0 = gb + 32 * q + lane;
-                    if (i0 < e) { cx[q] = J.sgid1[i0]; if (J.simp1) cc[q] = J.simp1[i0]; }
-                    if (cp[q] < J.limit) { cok[q] = cafe_old_kind(J, cp[q]); cof[q] = cafe_old_mflag(J, cp[q]); }
+                    Aok[q] = CAFE_EV_NONE; Aof[q] = 0;
+                    if (Ap[q] < J.limit) { Aok[q] = cafe_old_kind(J, Ap[q]); Aof[q] = cafe_old_mflag(J, Ap[q]); }
                 }
-                for (;;) {
-                    bool good = true;
+                const float acc_bound = acc;
+                float* const buf0 = s_c[wib];
+                float* const buf1 = s_d[wib];
+                bool good;
+                {
+                    bool g = true;
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) good = good && cp[q] < hbound && cx[q] == hx && cc[q] >= 0.f && cc[q] <= acc;
-                    if (!__all_sync(CAFE_FULL, good)) break;
+                    for (int q = 0; q < 4; ++q) g = g && Ap[q] < hbound && Ax[q] == hx && Ac[q] >= 0.f && Ac[q] <= acc_bound;
+                    good = __all_sync(CAFE_FULL, g);
+                }
+                if (good) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int i2 = gb + 256 + 32 * q + lane;
-                        n2p[q] = i2 < e ? J.ord1[i2] : INT32_MAX;
-                        xx[q] = 0; xok[q] = CAFE_EV_NONE; xof[q] = 0; xc[q] = 1.0f;
-                        const int i1 = gb + 128 + 32 * q + lane;
-                        if (i1 < e) { xx[q] = J.sgid1[i1]; if (J.simp1) xc[q] = J.simp1[i1]; }
-                        if (xp[q] < J.limit) { xok[q] = cafe_old_kind(J, xp[q]); xof[q] = cafe_old_mflag(J, xp[q]); }
+                    for (int q = 0; q < 4; ++q) buf0[32 * q + lane] = Ac[q];
+                }
+                // what goes back to the chunk pipeline: the first chunk of the first group that is not added up here
+                int h_p0 = Ap[0], h_p1 = Ap[1];
+                uint32_t h_x = Ax[0], h_ok = Aok[0], h_of = Aof[0];
+                float h_c = Ac[0];
+                int bsel = 0;
+// one group: C is added up, X is checked and parked, Y is requested
+#define CAFE_GROUP_STEP(C, X, Y)                                                                                          \
+                {                                                                                                         \
+                    _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                                       \
+                        const int i2 = gb + 256 + 32 * q + lane;                                                          \
+                        Y##p[q] = INT32_MAX; Y##x[q] = 0; Y##c[q] = 1.0f;                                                 \
+                        if (i2 < e) { Y##p[q] = J.ord1[i2]; Y##x[q] = J.sgid1[i2]; if (J.simp1) Y##c[q] = J.simp1[i2]; }  \
+                        X##ok[q] = CAFE_EV_NONE; X##of[q] = 0;                                                            \
+                        if (X##p[q] < J.limit) { X##ok[q] = cafe_old_kind(J, X##p[q]); X##of[q] = cafe_old_mflag(J, X##p[q]); } \
+                    }                                                                                                     \
+                    __syncwarp();                                                                                         \
+                    {                                                                                                     \
+                        const float4* cv = reinterpret_cast<const float4*>(bsel ? buf1 : buf0);                           \
+                        _Pragma("unroll") for (int q = 0; q < 32; ++q) {                                                  \
+                            const float4 t = cv[q];                                                                       \
+                            acc = acc + t.x; acc = acc + t.y; acc = acc + t.z; acc = acc + t.w;                           \
+                        }                                                                                                 \
+                    }                                                                                                     \
+                    if (!J.final_pass) {                                                                                  \
+                        _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                                   \
+                            if (C##of[q] != 0) J.mflag[C##p[q]] = 0;                                                      \
+                            if (!J.first_round) {                                                                         \
+                                if (C##ok[q] != CAFE_EV_NONE) cafe_withdraw_event(J, C##p[q]);                            \
+                                if (C##of[q] & CAFE_F_MISS) { J.mark2[cafe_hash(C##x[q], J.n2)] = 1; J.res->miss_changed = 1; } \
+                            }                                                                                             \
+                        }                                                                                                 \
+                    }                                                                                                     \
+                    gb += 128;                                                                                            \
+                    bool g = true;                                                                                        \
+                    _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                         \
+                        g = g && X##p[q] < hbound && X##x[q] == hx && X##c[q] >= 0.f && X##c[q] <= acc_bound;             \
+                    good = __all_sync(CAFE_FULL, g);                                                                      \
+                    bsel ^= 1;                                                                                            \
+                    if (good) {                                                                                           \
+                        float* const nb = bsel ? buf1 : buf0;                                                             \
+                        _Pragma("unroll") for (int q = 0; q < 4; ++q) nb[32 * q + lane] = X##c[q];                        \
+                    } else {                                                                                              \
+                        h_p0 = X##p[0]; h_p1 = X##p[1]; h_x = X##x[0]; h_ok = X##ok[0]; h_of = X##of[0]; h_c = X##c[0];   \
+                    }                                                                                                     \
+                }
+// the same in a first round, where no position has flags or an event yet: nothing to read there, nothing to clear
+// (entries past the bucket's end are read at the last entry and given a position that fails the check)
+#define CAFE_GROUP_STEP_FIRST(C, X, Y)                                                                                    \
+                {                                                                                                         \
+                    _Pragma("unroll") for (int q = 0; q < 4; ++q) {                                                       \
+                        const int i2 = gb + 256 + 32 * q + lane, i2c = min(i2, e - 1);                                    \
+                        const int yp = J.ord1[i2c];                                                                       \
+                        Y##x[q] = J.sgid1[i2c];                                                                           \
+                        Y##c[q] = imp1[i2c];                                                                              \
+                        Y##p[q] = i2 < e ? yp : INT32_MAX;                                                                \
+                    }                                                                                                     \
+                    __syncwarp();                                                                                         \
+                    {                                                                                                     \
+                        const float4* cv = reinterpret_cast<const float4*>(bsel ? buf1 : buf0);                           \
+                        _Pragma("unroll") for (int q = 0; q < 32; ++q) {                                                  \
+                            const float4 t = cv[q];                                                                       \
+                            acc = acc + t.x; acc = acc + t.y; acc = acc + t.z; acc = acc + t.w;                           \
+                        }                                                                                                 \
+                    }                                                                                                     \
+                    gb += 128;                                                                                            \
+                    bool g = true;                                                                                        \
+                    _Pragma("unroll") for (int q = 0; q < 4; ++q)                                                         \
+                        g = g && X##p[q] < hbound && X##x[q] == hx && X##c[q] >= 0.f && X##c[q] <= acc_bound;             \
+                    good = __all_sync(CAFE_FULL, g);                                                                      \
+                    bsel ^= 1;                                                                                            \
+                    if (good) {                                                                                           \
+                        float* const nb = bsel ? buf1 : buf0;                                                             \
+                        _Pragma("unroll") for (int q = 0; q < 4; ++q) nb[32 * q + lane] = X##c[q];                        \
+                    } else {                                                                                              \
+                        h_p0 = X##p[0]; h_p1 = X##p[1]; h_x = X##x[0]; h_c = X##c[0];                                     \
+                    }                                                                                                     \
+                }
+                if (J.first_round && !J.final_pass && J.simp1) {
+                    const float* __restrict__ imp1 = J.simp1;
+                    while (good) {
+                        CAFE_GROUP_STEP_FIRST(A, B, C)
+                        if (!good) break;
+                        CAFE_GROUP_STEP_FIRST(B, C, A)
+                        if (!good) break;
+                        CAFE_GROUP_STEP_FIRST(C, A, B)
                     }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) s_c[wib][32 * q + lane] = cc[q];
-                    __syncwarp();
-                    {
-                        const float4* cv = reinterpret_cast<const float4*>(s_c[wib]);
-#pragma unroll
-                        for (int q = 0; q < 32; ++q) {
-                            const float4 t = cv[q];
-                            acc = acc + t.x; acc = acc + t.y; acc = acc + t.z; acc = acc + t.w;
-                        }
-                    }
-                    __syncwarp();
-                    if (!J.final_pass) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            if (cof[q] != 0) J.mflag[cp[q]] = 0;
-                            if (!J.first_round) {
-                                if (cok[q] != CAFE_EV_NONE) cafe_withdraw_event(J, cp[q]);
-                                if (cof[q] & CAFE_F_MISS) J.mark2[cafe_hash(cx[q], J.n2)] = 1;
-                            }
-                        }
-                    }
-                    gb += 128;
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        cp[q] = xp[q]; cx[q] = xx[q]; cc[q] = xc[q]; cok[q] = xok[q]; cof[q] = xof[q];
-                        xp[q] = n2p[q];
+                } else {
+                    while (good) {
+                        CAFE_GROUP_STEP(A, B, C)
+                        if (!good) break;
+                        CAFE_GROUP_STEP(B, C, A)
+                        if (!good) break;
+                        CAFE_GROUP_STEP(C, A, B)
                     }
                 }
+#undef CAFE_GROUP_STEP
+#undef CAFE_GROUP_STEP_FIRST
                 if (gb != base) {
                     if (J.memo1 && g_start == base && gb - base >= 512 && lane == 0) {   // (walked, not jumped: remember it)
                         CafeCalmMemo mm;
@@ -364,8 +441,9 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     base = gb;
                     if (base >= e) break;
                     // hand the loaded lookups back to the chunk pipeline
-                    p_nx = cp[0]; x_nx = cx[0]; c_nx = cc[0]; ok_nx = cok[0]; of_nx = cof[0];
-                    p_n2 = cp[1];
+                    p_nx = h_p0; x_nx = h_x; c_nx = h_c; ok_nx = h_ok; of_nx = h_of;
+                    if (J.final_pass && p_nx < J.limit) of_nx |= (uint32_t)J.lflag[p_nx] << 8;
+                    p_n2 = h_p1;
                 }
             }
             const int streak_in = calm_streak;
@@ -377,7 +455,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
             p_n2 = (base + 64 + lane < e) ? J.ord1[base + 64 + lane] : INT32_MAX;
             x_nx = 0; ok_nx = CAFE_EV_NONE; of_nx = 0; c_nx = 1.0f;
             if (base + 32 + lane < e) { x_nx = J.sgid1[base + 32 + lane]; if (J.simp1) c_nx = J.simp1[base + 32 + lane]; }
-            if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); }
+            if (p_nx < J.limit) { ok_nx = cafe_old_kind(J, p_nx); of_nx = cafe_old_mflag(J, p_nx); if (J.final_pass) of_nx |= (uint32_t)J.lflag[p_nx] << 8; }
             const int n = min(32, e - base);
             // Whole chunk = 32 more lookups of the id the previous step dealt with, whose slot owns a hot
             // row: add the 32 counts in order, write 32 flags, nothing else can happen.
@@ -433,7 +511,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     if (nf != of) J.mflag[p] = (uint8_t)nf;
                     if (!J.first_round) {
                         if (ok != CAFE_EV_NONE) cafe_withdraw_event(J, p);
-                        if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                        if (of & CAFE_F_MISS) { J.mark2[cafe_hash(x, J.n2)] = 1; J.res->miss_changed = 1; }
                     }
                 }
                 continue;
@@ -478,7 +556,7 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                     bound = __shfl_sync(CAFE_FULL, bound, o);
                     ms = (x == bv0) ? 0 : (x == bv1) ? 1 : (x == bv2) ? 2 : (x == bv3) ? 3 : -1;
                     bool pure = lane >= j && lane < n && ms < 0 && p < bound && ok != CAFE_EV_OWN;
-                    if (pure && J.final_pass && (J.lflag[p] & CAFE_F_GOT) != 0) pure = false;
+                    if (pure && J.final_pass && ((of >> 8) & CAFE_F_GOT) != 0) pure = false;
                     const bool mine = lane >= j && lane < n && p < bound && (ms >= 0 || pure);
                     const unsigned q = __ballot_sync(CAFE_FULL, mine) >> j;
                     run = __ffs(~q) - 1;          // length of the run of set bits starting at lane j
@@ -545,12 +623,12 @@ __device__ __forceinline__ void cafe_main_body(const CafeJob& J, const CafeHot& 
                             if (nf != of) J.mflag[p] = (uint8_t)nf;
                             if (!J.first_round) {
                                 if (ok != CAFE_EV_NONE) cafe_withdraw_event(J, p);
-                                if (of & CAFE_F_MISS) J.mark2[cafe_hash(x, J.n2)] = 1;
+                                if (of & CAFE_F_MISS) { J.mark2[cafe_hash(x, J.n2)] = 1; J.res->miss_changed = 1; }
                             }
                         }
                         if (!J.final_pass && in_done && ms < 0) {   // goes to the LRU stage; that pass writes lflag
                             if (of != CAFE_F_MISS) J.mflag[p] = CAFE_F_MISS;
-                            if (!J.first_round && !(of & CAFE_F_MISS)) J.mark2[cafe_hash(x, J.n2)] = 1;   // new visitor
+                            if (!J.first_round && !(of & CAFE_F_MISS)) { J.mark2[cafe_hash(x, J.n2)] = 1; J.res->miss_changed = 1; }   // new visitor
                         }
                         if (done < run) hvalid = false;
                         j += done;
@@ -575,6 +653,7 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
     __shared__ __align__(16) float s_c[4][CAFE_STAGE_MAIN];  // per warp: counts of the staged tile / of the chunks being added up
     __shared__ int s_p[4][CAFE_STAGE_MAIN];                  // staged positions, ids, old event kind | old flags << 8
     __shared__ uint32_t s_x[4][CAFE_STAGE_MAIN], s_kf[4][CAFE_STAGE_MAIN];
+    __shared__ __align__(16) float s_d[PART == 0 ? 4 : 1][CAFE_STAGE_MAIN];   // list launch: the second buffer of the four-chunk path
     if (PART == 1) {
         const int k = blockIdx.x * blockDim.x + threadIdx.x;
         cafe_main_body<1>(J, H, k < J.n1 ? k : J.n1, s_c, s_p, s_x, s_kf);
@@ -582,7 +661,7 @@ __global__ void __launch_bounds__(128, PART == 1 ? 6 : 1) k_main_pass(const __gr
         for (;;) {
             const int k = cafe_next_listed(H, &J.res->list_cursor[J.final_pass ? 2 : 0], J.n1);
             if (k < 0) break;
-            cafe_main_body<0>(J, H, k, s_c, s_p, s_x, s_kf);
+            cafe_main_body<0>(J, H, k, s_c, s_p, s_x, s_kf, s_d);
         }
     }
 }
@@ -1296,8 +1375,10 @@ __device__ __forceinline__ int cafe_entry_missed(const CafeJob& J, int i) {
     const int p = J.ord2[i];
     return (p >= J.begin && p < J.limit && (J.mflag[p] & CAFE_F_MISS)) ? 1 : 0;
 }
+// (a later round in which no lookup entered or left the LRU stage keeps the lists of the round before)
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_count(const __grid_constant__ CafeJob J, const CafeMissList L) {
     __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    if (!J.all_active && !J.res->miss_changed) return;
     int c = 0;
 #pragma unroll
     for (int q = 0; q < CAFE_TL_PER; ++q) {
@@ -1310,6 +1391,7 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_count(const __grid
 }
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_emit(const __grid_constant__ CafeJob J, const CafeMissList L) {
     __shared__ int s_warp[CAFE_TL_THREADS / 32];
+    if (!J.all_active && !J.res->miss_changed) return;
     int v = 0;
     for (int q = threadIdx.x; q < (int)blockIdx.x; q += CAFE_TL_THREADS) v += L.blk[q];
     int base;
