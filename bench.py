@@ -603,11 +603,19 @@ def run_ours(args, rank, world, local_rank):
                 except Exception:
                     traffic = None
             fused = FUSED_BYTES_PER_ID(DIM, u_rows) * ids_per_step / (ms / K / 1e3) / 1e9 / world
+            main_roof = None
+            if "main_pass" in slots and slots["main_pass"][1] > 0:
+                mp_ms = slots["main_pass"][0] / slots["main_pass"][1]
+                mp_units = rank_ids / max(1.0, slots["main_pass"][1] / K)
+                mp_ach = alg_bytes("main_pass", DIM) * mp_units / (mp_ms / 1e3) / 1e9
+                main_roof = {"achieved": mp_ach, "frac": mp_ach / peak, "ms_per_launch": mp_ms, "ids_per_launch": mp_units,
+                             "note": "the all-bucket launches of the sketch's main pass (120 B per lookup)"}
             roof = {"bound": "hbm", "kernel": top, "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                     "traffic": traffic, "peak_kind": peak_kind, "alg_bytes_per_id": alg_bytes(top, DIM, u_rows),
                     "distinct_rows_per_lookup": u_rows,
-                    "ms_per_launch": per_launch_ms, "ids_per_launch": units,
+                    "ms_per_launch": per_launch_ms, "ids_per_launch": units, "main_pass": main_roof,
                     "fused_path": {"alg_bytes_per_id": FUSED_BYTES_PER_ID(DIM, u_rows), "achieved": fused, "frac": fused / peak,
+                                   "frac_every_lookup_its_own_row": FUSED_BYTES_PER_ID(DIM, 1.0) * ids_per_step / (ms / K / 1e3) / 1e9 / world / peak,
                                    "note": "per GPU: whole-step algorithmic bytes / step time / n_gpus"}}
         dl = st1["lookups"] - st0["lookups"]
         mix = {"lookups": dl, "main_hit_frac": (st1["main_hits"] - st0["main_hits"]) / max(1, dl),
