@@ -318,18 +318,7 @@ class ShardedSKEmbedding(torch.nn.Module):
             raise ValueError("more ranks than fields")
         self.embedding_dim = int(embedding_dim)
         self.global_batch = int(global_batch)
-        # The reference has one sketch and one hot table for all fields (dlrm_s_pytorch.py:1239-1240, 444-449).  Sharded
-        # by field, every rank owns a part of that capacity: in proportion to its number of fields ("fields": equal
-        # lookups per call meet equal capacity, whatever the fields' cardinalities) or as the reference's formula gives
-        # for the rank's own fields alone ("rows": a rank that holds only small fields then gets a sketch of a few
-        # buckets, or none).  Never below the 20 rows the sketch needs for a non-empty LRU stage (sketch.cpp:51-52).
-        if hot_rows_by == "fields":
-            total = sizing.hot_rows(sum(cards), compress_rate, hash_rate, self.embedding_dim)
-            hotn = max(20, total * len(mine) // len(cards))
-        elif hot_rows_by == "rows":
-            hotn = max(20, sizing.hot_rows(sum(cards[f] for f in mine), compress_rate, hash_rate, self.embedding_dim))
-        else:
-            raise ValueError("hot_rows_by must be 'fields' or 'rows'")
+        hotn = sizing.shard_hot_rows(cards, mine, compress_rate, hash_rate, self.embedding_dim, hot_rows_by)
         self.group = SKEmbeddingGroup([cards[f] for f in mine], embedding_dim, compress_rate, hash_rate, sketch_threshold,
                                       adjust_threshold, sketch_alpha, device=device, max_batch=global_batch, lr=lr,
                                       f_offsets=[offs[f] for f in mine], hotn=hotn,

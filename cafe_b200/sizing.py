@@ -27,3 +27,19 @@ def field_offsets(num_categories) -> list[int]:
         out.append(tot)
         tot += int(n)
     return out
+
+
+def shard_hot_rows(num_categories, local_fields, compress_rate: float, hash_rate: float, dim: int, by: str = "fields") -> int:
+    """Hot-table capacity of one shard of a field-sharded model.  The reference has one sketch and one hot table for
+    all fields (dlrm_s_pytorch.py:1239-1240, 444-449); a shard owns a part of that capacity: in proportion to its
+    number of fields ("fields": equal lookups per call meet equal capacity, whatever the fields' cardinalities) or
+    what the reference's formula gives for the shard's own fields alone ("rows": a shard that holds only small fields
+    then gets a sketch of a few buckets, or none).  Never below the 20 rows the sketch needs for a non-empty LRU
+    stage (sketch.cpp:51-52)."""
+    cards = [int(n) for n in num_categories]
+    mine = list(local_fields)
+    if by == "fields":
+        return max(20, hot_rows(sum(cards), compress_rate, hash_rate, dim) * len(mine) // len(cards))
+    if by == "rows":
+        return max(20, hot_rows(sum(cards[f] for f in mine), compress_rate, hash_rate, dim))
+    raise ValueError("hot_rows_by must be 'fields' or 'rows'")

@@ -115,3 +115,23 @@ def test_exchanges_on_a_subgroup_of_the_job():
     for p in procs:
         p.join(timeout=60)
     assert all(a and b for _, a, b in res), res
+
+
+def test_shard_capacity_by_fields_and_by_rows():
+    """Terabyte cardinalities at compress 1e-4 / hash-rate 0.2 / dim 128 over 8 ranks, fields round-robin: sized from
+    its own rows, the rank that owns fields 7, 15 and 23 (1 543 + 155 + 12 972 ids) would get a capacity of 1 (the
+    reference's constructor divides by int(0.1 * lim) = 0); sized by field count every rank gets 3/26 or 4/26 of the
+    13 733 rows the reference's formula gives for all fields."""
+    from cafe_b200 import sizing
+    from cafe_b200.synthetic import TERABYTE_CARDS
+    cards = list(TERABYTE_CARDS)
+    total = sizing.hot_rows(sum(cards), 1e-4, 0.2, 128)
+    assert total == 13733
+    shares = []
+    for r in range(8):
+        mine = list(range(r, 26, 8))
+        shares.append(sizing.shard_hot_rows(cards, mine, 1e-4, 0.2, 128, "fields"))
+        assert shares[-1] == total * len(mine) // 26
+    assert sum(shares) <= total and min(shares) >= 1584
+    assert sizing.hot_rows(sum(cards[f] for f in (7, 15, 23)), 1e-4, 0.2, 128) == 1
+    assert sizing.shard_hot_rows(cards, [7, 15, 23], 1e-4, 0.2, 128, "rows") == 20
