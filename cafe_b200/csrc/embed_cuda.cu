@@ -296,7 +296,7 @@ __device__ __forceinline__ void sgd_apply(float* w, float4 g, float lr) {
 #define NOKEY 0xffffffffu
 
 template <int G>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 k_scatter_chunks(const __grid_constant__ CafeFields F, const float* __restrict__ grad, int64_t field_stride,
                  int64_t sample_stride, const uint32_t* __restrict__ skey, const int32_t* __restrict__ spos, int M,
                  float lr, float* __restrict__ partial) {
