@@ -602,7 +602,10 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     A((void**)&ws->key_tmp, 4 * M);
     A((void**)&ws->bucket_key[0], 4 * M); A((void**)&ws->bucket_key[1], 4 * M);
     A((void**)&ws->sort_scratch, 4 * cafe_rs_scratch_elems(cap));
-    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
+    // (highest priority, like the sketch's sort streams: a chain of small kernels beside kernels that fill the SMs)
+    int prio_lo = 0, prio_hi = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ws->side, cudaStreamNonBlocking, prio_hi);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_join, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->late, cudaStreamNonBlocking);

@@ -1652,7 +1652,11 @@ struct CudaBackend {
             check(cudaMalloc(&pos_tmp[i], 4 * (size_t)cap));
             check(cudaMalloc(&sort_scratch[i], 4 * cafe_rs_scratch_elems(cap)));
             if (i == 0) continue;
-            check(cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking));
+            // (highest priority: the sorts are chains of small kernels that run beside streaming kernels filling every
+            // SM; their blocks must not queue behind those)
+            int lo = 0, hi = 0;
+            check(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+            check(cudaStreamCreateWithPriority(&side[i], cudaStreamNonBlocking, hi));
             check(cudaEventCreateWithFlags(&ev_fork[i], cudaEventDisableTiming));
             check(cudaEventCreateWithFlags(&ev_join[i], cudaEventDisableTiming));
         }
