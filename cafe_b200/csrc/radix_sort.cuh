@@ -2,11 +2,10 @@
 // three sorts: lookups by main-table bucket, lookups by LRU-table bucket (the order in which the sequential
 // insert of tricks/sketch.cpp:268-296 meets the ids of one bucket must be kept, hence stable), and the
 // scatter's lookups by table row.  Keys are bucket or row numbers of 17 to 20 bits, so two passes of up to
-// 10 bits do; a pass is three small kernels and one scatter:
+// 10 bits do; a pass is two small kernels and one scatter:
 //   k_rs_hist         digit histogram of every tile of CAFE_RS_TILE keys            -> hist[digit][tile]
 //   k_rs_scan_cols    per digit, exclusive prefix over the tiles (in place)         -> totals[digit]
-//   k_rs_scan_digits  exclusive prefix over the digits (in place)
-//   k_rs_scatter      every key to totals[digit] + hist[digit][tile] + its rank among the tile's keys of
+//   k_rs_scatter      every key to (totals of the digits before its own) + hist[digit][tile] + its rank among the tile's keys of
 //                     that digit, ranks taken in index order (warp match + per-warp counters), so equal
 //                     keys keep their order
 // The first pass can take its keys straight from the ids (hash of the id into nb buckets), and the last
@@ -88,15 +87,6 @@ k_rs_scan_cols(int32_t* __restrict__ hist, int tiles, int32_t* __restrict__ tota
     if (threadIdx.x == 0) totals[blockIdx.x] = run;
 }
 
-// one block: exclusive prefix over the digits, in place (bins <= CAFE_RS_MAX_BINS = block size)
-static __global__ void __launch_bounds__(CAFE_RS_MAX_BINS) k_rs_scan_digits(int32_t* __restrict__ totals, int bins) {
-    __shared__ int s_warp[CAFE_RS_MAX_BINS / 32];
-    const int v = (int)threadIdx.x < bins ? totals[threadIdx.x] : 0;
-    int tot;
-    const int ex = cafe_rs_block_exclusive(v, &tot, s_warp);
-    if ((int)threadIdx.x < bins) totals[threadIdx.x] = ex;
-}
-
 // val_in == null: the value of pair i is i.  gather_src != null: gather_out[sorted index] = gather_src[value].
 static __global__ void __launch_bounds__(CAFE_RS_THREADS)
 k_rs_scatter(const CafeKeySource S, const int32_t* __restrict__ val_in, uint32_t* __restrict__ key_out,
@@ -104,12 +94,32 @@ k_rs_scatter(const CafeKeySource S, const int32_t* __restrict__ val_in, uint32_t
              const int32_t* __restrict__ totals, const uint32_t* __restrict__ gather_src, uint32_t* __restrict__ gather_out) {
     __shared__ int s_hist[CAFE_RS_WARPS][CAFE_RS_MAX_BINS];   // per warp: keys of each digit seen so far, then the prefix over warps
     __shared__ int s_base[CAFE_RS_MAX_BINS];                  // first output index of the tile's keys of each digit
+    __shared__ int s_warp[CAFE_RS_WARPS];
     const int bins = 1 << bits;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
     for (int d = threadIdx.x; d < bins; d += CAFE_RS_THREADS) {
 #pragma unroll
         for (int q = 0; q < CAFE_RS_WARPS; ++q) s_hist[q][d] = 0;
-        s_base[d] = totals[d] + hist[(size_t)d * tiles + blockIdx.x];
+    }
+    {
+        // first output index of every digit = the digits' totals before it (every block adds them up itself: at most
+        // 1024 numbers, which saves a launch per pass) + the tile's place among the tiles' keys of that digit
+        constexpr int PER = CAFE_RS_MAX_BINS / CAFE_RS_THREADS;
+        int loc[PER], sum = 0;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = (int)threadIdx.x * PER + i;
+            loc[i] = d < bins ? totals[d] : 0;
+            sum += loc[i];
+        }
+        int tot;
+        int ex = cafe_rs_block_exclusive(sum, &tot, s_warp);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int d = (int)threadIdx.x * PER + i;
+            if (d < bins) s_base[d] = ex + hist[(size_t)d * tiles + blockIdx.x];
+            ex += loc[i];
+        }
     }
     __syncthreads();
     // a warp owns CAFE_RS_ITEMS * 32 consecutive pairs and walks them 32 at a time, so (iteration, lane) is index order
@@ -180,7 +190,6 @@ static inline cudaError_t cafe_radix_sort(const CafeKeySource& src, const int32_
         const int shift = p * bits;
         k_rs_hist<<<tiles, CAFE_RS_THREADS, 0, st>>>(S, n, shift, bits, hist, tiles);
         k_rs_scan_cols<<<1 << bits, CAFE_RS_THREADS, 0, st>>>(hist, tiles, totals);
-        k_rs_scan_digits<<<1, CAFE_RS_MAX_BINS, 0, st>>>(totals, 1 << bits);
         k_rs_scatter<<<tiles, CAFE_RS_THREADS, 0, st>>>(S, vin, ko, vo, n, shift, bits, hist, tiles, totals,
                                                          last ? gather_src : nullptr, last ? gather_out : nullptr);
         S.key = ko; S.gid = nullptr; S.nb = 0;

@@ -80,8 +80,11 @@ __global__ void k_post_query(const CafeMainBucket* __restrict__ mb, int n1, cons
 }
 
 // start[k] = first sorted index whose key is >= k, for k in [0, nb]
-__global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb, int32_t* __restrict__ start) {
+// (also zeroes the two counters of the long-bucket list that k_find_hot, the next launch, fills)
+__global__ void k_bucket_starts(const uint32_t* __restrict__ skey, int M, int nb, int32_t* __restrict__ start,
+                                int32_t* __restrict__ hot_count) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < 2) hot_count[i] = 0;
     if (i > M) return;
     const int lo = (i == 0) ? 0 : (int)skey[i - 1] + 1;
     const int hi = (i == M) ? nb : (int)skey[i];
@@ -122,18 +125,27 @@ struct CafeHot {
     const uint8_t* flag;
     int32_t cap2;   // capacity of the second region
 };
+// (also sets every bucket's flag, listed or not, and its cursor beg[k] = start[k])
 __global__ void k_find_hot(const int32_t* __restrict__ start, int nb, int hot_len, int long_len, int cap2, int32_t* list,
-                           int32_t* count, uint8_t* flag) {
+                           int32_t* count, uint8_t* flag, int32_t* __restrict__ beg) {
     int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= nb) return;
-    const int len = start[k + 1] - start[k];
-    if (len <= long_len) return;
-    if (len > hot_len) {
-        const int idx = atomicAdd(&count[0], 1);
-        if (idx < CAFE_HOT_CAP) { list[idx] = k; flag[k] = 1; return; }
+    const int s0 = start[k];
+    const int len = start[k + 1] - s0;
+    beg[k] = s0;
+    uint8_t listed = 0;
+    if (len > long_len) {
+        bool placed = false;
+        if (len > hot_len) {
+            const int idx = atomicAdd(&count[0], 1);
+            if (idx < CAFE_HOT_CAP) { list[idx] = k; listed = 1; placed = true; }
+        }
+        if (!placed) {
+            const int idx = atomicAdd(&count[1], 1);
+            if (idx < cap2) { list[CAFE_HOT_CAP + idx] = k; listed = 1; }
+        }
     }
-    const int idx = atomicAdd(&count[1], 1);
-    if (idx < cap2) { list[CAFE_HOT_CAP + idx] = k; flag[k] = 1; }
+    flag[k] = listed;
 }
 // next listed bucket for this warp (lane 0 owns it; -1 = none left); the cursor is zeroed with the round result
 __device__ __forceinline__ int cafe_next_listed(const CafeHot& H, int32_t* cursor, int nb) {
@@ -1719,20 +1731,18 @@ struct CudaBackend {
         src.key = given_key[lane]; src.gid = gid; src.nb = nb;
         check(cafe_radix_sort(src, nullptr, key_tmp[lane], pos_tmp[lane], key_out[lane], ord, M, bits_for(nb), sort_scratch[lane],
                               gid, sgid, st));
-        k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start);
-        check_launch();
         const int t = (nb == hot_nb[0]) ? 0 : 1;
-        check(cudaMemsetAsync(hot_count[t], 0, 8, st));
-        check(cudaMemsetAsync(hot_flag[t], 0, (size_t)nb, st));
+        k_bucket_starts<<<cafe_blocks((int64_t)M + 1), CAFE_TPB, 0, st>>>(key_out[lane], M, nb, start, hot_count[t]);
+        check_launch();
         // A warp feeding one long bucket leaves 31 lanes idle while it loads, so it pays where that bucket would
         // otherwise be a serial tail of the thread-per-bucket launch: more lookups than a few times the average
         // load -- but never more than 64, beyond which one thread's serial replay is the tail whatever the average
         // (a sketch of a few thousand rows fed 65536-id calls has hundreds of lookups in EVERY bucket).
         const int hot_len = std::max(CAFE_HOT_LEN, std::min((int)(16.0 * M / nb), 4096));
         const int long_len = std::max(16, std::min((int)(4.0 * M / nb), 64));
-        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, long_len, nb, hot_list[t], hot_count[t], hot_flag[t]);
+        k_find_hot<<<cafe_blocks(nb), CAFE_TPB, 0, st>>>(start, nb, hot_len, long_len, nb, hot_list[t], hot_count[t], hot_flag[t],
+                                                         beg);
         check_launch();
-        check(cudaMemcpyAsync(beg, start, 4 * (size_t)nb, cudaMemcpyDeviceToDevice, st));
         }
         if (aside) {
             check(cudaEventRecord(ev_join[lane], side[lane]));
