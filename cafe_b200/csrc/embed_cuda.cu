@@ -602,10 +602,7 @@ int cafe_embed_ws_init(CafeEmbedWorkspace* ws, int cap, int hotn) {
     A((void**)&ws->key_tmp, 4 * M);
     A((void**)&ws->bucket_key[0], 4 * M); A((void**)&ws->bucket_key[1], 4 * M);
     A((void**)&ws->sort_scratch, 4 * cafe_rs_scratch_elems(cap));
-    // (highest priority, like the sketch's sort streams: a chain of small kernels beside kernels that fill the SMs)
-    int prio_lo = 0, prio_hi = 0;
-    if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
-    if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&ws->side, cudaStreamNonBlocking, prio_hi);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->side, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ws->ev_join, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ws->late, cudaStreamNonBlocking);
@@ -989,14 +986,16 @@ static int backward_side_work(void* h, CafeEmbedWorkspace* ws, const CafeFields&
                        ws->begun_mode == insert_mode && gid_dev != nullptr;
     ws->begun_gid = nullptr; ws->begun_row = nullptr; ws->begun_total = 0;
     if (begun) return CAFE_OK;
-    int rc = scatter_prepare_aside(ws, FS, row_dev, total, hotn, st);
-    if (rc != CAFE_OK) return rc;
+    // the sketch's two sorts are queued first (the insert needs them long before the scatter needs the row sort) ...
     if (insert_mode != CAFE_INSERT_SEQUENTIAL) {
         // bucket numbers left by cafe_embed_resolve for exactly these lookups save the sorts their hashing
         const bool have = ws->keys_of == gid_dev && ws->keys_total == total;
         cafe_internal_presort(h, gid_dev, total, have ? ws->bucket_key[0] : nullptr, have ? ws->bucket_key[1] : nullptr, st);
     }
-    return CAFE_OK;
+    // ... and run on streams of the highest priority; the row sort's stream has the default one
+    const int rc = scatter_prepare_aside(ws, FS, row_dev, total, hotn, st);
+    if (rc != CAFE_OK && insert_mode != CAFE_INSERT_SEQUENTIAL) cafe_internal_presort(h, nullptr, 0, nullptr, nullptr, st);   // withdrawn
+    return rc;
 }
 static int scatter_join(CafeEmbedWorkspace* ws, cudaStream_t st) {
     return cudaStreamWaitEvent(st, ws->ev_join, 0) == cudaSuccess ? CAFE_OK : fail_cuda("scatter join wait");
