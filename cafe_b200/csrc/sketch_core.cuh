@@ -258,6 +258,7 @@ struct CafeJob {
     int32_t first_round;   // no beliefs exist yet: every bucket replays and nothing old is read
     int32_t all_active;    // every bucket replays (first round, or the job has just been shortened)
     int32_t cand_active;   // the FIFO timeline changed in the previous round: buckets with ids waiting for a row replay
+    int32_t lists_stale;   // the job has just been shortened: per-round lists built for the longer window are rebuilt
     int32_t final_pass;    // converged: buckets that handed out or received rows replay once more to
                            // record post_row; nothing else is written
     // beliefs: the promotion event of every position, kept in place and updated by the LRU pass
@@ -367,6 +368,20 @@ CAFE_HD void cafe_withdraw_event(const CafeJob& J, int p) {
     if (o.kind != CAFE_EV_NONE) J.mark_out1[cafe_hash(o.x, J.n1)] = 1;
     J.ev[p].kind = CAFE_EV_NONE;
     J.res->changed = 1;
+}
+
+// A job that is shortened to [begin, limit) after a round (a threshold re-fit falls due inside it) keeps what the
+// rounds so far worked out for the buckets that saw none of the dropped lookups.  The others replay in the next round:
+// the main bucket of every dropped lookup, its LRU bucket if it went there, and the main bucket its event was headed for.
+// `mark_next1` is the array the next round's main pass reads.
+CAFE_HD void cafe_mark_cut_position(const CafeJob& J, int p, uint8_t* mark_next1) {
+    const uint32_t x = J.gid[p];
+    mark_next1[cafe_hash(x, J.n1)] = 1;
+    if (J.mflag[p] & CAFE_F_MISS) {
+        J.mark_c2[cafe_hash(x, J.n2)] = 1;
+        const CafeEvent e = J.ev[p];
+        if (e.kind != CAFE_EV_NONE) mark_next1[cafe_hash(e.x, J.n1)] = 1;
+    }
 }
 
 // ---- round step 1: one main bucket ---------------------------------------------------------------

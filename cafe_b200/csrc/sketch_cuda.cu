@@ -1157,6 +1157,10 @@ __global__ void __launch_bounds__(128, 6) k_lru_pass_sparse(const __grid_constan
         cafe_lru_body<1>(J, H, k, nullptr);
     }
 }
+__global__ void k_mark_cut(const __grid_constant__ CafeJob J, int from, int to, uint8_t* mark_next1) {
+    const int p = from + blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < to) cafe_mark_cut_position(J, p, mark_next1);
+}
 __global__ void k_route(const __grid_constant__ CafeJob J) {
     int p = J.begin + blockIdx.x * blockDim.x + threadIdx.x;
     if (p < J.limit) cafe_route_position(J, p);
@@ -1390,7 +1394,7 @@ __device__ __forceinline__ int cafe_entry_missed(const CafeJob& J, int i) {
 // (a later round in which no lookup entered or left the LRU stage keeps the lists of the round before)
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_count(const __grid_constant__ CafeJob J, const CafeMissList L) {
     __shared__ int s_warp[CAFE_TL_THREADS / 32];
-    if (!J.all_active && !J.res->miss_changed) return;
+    if (!J.all_active && !J.lists_stale && !J.res->miss_changed) return;
     int c = 0;
 #pragma unroll
     for (int q = 0; q < CAFE_TL_PER; ++q) {
@@ -1403,7 +1407,7 @@ __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_count(const __grid
 }
 __global__ void __launch_bounds__(CAFE_TL_THREADS) k_lru_miss_emit(const __grid_constant__ CafeJob J, const CafeMissList L) {
     __shared__ int s_warp[CAFE_TL_THREADS / 32];
-    if (!J.all_active && !J.res->miss_changed) return;
+    if (!J.all_active && !J.lists_stale && !J.res->miss_changed) return;
     int v = 0;
     for (int q = threadIdx.x; q < (int)blockIdx.x; q += CAFE_TL_THREADS) v += L.blk[q];
     int base;
@@ -1801,6 +1805,12 @@ struct CudaBackend {
             k_main_pass_sparse<<<cafe_blocks(J.n1, 4 * 32 * its), 128, 0, stream>>>(J, hot(0), its);
         }
         pass_join();
+        check_launch();
+    }
+    void mark_cut(const CafeJob& J, int from, int to, uint8_t* mark_next1) {
+        if (to <= from) return;
+        CAFE_PROF(CAFE_P_SCAN, stream);
+        k_mark_cut<<<cafe_blocks(to - from), CAFE_TPB, 0, stream>>>(J, from, to, mark_next1);
         check_launch();
     }
     void route(const CafeJob& J) {

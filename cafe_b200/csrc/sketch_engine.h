@@ -41,6 +41,7 @@ public:
     int round_cap = 48;
     double cross_rate = -1.0;         // threshold crossings per lookup seen in recent jobs (-1: unknown)
     int window = CAFE_MAX_SEGMENTS;   // upper bound on the segments fused into one job
+    bool size_jobs_by_rate = true;    // end a job where the crossing rate predicts the next re-fit (off: tests of the cut path)
     int last_status = CAFE_OK;
     CafeSketchStats stats;
 
@@ -209,7 +210,7 @@ public:
                         double d2 = d * alpha;
                         if (d2 > CAFE_DECAY_BASE) break;
                         // stop where a threshold re-fit is expected (the exact test runs on the results)
-                        if (adjust && cross_rate >= 0 &&
+                        if (adjust && size_jobs_by_rate && cross_rate >= 0 &&
                             real_n + cross_rate * ((double)seg_off[e] - seg_off[s]) > lim * 1.2) break;
                         d = d2; ++e;
                     }
@@ -423,6 +424,7 @@ private:
         CafeRoundResult R;
         int rounds = 0;
         bool truncated = false, shortened = false, tl_changed_prev = true;
+        int dropped_from = 0, dropped_to = 0;   // positions a shortening has just dropped from the job
         bool first = true;
         for (;;) {
             if (rounds >= round_cap) {
@@ -437,9 +439,12 @@ private:
             J.first_round = first ? 1 : 0;
             J.mark_in1 = mark_w1[mark_par]; J.mark_out1 = mark_w1[mark_par ^ 1];
             mark_par ^= 1;   // what this round marks is what the next one reads
-            J.all_active = (first || shortened) ? 1 : 0;
+            J.all_active = first ? 1 : 0;
             J.cand_active = (first || tl_changed_prev) ? 1 : 0;
             J.final_pass = 0;
+            J.lists_stale = shortened ? 1 : 0;
+            // a job that has just been shortened: only what the dropped lookups touched replays (marked for this round)
+            if (shortened) be.mark_cut(J, dropped_from, dropped_to, const_cast<uint8_t*>(J.mark_in1));
             shortened = false;
             if (!first) {   // (the first round's mark2 + round result were cleared with the job's arrays)
                 be.fills(head, 0xff, 4 * (size_t)n1, mark_own, 0, span_clear);   // mark_own + mark2 + round result
@@ -468,12 +473,13 @@ private:
                     if ((double)rn > lim * 1.2) { cut = b; break; }
                 }
                 if (cut > 0) {
+                    dropped_from = J.seg_off[cut]; dropped_to = J.limit;
                     J.limit = J.seg_off[cut];
                     J.nseg = cut;
                     nseg = cut;
                     if (!truncated) ++stats.truncated_jobs;
                     truncated = true;
-                    shortened = true;   // bucket images written so far include lookups beyond the new end
+                    shortened = true;   // bucket images written so far may include lookups beyond the new end
                     if (J.limit == J.begin) { *done = cut; return CAFE_OK; }   // empty prefix: nothing to commit
                     continue;
                 }

@@ -47,6 +47,7 @@ class EmuSketch:
         lib.emu_refit.argtypes = [ctypes.c_void_p]
         lib.emu_set_window.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib.emu_set_round_cap.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        lib.emu_set_job_sizing.argtypes = [ctypes.c_void_p, ctypes.c_int]
         lib.emu_scalars.argtypes = [ctypes.c_void_p, _i64p, ctypes.POINTER(ctypes.c_double)]
         lib.emu_stats.argtypes = [ctypes.c_void_p, _i64p]
         lib.emu_dump.argtypes = [ctypes.c_void_p, _u32p, _f32p, _i32p, _u8p, _u32p, _f32p, _i32p, _i32p, _u8p, _u32p]
@@ -90,6 +91,9 @@ class EmuSketch:
 
     def set_round_cap(self, c):
         self._lib.emu_set_round_cap(self._h, c)
+
+    def set_job_sizing(self, by_rate):
+        self._lib.emu_set_job_sizing(self._h, 1 if by_rate else 0)
 
     def refit(self):
         return self._lib.emu_refit(self._h)

@@ -75,6 +75,9 @@ struct HostBackend {
         if (flip_order) for (int k = J.n1 - 1; k >= 0; --k) cafe_main_pass_bucket(J, k);
         else for (int k = 0; k < J.n1; ++k) cafe_main_pass_bucket(J, k);
     }
+    void mark_cut(const CafeJob& J, int from, int to, uint8_t* mark_next1) {
+        for (int p = from; p < to; ++p) cafe_mark_cut_position(J, p, mark_next1);
+    }
     void route(const CafeJob& J) {
         for (int p = J.limit - 1; p >= J.begin; --p) cafe_route_position(J, p);
     }
@@ -190,6 +193,7 @@ int emu_insert(void* h, const uint32_t* gid, const float* imp, const int* seg_of
 int emu_refit(void* h) { return ((Engine*)h)->refit_threshold(); }
 void emu_set_window(void* h, int w) { ((Engine*)h)->window = w; }
 void emu_set_round_cap(void* h, int c) { ((Engine*)h)->round_cap = c; }
+void emu_set_job_sizing(void* h, int by_rate) { ((Engine*)h)->size_jobs_by_rate = by_rate != 0; }
 // scalars[0..7] = thr bits, real_n, num, t, gflip, q_size, batch_num, window
 void emu_scalars(void* h, int64_t* out, double* decay) {
     Engine* e = (Engine*)h;

@@ -7,13 +7,15 @@ from oracle.hotsketch import OracleSketch, states_equal
 
 
 def drive(factory, lim, thr, alpha, calls, n, dom, fuse, parallel=True, seed=7, unit=False, zero_ids=False, window=None,
-          round_cap=None, ragged=False):
+          round_cap=None, ragged=False, size_jobs_by_rate=True):
     o = OracleSketch(lim, thr, 1, alpha)
     e = factory(lim, thr, 1, alpha, max(1, n * fuse), parallel)
     if window:
         e.set_window(window)
     if round_cap:
         e.set_round_cap(round_cap)
+    if not size_jobs_by_rate:
+        e.set_job_sizing(False)   # (host emulation only) every job takes all its segments: re-fits cut most of them short
     rng = SplitMix64(seed)
     for c in range(0, calls, fuse):
         idl, vl, ml, pl, off = [], [], [], [], [0]

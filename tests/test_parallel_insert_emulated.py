@@ -33,6 +33,20 @@ def test_fused_fields_with_refits_cutting_jobs():
     assert st["truncated_jobs"] > 0 and st["resets"] > 0 and st["seq_fallbacks"] == 0
 
 
+def test_many_shortened_jobs_replay_only_what_the_cut_touched():
+    """Jobs sized without the crossing-rate prediction: a threshold re-fit falls due inside most of them, the job is
+    shortened to the boundary before it, and only the buckets that the dropped lookups touched replay (several shapes,
+    random and unit counts)."""
+    st = drive(2000, 1, 1.0000005, 52, 1024, 200000, 26, seed=31, size_jobs_by_rate=False)
+    assert st["truncated_jobs"] >= 5 and st["seq_fallbacks"] == 0
+    st = drive(500, 1, 1.05, 48, 600, 20000, 12, seed=32, size_jobs_by_rate=False)
+    assert st["truncated_jobs"] >= 5 and st["seq_fallbacks"] == 0
+    st = drive(3000, 1, 1.0000005, 78, 2048, 2000000, 26, seed=34, size_jobs_by_rate=False, unit=True)
+    assert st["truncated_jobs"] >= 5 and st["seq_fallbacks"] == 0
+    st = drive(200, 1, 1.3, 52, 96, 3000, 13, seed=36, size_jobs_by_rate=False)
+    assert st["truncated_jobs"] >= 3 and st["seq_fallbacks"] == 0
+
+
 def test_kaggle_sized_sketch_fused_26():
     st = drive(13505, 1, 1.0000005, 260, 128, 33762577, 26)
     assert st["seq_fallbacks"] == 0
