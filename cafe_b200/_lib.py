@@ -69,6 +69,9 @@ SIGNATURES = {
                                           POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
     "cafe_embed_backward_imp": (c_int, [_vp, _vp, c_int64, c_int64, _vp, _vp, c_int, _vp, _vp, c_int, c_int, _i64p, _i32p,
                                         POINTER(_vp), _vp, c_int, c_int, c_float, c_int, _vp, _vp]),
+    "cafe_dot_interaction_forward": (c_int, [_vp, _vp, c_int64, c_int64, c_int, c_int, c_int, c_int, _vp, c_int64, _vp]),
+    "cafe_dot_interaction_backward": (c_int, [_vp, _vp, c_int64, c_int64, c_int, c_int, c_int, c_int, _vp, c_int64, _vp, _vp,
+                                              c_int64, c_int64, _vp]),
     "cafe_sigmod_create": (c_int, [POINTER(_vp), c_int, c_int, c_double, c_int]),
     "cafe_sigmod_destroy": (c_int, [_vp]),
     "cafe_sigmod_query": (c_int, [_vp, _vp, c_int, _vp, _vp]),

@@ -14,13 +14,13 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 SO = PKG / "libcafe_b200.so"
-SOURCES = ["sketch_cuda.cu", "embed_cuda.cu", "sigmod_cuda.cu", "ref_abi.cu", "prof.cu"]
+SOURCES = ["sketch_cuda.cu", "embed_cuda.cu", "sigmod_cuda.cu", "interact_cuda.cu", "ref_abi.cu", "prof.cu"]
 HEADERS = ["cafe_types.h", "cafe_internal.h", "sketch_core.cuh", "sketch_engine.h", "radix_sort.cuh"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr"]
 # the sketch arithmetic must not be contracted into fused multiply-adds: counts are compared bit for bit
 PER_FILE = {"sketch_cuda.cu": ["-fmad=false"], "sigmod_cuda.cu": ["-fmad=false"], "ref_abi.cu": ["-fmad=false"], "embed_cuda.cu": [],
-            "prof.cu": []}
+            "prof.cu": [], "interact_cuda.cu": []}
 
 
 def _nvcc() -> str:

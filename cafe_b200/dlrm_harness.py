@@ -43,6 +43,8 @@ def add_cafe_arguments(parser: argparse.ArgumentParser) -> argparse.ArgumentPars
     parser.add_argument("--adjust-threshold", type=int, default=1)
     parser.add_argument("--sketch-alpha", type=float, default=1.0)
     parser.add_argument("--notinsert-test", action="store_true", default=False)
+    # not a flag of the reference: its dot interaction (dlrm_s_pytorch.py:779-812) as one library kernel per direction
+    parser.add_argument("--fused-interaction", action="store_true", default=False)
     return parser
 
 
@@ -135,11 +137,55 @@ def dot_interaction(x, emb: torch.Tensor) -> torch.Tensor:
     return flat if x is None else torch.cat([x, flat], dim=1)
 
 
-class DLRMNet(nn.Module):
-    """DLRM_Net of dlrm_s_pytorch.py with the CAFE embedding layer: bottom MLP, dot interaction, top MLP."""
+class _FusedDotInteraction(torch.autograd.Function):
+    """dot_interaction as one library kernel per direction (cafe_dot_interaction_forward / _backward): no [B, F+1, F+1]
+    intermediate, no index gathers.  x [B, D] and emb [B, F, D] fp32 on the GPU."""
 
-    def __init__(self, ln_emb, dim, ln_bot, ln_top_hidden, emb_layer, seed=123):
+    @staticmethod
+    def forward(ctx, x, emb):
+        from . import _lib
+        lib = _lib.load()
+        x, emb = x.contiguous(), emb.contiguous()
+        B, F, D = emb.shape
+        nv = F + 1
+        out = torch.empty(B, D + nv * (nv - 1) // 2, dtype=torch.float32, device=emb.device)
+        st = torch.cuda.current_stream(emb.device).cuda_stream
+        with torch.cuda.device(emb.device):
+            _lib.check(lib.cafe_dot_interaction_forward(x.data_ptr(), emb.data_ptr(), D, F * D, B, F, D, 0, out.data_ptr(),
+                                                        out.shape[1], st), "cafe_dot_interaction_forward")
+        ctx.save_for_backward(x, emb)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import _lib
+        lib = _lib.load()
+        x, emb = ctx.saved_tensors
+        B, F, D = emb.shape
+        g = grad_out.contiguous()
+        gx, ge = torch.empty_like(x), torch.empty_like(emb)
+        st = torch.cuda.current_stream(emb.device).cuda_stream
+        with torch.cuda.device(emb.device):
+            _lib.check(lib.cafe_dot_interaction_backward(x.data_ptr(), emb.data_ptr(), D, F * D, B, F, D, 0, g.data_ptr(),
+                                                         g.shape[1], gx.data_ptr(), ge.data_ptr(), D, F * D, st),
+                       "cafe_dot_interaction_backward")
+        return gx, ge
+
+
+def fused_dot_interaction(x: torch.Tensor, emb: torch.Tensor) -> torch.Tensor:
+    """dot_interaction(x, emb) through the library's kernels; same values up to the order of the fp32 additions."""
+    if not (x.is_cuda and emb.is_cuda and x.dtype == torch.float32 and emb.dtype == torch.float32):
+        raise ValueError("fused_dot_interaction needs fp32 CUDA tensors")
+    return _FusedDotInteraction.apply(x, emb)
+
+
+class DLRMNet(nn.Module):
+    """DLRM_Net of dlrm_s_pytorch.py with the CAFE embedding layer: bottom MLP, dot interaction, top MLP.
+    `fused_interaction`: the interaction through the library's kernels instead of torch's cat / bmm / index ops."""
+
+    def __init__(self, ln_emb, dim, ln_bot, ln_top_hidden, emb_layer, seed=123, fused_interaction=False):
         super().__init__()
+        self.fused_interaction = bool(fused_interaction)
         rng = np.random.default_rng(seed)
         self.emb = emb_layer      # CafeEmbeddingLayer, or anything with the same forward / device / set_lr
         ln_bot = [int(v) for v in ln_bot]
@@ -157,6 +203,8 @@ class DLRMNet(nn.Module):
         with record_function("DLRM forward"):
             x = self.bot(dense_x)
             ly = self.emb(lS_o, lS_i, test)
+            if self.fused_interaction and ly.is_cuda:
+                return self.top(fused_dot_interaction(x, ly))
             return self.top(dot_interaction(x, ly))
 
 
@@ -258,7 +306,8 @@ def build_model(args, device="cuda"):
         return DCNNet(cards, dim, nd, deep, emb, seed=args.numpy_rand_seed)
     ln_bot = [int(v) for v in (args.arch_mlp_bot or bot).split("-")]
     ln_top = [int(v) for v in (args.arch_mlp_top or top).split("-")]
-    return DLRMNet(cards, dim, ln_bot, ln_top, emb, seed=args.numpy_rand_seed)
+    return DLRMNet(cards, dim, ln_bot, ln_top, emb, seed=args.numpy_rand_seed,
+                   fused_interaction=getattr(args, "fused_interaction", False))
 
 
 def run(args) -> dict:

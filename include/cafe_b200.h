@@ -302,6 +302,21 @@ int cafe_profile_enable(int on);
 int cafe_profile_read(double* ms_out, int64_t* launches_out);
 int64_t cafe_launch_count(void);
 
+/* ---- DLRM's dot interaction (dlrm_s_pytorch.py:779-812, `interact_features` with arch_interaction_op "dot") --------
+ * One kernel per direction instead of cat + bmm + two index gathers + cat.  x_dev [B, D] is the bottom MLP's output (null:
+ * no dense vector, as in the Avazu models); vector f of sample b of the pooled embeddings lies at emb_dev + b *
+ * sample_stride + f * field_stride (so the [B, F, D] output of cafe_embed_forward is read in place); out_dev [B,
+ * out_stride] receives { x | T_i . T_j for i ascending, j < i (itself = 0) or j <= i (itself = 1) }, T = { x, the F
+ * vectors }: the reference's order (:800-812).  F + 1 <= 64, D <= 128, fp32.  Status 6 if the sample does not fit
+ * 48 KB of shared memory. */
+int cafe_dot_interaction_forward(const float* x_dev, const float* emb_dev, int64_t field_stride, int64_t sample_stride, int B,
+                                 int F, int D, int itself, float* out_dev, int64_t out_stride, void* stream);
+/* Its backward: grad_x_dev [B, D] (when x_dev was given; includes the pass-through of the leading D columns) and the
+ * gradient of every embedding vector at grad_emb_dev + b * gsample_stride + f * gfield_stride. */
+int cafe_dot_interaction_backward(const float* x_dev, const float* emb_dev, int64_t field_stride, int64_t sample_stride, int B,
+                                  int F, int D, int itself, const float* grad_out_dev, int64_t out_stride, float* grad_x_dev,
+                                  float* grad_emb_dev, int64_t gfield_stride, int64_t gsample_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
