@@ -349,7 +349,7 @@ def run_reference(args, rank, world):
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": path.threads, "kind": path.kind, "sample": sample,
                              "host_cpus": os.cpu_count()},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(line)
 
 
 def cpu_baseline_leg(args, wl):
@@ -661,7 +661,7 @@ def run_ours(args, rank, world, local_rank):
                 line["cpu_baseline"] = cpu_baseline_leg(args, wl)
             except Exception as e:  # the baseline is informative; never lose the GPU number to it
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": repr(e)}
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -686,7 +686,27 @@ def dlrm_figures():
     return out
 
 
+_RESULT_OUT = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries loaded later write banners to file descriptor 1 (NCCL prints its version there at start-up).  The
+    descriptor is kept aside for the JSON line and everything else that would go to it is sent to stderr."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict):
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
