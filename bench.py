@@ -566,6 +566,13 @@ def run_ours(args, rank, world, local_rank):
                                   "this run; value / (n_gpus * this) is the strong-scaling efficiency of the sharded run"}
             del one, ids1, g1
         barrier()
+    dlrm_parallel = None
+    if dist is not None and not args.no_dlrm:
+        # every rank takes part (the steps contain collectives); a failure that every rank sees is reported, not raised
+        try:
+            dlrm_parallel = dlrm_figures_data_parallel()
+        except Exception as e:
+            dlrm_parallel = {"error": repr(e)}
     line = None
     if rank == 0:
         peak, peak_kind = read_peaks()
@@ -656,6 +663,8 @@ def run_ours(args, rank, world, local_rank):
                 line["dlrm_samples_per_s"] = dlrm_figures()
             except Exception as e:   # informative only
                 line["dlrm_samples_per_s"] = {"error": repr(e)}
+        if dlrm_parallel is not None:
+            line["dlrm_samples_per_s"] = dlrm_parallel
         if world == 1 and not args.no_cpu_baseline:
             try:
                 line["cpu_baseline"] = cpu_baseline_leg(args, wl)
@@ -683,6 +692,27 @@ def dlrm_figures():
                      "plain_fields": r["plain_fields"], "loss_last": r["loss_last"]}
     out["note"] = ("whole training steps: stock-PyTorch MLPs / interaction / loss / SGD around the library's embedding path; "
                    "ids arrive as host tensors every step")
+    return out
+
+
+def dlrm_figures_data_parallel():
+    """The same figure on several GPUs, weak scaling: every rank trains on its own batches of the single-GPU size, the
+    embedding fields are sharded over the ranks (their owners serve the global batch), the dense side is replicated
+    with its gradients summed every step.  Shapes whose fields all go through the sketch (Kaggle and Terabyte at
+    compress rate 0.001).  Called by every rank of the job; all return the whole job's samples/s."""
+    from cafe_b200 import dlrm_harness as H
+    out = {}
+    for name, argv in (("kaggle_dlrm_dim16_batch128_per_gpu", ["--data-set", "kaggle", "--mini-batch-size", "128", "--compress-rate",
+                                                                "0.001", "--hash-rate", "0.3", "--nbatches", "150"]),
+                       ("terabyte_dlrm_dim128_batch2048_per_gpu", ["--data-set", "terabyte", "--mini-batch-size", "2048",
+                                                                   "--compress-rate", "0.001", "--hash-rate", "0.3", "--nbatches", "60"])):
+        r = H.run_data_parallel(H.make_parser().parse_args(["--sketch-flag", "--sketch-alpha", "1.0000005", "--warmup-batches", "20"]
+                                                           + argv))
+        out[name] = {k: r[k] for k in ("samples_per_s", "ms_per_step", "ranks", "global_batch", "sketch_fields", "loss_last",
+                                       "replicas_in_step")}
+    out["note"] = ("whole training steps, weak scaling: fields sharded over the GPUs (lookup, insert, migration and SGD of the "
+                   "global batch on the owners), stock-PyTorch MLPs / interaction / loss / SGD replicated, dense gradients "
+                   "summed by one all-reduce per step; ids arrive as host tensors every step")
     return out
 
 

@@ -125,6 +125,52 @@ class CafeEmbeddingLayer(nn.Module):
         return torch.stack(cols, dim=1)
 
 
+class ShardedCafeEmbeddingLayer(nn.Module):
+    """The embedding layer of a data-parallel model whose embedding fields are sharded by field over the ranks of a
+    process group (ShardedSKEmbedding): every rank feeds the ids of ITS slice of the global batch, [F, B_local], and
+    gets back the pooled rows of that slice, [B_local, F, D], in the original field order.  The owners of the fields
+    run lookup, sketch insert, migration and SGD for the whole global batch inside backward.
+
+    Every field goes through a rank's sketch (the shards do not keep plain tables), so the layer takes shapes in which
+    every field is a sketch field by the reference's rule (more than 2000 * compress_rate ids, sizing.is_sketch_field);
+    other shapes raise."""
+
+    def __init__(self, ln_emb, dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1, sketch_alpha=1.0,
+                 device="cuda", local_batch=2048, lr=0.1, seed=0, group=None, exchange="peer", **_unused):
+        super().__init__()
+        import torch.distributed as dist
+        from .sharded import ShardedSKEmbedding
+        self.ln = [int(n) for n in ln_emb]
+        self.dim = int(dim)
+        self.device = torch.device(device)
+        small = [i for i, n in enumerate(self.ln) if not sizing.is_sketch_field(n, compress_rate)]
+        if small:
+            raise ValueError(f"fields {small} would be plain tables at compress_rate {compress_rate}; the sharded layer "
+                             "serves shapes whose fields all go through the sketch")
+        self.world = dist.get_world_size(group)
+        self.local_batch = int(local_batch)
+        self.sharded = ShardedSKEmbedding(self.ln, self.dim, compress_rate, hash_rate, sketch_threshold, adjust_threshold,
+                                          sketch_alpha, device=self.device, global_batch=self.local_batch * self.world, lr=lr,
+                                          seed=seed, group=group, exchange=exchange)
+        self.group = self.sharded.group            # this rank's fields (the outer optimizer skips its tables)
+        self.sketch_fields = list(range(len(self.ln)))
+        self.plain_fields = []
+        self.hotn = self.group.hotn
+
+    def set_lr(self, lr: float) -> None:
+        self.group.lr = float(lr)
+
+    def forward(self, lS_o, lS_i, test: bool = False) -> torch.Tensor:
+        ids = lS_i if isinstance(lS_i, torch.Tensor) else torch.stack(list(lS_i))
+        with record_function("CAFE sharded fields forward"):
+            if test:
+                with torch.no_grad():
+                    blocked = self.sharded(ids)
+            else:
+                blocked = self.sharded(ids)
+            return self.sharded.plan.unblock(blocked, ids.shape[1], self.dim)
+
+
 def dot_interaction(x, emb: torch.Tensor) -> torch.Tensor:
     """dlrm_s_pytorch.py:779-812 (arch_interaction_itself = False): pairwise dot products of the dense vector and
     the embedding vectors, lower triangle, concatenated behind the dense vector."""
@@ -265,6 +311,39 @@ def train_step(model, optimizer, dense_x, lS_o, lS_i, target, loss_fn=None):
     return loss, z
 
 
+def allreduce_gradients(params, group=None) -> None:
+    """Sums the gradients of `params` over the ranks of `group` in one collective (flattened), in place.  Parameters
+    without a gradient are skipped; every rank must hold gradients for the same parameters."""
+    import torch.distributed as dist
+    grads = [p.grad for p in params if p.grad is not None]
+    if not grads:
+        return
+    flat = torch._utils._flatten_dense_tensors(grads)
+    dist.all_reduce(flat, group=group)
+    for g, f in zip(grads, torch._utils._unflatten_dense_tensors(flat, grads)):
+        g.copy_(f)
+
+
+def train_step_data_parallel(model, optimizer, dense_x, lS_o, lS_i, target, group=None, loss_fn=None):
+    """train_step on one rank of a data-parallel job: the rank's loss is its mean over the local batch divided by the
+    number of ranks, so that the summed dense gradients and the gradients that reach the embedding owners are those
+    of the mean over the GLOBAL batch (one process fed the whole batch would compute the same).  Returns the
+    rank's share of the global loss and its predictions."""
+    import torch.distributed as dist
+    loss_fn = loss_fn or nn.functional.binary_cross_entropy
+    world = dist.get_world_size(group)
+    model.emb.set_lr(optimizer.param_groups[0]["lr"])
+    z = model(dense_x, lS_o, lS_i, False)
+    with record_function("DLRM loss compute"):
+        loss = loss_fn(z.squeeze(1), target) / world
+    with record_function("DLRM backward"):
+        optimizer.zero_grad()
+        loss.backward()
+        allreduce_gradients([p for g in optimizer.param_groups for p in g["params"]], group)
+        optimizer.step()
+    return loss, z
+
+
 def auc(y: np.ndarray, p: np.ndarray) -> float:
     order = np.argsort(p, kind="stable")
     y = y[order]
@@ -293,14 +372,21 @@ def synthetic_batch(shape: str, batch: int, seed: int, step: int, device):
     return dense, None, ids, y
 
 
-def build_model(args, device="cuda"):
+def build_model(args, device="cuda", group_of_ranks=None):
+    """The model the arguments name.  `group_of_ranks` = (process group or None for all ranks,): the embedding fields
+    sharded over those ranks (ShardedCafeEmbeddingLayer), the dense side replicated; args.mini_batch_size is then the
+    batch of ONE rank."""
     cards, nd, _, _, dim_default, bot, top = SHAPES[args.data_set]
     dim = args.arch_sparse_feature_size or dim_default
     emb_kwargs = dict(compress_rate=args.compress_rate, hash_rate=args.hash_rate, sketch_threshold=args.sketch_threshold,
                       adjust_threshold=args.adjust_threshold, sketch_alpha=args.sketch_alpha, sketch_flag=args.sketch_flag,
                       device=device, max_batch=args.mini_batch_size, lr=args.learning_rate, seed=args.numpy_rand_seed,
                       notinsert_test=args.notinsert_test)
-    emb = CafeEmbeddingLayer(cards, dim, **emb_kwargs)
+    if group_of_ranks is not None:
+        emb = ShardedCafeEmbeddingLayer(cards, dim, local_batch=args.mini_batch_size, group=group_of_ranks[0], **{
+            k: v for k, v in emb_kwargs.items() if k not in ("sketch_flag", "max_batch", "notinsert_test")})
+    else:
+        emb = CafeEmbeddingLayer(cards, dim, **emb_kwargs)
     if args.model == "dcn":
         deep = [int(v) for v in (args.arch_mlp_top or top).split("-")]
         return DCNNet(cards, dim, nd, deep, emb, seed=args.numpy_rand_seed)
@@ -338,6 +424,54 @@ def run(args) -> dict:
             "samples_per_s": (args.nbatches - warm) * B / dt, "ms_per_step": 1e3 * dt / max(1, args.nbatches - warm),
             "sketch_fields": len(model.emb.sketch_fields), "plain_fields": len(model.emb.plain_fields),
             "hot_rows": model.emb.hotn, "losses": losses}
+
+
+def run_data_parallel(args, group=None) -> dict:
+    """run() on every rank of an initialised NCCL process group (one rank per GPU): fields sharded over the ranks,
+    dense side replicated with its gradients summed every step, args.mini_batch_size samples per rank and step
+    (weak scaling).  Every rank returns the whole job's samples/s, timed on the host between barriers with the
+    device drained, the slowest rank's time counting."""
+    import torch.distributed as dist
+    dev = torch.device("cuda", torch.cuda.current_device())
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    model = build_model(args, dev, group_of_ranks=(group,))
+    opt = torch.optim.SGD(dense_and_plain_parameters(model), lr=args.learning_rate)
+    B = args.mini_batch_size
+    # rank r takes batches r, r + world, ... of the seeded stream: distinct samples on every rank
+    batches = [synthetic_batch(args.data_set, B, 2024, s * world + rank, dev) for s in range(args.nbatches)]
+    warm = min(args.warmup_batches, max(0, args.nbatches - 1))
+    losses = []
+    t0 = None
+    for s, (dense, lS_o, ids, y) in enumerate(batches):
+        if s == warm:
+            torch.cuda.synchronize()
+            dist.barrier(group)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+        loss, _ = train_step_data_parallel(model, opt, dense, lS_o, ids, y, group)
+        losses.append(loss.detach())
+    torch.cuda.synchronize()
+    dist.barrier(group)
+    torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX, group=group)
+    dt = float(dt.item())
+    tot = torch.stack(losses).double()
+    dist.all_reduce(tot, group=group)                 # the ranks' shares add up to the global mean
+    tot = tot.cpu().numpy()
+    tail = max(1, len(batches) // 4)
+    # the replicas must have stayed in step: the same dense parameters on every rank
+    flat = torch.cat([p.detach().reshape(-1) for p in model.bot.parameters()] + [p.detach().reshape(-1) for p in model.top.parameters()]) \
+        if hasattr(model, "bot") else torch.cat([p.detach().reshape(-1) for p in dense_and_plain_parameters(model)])
+    lo, hi = flat.clone(), flat.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
+    return {"data_set": args.data_set, "model": args.model, "ranks": world, "batch_per_rank": B, "global_batch": B * world,
+            "steps": args.nbatches, "loss_first": float(tot[0]), "loss_last": float(tot[-tail:].mean()),
+            "samples_per_s": (args.nbatches - warm) * B * world / dt, "ms_per_step": 1e3 * dt / max(1, args.nbatches - warm),
+            "sketch_fields": len(model.emb.sketch_fields), "plain_fields": 0, "hot_rows_this_rank": model.emb.hotn,
+            "replicas_in_step": bool(torch.equal(lo, hi)), "lookups_this_rank": int(model.emb.group.sketch.stats()["lookups"]),
+            "losses": [float(v) for v in tot]}
 
 
 def make_parser() -> argparse.ArgumentParser:

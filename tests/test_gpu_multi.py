@@ -1,5 +1,6 @@
 """The field-sharded module on two GPUs (skipped with fewer): every shard against its own CPU oracle, and the
-exchange variants against each other (tests/multi_gpu_parity.py)."""
+exchange variants against each other (tests/multi_gpu_parity.py); a data-parallel DLRM over the sharded fields
+(tests/multi_gpu_dlrm.py)."""
 import os
 import socket
 import subprocess
@@ -30,3 +31,16 @@ def test_shards_match_their_oracles_and_exchange_variants_agree_on_two_gpus():
                        timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "identical" in r.stdout
+
+
+def test_data_parallel_dlrm_over_sharded_fields_on_two_gpus():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = Path(__file__).resolve().parent / "multi_gpu_dlrm.py"
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", str(_free_port()), str(script)], env=env, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "in step" in r.stdout

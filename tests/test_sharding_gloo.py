@@ -135,3 +135,81 @@ def test_shard_capacity_by_fields_and_by_rows():
     assert sum(shares) <= total and min(shares) >= 1584
     assert sizing.hot_rows(sum(cards[f] for f in (7, 15, 23)), 1e-4, 0.2, 128) == 1
     assert sizing.shard_hot_rows(cards, [7, 15, 23], 1e-4, 0.2, 128, "rows") == 20
+
+
+class _ReplicatedTables(torch.nn.Module):
+    """CPU stand-in for the embedding layer of the DLRM harness: one dense table per field on every rank."""
+
+    def __init__(self, cards, D):
+        super().__init__()
+        g = torch.Generator().manual_seed(9)
+        self.tables = torch.nn.ParameterList([torch.nn.Parameter(torch.randn(n, D, generator=g) * 0.1) for n in cards])
+        self.device = torch.device("cpu")
+        self.group = None
+
+    def set_lr(self, lr):
+        pass
+
+    def forward(self, lS_o, lS_i, test=False):
+        return torch.stack([t[i] for t, i in zip(self.tables, lS_i)], dim=1)
+
+
+def _dlrm_batches(cards, B, steps):
+    g = torch.Generator().manual_seed(77)
+    out = []
+    for _ in range(steps):
+        ids = torch.stack([torch.randint(0, n, (B,), generator=g) for n in cards])
+        out.append((torch.randn(B, 5, generator=g), ids, (torch.rand(B, generator=g) < 0.3).float()))
+    return out
+
+
+def _dlrm_model(cards, D):
+    from cafe_b200 import dlrm_harness as H
+    return H.DLRMNet(cards, D, [5, 16, D], [16, 1], _ReplicatedTables(cards, D), seed=3)
+
+
+def _dp_worker(rank, world, port, cards, D, Bl, steps, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from cafe_b200 import dlrm_harness as H
+        torch.set_num_threads(1)
+        model = _dlrm_model(cards, D)
+        opt = torch.optim.SGD(H.dense_and_plain_parameters(model), lr=0.5)
+        shares = []
+        for dense, ids, y in _dlrm_batches(cards, Bl * world, steps):
+            sl = slice(rank * Bl, (rank + 1) * Bl)
+            loss, _ = H.train_step_data_parallel(model, opt, dense[sl], None, ids[:, sl], y[sl])
+            shares.append(float(loss.detach()))
+        q.put((rank, shares, [p.detach().numpy().copy() for p in model.parameters()]))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_data_parallel_step_equals_one_process_on_the_global_batch():
+    """Two ranks, each with half of every batch, against one process fed the whole batch: the ranks' loss shares add
+    up to the global loss and after three steps every parameter (MLPs and tables) agrees within fp32 rounding."""
+    from cafe_b200 import dlrm_harness as H
+    cards, D, Bl, steps, world = [50, 7, 300], 8, 12, 3, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_dp_worker, args=(r, world, port, cards, D, Bl, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted([q.get(timeout=120) for _ in range(world)], key=lambda t: t[0])
+    for p in procs:
+        p.join(timeout=60)
+    model = _dlrm_model(cards, D)
+    opt = torch.optim.SGD(H.dense_and_plain_parameters(model), lr=0.5)
+    losses = []
+    for dense, ids, y in _dlrm_batches(cards, Bl * world, steps):
+        loss, _ = H.train_step(model, opt, dense, None, ids, y)
+        losses.append(float(loss.detach()))
+    for s in range(steps):
+        assert abs(sum(r[1][s] for r in res) - losses[s]) < 1e-6
+    for r in res:
+        for a, b in zip(r[2], model.parameters()):
+            assert torch.allclose(torch.from_numpy(a), b.detach(), rtol=1e-5, atol=1e-7)
+    for a, b in zip(res[0][2], res[1][2]):
+        assert (a == b).all()
