@@ -566,13 +566,6 @@ def run_ours(args, rank, world, local_rank):
                                   "this run; value / (n_gpus * this) is the strong-scaling efficiency of the sharded run"}
             del one, ids1, g1
         barrier()
-    dlrm_parallel = None
-    if dist is not None and not args.no_dlrm:
-        # every rank takes part (the steps contain collectives); a failure that every rank sees is reported, not raised
-        try:
-            dlrm_parallel = dlrm_figures_data_parallel()
-        except Exception as e:
-            dlrm_parallel = {"error": repr(e)}
     line = None
     if rank == 0:
         peak, peak_kind = read_peaks()
@@ -663,13 +656,34 @@ def run_ours(args, rank, world, local_rank):
                 line["dlrm_samples_per_s"] = dlrm_figures()
             except Exception as e:   # informative only
                 line["dlrm_samples_per_s"] = {"error": repr(e)}
-        if dlrm_parallel is not None:
-            line["dlrm_samples_per_s"] = dlrm_parallel
         if world == 1 and not args.no_cpu_baseline:
             try:
                 line["cpu_baseline"] = cpu_baseline_leg(args, wl)
             except Exception as e:  # the baseline is informative; never lose the GPU number to it
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "unavailable", "sample": repr(e)}
+    if dist is not None and not args.no_dlrm:
+        # Every rank takes part (the steps contain collectives).  The line above is complete without this figure: a
+        # failure that every rank sees is reported in its place, and if the ranks stop answering each other a
+        # watchdog lets rank 0 print the line as it stands and ends the process, so the step's numbers are never lost.
+        import threading
+
+        def give_up():
+            if rank == 0:
+                line["dlrm_samples_per_s"] = {"error": "no answer within 150 s; the figure was abandoned"}
+                emit(line)
+            os._exit(0)
+        dog = threading.Timer(150.0, give_up)
+        dog.daemon = True
+        dog.start()
+        try:
+            fig = dlrm_figures_data_parallel()
+        except Exception as e:
+            fig = {"error": repr(e)}
+        dist.barrier()   # (under the watchdog: a rank that failed alone would wait here for ranks that never come)
+        dog.cancel()
+        if rank == 0:
+            line["dlrm_samples_per_s"] = fig
+    if rank == 0:
         emit(line)
     if dist is not None:
         dist.barrier()
