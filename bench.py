@@ -704,6 +704,13 @@ def dlrm_figures():
         r = H.run(H.make_parser().parse_args(["--sketch-flag", "--sketch-alpha", "1.0000005", "--warmup-batches", "20"] + argv))
         out[name] = {"samples_per_s": r["samples_per_s"], "ms_per_step": r["ms_per_step"], "sketch_fields": r["sketch_fields"],
                      "plain_fields": r["plain_fields"], "loss_last": r["loss_last"]}
+        if "dcn" not in argv:
+            # the same steps with the dot interaction through the library's kernels (not part of the figure above,
+            # whose dense side is stock PyTorch throughout)
+            r = H.run(H.make_parser().parse_args(["--sketch-flag", "--sketch-alpha", "1.0000005", "--warmup-batches", "20",
+                                                  "--fused-interaction"] + argv))
+            out[name]["with_fused_interaction"] = {"samples_per_s": r["samples_per_s"], "ms_per_step": r["ms_per_step"],
+                                                   "loss_last": r["loss_last"]}
     out["note"] = ("whole training steps: stock-PyTorch MLPs / interaction / loss / SGD around the library's embedding path; "
                    "ids arrive as host tensors every step")
     return out
@@ -712,18 +719,20 @@ def dlrm_figures():
 def dlrm_figures_data_parallel():
     """The same figure on several GPUs, weak scaling: every rank trains on its own batches of the single-GPU size, the
     embedding fields are sharded over the ranks (their owners serve the global batch), the dense side is replicated
-    with its gradients summed every step.  Shapes whose fields all go through the sketch (Kaggle and Terabyte at
-    compress rate 0.001).  Called by every rank of the job; all return the whole job's samples/s."""
+    with its gradients summed every step (the Avazu shape's 13 small plain tables are part of that replicated side;
+    its 9 sketch fields are sharded).  Called by every rank of the job; all return the whole job's samples/s."""
     from cafe_b200 import dlrm_harness as H
     out = {}
     for name, argv in (("kaggle_dlrm_dim16_batch128_per_gpu", ["--data-set", "kaggle", "--mini-batch-size", "128", "--compress-rate",
                                                                 "0.001", "--hash-rate", "0.3", "--nbatches", "150"]),
                        ("terabyte_dlrm_dim128_batch2048_per_gpu", ["--data-set", "terabyte", "--mini-batch-size", "2048",
-                                                                   "--compress-rate", "0.001", "--hash-rate", "0.3", "--nbatches", "60"])):
+                                                                   "--compress-rate", "0.001", "--hash-rate", "0.3", "--nbatches", "60"]),
+                       ("avazu_dcn_dim16_batch4096_per_gpu", ["--data-set", "avazu", "--model", "dcn", "--mini-batch-size", "4096",
+                                                              "--compress-rate", "0.1", "--hash-rate", "0.7", "--nbatches", "60"])):
         r = H.run_data_parallel(H.make_parser().parse_args(["--sketch-flag", "--sketch-alpha", "1.0000005", "--warmup-batches", "20"]
                                                            + argv))
-        out[name] = {k: r[k] for k in ("samples_per_s", "ms_per_step", "ranks", "global_batch", "sketch_fields", "loss_last",
-                                       "replicas_in_step")}
+        out[name] = {k: r[k] for k in ("samples_per_s", "ms_per_step", "ranks", "global_batch", "sketch_fields", "plain_fields",
+                                       "loss_last", "replicas_in_step")}
     out["note"] = ("whole training steps, weak scaling: fields sharded over the GPUs (lookup, insert, migration and SGD of the "
                    "global batch on the owners), stock-PyTorch MLPs / interaction / loss / SGD replicated, dense gradients "
                    "summed by one all-reduce per step; ids arrive as host tensors every step")

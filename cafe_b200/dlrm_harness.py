@@ -95,6 +95,7 @@ class CafeEmbeddingLayer(nn.Module):
             self.plain.append(ee)
         self.plain.to(self.device)
         self._arange = None
+        self._sk_index = None
 
     def set_lr(self, lr: float) -> None:
         if self.group is not None:
@@ -104,10 +105,10 @@ class CafeEmbeddingLayer(nn.Module):
         ids = lS_i if isinstance(lS_i, torch.Tensor) else torch.stack(list(lS_i))
         F, B = ids.shape
         cols = [None] * F
+        ids = ids.to(self.device, non_blocking=True)         # one copy for all fields
         if self.group is not None:
             with record_function("CAFE sketch fields forward"):
-                sk_ids = ids if not self.plain_fields else ids[self.sketch_fields]
-                sk_ids = sk_ids.to(self.device, non_blocking=True)
+                sk_ids = ids if not self.plain_fields else ids[self._sketch_index()]
                 if test:
                     with torch.no_grad():
                         emb = self.group(sk_ids)
@@ -121,19 +122,26 @@ class CafeEmbeddingLayer(nn.Module):
             self._arange = torch.arange(B, device=self.device)
         with record_function("plain embedding bags"):
             for j, i in enumerate(self.plain_fields):
-                cols[i] = self.plain[j](ids[i].to(self.device, non_blocking=True), self._arange)
+                cols[i] = self.plain[j](ids[i], self._arange)
         return torch.stack(cols, dim=1)
+
+    def _sketch_index(self) -> torch.Tensor:
+        if self._sk_index is None:
+            self._sk_index = torch.tensor(self.sketch_fields, dtype=torch.int64, device=self.device)
+        return self._sk_index
 
 
 class ShardedCafeEmbeddingLayer(nn.Module):
-    """The embedding layer of a data-parallel model whose embedding fields are sharded by field over the ranks of a
+    """The embedding layer of a data-parallel model whose sketch fields are sharded by field over the ranks of a
     process group (ShardedSKEmbedding): every rank feeds the ids of ITS slice of the global batch, [F, B_local], and
     gets back the pooled rows of that slice, [B_local, F, D], in the original field order.  The owners of the fields
     run lookup, sketch insert, migration and SGD for the whole global batch inside backward.
 
-    Every field goes through a rank's sketch (the shards do not keep plain tables), so the layer takes shapes in which
-    every field is a sketch field by the reference's rule (more than 2000 * compress_rate ids, sizing.is_sketch_field);
-    other shapes raise."""
+    Fields small enough to be plain tables by the reference's rule (at most 2000 * compress_rate ids,
+    dlrm_s_pytorch.py:309) are replicated on every rank as dense-gradient tables: they are a few hundred rows at
+    most, their gradients travel with the MLPs' in the step's one all-reduce, and every replica applies the same
+    update (for SGD a dense gradient with zero rows for untouched ids equals the reference's sparse one).  The hot-row
+    capacity is sized from the sketch fields' ids alone."""
 
     def __init__(self, ln_emb, dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1, sketch_alpha=1.0,
                  device="cuda", local_batch=2048, lr=0.1, seed=0, group=None, exchange="peer", **_unused):
@@ -143,32 +151,53 @@ class ShardedCafeEmbeddingLayer(nn.Module):
         self.ln = [int(n) for n in ln_emb]
         self.dim = int(dim)
         self.device = torch.device(device)
-        small = [i for i, n in enumerate(self.ln) if not sizing.is_sketch_field(n, compress_rate)]
-        if small:
-            raise ValueError(f"fields {small} would be plain tables at compress_rate {compress_rate}; the sharded layer "
-                             "serves shapes whose fields all go through the sketch")
+        offs = sizing.field_offsets(self.ln)
+        self.sketch_fields = [i for i, n in enumerate(self.ln) if sizing.is_sketch_field(n, compress_rate)]
+        self.plain_fields = [i for i in range(len(self.ln)) if i not in self.sketch_fields]
+        if not self.sketch_fields:
+            raise ValueError("no field is large enough for the sketch at this compress_rate: nothing to shard")
         self.world = dist.get_world_size(group)
         self.local_batch = int(local_batch)
-        self.sharded = ShardedSKEmbedding(self.ln, self.dim, compress_rate, hash_rate, sketch_threshold, adjust_threshold,
-                                          sketch_alpha, device=self.device, global_batch=self.local_batch * self.world, lr=lr,
-                                          seed=seed, group=group, exchange=exchange)
+        self.sharded = ShardedSKEmbedding([self.ln[i] for i in self.sketch_fields], self.dim, compress_rate, hash_rate,
+                                          sketch_threshold, adjust_threshold, sketch_alpha, device=self.device,
+                                          global_batch=self.local_batch * self.world, lr=lr, seed=seed, group=group,
+                                          exchange=exchange, f_offsets=[offs[i] for i in self.sketch_fields])
         self.group = self.sharded.group            # this rank's fields (the outer optimizer skips its tables)
-        self.sketch_fields = list(range(len(self.ln)))
-        self.plain_fields = []
         self.hotn = self.group.hotn
+        rng = np.random.default_rng(seed + 17)     # the same tables on every rank
+        self.plain = nn.ModuleList()
+        for i in self.plain_fields:
+            n = self.ln[i]
+            ee = nn.Embedding(n, self.dim)
+            b = np.sqrt(1 / max(n, 5))
+            ee.weight.data = torch.from_numpy(rng.uniform(-b, b, size=(n, self.dim)).astype(np.float32))
+            self.plain.append(ee)
+        self.plain.to(self.device)
+        self._sk_index = torch.tensor(self.sketch_fields, dtype=torch.int64, device=self.device)
 
     def set_lr(self, lr: float) -> None:
         self.group.lr = float(lr)
 
     def forward(self, lS_o, lS_i, test: bool = False) -> torch.Tensor:
         ids = lS_i if isinstance(lS_i, torch.Tensor) else torch.stack(list(lS_i))
+        ids = ids.to(self.device, non_blocking=True)         # one copy for all fields
         with record_function("CAFE sharded fields forward"):
+            sk_ids = ids if not self.plain_fields else ids[self._sk_index]
             if test:
                 with torch.no_grad():
-                    blocked = self.sharded(ids)
+                    blocked = self.sharded(sk_ids)
             else:
-                blocked = self.sharded(ids)
-            return self.sharded.plan.unblock(blocked, ids.shape[1], self.dim)
+                blocked = self.sharded(sk_ids)
+            emb = self.sharded.plan.unblock(blocked, ids.shape[1], self.dim)
+        if not self.plain_fields:
+            return emb
+        cols = [None] * len(self.ln)
+        for j, i in enumerate(self.sketch_fields):
+            cols[i] = emb[:, j, :]
+        with record_function("plain embedding tables"):
+            for j, i in enumerate(self.plain_fields):
+                cols[i] = self.plain[j](ids[i])
+        return torch.stack(cols, dim=1)
 
 
 def dot_interaction(x, emb: torch.Tensor) -> torch.Tensor:
@@ -461,15 +490,15 @@ def run_data_parallel(args, group=None) -> dict:
     tot = tot.cpu().numpy()
     tail = max(1, len(batches) // 4)
     # the replicas must have stayed in step: the same dense parameters on every rank
-    flat = torch.cat([p.detach().reshape(-1) for p in model.bot.parameters()] + [p.detach().reshape(-1) for p in model.top.parameters()]) \
-        if hasattr(model, "bot") else torch.cat([p.detach().reshape(-1) for p in dense_and_plain_parameters(model)])
+    flat = torch.cat([p.detach().reshape(-1) for p in dense_and_plain_parameters(model)])   # MLPs and plain tables
     lo, hi = flat.clone(), flat.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=group)
     return {"data_set": args.data_set, "model": args.model, "ranks": world, "batch_per_rank": B, "global_batch": B * world,
             "steps": args.nbatches, "loss_first": float(tot[0]), "loss_last": float(tot[-tail:].mean()),
             "samples_per_s": (args.nbatches - warm) * B * world / dt, "ms_per_step": 1e3 * dt / max(1, args.nbatches - warm),
-            "sketch_fields": len(model.emb.sketch_fields), "plain_fields": 0, "hot_rows_this_rank": model.emb.hotn,
+            "sketch_fields": len(model.emb.sketch_fields), "plain_fields": len(model.emb.plain_fields),
+            "hot_rows_this_rank": model.emb.hotn, "sketch_fields_this_rank": len(model.emb.sharded.plan.local_fields),
             "replicas_in_step": bool(torch.equal(lo, hi)), "lookups_this_rank": int(model.emb.group.sketch.stats()["lookups"]),
             "losses": [float(v) for v in tot]}
 
