@@ -138,10 +138,10 @@ class ShardedCafeEmbeddingLayer(nn.Module):
     run lookup, sketch insert, migration and SGD for the whole global batch inside backward.
 
     Fields small enough to be plain tables by the reference's rule (at most 2000 * compress_rate ids,
-    dlrm_s_pytorch.py:309) are replicated on every rank as dense-gradient tables: they are a few hundred rows at
-    most, their gradients travel with the MLPs' in the step's one all-reduce, and every replica applies the same
-    update (for SGD a dense gradient with zero rows for untouched ids equals the reference's sparse one).  The hot-row
-    capacity is sized from the sketch fields' ids alone."""
+    dlrm_s_pytorch.py:309) are replicated on every rank, all in one joint table of a few hundred rows: its gradient
+    (sparse on each rank, made dense for the exchange) travels with the MLPs' in the step's one all-reduce, and every
+    replica applies the same update (for SGD a dense gradient with zero rows for untouched ids equals the
+    reference's sparse one).  The hot-row capacity is sized from the sketch fields' ids alone."""
 
     def __init__(self, ln_emb, dim, compress_rate, hash_rate, sketch_threshold=1, adjust_threshold=1, sketch_alpha=1.0,
                  device="cuda", local_batch=2048, lr=0.1, seed=0, group=None, exchange="peer", **_unused):
@@ -164,15 +164,25 @@ class ShardedCafeEmbeddingLayer(nn.Module):
                                           exchange=exchange, f_offsets=[offs[i] for i in self.sketch_fields])
         self.group = self.sharded.group            # this rank's fields (the outer optimizer skips its tables)
         self.hotn = self.group.hotn
-        rng = np.random.default_rng(seed + 17)     # the same tables on every rank
-        self.plain = nn.ModuleList()
+        # the plain fields' tables lie one behind the other in ONE parameter (a few hundred rows): one lookup, one
+        # sparse gradient and one update per step for all of them.  Same values on every rank, initialised per table
+        # as the reference does (dlrm_s_pytorch.py:324-340).
+        rng = np.random.default_rng(seed + 17)
+        tables, starts, tot = [], [], 0
         for i in self.plain_fields:
             n = self.ln[i]
-            ee = nn.Embedding(n, self.dim)
             b = np.sqrt(1 / max(n, 5))
-            ee.weight.data = torch.from_numpy(rng.uniform(-b, b, size=(n, self.dim)).astype(np.float32))
-            self.plain.append(ee)
-        self.plain.to(self.device)
+            tables.append(torch.from_numpy(rng.uniform(-b, b, size=(n, self.dim)).astype(np.float32)))
+            starts.append(tot)
+            tot += n
+        self.plain_weight = None
+        if self.plain_fields:
+            self.plain_weight = nn.Parameter(torch.cat(tables).to(self.device))
+            self.register_buffer("_plain_start", torch.tensor(starts, dtype=torch.int64, device=self.device)[:, None], persistent=False)
+            self.register_buffer("_plain_index", torch.tensor(self.plain_fields, dtype=torch.int64, device=self.device), persistent=False)
+            order = self.sketch_fields + self.plain_fields           # column c of [sketch | plain] is field order[c]
+            place = [order.index(f) for f in range(len(self.ln))]
+            self.register_buffer("_place", torch.tensor(place, dtype=torch.int64, device=self.device), persistent=False)
         self._sk_index = torch.tensor(self.sketch_fields, dtype=torch.int64, device=self.device)
 
     def set_lr(self, lr: float) -> None:
@@ -191,13 +201,10 @@ class ShardedCafeEmbeddingLayer(nn.Module):
             emb = self.sharded.plan.unblock(blocked, ids.shape[1], self.dim)
         if not self.plain_fields:
             return emb
-        cols = [None] * len(self.ln)
-        for j, i in enumerate(self.sketch_fields):
-            cols[i] = emb[:, j, :]
         with record_function("plain embedding tables"):
-            for j, i in enumerate(self.plain_fields):
-                cols[i] = self.plain[j](ids[i])
-        return torch.stack(cols, dim=1)
+            rows = ids[self._plain_index] + self._plain_start                               # [P, B] rows of the joint table
+            pe = nn.functional.embedding(rows, self.plain_weight, sparse=True)               # [P, B, D]
+            return torch.cat([emb, pe.transpose(0, 1)], dim=1).index_select(1, self._place)
 
 
 def dot_interaction(x, emb: torch.Tensor) -> torch.Tensor:
@@ -342,8 +349,12 @@ def train_step(model, optimizer, dense_x, lS_o, lS_i, target, loss_fn=None):
 
 def allreduce_gradients(params, group=None) -> None:
     """Sums the gradients of `params` over the ranks of `group` in one collective (flattened), in place.  Parameters
-    without a gradient are skipped; every rank must hold gradients for the same parameters."""
+    without a gradient are skipped; every rank must hold gradients for the same parameters.  A sparse gradient is
+    made dense first (the ranks touch different rows)."""
     import torch.distributed as dist
+    for p in params:
+        if p.grad is not None and p.grad.is_sparse:      # (small tables looked up with sparse=True)
+            p.grad = p.grad.to_dense()
     grads = [p.grad for p in params if p.grad is not None]
     if not grads:
         return

@@ -151,7 +151,10 @@ class _ReplicatedTables(torch.nn.Module):
         pass
 
     def forward(self, lS_o, lS_i, test=False):
-        return torch.stack([t[i] for t, i in zip(self.tables, lS_i)], dim=1)
+        # the last table is looked up with a sparse gradient, as the small plain tables of the sharded layer are
+        cols = [t[i] for t, i in zip(self.tables[:-1], lS_i)]
+        cols.append(torch.nn.functional.embedding(lS_i[-1], self.tables[-1], sparse=True))
+        return torch.stack(cols, dim=1)
 
 
 def _dlrm_batches(cards, B, steps):
