@@ -94,3 +94,21 @@ def test_random_shapes(seed):
     dom = int(r.integers(20, 5000))
     fuse = int(r.integers(1, 9))
     drive(lim, thr, alpha, fuse * 8, n, dom, fuse, seed=100 + seed)
+
+
+@pytest.mark.parametrize("block", range(4))
+def test_random_configurations(block):
+    """Seeded random shapes on the emulated backend: sketches of 25 to 13 733 slots, calls of 50 to 12 000 ids over
+    domains of 12 ids (a few long buckets whose ids alternate) to 5 000 000, 1 to 26 calls fused, thresholds 1-4,
+    slow and fast decay, ragged and empty calls, id 0, unit counts; every other case sizes its jobs without the
+    crossing-rate prediction, so that re-fits fall due inside jobs and shorten them."""
+    for seed in range(block * 40, block * 40 + 40):
+        r = np.random.default_rng(seed)
+        lim = int(r.choice([25, 40, 100, 300, 1000, 3000, 13733]))
+        thr = int(r.integers(1, 5)); alpha = float(r.choice([1.0000005, 1.05, 1.5]))
+        n = int(r.choice([50, 200, 1000, 4000, 12000])); dom = int(r.choice([12, 30, 200, 3000, 200000, 5000000]))
+        fuse = int(r.integers(1, 27))
+        kw = dict(seed=5000 + seed, zero_ids=seed % 3 == 0, ragged=seed % 4 == 1, unit=seed % 5 == 2)
+        if seed % 2:
+            kw["size_jobs_by_rate"] = False
+        drive(lim, thr, alpha, fuse * int(r.integers(2, 6)), n, dom, fuse, **kw)
